@@ -1,0 +1,92 @@
+"""ctypes view of libxnor_b200.so -- the C ABI declared in include/xnor_b200.h.
+
+This module only loads the shared library and declares argument types; it holds no
+arithmetic.  If the library has not been built, importing ``lib()`` raises: there is no
+fallback implementation of any entry point.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libxnor_b200.so")
+
+OK = 0
+LINEAR = 0
+LEAKY = 1
+
+# Every symbol include/xnor_b200.h declares; tests check that the library exports each one.
+EXPORTS = (
+    "xnor_b200_strerror", "xnor_b200_last_cuda_error", "xnor_b200_conv_geometry",
+    "xnor_b200_binarize_weights", "xnor_b200_binary_align_weights", "xnor_b200_float_to_bit",
+    "xnor_b200_repack_input_bin", "xnor_b200_pack_input", "xnor_b200_gemm_bin_mean_transposed",
+    "xnor_b200_gemm_counts", "xnor_b200_scratch_bytes", "xnor_b200_conv_forward",
+    "xnor_b200_measure_popc_peak", "xnor_b200_measure_bmma_peak",
+)
+
+
+class ConvDesc(C.Structure):
+    """struct xnor_b200_conv_desc"""
+    _fields_ = [(n, C.c_int) for n in ("batch", "c", "h", "w", "n", "size", "stride", "pad", "activation")]
+
+
+class ConvGeom(C.Structure):
+    """struct xnor_b200_conv_geom"""
+    _fields_ = [(n, C.c_int) for n in ("out_h", "out_w", "n_out", "k", "new_lda", "bit_align", "word_path")] + \
+               [("weights_bytes", C.c_size_t), ("packed_input_bytes", C.c_size_t), ("output_floats", C.c_size_t)]
+
+
+class XnorError(RuntimeError):
+    def __init__(self, code: int, where: str) -> None:
+        self.code = code
+        msg = lib().xnor_b200_strerror(code).decode()
+        if code == 4:
+            msg += f" (cudaError {lib().xnor_b200_last_cuda_error()})"
+        super().__init__(f"{where}: {msg} [code {code}]")
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads libxnor_b200.so once.  Raises if it is missing -- build it with ``python -m darknet_b200.build``."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built (python -m darknet_b200.build). "
+            "There is no CPU or PyTorch fallback for this path.")
+    L = C.CDLL(LIB_PATH)
+    vp, ci, sz = C.c_void_p, C.c_int, C.c_size_t
+    dp, gp = C.POINTER(ConvDesc), C.POINTER(ConvGeom)
+    L.xnor_b200_strerror.restype = C.c_char_p
+    L.xnor_b200_strerror.argtypes = [ci]
+    L.xnor_b200_last_cuda_error.restype = ci
+    L.xnor_b200_conv_geometry.argtypes = [dp, gp]
+    L.xnor_b200_binarize_weights.argtypes = [vp, ci, ci, vp, vp, vp]
+    L.xnor_b200_binary_align_weights.argtypes = [dp, vp, vp, vp, ci, vp]
+    L.xnor_b200_float_to_bit.argtypes = [vp, vp, sz, vp]
+    L.xnor_b200_repack_input_bin.argtypes = [vp, vp, ci, ci, ci, vp]
+    L.xnor_b200_pack_input.argtypes = [dp, vp, vp, vp]
+    L.xnor_b200_gemm_bin_mean_transposed.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, vp, vp, ci, vp, vp, vp]
+    L.xnor_b200_gemm_counts.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp]
+    L.xnor_b200_scratch_bytes.restype = sz
+    L.xnor_b200_scratch_bytes.argtypes = [dp]
+    L.xnor_b200_conv_forward.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    L.xnor_b200_measure_popc_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]
+    L.xnor_b200_measure_bmma_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]
+    _lib = L
+    return L
+
+
+def check(code: int, where: str) -> None:
+    if code != OK:
+        raise XnorError(code, where)
+
+
+def geometry(desc: ConvDesc) -> ConvGeom:
+    g = ConvGeom()
+    check(lib().xnor_b200_conv_geometry(C.byref(desc), C.byref(g)), "xnor_b200_conv_geometry")
+    return g

@@ -1,0 +1,107 @@
+// Per-layer entry point and shared host-side helpers of the xnor_b200 C ABI.
+//
+// xnor_b200_conv_forward stands in for the xnor branch of forward_convolutional_layer_gpu
+// (src-lib/convolutional_kernels.cu:204-262): two launches per layer (pack, GEMM+epilogue) instead of the
+// reference's four, for every image of the batch instead of image 0 only.
+#include "xnor_common.cuh"
+
+namespace xnor
+{
+
+thread_local int g_last_cuda_error = 0;
+
+int sm_count()
+{
+	static int cached[64] = {0};
+	int dev = 0;
+	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { return 148; }
+	if (cached[dev] == 0)
+	{
+		int n = 0;
+		if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { n = 148; }
+		cached[dev] = n;
+	}
+	return cached[dev];
+}
+
+int validate_desc(const xnor_b200_conv_desc * d)
+{
+	if (d->batch <= 0 || d->c <= 0 || d->h <= 0 || d->w <= 0 || d->n <= 0) { return XNOR_B200_ERR_INVALID; }
+	if (d->size <= 0 || d->stride <= 0 || d->pad < 0) { return XNOR_B200_ERR_INVALID; }
+	if (d->activation != XNOR_B200_LINEAR && d->activation != XNOR_B200_LEAKY) { return XNOR_B200_ERR_INVALID; }
+	if (d->h + 2 * d->pad < d->size || d->w + 2 * d->pad < d->size) { return XNOR_B200_ERR_INVALID; }
+	// Everything below is indexed with 32-bit ints inside the kernels.
+	const long long k = (long long)d->size * d->size * d->c;
+	const long long n_out = (long long)conv_out_dim(d->h, d->size, d->stride, d->pad) * conv_out_dim(d->w, d->size, d->stride, d->pad);
+	if (k > (1 << 24) || n_out * d->batch > 0x7fffffffLL - 1024 || (long long)d->c * d->h * d->w > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
+	return XNOR_B200_OK;
+}
+
+}  // namespace xnor
+
+using namespace xnor;
+
+extern "C" const char * xnor_b200_strerror(int code)
+{
+	switch (code)
+	{
+		case XNOR_B200_OK:            return "ok";
+		case XNOR_B200_ERR_INVALID:   return "invalid size, stride or enum argument";
+		case XNOR_B200_ERR_NULL:      return "required pointer is NULL";
+		case XNOR_B200_ERR_SCRATCH:   return "scratch buffer too small";
+		case XNOR_B200_ERR_CUDA:      return "CUDA runtime call failed";
+		case XNOR_B200_ERR_ALIGNMENT: return "pointer or leading dimension not aligned";
+		case XNOR_B200_ERR_TOO_LARGE: return "size exceeds a fixed limit of this entry point";
+		default:                      return "unknown xnor_b200 error code";
+	}
+}
+
+extern "C" int xnor_b200_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int xnor_b200_conv_geometry(const xnor_b200_conv_desc * desc, xnor_b200_conv_geom * geom)
+{
+	if (desc == nullptr || geom == nullptr) { return XNOR_B200_ERR_NULL; }
+	int rc = validate_desc(desc);
+	if (rc != XNOR_B200_OK) { return rc; }
+	geom->out_h = conv_out_dim(desc->h, desc->size, desc->stride, desc->pad);
+	geom->out_w = conv_out_dim(desc->w, desc->size, desc->stride, desc->pad);
+	geom->n_out = geom->out_h * geom->out_w;
+	geom->k = desc->size * desc->size * desc->c;
+	geom->new_lda = aligned_lda(geom->k);
+	geom->bit_align = aligned_n(geom->n_out);
+	geom->word_path = (desc->c % 32 == 0) ? 1 : 0;
+	geom->weights_bytes = (size_t)desc->n * geom->new_lda / 8;
+	geom->packed_input_bytes = (size_t)desc->batch * geom->n_out * geom->new_lda / 8;
+	geom->output_floats = (size_t)desc->batch * desc->n * geom->n_out;
+	return XNOR_B200_OK;
+}
+
+extern "C" size_t xnor_b200_scratch_bytes(const xnor_b200_conv_desc * desc)
+{
+	xnor_b200_conv_geom g;
+	if (xnor_b200_conv_geometry(desc, &g) != XNOR_B200_OK) { return 0; }
+	return round_up(g.packed_input_bytes, 256);
+}
+
+extern "C" int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const float * input,
+		const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
+		float * output, const float * shortcut_in, float * shortcut_out,
+		void * scratch, size_t scratch_bytes, void * stream)
+{
+	if (desc == nullptr || input == nullptr || align_bit_weights == nullptr || mean_arr == nullptr
+			|| output == nullptr || scratch == nullptr) { return XNOR_B200_ERR_NULL; }
+	xnor_b200_conv_geom g;
+	int rc = xnor_b200_conv_geometry(desc, &g);
+	if (rc != XNOR_B200_OK) { return rc; }
+	if (scratch_bytes < round_up(g.packed_input_bytes, 256)) { return XNOR_B200_ERR_SCRATCH; }
+	if ((((uintptr_t)scratch) & 255u) != 0 || (((uintptr_t)align_bit_weights) & 15u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
+	if (shortcut_out != nullptr && shortcut_in == nullptr) { return XNOR_B200_ERR_NULL; }
+
+	cudaStream_t s = (cudaStream_t)stream;
+	rc = launch_pack_input(*desc, input, (uint32_t *)scratch, s);
+	if (rc != XNOR_B200_OK) { return rc; }
+	return launch_xnor_gemm(desc->n, desc->batch * g.n_out, g.n_out, g.k,
+			(const uint32_t *)align_bit_weights, g.new_lda / 32, (const uint32_t *)scratch, g.new_lda / 32,
+			output, g.n_out, mean_arr, biases, desc->activation == XNOR_B200_LEAKY,
+			shortcut_in, shortcut_out, nullptr, s);
+}

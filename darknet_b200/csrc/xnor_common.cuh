@@ -1,0 +1,50 @@
+// Shared helpers for the xnor_b200 kernels: error plumbing, geometry, launch-size helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "xnor_b200.h"
+
+namespace xnor
+{
+
+// Last failing CUDA status seen by this library on the calling thread.
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e)
+{
+	g_last_cuda_error = (int)e;
+	return XNOR_B200_ERR_CUDA;
+}
+
+// Checks the launch that was just issued.  cudaPeekAtLastError is legal under stream capture.
+inline int check_launch()
+{
+	cudaError_t e = cudaPeekAtLastError();
+	return e == cudaSuccess ? XNOR_B200_OK : cuda_fail(e);
+}
+
+// Number of SMs of the current device (cached per device index).
+int sm_count();
+
+inline int conv_out_dim(int in, int size, int stride, int pad) { return (in + 2 * pad - size) / stride + 1; }
+inline int aligned_lda(int k) { return k + (256 - k % 256); }        // always adds, even when k%256==0
+inline int aligned_n(int n) { return n + (32 - n % 32); }            // always adds, even when n%32==0
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int validate_desc(const xnor_b200_conv_desc * d);
+
+// Internal launchers shared between translation units --------------------------------------
+
+// GEMM with the batch folded into the column index: column j = b*n_per_image + p is written to
+// C[(b*M + i)*ldc + p].  counts != nullptr selects the integer-accumulator output instead of C.
+int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
+		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
+		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream);
+
+int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32_t * t_bit_input, cudaStream_t stream);
+
+}  // namespace xnor

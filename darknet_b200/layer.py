@@ -1,0 +1,117 @@
+"""Host-side mirror of Darknet's xnor convolutional layer life cycle, over the C ABI.
+
+The names follow the reference so that tests read like its call sequence:
+
+    l = make_convolutional_layer(batch, h, w, c, n, size, stride, pad, activation, xnor=1)
+    l.load_weights(weights, biases)          # what load_convolutional_weights + fuse_conv_batchnorm leave
+    binary_align_weights(l)                  # src-lib/convolutional_layer.cpp:1339
+    forward_convolutional_layer_gpu(l, x)    # src-lib/convolutional_kernels.cu:181 (xnor branch)
+
+torch is used for device memory and the current stream only; every computation is a call into
+libxnor_b200.so.  Nothing here has a CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import capi
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class ConvolutionalLayer:
+    """The Darknet::Layer fields the xnor path touches (src-lib/darknet_layers.hpp:39-83, :250-261)."""
+
+    def __init__(self, batch, h, w, c, n, size, stride, pad, activation, device="cuda:0") -> None:
+        self.desc = capi.ConvDesc(batch, c, h, w, n, size, stride, pad, activation)
+        g = capi.geometry(self.desc)
+        self.batch, self.h, self.w, self.c, self.n = batch, h, w, c, n
+        self.size, self.stride, self.pad, self.activation = size, stride, pad, activation
+        self.xnor = 1
+        self.out_h, self.out_w, self.out_c = g.out_h, g.out_w, n
+        self.outputs = n * g.n_out
+        self.lda_align = 256
+        self.new_lda = g.new_lda
+        self.bit_align = g.bit_align
+        self.geom = g
+        self.device = torch.device(device)
+        self.weights_gpu = torch.zeros(n, c * size * size, dtype=torch.float32, device=self.device)
+        self.biases_gpu = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.mean_arr_gpu = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.align_bit_weights_gpu: Optional[torch.Tensor] = None
+        self.output_gpu = torch.empty(batch, n, g.out_h, g.out_w, dtype=torch.float32, device=self.device)
+        self.scratch = torch.empty(capi.lib().xnor_b200_scratch_bytes(C.byref(self.desc)), dtype=torch.uint8, device=self.device)
+        self.bin_conv_shortcut_in_gpu: Optional[torch.Tensor] = None
+        self.bin_conv_shortcut_out_gpu: Optional[torch.Tensor] = None
+
+    def load_weights(self, weights: torch.Tensor, biases: torch.Tensor) -> None:
+        self.weights_gpu.copy_(weights.reshape(self.n, -1))
+        self.biases_gpu.copy_(biases)
+
+
+def make_convolutional_layer(batch, h, w, c, n, size, stride, pad, activation, xnor=1, device="cuda:0") -> ConvolutionalLayer:
+    """make_convolutional_layer (src-lib/convolutional_layer.cpp:715), xnor layers only."""
+    if not xnor:
+        raise ValueError("this package implements the xnor=1 path only")
+    return ConvolutionalLayer(batch, h, w, c, n, size, stride, pad, activation, device)
+
+
+def binarize_weights(weights: torch.Tensor, n: int, size: int):
+    """binarize_weights (src-lib/convolutional_layer.cpp:196): returns (binary [n][size], mean [n])."""
+    binary = torch.empty(n, size, dtype=torch.float32, device=weights.device)
+    mean = torch.empty(n, dtype=torch.float32, device=weights.device)
+    capi.check(capi.lib().xnor_b200_binarize_weights(weights.data_ptr(), n, size, binary.data_ptr(), mean.data_ptr(), _stream()),
+               "xnor_b200_binarize_weights")
+    return binary, mean
+
+
+def binary_align_weights(l: ConvolutionalLayer, invert: bool = False) -> None:
+    """binary_align_weights (src-lib/convolutional_layer.cpp:1339): fills align_bit_weights_gpu and mean_arr_gpu."""
+    l.align_bit_weights_gpu = torch.empty(l.geom.weights_bytes, dtype=torch.uint8, device=l.device)
+    capi.check(capi.lib().xnor_b200_binary_align_weights(C.byref(l.desc), l.weights_gpu.data_ptr(),
+                                                        l.align_bit_weights_gpu.data_ptr(), l.mean_arr_gpu.data_ptr(),
+                                                        int(invert), _stream()), "xnor_b200_binary_align_weights")
+
+
+def pack_input(l: ConvolutionalLayer, x: torch.Tensor) -> torch.Tensor:
+    """The packed, transposed activation operand (t_bit_input) of every image: uint8 [batch*N][new_ldb/8]."""
+    out = torch.empty(l.batch * l.geom.n_out, l.new_lda // 8, dtype=torch.uint8, device=l.device)
+    capi.check(capi.lib().xnor_b200_pack_input(C.byref(l.desc), x.data_ptr(), out.data_ptr(), _stream()), "xnor_b200_pack_input")
+    return out
+
+
+def gemm_nn_custom_bin_mean_transposed_gpu(M, N, K, A, lda, B, ldb, C_out, ldc, mean_arr, bias, leaky,
+                                           shortcut_in=None, shortcut_out=None) -> None:
+    """gemm_nn_custom_bin_mean_transposed_gpu (src-lib/im2col_kernels.cu:1156), non-inverted A."""
+    capi.check(capi.lib().xnor_b200_gemm_bin_mean_transposed(M, N, K, A.data_ptr(), lda, B.data_ptr(), ldb, C_out.data_ptr(), ldc,
+                                                            mean_arr.data_ptr(), _ptr(bias), int(leaky), _ptr(shortcut_in),
+                                                            _ptr(shortcut_out), _stream()), "xnor_b200_gemm_bin_mean_transposed")
+
+
+def gemm_counts(M, N, K, A, lda, B, ldb) -> torch.Tensor:
+    counts = torch.empty(M, N, dtype=torch.int32, device=A.device)
+    capi.check(capi.lib().xnor_b200_gemm_counts(M, N, K, A.data_ptr(), lda, B.data_ptr(), ldb, counts.data_ptr(), _stream()),
+               "xnor_b200_gemm_counts")
+    return counts
+
+
+def forward_convolutional_layer_gpu(l: ConvolutionalLayer, x: torch.Tensor) -> torch.Tensor:
+    """The xnor branch of forward_convolutional_layer_gpu (src-lib/convolutional_kernels.cu:204-262), whole batch."""
+    if l.align_bit_weights_gpu is None:
+        raise RuntimeError("binary_align_weights() has not been called for this layer")
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.numel() != l.batch * l.c * l.h * l.w:
+        raise ValueError("input must be a contiguous fp32 tensor of batch*c*h*w elements")
+    capi.check(capi.lib().xnor_b200_conv_forward(C.byref(l.desc), x.data_ptr(), l.align_bit_weights_gpu.data_ptr(),
+                                                l.mean_arr_gpu.data_ptr(), l.biases_gpu.data_ptr(), l.output_gpu.data_ptr(),
+                                                _ptr(l.bin_conv_shortcut_in_gpu), _ptr(l.bin_conv_shortcut_out_gpu),
+                                                l.scratch.data_ptr(), l.scratch.numel(), _stream()), "xnor_b200_conv_forward")
+    return l.output_gpu

@@ -1,0 +1,160 @@
+/*
+ * xnor_b200 -- C ABI of the B200 (sm_100a) XNOR-Net binarized-convolution forward path.
+ *
+ * Every entry point replaces one function (or one fused run of functions) of hank-ai/darknet's
+ * xnor path; the comment above each declaration names the reference interface it stands in for
+ * (file:line inside the darknet tree).  All pointers are DEVICE pointers unless a parameter
+ * says "host".  `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ * No entry point synchronises, allocates or frees device memory unless its comment says so,
+ * so every launch may be captured into a CUDA graph.
+ *
+ * Semantics are those of the reference's CPU bit path (the only one that is defined for every
+ * layer shape): sign(v) = v > 0, out-of-image taps count as "not > 0", zero padding bits.
+ * Bit i of a bit tensor lives in byte i/8 at position i%8.
+ *
+ * Return value: 0 on success, otherwise one of the XNOR_B200_ERR_* codes; nothing is launched
+ * when an argument check fails.  There is no CPU fallback anywhere behind this interface.
+ */
+#ifndef XNOR_B200_H
+#define XNOR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Exported-symbol marker: the library is built with hidden visibility by default. */
+#if defined(XNOR_B200_BUILD) && defined(__GNUC__)
+#define XNOR_B200_API __attribute__((visibility("default")))
+#else
+#define XNOR_B200_API
+#endif
+
+#define XNOR_B200_OK               0
+#define XNOR_B200_ERR_INVALID      1  /* a size, stride or enum argument is out of range            */
+#define XNOR_B200_ERR_NULL         2  /* a required pointer is NULL                                */
+#define XNOR_B200_ERR_SCRATCH      3  /* scratch buffer smaller than xnor_b200_scratch_bytes()     */
+#define XNOR_B200_ERR_CUDA         4  /* a CUDA runtime call failed; see xnor_b200_last_cuda_error */
+#define XNOR_B200_ERR_ALIGNMENT    5  /* a pointer or leading dimension is not aligned as required */
+#define XNOR_B200_ERR_TOO_LARGE    6  /* a size exceeds a stated fixed limit of the entry point    */
+
+#define XNOR_B200_LINEAR 0
+#define XNOR_B200_LEAKY  1
+
+/* Geometry of one [convolutional] xnor=1 layer: the fields of Darknet::Layer that the path reads
+ * (src-lib/darknet_layers.hpp:39-78: batch, c, h, w, n, size, stride, pad, activation). */
+typedef struct xnor_b200_conv_desc
+{
+	int batch;       /* images per call; the path computes ALL of them (the reference only image 0) */
+	int c, h, w;     /* input channels, height, width (NCHW fp32)                                   */
+	int n;           /* filters                                                                     */
+	int size;        /* square kernel size                                                          */
+	int stride;      /* stride_x == stride_y                                                        */
+	int pad;         /* padding in pixels                                                           */
+	int activation;  /* XNOR_B200_LINEAR or XNOR_B200_LEAKY (fused into the GEMM epilogue)          */
+} xnor_b200_conv_desc;
+
+/* Derived sizes, following make_convolutional_layer (src-lib/convolutional_layer.cpp:833-853)
+ * and binary_align_weights (src-lib/convolutional_layer.cpp:1343-1351). */
+typedef struct xnor_b200_conv_geom
+{
+	int out_h, out_w;
+	int n_out;                 /* out_h*out_w, the GEMM N of one image                              */
+	int k;                     /* size*size*c, the GEMM K in bits                                   */
+	int new_lda;               /* k + (256 - k%256): bits per packed row of A and of B              */
+	int bit_align;             /* n_out + (32 - n_out%32)                                           */
+	int word_path;             /* 1 when c%32==0 (K ordered [c/32][tap][32]), else plain [c][tap]   */
+	size_t weights_bytes;      /* n*new_lda/8: packed weights (the reference allocates one more)    */
+	size_t packed_input_bytes; /* batch*n_out*new_lda/8: the packed, transposed B operand           */
+	size_t output_floats;      /* batch*n*n_out                                                     */
+} xnor_b200_conv_geom;
+
+XNOR_B200_API const char * xnor_b200_strerror(int code);
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
+XNOR_B200_API int xnor_b200_last_cuda_error(void);
+
+/* Fills *geom.  Replaces the size arithmetic of make_convolutional_layer
+ * (src-lib/convolutional_layer.cpp:833-853) and binary_align_weights (:1343-1351). */
+XNOR_B200_API int xnor_b200_conv_geometry(const xnor_b200_conv_desc * desc, xnor_b200_conv_geom * geom);
+
+/* binarize_weights (src-lib/convolutional_layer.cpp:196-213) / fast_binarize_weights_gpu
+ * (src-lib/convolutional_kernels.cu:116-132): per filter mean = (sequential fp32 sum of |w|)/size,
+ * binary = w > 0 ? +mean : -mean.  weights, binary: [n][size] fp32; mean_arr: [n] (may be NULL).
+ * The sum is taken in index order so the result equals the reference CPU value bit for bit. */
+XNOR_B200_API int xnor_b200_binarize_weights(const float * weights, int n, int size, float * binary, float * mean_arr, void * stream);
+
+/* binary_align_weights (src-lib/convolutional_layer.cpp:1339-1411) + get_mean_array (:131-140):
+ * weights [n][c*size*size] fp32 (batch-norm already folded) -> align_bit_weights
+ * (geom.weights_bytes bytes, row f at bit f*new_lda, K order per geom.word_path, zero padding)
+ * and mean_arr [n].  invert != 0 complements every byte when c%32==0, the layout the reference
+ * stores in GPU builds (:1395-1401); the GEMM below expects invert == 0.  Load-time step. */
+XNOR_B200_API int xnor_b200_binary_align_weights(const xnor_b200_conv_desc * desc, const float * weights,
+		uint8_t * align_bit_weights, float * mean_arr, int invert, void * stream);
+
+/* float_to_bit (src-lib/gemm.cpp:1510-1534) / float_to_bit_gpu (src-lib/im2col_kernels.cu:310-317):
+ * bit i of dst = src[i] > 0.  dst receives ceil(size/32)*4 bytes and must be 4-byte aligned. */
+XNOR_B200_API int xnor_b200_float_to_bit(const float * src, uint8_t * dst, size_t size, void * stream);
+
+/* repack_input + float_to_bit (src-lib/gemm.cpp:2202-2220, :1510) / repack_input_gpu_bin
+ * (src-lib/im2col_kernels.cu:715-724): input [c][h*w] fp32 -> packed [c/32][h*w] uint32,
+ * bit (ch%32) = input > 0.  Requires c%32 == 0. */
+XNOR_B200_API int xnor_b200_repack_input_bin(const float * input, uint32_t * packed, int w, int h, int c, void * stream);
+
+/* The whole input-side chain in one kernel, no float im2col buffer:
+ *   c%32==0: repack_input_gpu_bin -> im2col_ongpu -> transpose_uint32_gpu
+ *            (src-lib/convolutional_kernels.cu:220-231; CPU src-lib/convolutional_layer.cpp:1475-1517)
+ *   else:    im2col_align_ongpu -> float_to_bit_gpu -> transpose_bin_gpu
+ *            (src-lib/convolutional_kernels.cu:236-245; CPU im2col_cpu_custom_bin + transpose_bin,
+ *            src-lib/convolutional_layer.cpp:1534-1541)
+ * input [batch][c][h][w] fp32 -> t_bit_input [batch*n_out][new_lda/8] bytes: row (b*n_out + p) holds
+ * the K sign bits of output pixel p of image b followed by zero padding (the reference leaves that
+ * padding unwritten on the GPU).  t_bit_input must be 16-byte aligned. */
+XNOR_B200_API int xnor_b200_pack_input(const xnor_b200_conv_desc * desc, const float * input, uint8_t * t_bit_input, void * stream);
+
+/* gemm_nn_custom_bin_mean_transposed_gpu (src-lib/im2col_kernels.cu:1156-1193), CPU
+ * gemm_nn_custom_bin_mean_transposed (src-lib/gemm.cpp:907-1019) + add_bias
+ * (src-lib/convolutional_layer.cpp:1269-1289) + leaky (src-lib/gemm.cpp:1472-1498):
+ *   count = #agreeing bits of A row i and B row j among the first K;
+ *   C[i*ldc + j] = act( fl( fl((2*count - K) * mean_arr[i]) + bias[i] ) );
+ *   if shortcut_out: shortcut_out[i*ldc + j] = shortcut_in[i*ldc + j] + C[i*ldc + j].
+ * A: M rows of lda bits, B: N rows of ldb bits, both with ZERO padding bits beyond K (A is NOT
+ * inverted).  lda, ldb multiples of 128 and >= K; A, B 16-byte aligned.  bias, shortcut_* may be NULL. */
+XNOR_B200_API int xnor_b200_gemm_bin_mean_transposed(int M, int N, int K,
+		const uint8_t * A, int lda, const uint8_t * B, int ldb,
+		float * C, int ldc, const float * mean_arr, const float * bias, int leaky_activation,
+		const float * shortcut_in, float * shortcut_out, void * stream);
+
+/* The integer accumulators of the GEMM above, for bit-exact checks: counts[i*N + j] = number of
+ * agreeing bits among the first K -- the reference's `count` after `count - f1`
+ * (src-lib/gemm.cpp:964-970, src-lib/im2col_kernels.cu:930-936). */
+XNOR_B200_API int xnor_b200_gemm_counts(int M, int N, int K, const uint8_t * A, int lda, const uint8_t * B, int ldb,
+		int32_t * counts, void * stream);
+
+/* Bytes of scratch xnor_b200_conv_forward needs (= geom.packed_input_bytes, 256-byte rounded).  The
+ * reference sizes net.workspace from other layers and over-allocates two bit_align*K*4-byte buffers
+ * per layer (src-lib/convolutional_layer.cpp:1413-1418); this path owns its scratch explicitly. */
+XNOR_B200_API size_t xnor_b200_scratch_bytes(const xnor_b200_conv_desc * desc);
+
+/* The xnor branch of forward_convolutional_layer_gpu (src-lib/convolutional_kernels.cu:204-262) for the
+ * whole batch: pack_input into scratch, then the GEMM with the batch folded into N and the epilogue
+ * writing NCHW output [batch][n][out_h*out_w].  align_bit_weights / mean_arr come from
+ * xnor_b200_binary_align_weights(invert = 0); biases [n]; shortcut_in/out [batch][n][n_out] or NULL
+ * (the fused [shortcut] of src-lib/darknet_network.cpp:1799-1813).  scratch 256-byte aligned. */
+XNOR_B200_API int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const float * input,
+		const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
+		float * output, const float * shortcut_in, float * shortcut_out,
+		void * scratch, size_t scratch_bytes, void * stream);
+
+/* Measurement helpers (no reference counterpart: the reference ships no peak figures).  Each runs a
+ * register-resident loop on every SM, synchronises, and returns giga binary-ops per second
+ * (64 per 32-bit XOR+POPC+ADD; 2*16*8*256 per b1 mma) in *gops, with the elapsed milliseconds in *ms.
+ * These two calls synchronise the device. */
+XNOR_B200_API int xnor_b200_measure_popc_peak(int iters, double * gops, double * ms);
+XNOR_B200_API int xnor_b200_measure_bmma_peak(int iters, double * gops, double * ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XNOR_B200_H */
