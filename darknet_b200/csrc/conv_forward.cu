@@ -5,6 +5,9 @@
 // reference's four, for every image of the batch instead of image 0 only.
 #include "xnor_common.cuh"
 
+#include <mutex>
+#include <vector>
+
 namespace xnor
 {
 
@@ -22,6 +25,33 @@ int sm_count()
 		cached[dev] = n;
 	}
 	return cached[dev];
+}
+
+int ensure_dynamic_smem(const void * kernel, size_t bytes)
+{
+	if (bytes <= 48 * 1024) { return XNOR_B200_OK; }
+	struct Entry { const void * kernel; int device; size_t bytes; };
+	static std::mutex mu;
+	static std::vector<Entry> done;
+	int dev = 0;
+	cudaError_t e = cudaGetDevice(&dev);
+	if (e != cudaSuccess) { return cuda_fail(e); }
+	std::lock_guard<std::mutex> lock(mu);
+	for (Entry & en : done)
+	{
+		if (en.kernel == kernel && en.device == dev)
+		{
+			if (en.bytes >= bytes) { return XNOR_B200_OK; }
+			e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+			if (e != cudaSuccess) { return cuda_fail(e); }
+			en.bytes = bytes;
+			return XNOR_B200_OK;
+		}
+	}
+	e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+	if (e != cudaSuccess) { return cuda_fail(e); }
+	done.push_back({kernel, dev, bytes});
+	return XNOR_B200_OK;
 }
 
 int validate_desc(const xnor_b200_conv_desc * d)

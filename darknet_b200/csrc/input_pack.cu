@@ -277,25 +277,18 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 	const long long grid = (long long)d.batch * p.tiles_per_image;
 	if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
 
-	cudaError_t e;
 	if (word_path)
 	{
 		const bool vec4 = (d.w % 4 == 0) && (((uintptr_t)input & 15u) == 0);
 		auto kern = vec4 ? pack_input_words_kernel<true> : pack_input_words_kernel<false>;
-		if (smem > 48 * 1024)
-		{
-			e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PK_MAX_SMEM);
-			if (e != cudaSuccess) { return cuda_fail(e); }
-		}
+		int rc = ensure_dynamic_smem((const void *)kern, smem > 48 * 1024 ? PK_MAX_SMEM : 0);
+		if (rc != XNOR_B200_OK) { return rc; }
 		kern<<<(unsigned)grid, PK_THREADS, smem, stream>>>(p);
 	}
 	else
 	{
-		if (smem > 48 * 1024)
-		{
-			e = cudaFuncSetAttribute(pack_input_bits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PK_MAX_SMEM);
-			if (e != cudaSuccess) { return cuda_fail(e); }
-		}
+		int rc = ensure_dynamic_smem((const void *)pack_input_bits_kernel, smem > 48 * 1024 ? PK_MAX_SMEM : 0);
+		if (rc != XNOR_B200_OK) { return rc; }
 		pack_input_bits_kernel<<<(unsigned)grid, PK_THREADS, smem, stream>>>(p);
 	}
 	return check_launch();

@@ -36,6 +36,10 @@ inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 int validate_desc(const xnor_b200_conv_desc * d);
 
+// Raises a kernel's dynamic shared-memory limit once per (device, kernel); later calls are a table lookup,
+// so launchers stay free of runtime attribute calls once warmed up (e.g. while a stream is being captured).
+int ensure_dynamic_smem(const void * kernel, size_t bytes);
+
 // Internal launchers shared between translation units --------------------------------------
 
 // GEMM with the batch folded into the column index: column j = b*n_per_image + p is written to

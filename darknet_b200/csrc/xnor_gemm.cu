@@ -83,7 +83,8 @@ xnor_gemm_kernel(const GemmParams p)
 		{
 			const int r = ch / CHUNKS_ROW;
 			const int kc = (ch - r * CHUNKS_ROW) * 4;
-			const bool ok = (m0 + r < p.M) && (k0 + kc < p.kw);
+			if (k0 + kc >= p.kw) { continue; }          // never read by the compute loop
+			const bool ok = (m0 + r < p.M);
 			const uint32_t * src = ok ? p.A + (size_t)(m0 + r) * p.lda_words + k0 + kc : p.A;
 			cp_async_16(dA + r * PITCH + kc, src, ok);
 		}
@@ -91,7 +92,8 @@ xnor_gemm_kernel(const GemmParams p)
 		{
 			const int r = ch / CHUNKS_ROW;
 			const int kc = (ch - r * CHUNKS_ROW) * 4;
-			const bool ok = (n0 + r < p.n_total) && (k0 + kc < p.kw);
+			if (k0 + kc >= p.kw) { continue; }
+			const bool ok = (n0 + r < p.n_total);
 			const uint32_t * src = ok ? p.B + (size_t)(n0 + r) * p.ldb_words + k0 + kc : p.B;
 			cp_async_16(dB + r * PITCH + kc, src, ok);
 		}
@@ -124,8 +126,7 @@ xnor_gemm_kernel(const GemmParams p)
 		}
 		const uint32_t * cA = sA + (kt % STAGES) * A_STAGE + ty * PITCH;
 		const uint32_t * cB = sB + (kt % STAGES) * B_STAGE + tx * PITCH;
-		#pragma unroll
-		for (int k4 = 0; k4 < KT; k4 += 4)
+		auto step = [&](int k4)
 		{
 			uint4 a[TM], b[TN];
 			#pragma unroll
@@ -142,6 +143,16 @@ xnor_gemm_kernel(const GemmParams p)
 							+ __popc(a[i].z ^ b[j].z) + __popc(a[i].w ^ b[j].w);
 				}
 			}
+		};
+		const int kvalid = min(KT, p.kw - kt * KT);   // the last stage of a short K holds fewer words
+		if (kvalid == KT)
+		{
+			#pragma unroll
+			for (int k4 = 0; k4 < KT; k4 += 4) { step(k4); }
+		}
+		else
+		{
+			for (int k4 = 0; k4 < kvalid; k4 += 4) { step(k4); }
 		}
 	}
 	cp_async_wait<0>();
@@ -181,15 +192,8 @@ static int launch_config(GemmParams & p, cudaStream_t stream)
 	constexpr int NT = (BM / TM) * (BN / TN);
 	constexpr size_t SMEM = (size_t)STAGES * (BM + BN) * (KT + 4) * 4;
 	auto kern = xnor_gemm_kernel<BM, BN, TM, TN, KT, STAGES>;
-	static thread_local int configured_device = -1;
-	int dev = 0;
-	cudaGetDevice(&dev);
-	if (SMEM > 48 * 1024 && configured_device != dev)
-	{
-		cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-		if (e != cudaSuccess) { return cuda_fail(e); }
-		configured_device = dev;
-	}
+	int rc = ensure_dynamic_smem((const void *)kern, SMEM);
+	if (rc != XNOR_B200_OK) { return rc; }
 	p.tiles_m = (p.M + BM - 1) / BM;
 	p.tiles_n = (p.n_total + BN - 1) / BN;
 	const long long grid = (long long)p.tiles_m * p.tiles_n;

@@ -1,0 +1,347 @@
+"""Host-side network runner for Darknet xnor networks: cfg parser, .weights reader/writer, load-time
+preparation and the forward loop.
+
+It mirrors the reference's call sequence (names kept):
+
+    net = parse_network_cfg(cfg_path, batch)         # src-lib/weights.cpp:47, src-lib/darknet_cfg.cpp:797-1068
+    load_weights(net, weights_path)                  # src-lib/weights.cpp:421
+    fuse_conv_batchnorm(net)                         # src-lib/darknet_network.cpp:1667
+    calculate_binary_weights(net)                    # src-lib/darknet_network.cpp:1778
+    out = network_predict_gpu(net, x)                # src-lib/network_kernels.cu:709 -> forward_network_gpu :30
+
+Every [convolutional] xnor=1 layer runs through libxnor_b200.so (this package's product).  The layers
+around the path -- the float convolutions, maxpool, route, upsample, shortcut, avgpool, softmax and
+the yolo/region activations -- are not part of it; like Darknet, which hands them to cuDNN and its own
+small kernels, this runner hands them to cuDNN/ATen through torch, in fp32 with TF32 disabled.
+Only the section types and keys that occur in the three shipped xnor cfgs are understood.
+"""
+from __future__ import annotations
+
+import math
+import struct
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from . import capi
+from . import layer as L
+
+
+# ---- cfg -----------------------------------------------------------------------------------------
+
+def read_cfg(text: str) -> List[Tuple[str, Dict[str, str]]]:
+    """INI-like sections in file order; '#' and ';' start comments; keys are stripped of blanks."""
+    sections: List[Tuple[str, Dict[str, str]]] = []
+    for raw in text.splitlines():
+        line = raw.strip()
+        if not line or line[0] in "#;":
+            continue
+        if line.startswith("["):
+            sections.append((line.strip("[] \t").lower(), {}))
+        elif "=" in line and sections:
+            k, v = line.split("=", 1)
+            sections[-1][1][k.strip()] = v.strip()
+    return sections
+
+
+@dataclass
+class Layer:
+    type: str
+    index: int
+    c: int = 0
+    h: int = 0
+    w: int = 0
+    out_c: int = 0
+    out_h: int = 0
+    out_w: int = 0
+    opts: Dict[str, str] = field(default_factory=dict)
+    # convolutional
+    n: int = 0
+    size: int = 1
+    stride: int = 1
+    pad: int = 0
+    activation: str = "linear"
+    batch_normalize: int = 0
+    xnor: int = 0
+    use_bin_output: int = 0
+    weights: Optional[np.ndarray] = None
+    biases: Optional[np.ndarray] = None
+    scales: Optional[np.ndarray] = None
+    rolling_mean: Optional[np.ndarray] = None
+    rolling_variance: Optional[np.ndarray] = None
+    weights_gpu: Optional[torch.Tensor] = None
+    biases_gpu: Optional[torch.Tensor] = None
+    xnor_layer: Optional[L.ConvolutionalLayer] = None
+    # route / shortcut
+    input_layers: List[int] = field(default_factory=list)
+    # shortcut fused into the preceding xnor conv (src-lib/darknet_network.cpp:1799-1813)
+    blank: bool = False
+    output_gpu: Optional[torch.Tensor] = None
+
+    @property
+    def outputs(self) -> int:
+        return self.out_c * self.out_h * self.out_w
+
+
+@dataclass
+class Network:
+    batch: int
+    c: int
+    h: int
+    w: int
+    layers: List[Layer]
+    device: torch.device
+    xnor_launches_per_forward: int = 0
+
+
+def parse_network_cfg(path: str, batch: int = 1, device: str = "cuda:0") -> Network:
+    with open(path) as fh:
+        sections = read_cfg(fh.read())
+    if not sections or sections[0][0] not in ("net", "network"):
+        raise ValueError("first cfg section must be [net]")
+    net_opts = sections[0][1]
+    c, h, w = int(net_opts.get("channels", 3)), int(net_opts.get("height", 0)), int(net_opts.get("width", 0))
+    net = Network(batch, c, h, w, [], torch.device(device))
+    for idx, (name, o) in enumerate(sections[1:]):
+        l = Layer(name, idx, c, h, w, opts=o)
+        if name == "convolutional":
+            l.n = int(o.get("filters", 1))
+            l.size = int(o.get("size", 1))
+            l.stride = int(o.get("stride", 1))
+            l.pad = l.size // 2 if int(o.get("pad", 0)) else int(o.get("padding", 0))
+            l.activation = o.get("activation", "logistic")
+            l.batch_normalize = int(o.get("batch_normalize", 0))
+            l.xnor = int(o.get("xnor", 0))
+            l.use_bin_output = int(o.get("bin_output", 0))
+            l.out_c = l.n
+            l.out_h = (h + 2 * l.pad - l.size) // l.stride + 1
+            l.out_w = (w + 2 * l.pad - l.size) // l.stride + 1
+        elif name == "maxpool":
+            l.size = int(o.get("size", 2))
+            l.stride = int(o.get("stride", 1))
+            l.pad = int(o.get("padding", l.size - 1))
+            l.out_c = c
+            l.out_h = (h + l.pad - l.size) // l.stride + 1       # src-lib/maxpool_layer.cpp:129-130
+            l.out_w = (w + l.pad - l.size) // l.stride + 1
+        elif name == "route":
+            refs = [int(v) for v in o["layers"].split(",")]
+            l.input_layers = [r if r >= 0 else idx + r for r in refs]
+            first = net.layers[l.input_layers[0]]
+            l.out_h, l.out_w = first.out_h, first.out_w
+            l.out_c = sum(net.layers[i].out_c for i in l.input_layers)
+            for i in l.input_layers:                              # src-lib/darknet_cfg.cpp:833-845
+                net.layers[i].use_bin_output = 0
+        elif name == "shortcut":
+            frm = int(o["from"])
+            l.input_layers = [frm if frm >= 0 else idx + frm]
+            l.activation = o.get("activation", "linear")
+            l.out_c, l.out_h, l.out_w = c, h, w
+            net.layers[idx - 1].use_bin_output = 0               # src-lib/darknet_cfg.cpp:846-856
+            net.layers[l.input_layers[0]].use_bin_output = 0
+        elif name == "upsample":
+            l.stride = int(o.get("stride", 2))
+            l.out_c, l.out_h, l.out_w = c, h * l.stride, w * l.stride
+        elif name == "avgpool":
+            l.out_c, l.out_h, l.out_w = c, 1, 1
+        elif name in ("yolo", "region", "softmax"):
+            l.out_c, l.out_h, l.out_w = c, h, w
+        else:
+            raise ValueError(f"cfg section [{name}] is outside the xnor cfgs this runner understands")
+        net.layers.append(l)
+        c, h, w = l.out_c, l.out_h, l.out_w
+    return net
+
+
+# ---- .weights ------------------------------------------------------------------------------------
+# header: int32 major, minor, revision; `seen` uint64 when major*10+minor >= 2 else uint32
+# (src-lib/weights.cpp:460-478); per conv: biases[n], then scales/rolling_mean/rolling_variance[n] when
+# batch_normalize, then weights[n*c*size*size] fp32 (src-lib/weights.cpp:369-398).
+
+def write_synthetic_weights(net: Network, path: str, seed: int = 1) -> None:
+    """Seeded weights: w ~ N(0, 0.05), b ~ N(0, 0.01), BN scales 1, rolling mean 0, rolling variance 1."""
+    rng = np.random.default_rng(seed)
+    with open(path, "wb") as fh:
+        fh.write(struct.pack("<iiiQ", 0, 2, 5, 0))
+        for l in net.layers:
+            if l.type != "convolutional":
+                continue
+            fh.write((rng.standard_normal(l.n) * 0.01).astype("<f4").tobytes())
+            if l.batch_normalize:
+                fh.write(np.ones(l.n, "<f4").tobytes())
+                fh.write(np.zeros(l.n, "<f4").tobytes())
+                fh.write(np.ones(l.n, "<f4").tobytes())
+            fh.write((rng.standard_normal(l.n * l.c * l.size * l.size) * 0.05).astype("<f4").tobytes())
+
+
+def load_weights(net: Network, path: str) -> None:
+    with open(path, "rb") as fh:
+        major, minor, _rev = struct.unpack("<iii", fh.read(12))
+        fh.read(8 if major * 10 + minor >= 2 else 4)
+
+        def take(count: int) -> np.ndarray:
+            buf = fh.read(4 * count)
+            if len(buf) != 4 * count:
+                raise ValueError("weights file ended early")
+            return np.frombuffer(buf, "<f4").astype(np.float32)
+
+        for l in net.layers:
+            if l.type != "convolutional":
+                continue
+            l.biases = take(l.n)
+            if l.batch_normalize:
+                l.scales, l.rolling_mean, l.rolling_variance = take(l.n), take(l.n), take(l.n)
+            l.weights = take(l.n * l.c * l.size * l.size).reshape(l.n, l.c, l.size, l.size)
+
+
+# ---- load-time preparation -----------------------------------------------------------------------
+
+def fuse_conv_batchnorm(net: Network) -> None:
+    """Folds batch-norm into weights and biases in double precision (src-lib/darknet_network.cpp:1667-1708)."""
+    for l in net.layers:
+        if l.type == "convolutional" and l.batch_normalize:
+            std = np.sqrt(l.rolling_variance.astype(np.float64) + 0.00001)
+            l.biases = (l.biases.astype(np.float64) - l.scales.astype(np.float64) * l.rolling_mean.astype(np.float64) / std).astype(np.float32)
+            pre = l.scales.astype(np.float64) / std
+            l.weights = (l.weights.astype(np.float64) * pre[:, None, None, None]).astype(np.float32)
+            l.batch_normalize = 0
+
+
+def calculate_binary_weights(net: Network) -> None:
+    """Packs every xnor conv through the C ABI, drops the activation of bin_output layers and fuses a
+    same-shape [shortcut] that directly follows an xnor conv (src-lib/darknet_network.cpp:1778-1817)."""
+    dev = net.device
+    for j, l in enumerate(net.layers):
+        if l.type != "convolutional":
+            continue
+        l.weights_gpu = torch.from_numpy(l.weights).to(dev)
+        l.biases_gpu = torch.from_numpy(l.biases).to(dev)
+        if not l.xnor:
+            continue
+        if l.use_bin_output:
+            l.activation = "linear"
+        if l.activation not in ("linear", "leaky"):
+            raise ValueError("xnor layers in the shipped cfgs are leaky or linear")
+        act = capi.LEAKY if l.activation == "leaky" else capi.LINEAR
+        xl = L.make_convolutional_layer(net.batch, l.h, l.w, l.c, l.n, l.size, l.stride, l.pad, act, device=str(dev))
+        xl.load_weights(l.weights_gpu, l.biases_gpu)
+        L.binary_align_weights(xl)
+        l.xnor_layer = xl
+        l.output_gpu = xl.output_gpu
+        net.xnor_launches_per_forward += 2
+        if j + 1 < len(net.layers):
+            sc = net.layers[j + 1]
+            if sc.type == "shortcut" and (sc.w, sc.h, sc.c) == (sc.out_w, sc.out_h, sc.out_c) and sc.activation == "linear":
+                sc.blank = True
+                sc.output_gpu = torch.empty(net.batch, sc.out_c, sc.out_h, sc.out_w, device=dev)
+                xl.bin_conv_shortcut_out_gpu = sc.output_gpu
+    torch.cuda.synchronize(dev)
+
+
+# ---- forward -------------------------------------------------------------------------------------
+
+def _activate(x: torch.Tensor, a: str) -> torch.Tensor:
+    if a == "linear":
+        return x
+    if a == "leaky":
+        return torch.where(x > 0, x, x * 0.1)
+    if a == "logistic":
+        return torch.sigmoid(x)
+    raise ValueError(f"activation {a} not used by the xnor cfgs")
+
+
+def _maxpool(x: torch.Tensor, l: Layer) -> torch.Tensor:
+    # window origin = -pad/2, out-of-image taps ignored (src-lib/maxpool_layer_kernels.cu:48-86)
+    lo = l.pad // 2
+    need_h = (l.out_h - 1) * l.stride + l.size - lo
+    need_w = (l.out_w - 1) * l.stride + l.size - lo
+    x = F.pad(x, (lo, max(need_w - l.w, 0), lo, max(need_h - l.h, 0)), value=float("-inf"))
+    return F.max_pool2d(x, l.size, l.stride)[:, :, :l.out_h, :l.out_w]
+
+
+def _yolo(x: torch.Tensor, l: Layer) -> torch.Tensor:
+    # logistic on x, y, objectness and classes; w, h raw (src-lib/yolo_layer.cpp:1439-1489)
+    mask = [int(v) for v in l.opts["mask"].split(",")]
+    classes = int(l.opts.get("classes", 20))
+    b = x.shape[0]
+    v = x.reshape(b, len(mask), 5 + classes, l.h * l.w).clone()
+    v[:, :, 0:2] = torch.sigmoid(v[:, :, 0:2])
+    v[:, :, 4:] = torch.sigmoid(v[:, :, 4:])
+    return v.reshape(b, -1, l.h, l.w)
+
+
+def _region(x: torch.Tensor, l: Layer) -> torch.Tensor:
+    # logistic on x, y and objectness, softmax over classes (src-lib/region_layer.cpp:494-537)
+    num = int(l.opts.get("num", 1))
+    classes = int(l.opts.get("classes", 20))
+    coords = int(l.opts.get("coords", 4))
+    b = x.shape[0]
+    v = x.reshape(b, num, coords + 1 + classes, l.h * l.w).clone()
+    v[:, :, 0:2] = torch.sigmoid(v[:, :, 0:2])
+    v[:, :, coords] = torch.sigmoid(v[:, :, coords])
+    if int(l.opts.get("softmax", 0)):
+        v[:, :, coords + 1:] = torch.softmax(v[:, :, coords + 1:], dim=2)
+    return v.reshape(b, -1, l.h, l.w)
+
+
+def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
+    """The layer loop of forward_network_gpu (src-lib/network_kernels.cu:30-65).  Returns the outputs of the
+    network's head layers (yolo / region / softmax)."""
+    heads: List[torch.Tensor] = []
+    cur = x
+    for l in net.layers:
+        if l.type == "convolutional":
+            if l.xnor:
+                xl = l.xnor_layer
+                nxt = net.layers[l.index + 1] if l.index + 1 < len(net.layers) else None
+                if nxt is not None and nxt.blank:
+                    xl.bin_conv_shortcut_in_gpu = net.layers[nxt.input_layers[0]].output_gpu
+                cur = L.forward_convolutional_layer_gpu(xl, cur)
+            else:
+                cur = _activate(F.conv2d(cur, l.weights_gpu, l.biases_gpu, l.stride, l.pad), l.activation)
+        elif l.type == "maxpool":
+            cur = _maxpool(cur, l)
+        elif l.type == "route":
+            cur = net.layers[l.input_layers[0]].output_gpu if len(l.input_layers) == 1 else \
+                torch.cat([net.layers[i].output_gpu for i in l.input_layers], 1)
+        elif l.type == "shortcut":
+            cur = l.output_gpu if l.blank else _activate(cur + net.layers[l.input_layers[0]].output_gpu, l.activation)
+        elif l.type == "upsample":
+            cur = F.interpolate(cur, scale_factor=l.stride, mode="nearest")
+        elif l.type == "avgpool":
+            cur = cur.mean((2, 3), keepdim=True)
+        elif l.type == "softmax":
+            cur = torch.softmax(cur.reshape(cur.shape[0], -1), 1).reshape(cur.shape)
+            heads.append(cur)
+        elif l.type == "yolo":
+            cur = _yolo(cur, l)
+            heads.append(cur)
+        elif l.type == "region":
+            cur = _region(cur, l)
+            heads.append(cur)
+        l.output_gpu = cur
+    return heads
+
+
+def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "cuda:0") -> Network:
+    """load_network_custom (src-lib/weights.cpp:665-691): parse, load, fold batch-norm, pack binary weights."""
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    net = parse_network_cfg(cfg, batch, device)
+    load_weights(net, weights)
+    fuse_conv_batchnorm(net)
+    calculate_binary_weights(net)
+    return net
+
+
+def xnor_layer_shapes(net: Network) -> List[dict]:
+    """Per xnor layer: GEMM sizes and binary-op count per image (2*M*N*K, unpadded K)."""
+    rows = []
+    for l in net.layers:
+        if l.type == "convolutional" and l.xnor:
+            M, N, K = l.n, l.out_h * l.out_w, l.size * l.size * l.c
+            rows.append(dict(index=l.index, c=l.c, h=l.h, w=l.w, n=l.n, size=l.size, stride=l.stride, pad=l.pad,
+                             activation=l.activation, M=M, N=N, K=K, binops=2 * M * N * K))
+    return rows
