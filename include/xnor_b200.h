@@ -147,6 +147,28 @@ XNOR_B200_API int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const
 		float * output, const float * shortcut_in, float * shortcut_out,
 		void * scratch, size_t scratch_bytes, void * stream);
 
+/* Bytes of the library-resident scratch array behind xnor_b200_conv_forward_static. */
+#define XNOR_B200_STATIC_SCRATCH_BYTES (8u << 20)
+
+/* xnor_b200_conv_forward for callers that cannot allocate device memory or pass a scratch buffer (a plugin
+ * slot that is handed nothing but layer inputs and outputs, a server whose memory pool is sealed after
+ * start-up, a real-time loop in which cudaMalloc's implicit synchronisation is not acceptable).  It has no
+ * counterpart in the reference, whose layers always borrow net.workspace.  Same arguments and results as
+ * xnor_b200_conv_forward, minus scratch: the packed activation operand goes into a fixed
+ * XNOR_B200_STATIC_SCRATCH_BYTES array that is part of the library image (every GPU that loads the library
+ * holds those bytes until the process exits).  The call makes no cudaMalloc/cudaFree and uses no allocating
+ * library routine.
+ *   - Limit: returns XNOR_B200_ERR_TOO_LARGE when geom.packed_input_bytes (batch*n_out*new_lda/8) exceeds
+ *     XNOR_B200_STATIC_SCRATCH_BYTES; nothing is launched in that case.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current) and remembers it; make that first call before starting any stream capture.
+ *   - All calls on one device share the one array and it keeps the previous call's contents.  Nothing in it
+ *     needs clearing (each call rewrites every word it later reads), but two calls whose kernels can overlap
+ *     on the GPU -- different streams, or graph branches -- race on it: serialise them. */
+XNOR_B200_API int xnor_b200_conv_forward_static(const xnor_b200_conv_desc * desc, const float * input,
+		const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
+		float * output, const float * shortcut_in, float * shortcut_out, void * stream);
+
 /* Measurement helpers (no reference counterpart: the reference ships no peak figures).  Each runs a
  * register-resident loop on every SM, synchronises, and returns giga binary-ops per second
  * (64 per 32-bit XOR+POPC+ADD; 2*16*8*256 per b1 mma) in *gops, with the elapsed milliseconds in *ms.
