@@ -23,7 +23,7 @@ EXPORTS = (
     "xnor_b200_binarize_weights", "xnor_b200_binary_align_weights", "xnor_b200_float_to_bit",
     "xnor_b200_repack_input_bin", "xnor_b200_pack_input", "xnor_b200_gemm_bin_mean_transposed",
     "xnor_b200_gemm_counts", "xnor_b200_scratch_bytes", "xnor_b200_conv_forward",
-    "xnor_b200_conv_forward_static",
+    "xnor_b200_conv_forward_static", "xnor_b200_take_device_status",
     "xnor_b200_measure_popc_peak", "xnor_b200_measure_bmma_peak",
 )
 
@@ -78,6 +78,7 @@ def lib() -> C.CDLL:
     L.xnor_b200_scratch_bytes.argtypes = [dp]
     L.xnor_b200_conv_forward.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
     L.xnor_b200_conv_forward_static.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
+    L.xnor_b200_take_device_status.argtypes = [C.POINTER(ci)]
     L.xnor_b200_measure_popc_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]
     L.xnor_b200_measure_bmma_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]
     _lib = L

@@ -88,6 +88,14 @@ extern "C" const char * xnor_b200_strerror(int code)
 
 extern "C" int xnor_b200_last_cuda_error(void) { return g_last_cuda_error; }
 
+extern "C" int xnor_b200_take_device_status(int * status)
+{
+	if (status == nullptr) { return XNOR_B200_ERR_NULL; }
+	cudaError_t e = cudaDeviceSynchronize();
+	if (e != cudaSuccess) { return cuda_fail(e); }
+	return read_tc_error(status, true);
+}
+
 extern "C" int xnor_b200_conv_geometry(const xnor_b200_conv_desc * desc, xnor_b200_conv_geom * geom)
 {
 	if (desc == nullptr || geom == nullptr) { return XNOR_B200_ERR_NULL; }

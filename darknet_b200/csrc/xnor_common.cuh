@@ -49,6 +49,15 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
 		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream);
 
+// Tensor-core (tcgen05, kind::i8 on bytes expanded in shared memory) variant of the same GEMM for large layers.
+bool tc_gemm_eligible(int M, int n_total, int K);
+int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
+		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
+		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream);
+// Sticky device-side status (bounded wait expired in the tensor-core kernel); synchronous copy from the device.
+int read_tc_error(int * out, bool clear);
+
 int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32_t * t_bit_input, cudaStream_t stream);
 
 }  // namespace xnor

@@ -11,12 +11,26 @@
 // disagreeing bits among the first K, so   2*count - K  =  K - 2*sum popc(a ^ b)   with no padding
 // correction term (the reference subtracts f1 because its A padding is complemented).
 //
-// Tiling: a CTA computes a BM x BN tile; operands are staged through a STAGES-deep cp.async ring in shared
-// memory (row pitch KT+4 words so that 16-byte reads of 8 consecutive rows hit 32 distinct banks); every
-// thread owns a TM x TN register tile of int32 accumulators and consumes four K-words per 16-byte shared
-// load.  Accumulators are exact integers; the epilogue mirrors the reference CPU rounding order: one
-// fp32 multiply, one fp32 add, then the leaky blend -- never a fused multiply-add.
+// Tiling: a CTA computes a BM x BN tile over one K slice; operands are staged through a STAGES-deep cp.async
+// ring in shared memory (row pitch KT+4 words so that 16-byte reads of 8 consecutive rows hit 32 distinct
+// banks); every thread owns a TM x TN register tile of int32 accumulators and consumes four K-words per
+// 16-byte shared load.
+//
+// Split-K over a thread-block cluster: layers with many filters but few output pixels (13x13 maps at batch 1)
+// have too few tiles to occupy 148 SMs.  For those the K range is divided among the S CTAs of a (1,1,S)
+// cluster; the non-leading CTAs park their integer partial sums in their own shared memory, and the leading
+// CTA adds them through distributed shared memory before running the epilogue.  No global scratch, no
+// atomics, no second launch, and the sums stay exact integers in any order.
+//
+// The epilogue mirrors the reference CPU rounding order: one fp32 multiply, one fp32 add, then the leaky blend
+// -- never a fused multiply-add.
 #include "xnor_common.cuh"
+
+#include <cooperative_groups.h>
+#include <cstdio>
+#include <cstdlib>
+
+namespace cg = cooperative_groups;
 
 namespace xnor
 {
@@ -27,7 +41,9 @@ struct GemmParams
 	const uint32_t * B;
 	int M, n_total, n_per_image, K;
 	int lda_words, ldb_words;
-	int kw;                 // K-words to visit, multiple of 4 (<= lda_words, ldb_words)
+	int kw;                 // K-words to visit in total, multiple of 4 (<= lda_words, ldb_words)
+	int kw_slice;           // K-words per cluster rank, multiple of 4
+	int split;              // cluster size along K (gridDim.z)
 	float * C;
 	int ldc;
 	const float * mean_arr;
@@ -61,6 +77,7 @@ xnor_gemm_kernel(const GemmParams p)
 	constexpr int B_STAGE = BN * PITCH;
 	constexpr int CHUNKS_ROW = KT / 4;          // 16-byte chunks per staged row
 	static_assert(KT % 4 == 0, "KT must be a multiple of 4 words");
+	static_assert(STAGES * (BM + BN) * PITCH >= NT * TM * TN, "ring too small to park split-K partial sums");
 
 	extern __shared__ __align__(16) uint32_t smem[];
 	uint32_t * sA = smem;
@@ -74,6 +91,8 @@ xnor_gemm_kernel(const GemmParams p)
 	const int n0 = tile_n * BN;
 	const int tx = threadIdx.x % TX;
 	const int ty = threadIdx.x / TX;
+	const int k_begin = blockIdx.z * p.kw_slice;
+	const int k_end = min(k_begin + p.kw_slice, p.kw);
 
 	auto load_stage = [&](int stage, int k0)
 	{
@@ -83,7 +102,7 @@ xnor_gemm_kernel(const GemmParams p)
 		{
 			const int r = ch / CHUNKS_ROW;
 			const int kc = (ch - r * CHUNKS_ROW) * 4;
-			if (k0 + kc >= p.kw) { continue; }          // never read by the compute loop
+			if (k0 + kc >= k_end) { continue; }          // never read by the compute loop
 			const bool ok = (m0 + r < p.M);
 			const uint32_t * src = ok ? p.A + (size_t)(m0 + r) * p.lda_words + k0 + kc : p.A;
 			cp_async_16(dA + r * PITCH + kc, src, ok);
@@ -92,7 +111,7 @@ xnor_gemm_kernel(const GemmParams p)
 		{
 			const int r = ch / CHUNKS_ROW;
 			const int kc = (ch - r * CHUNKS_ROW) * 4;
-			if (k0 + kc >= p.kw) { continue; }
+			if (k0 + kc >= k_end) { continue; }
 			const bool ok = (n0 + r < p.n_total);
 			const uint32_t * src = ok ? p.B + (size_t)(n0 + r) * p.ldb_words + k0 + kc : p.B;
 			cp_async_16(dB + r * PITCH + kc, src, ok);
@@ -107,11 +126,11 @@ xnor_gemm_kernel(const GemmParams p)
 		for (int j = 0; j < TN; ++j) { acc[i][j] = 0; }
 	}
 
-	const int num_kt = (p.kw + KT - 1) / KT;
+	const int num_kt = (max(k_end - k_begin, 0) + KT - 1) / KT;
 	#pragma unroll
 	for (int s = 0; s < STAGES - 1; ++s)
 	{
-		if (s < num_kt) { load_stage(s, s * KT); }
+		if (s < num_kt) { load_stage(s, k_begin + s * KT); }
 		cp_async_commit();
 	}
 
@@ -121,7 +140,7 @@ xnor_gemm_kernel(const GemmParams p)
 		__syncthreads();
 		{
 			const int nk = kt + STAGES - 1;
-			if (nk < num_kt) { load_stage(nk % STAGES, nk * KT); }
+			if (nk < num_kt) { load_stage(nk % STAGES, k_begin + nk * KT); }
 			cp_async_commit();
 		}
 		const uint32_t * cA = sA + (kt % STAGES) * A_STAGE + ty * PITCH;
@@ -144,7 +163,7 @@ xnor_gemm_kernel(const GemmParams p)
 				}
 			}
 		};
-		const int kvalid = min(KT, p.kw - kt * KT);   // the last stage of a short K holds fewer words
+		const int kvalid = min(KT, k_end - k_begin - kt * KT);   // the last stage of a slice may hold fewer words
 		if (kvalid == KT)
 		{
 			#pragma unroll
@@ -156,6 +175,39 @@ xnor_gemm_kernel(const GemmParams p)
 		}
 	}
 	cp_async_wait<0>();
+
+	// Split-K: fold the partial sums of cluster ranks 1..S-1 into rank 0 through distributed shared memory.
+	if (p.split > 1)
+	{
+		cg::cluster_group cluster = cg::this_cluster();
+		__syncthreads();                                   // everyone is done reading the operand ring
+		int * park = reinterpret_cast<int *>(smem);        // [TM*TN][NT]: consecutive threads, consecutive words
+		if (blockIdx.z != 0)
+		{
+			#pragma unroll
+			for (int i = 0; i < TM; ++i)
+			{
+				#pragma unroll
+				for (int j = 0; j < TN; ++j) { park[(i * TN + j) * NT + threadIdx.x] = acc[i][j]; }
+			}
+		}
+		cluster.sync();
+		if (blockIdx.z == 0)
+		{
+			for (int r = 1; r < p.split; ++r)
+			{
+				const int * peer = cluster.map_shared_rank(park, r);
+				#pragma unroll
+				for (int i = 0; i < TM; ++i)
+				{
+					#pragma unroll
+					for (int j = 0; j < TN; ++j) { acc[i][j] += peer[(i * TN + j) * NT + threadIdx.x]; }
+				}
+			}
+		}
+		cluster.sync();                                    // peers keep their shared memory alive until it has been read
+		if (blockIdx.z != 0) { return; }
+	}
 
 	// epilogue
 	#pragma unroll
@@ -186,6 +238,15 @@ xnor_gemm_kernel(const GemmParams p)
 	}
 }
 
+// ---- configurations ----------------------------------------------------------------------------
+
+struct TileConfig
+{
+	int bm, bn;
+	float cost;             // relative cost of one (row, column, K-word) product in this register tile
+	int (*launch)(GemmParams &, cudaStream_t);
+};
+
 template <int BM, int BN, int TM, int TN, int KT, int STAGES>
 static int launch_config(GemmParams & p, cudaStream_t stream)
 {
@@ -198,8 +259,48 @@ static int launch_config(GemmParams & p, cudaStream_t stream)
 	p.tiles_n = (p.n_total + BN - 1) / BN;
 	const long long grid = (long long)p.tiles_m * p.tiles_n;
 	if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
-	kern<<<(unsigned)grid, NT, SMEM, stream>>>(p);
+
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = dim3((unsigned)grid, 1, (unsigned)p.split);
+	cfg.blockDim = dim3(NT, 1, 1);
+	cfg.dynamicSmemBytes = SMEM;
+	cfg.stream = stream;
+	cudaLaunchAttribute attr[1];
+	attr[0].id = cudaLaunchAttributeClusterDimension;
+	attr[0].val.clusterDim.x = 1;
+	attr[0].val.clusterDim.y = 1;
+	attr[0].val.clusterDim.z = (unsigned)p.split;
+	cfg.attrs = attr;
+	cfg.numAttrs = 1;
+	cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+	if (e != cudaSuccess) { return cuda_fail(e); }
 	return check_launch();
+}
+
+// Measured on B200: the POPC unit is the limiter for every register tile, so small tiles with many resident
+// warps (index 2..5) beat the classic large tiles (0, 1: one 8-warp CTA per SM, latency-bound); the large
+// ones are kept for the tuning sweep only and are never chosen automatically.
+static const TileConfig g_configs[] = {
+	{128, 128, 2.00f, launch_config<128, 128, 8, 8, 32, 3>},
+	{ 64, 128, 1.40f, launch_config< 64, 128, 4, 8, 32, 3>},
+	{ 64,  64, 1.00f, launch_config< 64,  64, 4, 4, 32, 3>},
+	{ 32, 128, 1.00f, launch_config< 32, 128, 4, 4, 16, 3>},
+	{ 32,  64, 1.02f, launch_config< 32,  64, 2, 4, 16, 3>},
+	{ 32,  32, 1.04f, launch_config< 32,  32, 2, 4, 16, 3>},
+};
+constexpr int NUM_CONFIGS = (int)(sizeof(g_configs) / sizeof(g_configs[0]));
+
+// Estimated duration in SM cycles of one launch: CTAs on one SM share its POPC unit (one warp instruction
+// every other cycle per SM), so the busiest SM sets the time; every wave also pays a fixed latency for its
+// first loads and its epilogue, and a cluster pays for the reduction.
+static float estimate_cycles(const TileConfig & c, int M, int n_total, int kw, int split, int sms)
+{
+	const long long tiles = (long long)((M + c.bm - 1) / c.bm) * ((n_total + c.bn - 1) / c.bn) * split;
+	const long long per_sm = (tiles + sms - 1) / sms;
+	const int kw_slice = (int)round_up((size_t)(kw + split - 1) / split, 4);
+	const float cta_cycles = (float)c.bm * c.bn / 32.0f * kw_slice * 2.0f * c.cost;
+	const float fixed = 4000.0f + 0.25f * c.bm * c.bn + (split > 1 ? 800.0f + 150.0f * split : 0.0f);
+	return per_sm * (cta_cycles + 700.0f + 0.25f * c.bm * c.bn) + fixed;
 }
 
 int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
@@ -215,15 +316,44 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	p.C = C; p.ldc = ldc; p.mean_arr = mean_arr; p.bias = bias; p.leaky = leaky;
 	p.shortcut_in = shortcut_in; p.shortcut_out = shortcut_out; p.counts = counts;
 
-	// Pick the largest tile that still yields at least one CTA per SM; small problems fall through to
-	// the smallest tile so that batch-1 tail layers (N = 169) spread over more SMs.
+	// Large layers go to the tensor-core kernel.  XNOR_B200_GEMM_TC=0 keeps everything on the integer pipe,
+	// =1 sends every shape to the tensor-core kernel (tuning and test aid).
+	{
+		const char * tc = std::getenv("XNOR_B200_GEMM_TC");
+		const bool use_tc = (tc != nullptr) ? (tc[0] == '1') : tc_gemm_eligible(M, n_total, K);
+		if (use_tc)
+		{
+			return launch_xnor_gemm_tc(M, n_total, n_per_image, K, A, lda_words, B, ldb_words, C, ldc, mean_arr, bias, leaky,
+					shortcut_in, shortcut_out, counts, stream);
+		}
+	}
+
 	const int sms = sm_count();
-	auto tiles = [&](int bm, int bn) { return (long long)((M + bm - 1) / bm) * ((n_total + bn - 1) / bn); };
-	if (M > 64 && tiles(128, 128) >= sms) { return launch_config<128, 128, 8, 8, 32, 3>(p, stream); }
-	if (M > 32 && tiles(64, 128) >= sms)  { return launch_config<64, 128, 4, 8, 32, 3>(p, stream); }
-	if (M <= 32 && tiles(32, 256) >= sms) { return launch_config<32, 256, 4, 8, 32, 3>(p, stream); }
-	if (tiles(64, 64) >= sms)             { return launch_config<64, 64, 4, 4, 32, 3>(p, stream); }
-	return launch_config<32, 32, 2, 4, 32, 3>(p, stream);
+	int best_cfg = 0, best_split = 1;
+	float best = 3.0e38f;
+	for (int c = 2; c < NUM_CONFIGS; ++c)
+	{
+		if (g_configs[c].bm > 32 && g_configs[c].bm / 2 >= M) { continue; }      // more than half the tile rows would be empty
+		for (int split = 1; split <= 8; ++split)
+		{
+			if (split > 1 && p.kw / split < 8) { break; }                        // slices shorter than 8 words are all overhead
+			const float t = estimate_cycles(g_configs[c], M, n_total, p.kw, split, sms);
+			if (t < best) { best = t; best_cfg = c; best_split = split; }
+		}
+	}
+	// Tuning aid: XNOR_B200_GEMM_FORCE="<config index>,<split>" overrides the choice (used by the sweep scripts).
+	if (const char * force = std::getenv("XNOR_B200_GEMM_FORCE"))
+	{
+		int c = -1, s = 1;
+		if (std::sscanf(force, "%d,%d", &c, &s) >= 1 && c >= 0 && c < NUM_CONFIGS && s >= 1 && s <= 8)
+		{
+			best_cfg = c;
+			best_split = s;
+		}
+	}
+	p.split = best_split;
+	p.kw_slice = (int)round_up((size_t)(p.kw + best_split - 1) / best_split, 4);
+	return g_configs[best_cfg].launch(p, stream);
 }
 
 }  // namespace xnor

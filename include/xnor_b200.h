@@ -132,6 +132,12 @@ XNOR_B200_API int xnor_b200_gemm_bin_mean_transposed(int M, int N, int K,
 XNOR_B200_API int xnor_b200_gemm_counts(int M, int N, int K, const uint8_t * A, int lda, const uint8_t * B, int ldb,
 		int32_t * counts, void * stream);
 
+/* Diagnostics (no reference counterpart; Darknet aborts on any CUDA error instead).  The tensor-core GEMM
+ * bounds every wait on a shared-memory barrier; if a wait ever runs out, the kernel skips its remaining work,
+ * releases its tensor memory and sets a sticky device-side status word.  This call synchronises the device,
+ * stores that word in *status (0 = nothing happened) and clears it. */
+XNOR_B200_API int xnor_b200_take_device_status(int * status);
+
 /* Bytes of scratch xnor_b200_conv_forward needs (= geom.packed_input_bytes, 256-byte rounded).  The
  * reference sizes net.workspace from other layers and over-allocates two bit_align*K*4-byte buffers
  * per layer (src-lib/convolutional_layer.cpp:1413-1418); this path owns its scratch explicitly. */
