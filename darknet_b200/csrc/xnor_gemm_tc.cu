@@ -3,44 +3,44 @@
 // tcgen05.mma has no 1-bit operand kind, and the legacy mma.sync b1 path measures slower than the integer
 // pipe on this GPU.  A binary dot product is nevertheless an integer GEMM: with both operands expanded to
 // bytes holding 0 or 1,
-//     D[i][j] = sum_k a_ik * b_jk = popc(A_i & B_j)            (kind::i8, u8 x u8 -> s32, exact)
-//     agreeing bits = K - popc(A_i) - popc(B_j) + 2 * D[i][j]
-// so the packed operands stay 1 bit per element in HBM and L2 (same buffers as the integer-pipe kernel) and
-// are widened to bytes only inside shared memory, by the same threads that feed the tensor core:
+//     D[j][i] = sum_k b_jk * a_ik = popc(B_j & A_i)            (kind::i8, u8 x u8 -> s32, exact)
+//     agreeing bits = K - popc(A_i) - popc(B_j) + 2 * D[j][i]
+// so the packed operands stay 1 bit per element in HBM and L2 (the same buffers the integer-pipe kernel reads)
+// and are widened to bytes only inside shared memory, next to the tensor core that consumes them.
 //
-//   per 128-bit K block and stage:
-//     256 threads: thread t < 128 expands A row t, thread t >= 128 expands B row t-128 (16 bytes of bits ->
-//                  128 bytes of 0/1) straight into the canonical K-major SWIZZLE_128B tile layout, and keeps a
-//                  running popcount of its row;
-//     one thread:  4 x tcgen05.mma.cta_group::1.kind::i8 (M=128, N=128, K=32) accumulating into TMEM, then
-//                  tcgen05.commit onto the stage's mbarrier so the stage can be refilled.
-//   The MMAs of block k run while the threads expand block k+1; two CTAs fit on one SM and overlap further.
-//   Epilogue: tcgen05.ld brings the s32 accumulators back (one TMEM lane = one output row per thread), the
-//   popcount correction, mean scale, bias and leaky are applied with the same two-rounding fp32 sequence as the
-//   integer-pipe kernel, so both kernels give bit-identical outputs.
+// Orientation: the UMMA "M" dimension (128 TMEM lanes) carries OUTPUT PIXELS, the "N" dimension (TMEM columns)
+// carries FILTERS.  After tcgen05.ld each thread then owns one pixel and 32 consecutive filters per load, so
+// for every filter the 32 lanes of a warp store 32 consecutive pixels: NCHW output rows are written with fully
+// coalesced 128-byte stores.
 //
-// Every wait on an mbarrier is bounded; on expiry the kernel records a code in g_tc_error, skips the remaining
-// work, still releases its TMEM columns and returns.
+// One CTA = 128 pixels x NF filters (NF = 128 or 256), warp-specialised:
+//   warp 0            allocates TMEM; one lane issues, per 128-bit K block, 4 x tcgen05.mma.cta_group::1.kind::i8
+//                     (M=128, N=NF, K=32) and a tcgen05.commit that frees the stage when the MMAs have read it;
+//   warps 1..(128+NF)/32   producers: each thread owns one operand row (pixel row or filter row), keeps three
+//                     K blocks of packed bits in flight from L2, expands 128 bits -> 128 bytes straight into the
+//                     canonical K-major SWIZZLE_128B tile of the current stage, counts its row's set bits, and
+//                     its warp arrives on the stage's "full" barrier; the same warps run the epilogue.
+// Two stages per CTA and two CTAs per SM: while one CTA drains its accumulators the other keeps the tensor
+// core busy.  The epilogue applies the popcount correction, mean scale, bias and leaky with the same
+// two-rounding fp32 sequence as the integer-pipe kernel, so both kernels give bit-identical outputs.
+//
+// Every wait on an mbarrier is bounded; on expiry the kernel records a code in g_tc_error, all roles drop out
+// of their loops, the TMEM columns are still released, and the kernel returns.
 #include "xnor_common.cuh"
 
 namespace xnor
 {
 
-constexpr int TC_BM = 128;
-constexpr int TC_BN = 128;
-constexpr int TC_THREADS = 256;
-constexpr int TC_STAGES = 3;
-constexpr int TC_TILE_BYTES = 128 * 128;                 // one operand tile of one stage: 128 rows x 128 bytes
-constexpr int TC_STAGE_BYTES = 2 * TC_TILE_BYTES;
-constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024;   // + slack to align the ring to 1024 bytes
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
+constexpr int TC_PIX = 128;                               // pixels per tile = UMMA M = TMEM lanes
+constexpr int TC_STAGES = 2;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 
 __device__ int g_tc_error = 0;
 
 struct TcParams
 {
-	const uint32_t * A;
-	const uint32_t * B;
+	const uint32_t * A;     // filters   [M][lda_words]
+	const uint32_t * B;     // pixels    [n_total][ldb_words]
 	int M, n_total, n_per_image, K;
 	int lda_words, ldb_words;
 	int kblocks;            // number of 128-bit K blocks
@@ -52,7 +52,7 @@ struct TcParams
 	const float * shortcut_in;
 	float * shortcut_out;
 	int32_t * counts;
-	int tiles_m;
+	int tiles_f;            // filter tiles (fastest-varying in blockIdx.x)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -62,8 +62,14 @@ __device__ __forceinline__ void mbar_init(uint64_t * bar, uint32_t count)
 	asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
 }
 
-// Bounded wait for the phase with the given parity; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t * bar, uint32_t parity)
+__device__ __forceinline__ void mbar_arrive(uint64_t * bar)
+{
+	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+
+// Bounded wait for the phase with the given parity.  Gives up (returns false) when the limit runs out or when
+// another thread of the CTA has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t * bar, uint32_t parity, volatile int * failed)
 {
 	const uint32_t addr = smem_u32(bar);
 	for (uint32_t spin = 0; spin < TC_SPIN_LIMIT; ++spin)
@@ -75,7 +81,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t * bar, uint32_t parity)
 			"selp.u32 %0, 1, 0, p;\n\t}"
 			: "=r"(done) : "r"(addr), "r"(parity) : "memory");
 		if (done) { return true; }
+		if ((spin & 1023u) == 1023u && *failed != 0) { return false; }
 	}
+	*failed = 1;
 	return false;
 }
 
@@ -90,7 +98,7 @@ __device__ __forceinline__ uint4 expand16(uint32_t bits)
 	return v;
 }
 
-// One row of one K block: 128 bits -> 128 bytes at row r of a 128-row K-major tile with the 128-byte swizzle
+// One row of one K block: 128 bits -> 128 bytes at row r of a K-major tile with the 128-byte swizzle
 // (16-byte chunk c of row r is stored at chunk position c ^ (r % 8); tile base 1024-byte aligned).
 __device__ __forceinline__ void expand_row(uint32_t tile_addr, int r, const uint4 w)
 {
@@ -118,130 +126,177 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr)
 	return d;
 }
 
-__global__ void __launch_bounds__(TC_THREADS)
+template <int NF>
+struct TcShape
+{
+	static constexpr int ROWS = TC_PIX + NF;                     // operand rows per stage
+	static constexpr int PRODUCER_WARPS = ROWS / 32;
+	static constexpr int THREADS = 32 + ROWS;                    // warp 0 + producers
+	static constexpr int PIX_TILE_BYTES = TC_PIX * 128;
+	static constexpr int STAGE_BYTES = ROWS * 128;
+	static constexpr int SMEM_BYTES = TC_STAGES * STAGE_BYTES + 1024;   // + slack to align the ring to 1024 bytes
+};
+
+template <int NF>
+__global__ void __launch_bounds__(TcShape<NF>::THREADS)
 xnor_gemm_tc_kernel(const TcParams p)
 {
+	using S = TcShape<NF>;
 	extern __shared__ uint8_t tc_smem_raw[];
+	__shared__ uint64_t bar_full[TC_STAGES];
 	__shared__ uint64_t bar_empty[TC_STAGES];
 	__shared__ uint64_t bar_done;
 	__shared__ uint32_t tmem_base_slot;
-	__shared__ int s_pop[TC_BM + TC_BN];
-	__shared__ int s_failed;
+	__shared__ int s_pop[S::ROWS];
+	__shared__ float s_mean[NF];
+	__shared__ float s_bias[NF];
+	__shared__ int s_failed_storage;
+	volatile int * s_failed = &s_failed_storage;
 
 	const int tid = threadIdx.x;
 	const int warp = tid >> 5;
 	const int lane = tid & 31;
 	const uint32_t ring = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
 
-	const int tile_m = blockIdx.x % p.tiles_m;
-	const int tile_n = blockIdx.x / p.tiles_m;
-	const int m0 = tile_m * TC_BM;
-	const int n0 = tile_n * TC_BN;
+	const int tile_f = blockIdx.x % p.tiles_f;
+	const int tile_p = blockIdx.x / p.tiles_f;
+	const int f0 = tile_f * NF;
+	const int n0 = tile_p * TC_PIX;
 
 	if (tid == 0)
 	{
-		for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&bar_empty[s], 1); }
+		for (int s = 0; s < TC_STAGES; ++s)
+		{
+			mbar_init(&bar_full[s], S::PRODUCER_WARPS);
+			mbar_init(&bar_empty[s], 1);
+		}
 		mbar_init(&bar_done, 1);
-		s_failed = 0;
+		s_failed_storage = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
 	if (warp == 0)
 	{
 		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-				:: "r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)TC_BN) : "memory");
+				:: "r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)NF) : "memory");
 		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+	}
+	for (int i = tid; i < NF; i += S::THREADS)
+	{
+		const int f = f0 + i;
+		s_mean[i] = (f < p.M && p.mean_arr != nullptr) ? __ldg(p.mean_arr + f) : 0.0f;
+		s_bias[i] = (f < p.M && p.bias != nullptr) ? __ldg(p.bias + f) : 0.0f;
 	}
 	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 	__syncthreads();
 	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 	const uint32_t tmem_base = tmem_base_slot;
 
-	// this thread's operand row
-	const bool is_a = tid < TC_BM;
-	const int r = is_a ? tid : tid - TC_BM;
-	const bool row_ok = is_a ? (m0 + r < p.M) : (n0 + r < p.n_total);
-	const uint32_t * src = is_a ? p.A + (size_t)(row_ok ? m0 + r : 0) * p.lda_words
-	                            : p.B + (size_t)(row_ok ? n0 + r : 0) * p.ldb_words;
-	int pop = 0;
-
-	// instruction descriptor: D = s32, A = B = u8, both K-major, N = 128, M = 128
-	const uint32_t idesc = (2u << 4) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-
-	uint4 next = make_uint4(0, 0, 0, 0);
-	if (row_ok && p.kblocks > 0) { next = __ldg(reinterpret_cast<const uint4 *>(src)); }
-	bool failed = false;
-
-	for (int kb = 0; kb < p.kblocks; ++kb)
+	if (warp == 0)
 	{
-		const int s = kb % TC_STAGES;
-		const uint4 cur = next;
-		if (row_ok && kb + 1 < p.kblocks) { next = __ldg(reinterpret_cast<const uint4 *>(src) + kb + 1); }
-		if (kb >= TC_STAGES && !failed)
+		// ---- MMA issuer -------------------------------------------------------------------------
+		if (lane == 0)
 		{
-			// the MMAs that read this stage (issued STAGES blocks ago) must have completed
-			if (!mbar_wait(&bar_empty[s], (uint32_t)((kb / TC_STAGES - 1) & 1))) { failed = true; s_failed = 1; }
-		}
-		if (!failed)
-		{
-			expand_row(ring + (uint32_t)s * TC_STAGE_BYTES + (is_a ? 0u : (uint32_t)TC_TILE_BYTES), r, cur);
-			pop += __popc(cur.x) + __popc(cur.y) + __popc(cur.z) + __popc(cur.w);
-		}
-		// generic-proxy writes -> visible to the tensor core's async proxy, then hand over to the issuing thread
-		asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-		asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-		__syncthreads();
-		failed = failed || (s_failed != 0);
-		if (tid == 0 && !failed)
-		{
-			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-			const uint32_t a_addr = ring + (uint32_t)s * TC_STAGE_BYTES;
-			const uint32_t b_addr = a_addr + TC_TILE_BYTES;
-			#pragma unroll
-			for (int k = 0; k < 4; ++k)
+			// instruction descriptor: D = s32, A = B = u8, both K-major, N = NF, M = 128
+			const uint32_t idesc = (2u << 4) | ((uint32_t)(NF >> 3) << 17) | ((uint32_t)(TC_PIX >> 4) << 24);
+			bool ok = true;
+			for (int kb = 0; kb < p.kblocks && ok; ++kb)
 			{
-				const uint64_t adesc = make_smem_desc(a_addr + k * 32);
-				const uint64_t bdesc = make_smem_desc(b_addr + k * 32);
-				const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-				asm volatile(
-					"{\n\t.reg .pred p;\n\t"
-					"setp.ne.b32 p, %4, 0;\n\t"
-					"tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-					:: "r"(tmem_base), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate),
-					   "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+				const int s = kb % TC_STAGES;
+				ok = mbar_wait(&bar_full[s], (uint32_t)((kb / TC_STAGES) & 1), s_failed);
+				if (!ok) { break; }
+				asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+				const uint32_t pix_addr = ring + (uint32_t)s * S::STAGE_BYTES;
+				const uint32_t fil_addr = pix_addr + S::PIX_TILE_BYTES;
+				#pragma unroll
+				for (int k = 0; k < 4; ++k)
+				{
+					const uint64_t adesc = make_smem_desc(pix_addr + k * 32);
+					const uint64_t bdesc = make_smem_desc(fil_addr + k * 32);
+					const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+					asm volatile(
+						"{\n\t.reg .pred p;\n\t"
+						"setp.ne.b32 p, %4, 0;\n\t"
+						"tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+						:: "r"(tmem_base), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate),
+						   "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+				}
+				// arrives on the stage's barrier once every MMA issued so far has finished reading shared memory
+				asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+						:: "r"(smem_u32(&bar_empty[s])) : "memory");
 			}
-			// arrives on the stage's barrier once every MMA issued so far has finished reading shared memory
-			asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-					:: "r"(smem_u32(&bar_empty[s])) : "memory");
+			if (ok)
+			{
+				asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+						:: "r"(smem_u32(&bar_done)) : "memory");
+			}
 		}
+		__syncwarp();
+	}
+	else
+	{
+		// ---- producers ----------------------------------------------------------------------------
+		const int r = tid - 32;                               // operand row of this thread within the stage
+		const bool is_pix = r < TC_PIX;
+		const int row_in_tile = is_pix ? r : r - TC_PIX;
+		const bool row_ok = is_pix ? (n0 + row_in_tile < p.n_total) : (f0 + row_in_tile < p.M);
+		const uint4 * src = reinterpret_cast<const uint4 *>(
+				is_pix ? p.B + (size_t)(row_ok ? n0 + row_in_tile : 0) * p.ldb_words
+				       : p.A + (size_t)(row_ok ? f0 + row_in_tile : 0) * p.lda_words);
+		const uint32_t tile_off = is_pix ? 0u : (uint32_t)S::PIX_TILE_BYTES;
+		const uint4 zero4 = make_uint4(0, 0, 0, 0);
+		uint4 w0 = (row_ok && 0 < p.kblocks) ? __ldg(src + 0) : zero4;
+		uint4 w1 = (row_ok && 1 < p.kblocks) ? __ldg(src + 1) : zero4;
+		uint4 w2 = (row_ok && 2 < p.kblocks) ? __ldg(src + 2) : zero4;
+		int pop = 0;
+		bool ok = true;
+		for (int kb = 0; kb < p.kblocks; ++kb)
+		{
+			const int s = kb % TC_STAGES;
+			const uint4 cur = w0;
+			w0 = w1;
+			w1 = w2;
+			w2 = (row_ok && kb + 3 < p.kblocks) ? __ldg(src + kb + 3) : zero4;
+			if (kb >= TC_STAGES)
+			{
+				// the MMAs that read this stage (issued STAGES blocks ago) must have completed
+				ok = mbar_wait(&bar_empty[s], (uint32_t)((kb / TC_STAGES - 1) & 1), s_failed);
+				if (!ok) { break; }
+			}
+			expand_row(ring + (uint32_t)s * S::STAGE_BYTES + tile_off, row_in_tile, cur);
+			pop += __popc(cur.x) + __popc(cur.y) + __popc(cur.z) + __popc(cur.w);
+			// generic-proxy writes -> visible to the tensor core's async proxy; then one arrival per warp
+			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+			__syncwarp();
+			if (lane == 0) { mbar_arrive(&bar_full[s]); }
+		}
+		s_pop[r] = pop;
 	}
 
-	if (tid == 0 && !failed)
-	{
-		asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-				:: "r"(smem_u32(&bar_done)) : "memory");
-	}
-	s_pop[tid] = pop;
-	if (!failed && !mbar_wait(&bar_done, 0)) { failed = true; s_failed = 1; }
+	// ---- everyone: wait for the accumulators ----------------------------------------------------------
+	mbar_wait(&bar_done, 0, s_failed);
 	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 	__syncthreads();
 	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-	failed = failed || (s_failed != 0);
+	const bool failed = (*s_failed != 0);
 
-	if (!failed)
+	if (!failed && warp != 0)
 	{
-		// Warp w may read TMEM lanes 32*(w%4) .. +31; warps 0-3 take columns 0-63, warps 4-7 columns 64-127.
-		const int lane_base = 32 * (warp & 3);
-		const int row_local = lane_base + lane;
-		const int m = m0 + row_local;
-		const int pop_a = s_pop[row_local];
-		const float mean = (m < p.M && p.mean_arr != nullptr) ? __ldg(p.mean_arr + m) : 0.0f;
-		const float bias = (m < p.M && p.bias != nullptr) ? __ldg(p.bias + m) : 0.0f;
+		// A warp may read TMEM lanes 32*(warp%4) .. +31.  The producer warps 1..PRODUCER_WARPS cover every lane
+		// quarter PRODUCER_WARPS/4 times; warps sharing a quarter interleave over the 32-column chunks.
+		const int quarter = warp & 3;
+		const int share = (warp - 1) >> 2;                    // 0 .. PRODUCER_WARPS/4 - 1
+		constexpr int SHARES = S::PRODUCER_WARPS / 4;
+		const int pix_local = quarter * 32 + lane;
+		const int col = n0 + pix_local;                       // global pixel (column of C)
+		const bool col_ok = col < p.n_total;
+		const int img = col_ok ? col / p.n_per_image : 0;
+		const int pix = col_ok ? col - img * p.n_per_image : 0;
+		const int pop_b = s_pop[pix_local];
 		#pragma unroll 1
-		for (int chunk = 0; chunk < 2; ++chunk)
+		for (int chunk = share; chunk < NF / 32; chunk += SHARES)
 		{
-			const int col0 = (warp >> 2) * 64 + chunk * 32;
 			uint32_t d[32];
-			const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)col0;
+			const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(chunk * 32);
 			asm volatile(
 				"tcgen05.ld.sync.aligned.32x32b.x32.b32 "
 				"{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -252,38 +307,36 @@ xnor_gemm_tc_kernel(const TcParams p)
 				  "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
 				: "r"(taddr) : "memory");
 			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-			if (m < p.M)
+			if (col_ok)
 			{
-				int col = n0 + col0;
-				int img = col / p.n_per_image;
-				int pix = col - img * p.n_per_image;
 				#pragma unroll
-				for (int j = 0; j < 32; ++j, ++col)
+				for (int j = 0; j < 32; ++j)
 				{
-					if (col < p.n_total)
+					const int fl = chunk * 32 + j;            // filter within the tile
+					const int f = f0 + fl;
+					if (f < p.M)
 					{
 						// agreeing bits among the first K
-						const int count = p.K - pop_a - s_pop[TC_BM + col0 + j] + 2 * (int)d[j];
+						const int count = p.K - s_pop[TC_PIX + fl] - pop_b + 2 * (int)d[j];
 						if (p.counts != nullptr)
 						{
-							p.counts[(size_t)m * p.n_total + col] = count;
+							p.counts[(size_t)f * p.n_total + col] = count;
 						}
 						else
 						{
-							const size_t idx = ((size_t)img * p.M + m) * p.ldc + pix;
-							float v = __fmul_rn((float)(2 * count - p.K), mean);
-							if (p.bias != nullptr) { v = __fadd_rn(v, bias); }
+							const size_t idx = ((size_t)img * p.M + f) * p.ldc + pix;
+							float v = __fmul_rn((float)(2 * count - p.K), s_mean[fl]);
+							if (p.bias != nullptr) { v = __fadd_rn(v, s_bias[fl]); }
 							if (p.leaky) { v = (v < 0.0f) ? __fmul_rn(v, 0.1f) : v; }
 							p.C[idx] = v;
 							if (p.shortcut_out != nullptr) { p.shortcut_out[idx] = __fadd_rn(__ldg(p.shortcut_in + idx), v); }
 						}
 					}
-					if (++pix == p.n_per_image) { pix = 0; ++img; }
 				}
 			}
 		}
 	}
-	else if (tid == 0)
+	else if (failed && tid == 0)
 	{
 		atomicExch(&g_tc_error, 1);
 	}
@@ -292,17 +345,31 @@ xnor_gemm_tc_kernel(const TcParams p)
 	__syncthreads();
 	if (warp == 0)
 	{
-		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TC_BN) : "memory");
+		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)NF) : "memory");
 	}
 }
 
 bool tc_gemm_eligible(int M, int n_total, int K)
 {
-	// Needs full 128-row tiles to pay off, enough K to amortise the TMEM round trip, and at least about one
-	// tile per SM; everything else stays on the integer-pipe kernel.
-	if (M < 96 || K < 512) { return false; }
-	const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((n_total + TC_BN - 1) / TC_BN);
+	// Needs enough filters to fill the N side of the MMA, enough K to amortise the TMEM round trip, and at
+	// least about one tile per SM; everything else stays on the integer-pipe kernel.
+	if (M < 96 || K < 1024) { return false; }
+	const int nf = (M > 128) ? 256 : 128;
+	const long long tiles = (long long)((M + nf - 1) / nf) * ((n_total + TC_PIX - 1) / TC_PIX);
 	return tiles >= sm_count();
+}
+
+template <int NF>
+static int launch_tc(TcParams & p, cudaStream_t stream)
+{
+	using S = TcShape<NF>;
+	p.tiles_f = (p.M + NF - 1) / NF;
+	const long long grid = (long long)p.tiles_f * ((p.n_total + TC_PIX - 1) / TC_PIX);
+	if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
+	int rc = ensure_dynamic_smem((const void *)xnor_gemm_tc_kernel<NF>, S::SMEM_BYTES);
+	if (rc != XNOR_B200_OK) { return rc; }
+	xnor_gemm_tc_kernel<NF><<<(unsigned)grid, S::THREADS, S::SMEM_BYTES, stream>>>(p);
+	return check_launch();
 }
 
 int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
@@ -317,13 +384,7 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	p.kblocks = (K + 127) / 128;
 	p.C = C; p.ldc = ldc; p.mean_arr = mean_arr; p.bias = bias; p.leaky = leaky;
 	p.shortcut_in = shortcut_in; p.shortcut_out = shortcut_out; p.counts = counts;
-	p.tiles_m = (M + TC_BM - 1) / TC_BM;
-	const long long grid = (long long)p.tiles_m * ((n_total + TC_BN - 1) / TC_BN);
-	if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
-	int rc = ensure_dynamic_smem((const void *)xnor_gemm_tc_kernel, TC_SMEM_BYTES);
-	if (rc != XNOR_B200_OK) { return rc; }
-	xnor_gemm_tc_kernel<<<(unsigned)grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(p);
-	return check_launch();
+	return (M > 128) ? launch_tc<256>(p, stream) : launch_tc<128>(p, stream);
 }
 
 int read_tc_error(int * out, bool clear)
