@@ -98,19 +98,18 @@ __device__ __forceinline__ uint4 expand16(uint32_t bits)
 	return v;
 }
 
-// One row of one K block: 128 bits -> 128 bytes at row r of a K-major tile with the 128-byte swizzle
-// (16-byte chunk c of row r is stored at chunk position c ^ (r % 8); tile base 1024-byte aligned).
-__device__ __forceinline__ void expand_row(uint32_t tile_addr, int r, const uint4 w)
+// One row of one K block: 128 bits -> 128 bytes of a K-major tile with the 128-byte swizzle: 16-byte chunk c of
+// row r lives at chunk position c ^ (r % 8) (tile base 1024-byte aligned, rows 128 bytes apart).  row_swz is
+// the row's byte address with (r % 8) << 4 already XOR-ed in, so each chunk address is one XOR with a constant.
+__device__ __forceinline__ void expand_row(uint32_t row_swz, const uint4 w)
 {
-	const uint32_t row = tile_addr + (uint32_t)r * 128u;
-	const uint32_t sw = (uint32_t)(r & 7);
 	const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 	#pragma unroll
 	for (int c = 0; c < 8; ++c)
 	{
 		const uint4 v = expand16(words[c >> 1] >> ((c & 1) * 16));
 		asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-				:: "r"(row + (((uint32_t)c ^ sw) << 4)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+				:: "r"(row_swz ^ (uint32_t)(c << 4)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 	}
 }
 
@@ -242,7 +241,9 @@ xnor_gemm_tc_kernel(const TcParams p)
 		const uint4 * src = reinterpret_cast<const uint4 *>(
 				is_pix ? p.B + (size_t)(row_ok ? n0 + row_in_tile : 0) * p.ldb_words
 				       : p.A + (size_t)(row_ok ? f0 + row_in_tile : 0) * p.lda_words);
-		const uint32_t tile_off = is_pix ? 0u : (uint32_t)S::PIX_TILE_BYTES;
+		// byte address of this thread's row in stage 0, swizzle term folded in
+		const uint32_t row_swz0 = (ring + (is_pix ? 0u : (uint32_t)S::PIX_TILE_BYTES) + (uint32_t)row_in_tile * 128u)
+				^ ((uint32_t)(row_in_tile & 7) << 4);
 		const uint4 zero4 = make_uint4(0, 0, 0, 0);
 		uint4 w0 = (row_ok && 0 < p.kblocks) ? __ldg(src + 0) : zero4;
 		uint4 w1 = (row_ok && 1 < p.kblocks) ? __ldg(src + 1) : zero4;
@@ -262,7 +263,7 @@ xnor_gemm_tc_kernel(const TcParams p)
 				ok = mbar_wait(&bar_empty[s], (uint32_t)((kb / TC_STAGES - 1) & 1), s_failed);
 				if (!ok) { break; }
 			}
-			expand_row(ring + (uint32_t)s * S::STAGE_BYTES + tile_off, row_in_tile, cur);
+			expand_row(row_swz0 + (uint32_t)s * S::STAGE_BYTES, cur);
 			pop += __popc(cur.x) + __popc(cur.y) + __popc(cur.z) + __popc(cur.w);
 			// generic-proxy writes -> visible to the tensor core's async proxy; then one arrival per warp
 			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -353,7 +354,7 @@ bool tc_gemm_eligible(int M, int n_total, int K)
 {
 	// Needs enough filters to fill the N side of the MMA, enough K to amortise the TMEM round trip, and at
 	// least about one tile per SM; everything else stays on the integer-pipe kernel.
-	if (M < 96 || K < 1024) { return false; }
+	if (M < 96 || K < 256) { return false; }
 	const int nf = (M > 128) ? 256 : 128;
 	const long long tiles = (long long)((M + nf - 1) / nf) * ((n_total + TC_PIX - 1) / TC_PIX);
 	return tiles >= sm_count();
