@@ -8,12 +8,15 @@
 // and writes the reference's t_bit_input layout: row (b*N + p) = the K sign bits of output pixel p of
 // image b, followed by zero padding up to new_ldb bits.
 //
-// Structure of both kernels: one CTA owns a strip of output rows of one image.
+// Structure of both kernels: one CTA owns a strip of output rows of one image (word path: and a group of
+// 32-channel blocks, so that small feature maps still spread over many SMs).
 //   phase A  reads the fp32 input rows the strip needs exactly once, coalesced (float4 where the row
-//            pitch allows), and leaves sign bits in shared memory (32 channels per word on the word
-//            path; one bit plane per channel, built with __ballot_sync, on the bit path);
-//   phase B  assembles complete rows of the packed operand from shared memory and stores them with
-//            16-byte writes, so global stores are contiguous along K.
+//            pitch allows), and leaves sign bits in shared memory: 32 channels per word on the word path
+//            (four threads share a word, eight channels each, to keep more loads in flight), one bit plane
+//            per channel built with __ballot_sync on the bit path;
+//   phase B  assembles the packed rows from shared memory and stores them with 16-byte writes, contiguous
+//            along K.  On the bit path a thread pulls `size` adjacent bits of one (channel, kernel row) per
+//            step out of a bit plane with a funnel shift instead of testing taps one by one.
 // HBM traffic per image is therefore 4*C*H*W bytes read (plus halo rows, served by L2) and
 // N*new_ldb/8 bytes written.
 #include "xnor_common.cuh"
@@ -31,81 +34,100 @@ struct PackParams
 	int C, H, W, OH, OW;
 	int ks, stride, pad;
 	int rows_per_cta;    // output rows per CTA
-	int tiles_per_image;
+	int tiles_per_image; // row strips per image
+	int cb_per_cta;      // word path: 32-channel blocks per CTA (a multiple of 4 unless it covers all of them)
+	int groups;          // word path: channel-block groups per strip
 	int ldw;             // words per packed row (new_ldb/32)
 	int K;               // bits per row that carry data
-	int max_in_rows;     // input rows a strip can touch
 };
 
 // ---- word path -----------------------------------------------------------------------------
-// shared: packed[CB][R][W] words, CB = C/32, R = input rows of this strip.
+// shared: packed[cb_local][R][W] words, R = input rows of this strip.
 template <bool VEC4>
 __global__ void __launch_bounds__(PK_THREADS)
 pack_input_words_kernel(const PackParams p)
 {
 	extern __shared__ uint32_t s_words[];
-	const int b = blockIdx.x / p.tiles_per_image;
-	const int tile = blockIdx.x - b * p.tiles_per_image;
+	const int g = blockIdx.x % p.groups;
+	const int rest = blockIdx.x / p.groups;
+	const int tile = rest % p.tiles_per_image;
+	const int b = rest / p.tiles_per_image;
 	const int y0 = tile * p.rows_per_cta;
 	const int y1 = min(y0 + p.rows_per_cta, p.OH);
 	const int iy_lo = max(y0 * p.stride - p.pad, 0);
 	const int iy_hi = min((y1 - 1) * p.stride - p.pad + p.ks - 1, p.H - 1);
 	const int R = iy_hi - iy_lo + 1;          // may be <= 0 when the strip only sees padding
 	const int CB = p.C >> 5;
+	const int cb0 = g * p.cb_per_cta;
+	const int cbn = min(p.cb_per_cta, CB - cb0);
 	const int span = max(R, 0) * p.W;         // contiguous floats per channel
 	const size_t chan_stride = (size_t)p.H * p.W;
-	const float * img = p.in + (size_t)b * p.C * chan_stride + (size_t)iy_lo * p.W;
+	const float * img = p.in + ((size_t)b * p.C + (size_t)cb0 * 32) * chan_stride + (size_t)iy_lo * p.W;
+	uint8_t * s_bytes = reinterpret_cast<uint8_t *>(s_words);
 
-	// phase A: 32 channels -> one word per input pixel
+	// phase A: 32 channels -> one word per input pixel; thread (item, sub) covers channels 8*sub .. 8*sub+7
 	if (VEC4)
 	{
 		const int span4 = span >> 2;
-		for (int idx = threadIdx.x; idx < CB * span4; idx += PK_THREADS)
+		const int items = cbn * span4;
+		for (int idx = threadIdx.x; idx < items * 4; idx += PK_THREADS)
 		{
-			const int cb = idx / span4;
-			const int e4 = idx - cb * span4;
-			const float4 * src = reinterpret_cast<const float4 *>(img + (size_t)cb * 32 * chan_stride) + e4;
+			const int sub = idx / items;
+			const int item = idx - sub * items;
+			const int cbl = item / span4;
+			const int e4 = item - cbl * span4;
+			const float * src = img + ((size_t)cbl * 32 + sub * 8) * chan_stride + (size_t)e4 * 4;
 			uint32_t w0 = 0, w1 = 0, w2 = 0, w3 = 0;
 			#pragma unroll
-			for (int ch = 0; ch < 32; ++ch)
+			for (int ch = 0; ch < 8; ++ch)
 			{
-				const float4 v = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(src) + (size_t)ch * chan_stride));
+				const float4 v = __ldg(reinterpret_cast<const float4 *>(src + (size_t)ch * chan_stride));
 				w0 |= (v.x > 0 ? 1u : 0u) << ch;
 				w1 |= (v.y > 0 ? 1u : 0u) << ch;
 				w2 |= (v.z > 0 ? 1u : 0u) << ch;
 				w3 |= (v.w > 0 ? 1u : 0u) << ch;
 			}
-			reinterpret_cast<uint4 *>(s_words)[idx] = make_uint4(w0, w1, w2, w3);
+			uint8_t * dst = s_bytes + (size_t)item * 16 + sub;
+			dst[0] = (uint8_t)w0;
+			dst[4] = (uint8_t)w1;
+			dst[8] = (uint8_t)w2;
+			dst[12] = (uint8_t)w3;
 		}
 	}
 	else
 	{
-		for (int idx = threadIdx.x; idx < CB * span; idx += PK_THREADS)
+		const int items = cbn * span;
+		for (int idx = threadIdx.x; idx < items * 4; idx += PK_THREADS)
 		{
-			const int cb = idx / span;
-			const int e = idx - cb * span;
-			const float * src = img + (size_t)cb * 32 * chan_stride + e;
+			const int sub = idx / items;
+			const int item = idx - sub * items;
+			const int cbl = item / span;
+			const int e = item - cbl * span;
+			const float * src = img + ((size_t)cbl * 32 + sub * 8) * chan_stride + e;
 			uint32_t w0 = 0;
 			#pragma unroll
-			for (int ch = 0; ch < 32; ++ch)
+			for (int ch = 0; ch < 8; ++ch)
 			{
 				w0 |= (__ldg(src + (size_t)ch * chan_stride) > 0 ? 1u : 0u) << ch;
 			}
-			s_words[idx] = w0;
+			s_bytes[(size_t)item * 4 + sub] = (uint8_t)w0;
 		}
 	}
 	__syncthreads();
 
-	// phase B: one uint4 (4 K-words) per thread-iteration
+	// phase B: one uint4 (4 K-words) per thread-iteration over this CTA's word range
 	const int taps = p.ks * p.ks;
 	const int new_k = CB * taps;
-	const int ldq = p.ldw >> 2;
+	const bool last_group = (g == p.groups - 1);
+	const int q_lo = (cb0 * taps) >> 2;                                   // cb0 % 4 == 0 whenever groups > 1
+	const int q_hi = last_group ? (p.ldw >> 2) : (((cb0 + cbn) * taps) >> 2);
+	const int nq = q_hi - q_lo;
 	const int pixels = (y1 - y0) * p.OW;
 	const size_t row_base = (size_t)b * p.OH * p.OW + (size_t)y0 * p.OW;
-	for (int q = threadIdx.x; q < pixels * ldq; q += PK_THREADS)
+	for (int q = threadIdx.x; q < pixels * nq; q += PK_THREADS)
 	{
-		const int pl = q / ldq;
-		const int wq = q - pl * ldq;
+		const int pl = q / nq;
+		const int wq = q_lo + (q - pl * nq);
 		const int yl = pl / p.OW;
 		const int x = pl - yl * p.OW;
 		const int iy_base = (y0 + yl) * p.stride - p.pad - iy_lo;   // relative to the staged rows
@@ -124,7 +146,7 @@ pack_input_words_kernel(const PackParams p)
 				const int kx = t - ky * p.ks;
 				const int r = iy_base + ky;
 				const int ix = ix_base + kx;
-				if (r >= 0 && r < R && ix >= 0 && ix < p.W) { word = s_words[(cb * R + r) * p.W + ix]; }
+				if (r >= 0 && r < R && ix >= 0 && ix < p.W) { word = s_words[((cb - cb0) * R + r) * p.W + ix]; }
 			}
 			v[u] = word;
 		}
@@ -133,44 +155,48 @@ pack_input_words_kernel(const PackParams p)
 }
 
 // ---- bit path ------------------------------------------------------------------------------
-// shared: planes[C][R][PW] words, PW = ceil(W/32); bit x of plane row (c, r) = input(c, iy_lo+r, x) > 0.
+// shared: planes[C][RR][PW] words.  Row rr of a strip is input row y0*stride - pad + rr (rows outside the image
+// are all zero); bit (ix + pad) of a plane row = input(c, row, ix) > 0, so the `ks` taps of one kernel row of
+// output column x are the adjacent bits x*stride .. x*stride + ks - 1.  PW has one spare word for the funnel shift.
 __global__ void __launch_bounds__(PK_THREADS)
 pack_input_bits_kernel(const PackParams p)
 {
 	extern __shared__ uint32_t s_words[];
+	const int tile = blockIdx.x % p.tiles_per_image;
 	const int b = blockIdx.x / p.tiles_per_image;
-	const int tile = blockIdx.x - b * p.tiles_per_image;
 	const int y0 = tile * p.rows_per_cta;
 	const int y1 = min(y0 + p.rows_per_cta, p.OH);
-	const int iy_lo = max(y0 * p.stride - p.pad, 0);
-	const int iy_hi = min((y1 - 1) * p.stride - p.pad + p.ks - 1, p.H - 1);
-	const int R = max(iy_hi - iy_lo + 1, 0);
-	const int PW = (p.W + 31) >> 5;
+	const int RR = (y1 - y0 - 1) * p.stride + p.ks;
+	const int PW = ((p.W + 2 * p.pad + 31) >> 5) + 1;
 	const size_t chan_stride = (size_t)p.H * p.W;
 	const float * img = p.in + (size_t)b * p.C * chan_stride;
+	const int iy0 = y0 * p.stride - p.pad;
 
-	// phase A: one warp ballot per 32 consecutive pixels of one (channel, row)
+	// phase A: one warp ballot per 32 consecutive padded positions of one (channel, row)
 	const int lane = threadIdx.x & 31;
 	const int warp = threadIdx.x >> 5;
-	const int items = p.C * R * PW;
+	const int items = p.C * RR * PW;
 	for (int it = warp; it < items; it += PK_THREADS / 32)
 	{
 		const int xw = it % PW;
 		const int cr = it / PW;
-		const int r = cr % R;
-		const int c = cr / R;
-		const int x = xw * 32 + lane;
+		const int rr = cr % RR;
+		const int c = cr / RR;
+		const int ix = xw * 32 + lane - p.pad;
+		const int iy = iy0 + rr;
 		float v = 0.0f;
-		if (x < p.W) { v = __ldg(img + (size_t)c * chan_stride + (size_t)(iy_lo + r) * p.W + x); }
+		if (ix >= 0 && ix < p.W && iy >= 0 && iy < p.H) { v = __ldg(img + (size_t)c * chan_stride + (size_t)iy * p.W + ix); }
 		const uint32_t word = __ballot_sync(0xffffffffu, v > 0);
 		if (lane == 0) { s_words[it] = word; }
 	}
 	__syncthreads();
 
-	// phase B: thread builds 4 consecutive K-words of one output row; k = c*taps + ky*ks + kx
-	const int taps = p.ks * p.ks;
+	// phase B: thread builds 4 consecutive K-words (bits k0 .. k0+127) of one output row.
+	// K order: k = (c*ks + ky)*ks + kx, i.e. consecutive groups (c, ky) of ks bits each.
 	const int ldq = p.ldw >> 2;
 	const int pixels = (y1 - y0) * p.OW;
+	const int n_groups = p.C * p.ks;
+	const uint32_t tap_mask = (p.ks >= 32) ? 0xffffffffu : ((1u << p.ks) - 1u);
 	const size_t row_base = (size_t)b * p.OH * p.OW + (size_t)y0 * p.OW;
 	for (int q = threadIdx.x; q < pixels * ldq; q += PK_THREADS)
 	{
@@ -178,34 +204,35 @@ pack_input_bits_kernel(const PackParams p)
 		const int wq = q - pl * ldq;
 		const int yl = pl / p.OW;
 		const int x = pl - yl * p.OW;
-		const int iy_base = (y0 + yl) * p.stride - p.pad - iy_lo;
-		const int ix_base = x * p.stride - p.pad;
-		int k = wq * 128;
-		int c = k / taps;
-		int t = k - c * taps;
-		int ky = t / p.ks;
-		int kx = t - ky * p.ks;
-		uint32_t v[4];
-		#pragma unroll
-		for (int u = 0; u < 4; ++u)
+		const int p0 = x * p.stride;                       // first tap, in padded plane coordinates
+		const int sh = p0 & 31;
+		const int k0 = wq * 128;
+		int grp = k0 / p.ks;
+		int skip = k0 - grp * p.ks;                        // bits of the first group that belong to the previous quad
+		int c = grp / p.ks;
+		int ky = grp - c * p.ks;
+		const uint32_t * plane = s_words + ((size_t)c * RR + (size_t)yl * p.stride) * PW + (p0 >> 5);
+		uint32_t v[4] = {0u, 0u, 0u, 0u};
+		unsigned long long buf = 0ull;
+		int fill = 0, outw = 0;
+		while (outw < 4 && grp < n_groups)
 		{
-			uint32_t word = 0;
-			for (int bit = 0; bit < 32; ++bit)
+			const uint32_t * row = plane + ky * PW;
+			uint32_t bits = __funnelshift_r(row[0], row[1], sh) & tap_mask;
+			bits >>= skip;
+			buf |= (unsigned long long)bits << fill;
+			fill += p.ks - skip;
+			skip = 0;
+			if (fill >= 32)
 			{
-				if (k < p.K)
-				{
-					const int r = iy_base + ky;
-					const int ix = ix_base + kx;
-					if (r >= 0 && r < R && ix >= 0 && ix < p.W)
-					{
-						word |= ((s_words[(c * R + r) * PW + (ix >> 5)] >> (ix & 31)) & 1u) << bit;
-					}
-				}
-				++k;
-				if (++kx == p.ks) { kx = 0; if (++ky == p.ks) { ky = 0; ++c; } }
+				v[outw++] = (uint32_t)buf;
+				buf >>= 32;
+				fill -= 32;
 			}
-			v[u] = word;
+			++grp;
+			if (++ky == p.ks) { ky = 0; plane += (size_t)RR * PW; }
 		}
+		if (outw < 4 && fill > 0) { v[outw] = (uint32_t)buf; }
 		reinterpret_cast<uint4 *>(p.out + (row_base + pl) * p.ldw)[wq] = make_uint4(v[0], v[1], v[2], v[3]);
 	}
 }
@@ -256,29 +283,37 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 	p.K = d.size * d.size * d.c;
 	p.ldw = aligned_lda(p.K) / 32;
 	const bool word_path = (d.c % 32 == 0);
-
-	// bytes of shared memory per staged input row
-	const size_t row_bytes = word_path ? (size_t)(d.c / 32) * d.w * 4 : (size_t)d.c * ((d.w + 31) / 32) * 4;
-	auto in_rows = [&](int out_rows) { return (out_rows - 1) * d.stride + d.size; };
-	if (row_bytes * (size_t)min(in_rows(1), d.h) > PK_MAX_SMEM) { return XNOR_B200_ERR_TOO_LARGE; }
-
-	// Largest strip that (a) fits shared memory and (b) still leaves about two CTAs per SM.
 	const int want_ctas = 2 * sm_count();
-	int rows = p.OH;
-	while (rows > 1 && (row_bytes * (size_t)min(in_rows(rows), d.h) > PK_MAX_SMEM
-			|| (long long)d.batch * ((p.OH + rows - 1) / rows) < want_ctas))
-	{
-		--rows;
-	}
-	p.rows_per_cta = rows;
-	p.tiles_per_image = (p.OH + rows - 1) / rows;
-	p.max_in_rows = min(in_rows(rows), d.h);
-	const size_t smem = round_up(row_bytes * (size_t)p.max_in_rows, 16);
-	const long long grid = (long long)d.batch * p.tiles_per_image;
-	if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
+	auto in_rows = [&](int out_rows) { return (out_rows - 1) * d.stride + d.size; };
 
 	if (word_path)
 	{
+		const int CB = d.c / 32;
+		// Channel-block groups: only when the strips alone cannot fill the GPU; group borders stay on multiples
+		// of 4 blocks so that every group's word range starts on a 16-byte boundary of the packed row.
+		int cb_per_cta = CB;
+		if ((long long)d.batch * p.OH < want_ctas && CB >= 8)
+		{
+			const long long strips = (long long)d.batch * p.OH;
+			int groups = (int)min((long long)(CB / 4), (want_ctas + strips - 1) / strips);
+			cb_per_cta = (int)round_up((size_t)(CB + groups - 1) / groups, 4);
+		}
+		p.cb_per_cta = cb_per_cta;
+		p.groups = (CB + cb_per_cta - 1) / cb_per_cta;
+		const size_t row_bytes = (size_t)cb_per_cta * d.w * 4;
+		if (row_bytes * (size_t)min(in_rows(1), d.h) > PK_MAX_SMEM) { return XNOR_B200_ERR_TOO_LARGE; }
+		// Largest strip that (a) fits shared memory and (b) still leaves about two CTAs per SM.
+		int rows = p.OH;
+		while (rows > 1 && (row_bytes * (size_t)min(in_rows(rows), d.h) > PK_MAX_SMEM
+				|| (long long)d.batch * ((p.OH + rows - 1) / rows) * p.groups < want_ctas))
+		{
+			--rows;
+		}
+		p.rows_per_cta = rows;
+		p.tiles_per_image = (p.OH + rows - 1) / rows;
+		const size_t smem = round_up(row_bytes * (size_t)min(in_rows(rows), d.h), 16);
+		const long long grid = (long long)d.batch * p.tiles_per_image * p.groups;
+		if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
 		const bool vec4 = (d.w % 4 == 0) && (((uintptr_t)input & 15u) == 0);
 		auto kern = vec4 ? pack_input_words_kernel<true> : pack_input_words_kernel<false>;
 		int rc = ensure_dynamic_smem((const void *)kern, smem > 48 * 1024 ? PK_MAX_SMEM : 0);
@@ -287,6 +322,23 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 	}
 	else
 	{
+		if (d.size > 24) { return XNOR_B200_ERR_TOO_LARGE; }      // a kernel row must fit the 64-bit assembly buffer
+		p.cb_per_cta = 0;
+		p.groups = 1;
+		const int PW = ((d.w + 2 * d.pad + 31) >> 5) + 1;
+		const size_t row_bytes = (size_t)d.c * PW * 4;
+		if (row_bytes * (size_t)in_rows(1) > PK_MAX_SMEM) { return XNOR_B200_ERR_TOO_LARGE; }
+		int rows = p.OH;
+		while (rows > 1 && (row_bytes * (size_t)in_rows(rows) > PK_MAX_SMEM
+				|| (long long)d.batch * ((p.OH + rows - 1) / rows) < want_ctas))
+		{
+			--rows;
+		}
+		p.rows_per_cta = rows;
+		p.tiles_per_image = (p.OH + rows - 1) / rows;
+		const size_t smem = round_up(row_bytes * (size_t)in_rows(rows), 16);
+		const long long grid = (long long)d.batch * p.tiles_per_image;
+		if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
 		int rc = ensure_dynamic_smem((const void *)pack_input_bits_kernel, smem > 48 * 1024 ? PK_MAX_SMEM : 0);
 		if (rc != XNOR_B200_OK) { return rc; }
 		pack_input_bits_kernel<<<(unsigned)grid, PK_THREADS, smem, stream>>>(p);
