@@ -21,6 +21,8 @@
 // N*new_ldb/8 bytes written.
 #include "xnor_common.cuh"
 
+#include <cstdlib>
+
 namespace xnor
 {
 
@@ -176,18 +178,34 @@ pack_input_bits_kernel(const PackParams p)
 	const int lane = threadIdx.x & 31;
 	const int warp = threadIdx.x >> 5;
 	const int items = p.C * RR * PW;
-	for (int it = warp; it < items; it += PK_THREADS / 32)
+	constexpr int NWARPS = PK_THREADS / 32;
+	constexpr int UNROLL = 8;                              // loads in flight per lane before the first ballot
+	for (int base = warp; base < items; base += UNROLL * NWARPS)
 	{
-		const int xw = it % PW;
-		const int cr = it / PW;
-		const int rr = cr % RR;
-		const int c = cr / RR;
-		const int ix = xw * 32 + lane - p.pad;
-		const int iy = iy0 + rr;
-		float v = 0.0f;
-		if (ix >= 0 && ix < p.W && iy >= 0 && iy < p.H) { v = __ldg(img + (size_t)c * chan_stride + (size_t)iy * p.W + ix); }
-		const uint32_t word = __ballot_sync(0xffffffffu, v > 0);
-		if (lane == 0) { s_words[it] = word; }
+		float v[UNROLL];
+		#pragma unroll
+		for (int u = 0; u < UNROLL; ++u)
+		{
+			const int it = base + u * NWARPS;
+			const int xw = it % PW;
+			const int cr = it / PW;
+			const int rr = cr % RR;
+			const int c = cr / RR;
+			const int ix = xw * 32 + lane - p.pad;
+			const int iy = iy0 + rr;
+			v[u] = 0.0f;
+			if (it < items && ix >= 0 && ix < p.W && iy >= 0 && iy < p.H)
+			{
+				v[u] = __ldg(img + (size_t)c * chan_stride + (size_t)iy * p.W + ix);
+			}
+		}
+		#pragma unroll
+		for (int u = 0; u < UNROLL; ++u)
+		{
+			const int it = base + u * NWARPS;
+			const uint32_t word = __ballot_sync(0xffffffffu, v[u] > 0);
+			if (lane == 0 && it < items) { s_words[it] = word; }
+		}
 	}
 	__syncthreads();
 
@@ -283,32 +301,34 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 	p.K = d.size * d.size * d.c;
 	p.ldw = aligned_lda(p.K) / 32;
 	const bool word_path = (d.c % 32 == 0);
-	const int want_ctas = 2 * sm_count();
+	// CTAs to aim for.  Each CTA loads, synchronises, then stores, so overlap of loads and stores comes from
+	// several CTAs sharing an SM.  XNOR_B200_PACK_CTAS_PER_SM overrides the factor (tuning aid).
+	int ctas_per_sm = 4;
+	if (const char * e = std::getenv("XNOR_B200_PACK_CTAS_PER_SM")) { ctas_per_sm = max(1, atoi(e)); }
+	const int want_ctas = ctas_per_sm * sm_count();
 	auto in_rows = [&](int out_rows) { return (out_rows - 1) * d.stride + d.size; };
 
 	if (word_path)
 	{
 		const int CB = d.c / 32;
-		// Channel-block groups: only when the strips alone cannot fill the GPU; group borders stay on multiples
-		// of 4 blocks so that every group's word range starts on a 16-byte boundary of the packed row.
+		// Parallelism is taken in order of cost: images (free), then groups of 32-channel blocks (free, no halo;
+		// group borders stay on multiples of 4 blocks so that every group's word range starts on a 16-byte
+		// boundary of the packed row), then row strips (each strip re-reads size-1 halo rows).
+		long long ctas = d.batch;
 		int cb_per_cta = CB;
-		if ((long long)d.batch * p.OH < want_ctas && CB >= 8)
+		if (ctas < want_ctas && CB >= 8)
 		{
-			const long long strips = (long long)d.batch * p.OH;
-			int groups = (int)min((long long)(CB / 4), (want_ctas + strips - 1) / strips);
+			const int groups = (int)min((long long)(CB / 4), (want_ctas + ctas - 1) / ctas);
 			cb_per_cta = (int)round_up((size_t)(CB + groups - 1) / groups, 4);
 		}
 		p.cb_per_cta = cb_per_cta;
 		p.groups = (CB + cb_per_cta - 1) / cb_per_cta;
+		ctas *= p.groups;
 		const size_t row_bytes = (size_t)cb_per_cta * d.w * 4;
 		if (row_bytes * (size_t)min(in_rows(1), d.h) > PK_MAX_SMEM) { return XNOR_B200_ERR_TOO_LARGE; }
-		// Largest strip that (a) fits shared memory and (b) still leaves about two CTAs per SM.
-		int rows = p.OH;
-		while (rows > 1 && (row_bytes * (size_t)min(in_rows(rows), d.h) > PK_MAX_SMEM
-				|| (long long)d.batch * ((p.OH + rows - 1) / rows) * p.groups < want_ctas))
-		{
-			--rows;
-		}
+		const int strips = (int)min((long long)p.OH, max(1LL, (want_ctas + ctas - 1) / ctas));
+		int rows = (p.OH + strips - 1) / strips;
+		while (rows > 1 && row_bytes * (size_t)min(in_rows(rows), d.h) > PK_MAX_SMEM) { --rows; }
 		p.rows_per_cta = rows;
 		p.tiles_per_image = (p.OH + rows - 1) / rows;
 		const size_t smem = round_up(row_bytes * (size_t)min(in_rows(rows), d.h), 16);

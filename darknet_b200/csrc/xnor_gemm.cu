@@ -243,7 +243,9 @@ xnor_gemm_kernel(const GemmParams p)
 struct TileConfig
 {
 	int bm, bn;
-	float cost;             // relative cost of one (row, column, K-word) product in this register tile
+	int warps;              // warps per CTA
+	int max_resident;       // CTAs that fit on one SM (threads / shared memory)
+	float store_cost;       // epilogue cycles per output (narrow thread columns coalesce worse)
 	int (*launch)(GemmParams &, cudaStream_t);
 };
 
@@ -277,30 +279,33 @@ static int launch_config(GemmParams & p, cudaStream_t stream)
 	return check_launch();
 }
 
-// Measured on B200: the POPC unit is the limiter for every register tile, so small tiles with many resident
-// warps (index 2..5) beat the classic large tiles (0, 1: one 8-warp CTA per SM, latency-bound); the large
-// ones are kept for the tuning sweep only and are never chosen automatically.
+// Measured on B200: the POPC unit is the limiter for every register tile and it only saturates with about 20
+// resident warps per SM, so small tiles with many co-resident CTAs (index 2..5) beat the classic large tiles
+// (0, 1: one 8-warp CTA per SM, latency-bound); the large ones are kept for the tuning sweep only.
 static const TileConfig g_configs[] = {
-	{128, 128, 2.00f, launch_config<128, 128, 8, 8, 32, 3>},
-	{ 64, 128, 1.40f, launch_config< 64, 128, 4, 8, 32, 3>},
-	{ 64,  64, 1.00f, launch_config< 64,  64, 4, 4, 32, 3>},
-	{ 32, 128, 1.00f, launch_config< 32, 128, 4, 4, 16, 3>},
-	{ 32,  64, 1.02f, launch_config< 32,  64, 2, 4, 16, 3>},
-	{ 32,  32, 1.04f, launch_config< 32,  32, 2, 4, 16, 3>},
+	{128, 128, 8,  1, 0.30f, launch_config<128, 128, 8, 8, 32, 3>},
+	{ 64, 128, 8,  2, 0.30f, launch_config< 64, 128, 4, 8, 32, 3>},
+	{ 64,  64, 8,  4, 0.30f, launch_config< 64,  64, 4, 4, 32, 3>},
+	{ 32, 128, 8,  6, 0.25f, launch_config< 32, 128, 4, 4, 16, 3>},
+	{ 32,  64, 8,  8, 0.30f, launch_config< 32,  64, 2, 4, 16, 3>},
+	{ 32,  32, 4, 14, 0.60f, launch_config< 32,  32, 2, 4, 16, 3>},
 };
 constexpr int NUM_CONFIGS = (int)(sizeof(g_configs) / sizeof(g_configs[0]));
 
-// Estimated duration in SM cycles of one launch: CTAs on one SM share its POPC unit (one warp instruction
-// every other cycle per SM), so the busiest SM sets the time; every wave also pays a fixed latency for its
-// first loads and its epilogue, and a cluster pays for the reduction.
+// Estimated duration in SM cycles of one launch.  CTAs on one SM share its POPC unit (one warp instruction every
+// other cycle per SM when enough warps are resident), so the busiest SM sets the time; stores add a per-output
+// cost; every launch pays a fixed latency for its first loads, and a cluster pays for the reduction.
 static float estimate_cycles(const TileConfig & c, int M, int n_total, int kw, int split, int sms)
 {
 	const long long tiles = (long long)((M + c.bm - 1) / c.bm) * ((n_total + c.bn - 1) / c.bn) * split;
 	const long long per_sm = (tiles + sms - 1) / sms;
 	const int kw_slice = (int)round_up((size_t)(kw + split - 1) / split, 4);
-	const float cta_cycles = (float)c.bm * c.bn / 32.0f * kw_slice * 2.0f * c.cost;
-	const float fixed = 4000.0f + 0.25f * c.bm * c.bn + (split > 1 ? 800.0f + 150.0f * split : 0.0f);
-	return per_sm * (cta_cycles + 700.0f + 0.25f * c.bm * c.bn) + fixed;
+	const float resident_warps = (float)min(per_sm, (long long)c.max_resident) * c.warps;
+	const float eff = fminf(1.0f, 0.3f + resident_warps / 30.0f);
+	const float cta_cycles = (float)c.bm * c.bn / 32.0f * kw_slice * 2.0f / eff;
+	const float store_cycles = (float)c.bm * c.bn * c.store_cost / split;
+	const float fixed = 4000.0f + (split > 1 ? 3000.0f + 200.0f * split : 0.0f);
+	return per_sm * (cta_cycles + store_cycles) + 700.0f * ((per_sm + c.max_resident - 1) / c.max_resident) + fixed;
 }
 
 int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
