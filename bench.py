@@ -284,7 +284,7 @@ def run_gpu_arm(args) -> None:
     e2e_value = world * batch * args.steps / (ms_e2e * 1e-3)
 
     # ---- roofline of the dominant kernel (XNOR GEMM), rank 0 only ----
-    roofline = pack_roofline = cpu_baseline = None
+    roofline = pack_roofline = large_roofline = cpu_baseline = None
     if rank == 0:
         lib = capi.lib()
         xl_layers = [l.xnor_layer for l in net.layers if l.type == "convolutional" and l.xnor]
@@ -356,6 +356,32 @@ def run_gpu_arm(args) -> None:
             "frac": pack_gbs / hbm_peak, "traffic": None, "ms_per_forward": ms_pack,
             "peak_source": "MEASURED_PEAKS.json (of measured)" if peaks else "fallback 6650 GB/s (of fallback)",
         }
+        # The same GEMM entry point on a batch-64 layer (BASELINE config 1 shape: 256 -> 512 filters, 26x26, 3x3), where the
+        # library switches to the tcgen05 kernel: reported beside the headline because batch-1 launches are latency-bound.
+        capi.check(lib.xnor_b200_measure_umma_i8_peak(4000, C.byref(g_), C.byref(m_)), "umma peak")
+        umma_peak_tops = g_.value / 1e3
+        M_, N_, K_ = 512, 64 * 676, 2304
+        lda_ = K_ + (256 - K_ % 256)
+        A_ = torch.randint(0, 256, (M_, lda_ // 8), dtype=torch.uint8, device=dev)
+        B_ = torch.randint(0, 256, (N_, lda_ // 8), dtype=torch.uint8, device=dev)
+        A_[:, K_ // 8:] = 0
+        B_[:, K_ // 8:] = 0
+        C_ = torch.empty(M_, N_, device=dev)
+        mean_ = torch.rand(M_, device=dev)
+        bias_ = torch.rand(M_, device=dev)
+
+        def big_gemm():
+            capi.check(lib.xnor_b200_gemm_bin_mean_transposed(M_, N_, K_, A_.data_ptr(), lda_, B_.data_ptr(), lda_, C_.data_ptr(), N_,
+                                                              mean_.data_ptr(), bias_.data_ptr(), 1, None, None,
+                                                              torch.cuda.current_stream().cuda_stream), "gemm")
+        ms_big = time_launches(big_gemm)
+        big_tops = 2.0 * M_ * N_ * K_ / (ms_big * 1e-3) / 1e12
+        large_roofline = {
+            "kernel": "xnor_gemm_tc_kernel<256> (tcgen05 kind::i8), M=512 N=64x676 K=2304", "bound": "tensor", "achieved": big_tops,
+            "peak": umma_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": big_tops / umma_peak_tops, "traffic": None,
+            "peak_source": "measured in this run: back-to-back tcgen05.mma kind::i8 128x256x32 from resident shared memory",
+            "vs_int_popc_peak": big_tops / popc_peak_tops, "ms": ms_big,
+        }
         if world == 1:
             ips, kind, cores, sample = time_cpu_reference(args.cpu_baseline_seconds)
             cpu_baseline = {"value": ips, "unit": "images/s", "cores": cores, "kind": kind, "sample": sample}
@@ -370,7 +396,7 @@ def run_gpu_arm(args) -> None:
                        "float_layers": "cuDNN/ATen fp32 (outside the path, as in Darknet)",
                        "xnor_binops_per_image": binops_per_image},
             "xnor_gemm_tops": roofline["achieved"] if roofline else None,
-            "roofline": roofline, "roofline_pack": pack_roofline, "cpu_baseline": cpu_baseline,
+            "roofline": roofline, "roofline_pack": pack_roofline, "roofline_large_batch": large_roofline, "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": args.steps * net.xnor_launches_per_forward,

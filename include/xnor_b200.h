@@ -181,6 +181,9 @@ XNOR_B200_API int xnor_b200_conv_forward_static(const xnor_b200_conv_desc * desc
  * These two calls synchronise the device. */
 XNOR_B200_API int xnor_b200_measure_popc_peak(int iters, double * gops, double * ms);
 XNOR_B200_API int xnor_b200_measure_bmma_peak(int iters, double * gops, double * ms);
+/* Same, for the tensor-core route: back-to-back tcgen05.mma kind::i8 (M=128, N=256, K=32) from resident
+ * shared-memory tiles on every SM, counted as 2*M*N*K operations per MMA (the GEMM's own convention). */
+XNOR_B200_API int xnor_b200_measure_umma_i8_peak(int iters, double * gops, double * ms);
 
 #ifdef __cplusplus
 }
