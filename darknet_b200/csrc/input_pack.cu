@@ -45,7 +45,10 @@ struct PackParams
 
 // ---- word path -----------------------------------------------------------------------------
 // shared: packed[cb_local][R][W] words, R = input rows of this strip.
-template <bool VEC4>
+// VEC  = floats per load (4, 2 or 1, as the row pitch and pointer alignment allow);
+// SUBS = threads sharing one output word, each covering 32/SUBS channels (4 on small problems, to put more threads
+//        to work; 1 on large ones, where a thread then keeps 32 independent loads in flight).
+template <int VEC, int SUBS>
 __global__ void __launch_bounds__(PK_THREADS)
 pack_input_words_kernel(const PackParams p)
 {
@@ -65,54 +68,57 @@ pack_input_words_kernel(const PackParams p)
 	const int span = max(R, 0) * p.W;         // contiguous floats per channel
 	const size_t chan_stride = (size_t)p.H * p.W;
 	const float * img = p.in + ((size_t)b * p.C + (size_t)cb0 * 32) * chan_stride + (size_t)iy_lo * p.W;
-	uint8_t * s_bytes = reinterpret_cast<uint8_t *>(s_words);
 
-	// phase A: 32 channels -> one word per input pixel; thread (item, sub) covers channels 8*sub .. 8*sub+7
-	if (VEC4)
+	// phase A: 32 channels -> one word per input pixel
 	{
-		const int span4 = span >> 2;
-		const int items = cbn * span4;
-		for (int idx = threadIdx.x; idx < items * 4; idx += PK_THREADS)
+		constexpr int CH = 32 / SUBS;             // channels per thread-task
+		const int spanv = span / VEC;             // VEC divides W, hence span
+		const int items = cbn * spanv;
+		for (int idx = threadIdx.x; idx < items * SUBS; idx += PK_THREADS)
 		{
 			const int sub = idx / items;
 			const int item = idx - sub * items;
-			const int cbl = item / span4;
-			const int e4 = item - cbl * span4;
-			const float * src = img + ((size_t)cbl * 32 + sub * 8) * chan_stride + (size_t)e4 * 4;
-			uint32_t w0 = 0, w1 = 0, w2 = 0, w3 = 0;
+			const int cbl = item / spanv;
+			const int ev = item - cbl * spanv;
+			const float * src = img + ((size_t)cbl * 32 + sub * CH) * chan_stride + (size_t)ev * VEC;
+			uint32_t w[VEC];
 			#pragma unroll
-			for (int ch = 0; ch < 8; ++ch)
-			{
-				const float4 v = __ldg(reinterpret_cast<const float4 *>(src + (size_t)ch * chan_stride));
-				w0 |= (v.x > 0 ? 1u : 0u) << ch;
-				w1 |= (v.y > 0 ? 1u : 0u) << ch;
-				w2 |= (v.z > 0 ? 1u : 0u) << ch;
-				w3 |= (v.w > 0 ? 1u : 0u) << ch;
-			}
-			uint8_t * dst = s_bytes + (size_t)item * 16 + sub;
-			dst[0] = (uint8_t)w0;
-			dst[4] = (uint8_t)w1;
-			dst[8] = (uint8_t)w2;
-			dst[12] = (uint8_t)w3;
-		}
-	}
-	else
-	{
-		const int items = cbn * span;
-		for (int idx = threadIdx.x; idx < items * 4; idx += PK_THREADS)
-		{
-			const int sub = idx / items;
-			const int item = idx - sub * items;
-			const int cbl = item / span;
-			const int e = item - cbl * span;
-			const float * src = img + ((size_t)cbl * 32 + sub * 8) * chan_stride + e;
-			uint32_t w0 = 0;
+			for (int j = 0; j < VEC; ++j) { w[j] = 0; }
 			#pragma unroll
-			for (int ch = 0; ch < 8; ++ch)
+			for (int ch = 0; ch < CH; ++ch)
 			{
-				w0 |= (__ldg(src + (size_t)ch * chan_stride) > 0 ? 1u : 0u) << ch;
+				const float * q = src + (size_t)ch * chan_stride;
+				if (VEC == 4)
+				{
+					const float4 v = __ldg(reinterpret_cast<const float4 *>(q));
+					w[0] |= (v.x > 0 ? 1u : 0u) << ch;
+					w[1 % VEC] |= (v.y > 0 ? 1u : 0u) << ch;
+					w[2 % VEC] |= (v.z > 0 ? 1u : 0u) << ch;
+					w[3 % VEC] |= (v.w > 0 ? 1u : 0u) << ch;
+				}
+				else if (VEC == 2)
+				{
+					const float2 v = __ldg(reinterpret_cast<const float2 *>(q));
+					w[0] |= (v.x > 0 ? 1u : 0u) << ch;
+					w[1 % VEC] |= (v.y > 0 ? 1u : 0u) << ch;
+				}
+				else
+				{
+					w[0] |= (__ldg(q) > 0 ? 1u : 0u) << ch;
+				}
 			}
-			s_bytes[(size_t)item * 4 + sub] = (uint8_t)w0;
+			if (SUBS == 1)
+			{
+				#pragma unroll
+				for (int j = 0; j < VEC; ++j) { s_words[(size_t)item * VEC + j] = w[j]; }
+			}
+			else
+			{
+				// SUBS == 4: this thread owns byte `sub` of each word
+				uint8_t * dst = reinterpret_cast<uint8_t *>(s_words) + (size_t)item * VEC * 4 + sub;
+				#pragma unroll
+				for (int j = 0; j < VEC; ++j) { dst[j * 4] = (uint8_t)w[j]; }
+			}
 		}
 	}
 	__syncthreads();
@@ -334,8 +340,15 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 		const size_t smem = round_up(row_bytes * (size_t)min(in_rows(rows), d.h), 16);
 		const long long grid = (long long)d.batch * p.tiles_per_image * p.groups;
 		if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
-		const bool vec4 = (d.w % 4 == 0) && (((uintptr_t)input & 15u) == 0);
-		auto kern = vec4 ? pack_input_words_kernel<true> : pack_input_words_kernel<false>;
+		const int vec = ((d.w % 4 == 0) && (((uintptr_t)input & 15u) == 0)) ? 4
+				: ((d.w % 2 == 0) && (((uintptr_t)input & 7u) == 0)) ? 2 : 1;
+		// words per CTA in phase A; below two per thread the channel split keeps more threads busy
+		const long long words_per_cta = (long long)cb_per_cta * min(in_rows(rows), d.h) * d.w;
+		const bool split = words_per_cta < 2LL * PK_THREADS * vec;
+		void (*kern)(const PackParams) =
+				vec == 4 ? (split ? pack_input_words_kernel<4, 4> : pack_input_words_kernel<4, 1>)
+				: vec == 2 ? (split ? pack_input_words_kernel<2, 4> : pack_input_words_kernel<2, 1>)
+				: (split ? pack_input_words_kernel<1, 4> : pack_input_words_kernel<1, 1>);
 		int rc = ensure_dynamic_smem((const void *)kern, smem > 48 * 1024 ? PK_MAX_SMEM : 0);
 		if (rc != XNOR_B200_OK) { return rc; }
 		kern<<<(unsigned)grid, PK_THREADS, smem, stream>>>(p);
