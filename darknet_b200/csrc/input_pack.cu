@@ -41,6 +41,8 @@ struct PackParams
 	int groups;          // word path: channel-block groups per strip
 	int ldw;             // words per packed row (new_ldb/32)
 	int K;               // bits per row that carry data
+	int tab_offset;      // word path: offset (in words) of the K-word table behind the staged rows
+	int lpp_shift;       // word path: log2 of the lanes that share one output pixel in phase B
 };
 
 // ---- word path -----------------------------------------------------------------------------
@@ -123,42 +125,101 @@ pack_input_words_kernel(const PackParams p)
 	}
 	__syncthreads();
 
-	// phase B: one uint4 (4 K-words) per thread-iteration over this CTA's word range
+	// phase B: one uint4 (4 K-words) per thread-iteration over this CTA's word range.
+	// A small table maps every K-word of the range to (offset inside the staged rows, ky, kx) once per CTA, so
+	// the per-word work is a table read, two bounds checks and one shared load -- no integer division.
 	const int taps = p.ks * p.ks;
 	const int new_k = CB * taps;
 	const bool last_group = (g == p.groups - 1);
 	const int q_lo = (cb0 * taps) >> 2;                                   // cb0 % 4 == 0 whenever groups > 1
 	const int q_hi = last_group ? (p.ldw >> 2) : (((cb0 + cbn) * taps) >> 2);
 	const int nq = q_hi - q_lo;
+	uint32_t * s_tab = s_words + p.tab_offset;                            // nq*4 entries: off | ky << 20 | kx << 26
+	for (int i = threadIdx.x; i < nq * 4; i += PK_THREADS)
+	{
+		const int wi = q_lo * 4 + i;
+		uint32_t e = 0xffffffffu;                                         // padding word
+		if (wi < new_k)
+		{
+			const int cb = wi / taps;
+			const int t = wi - cb * taps;
+			const int ky = t / p.ks;
+			const int kx = t - ky * p.ks;
+			e = (uint32_t)(((cb - cb0) * R + ky) * p.W + kx) | ((uint32_t)ky << 20) | ((uint32_t)kx << 26);
+		}
+		s_tab[i] = e;
+	}
+	__syncthreads();
+
 	const int pixels = (y1 - y0) * p.OW;
 	const size_t row_base = (size_t)b * p.OH * p.OW + (size_t)y0 * p.OW;
-	for (int q = threadIdx.x; q < pixels * nq; q += PK_THREADS)
+	const int lpp = 1 << p.lpp_shift;                                     // lanes per pixel: power of two >= min(nq, 32)
+	const int wq_first = threadIdx.x & (lpp - 1);
+	for (int pl = threadIdx.x >> p.lpp_shift; pl < pixels; pl += PK_THREADS >> p.lpp_shift)
 	{
-		const int pl = q / nq;
-		const int wq = q_lo + (q - pl * nq);
 		const int yl = pl / p.OW;
 		const int x = pl - yl * p.OW;
 		const int iy_base = (y0 + yl) * p.stride - p.pad - iy_lo;   // relative to the staged rows
 		const int ix_base = x * p.stride - p.pad;
-		uint32_t v[4];
-		#pragma unroll
-		for (int u = 0; u < 4; ++u)
+		const int base_off = iy_base * p.W + ix_base;
+		uint4 * dst = reinterpret_cast<uint4 *>(p.out + (row_base + pl) * p.ldw) + q_lo;
+		for (int wq = wq_first; wq < nq; wq += lpp)
 		{
-			const int wi = wq * 4 + u;
-			uint32_t word = 0;
-			if (wi < new_k)
+			const uint4 e4 = reinterpret_cast<const uint4 *>(s_tab)[wq];
+			const uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
+			uint32_t v[4];
+			#pragma unroll
+			for (int u = 0; u < 4; ++u)
 			{
-				const int cb = wi / taps;
-				const int t = wi - cb * taps;
-				const int ky = t / p.ks;
-				const int kx = t - ky * p.ks;
-				const int r = iy_base + ky;
-				const int ix = ix_base + kx;
-				if (r >= 0 && r < R && ix >= 0 && ix < p.W) { word = s_words[((cb - cb0) * R + r) * p.W + ix]; }
+				uint32_t word = 0;
+				if (e[u] != 0xffffffffu)
+				{
+					const int r = iy_base + (int)((e[u] >> 20) & 63u);
+					const int ix = ix_base + (int)(e[u] >> 26);
+					if (r >= 0 && r < R && ix >= 0 && ix < p.W) { word = s_words[base_off + (int)(e[u] & 0xfffffu)]; }
+				}
+				v[u] = word;
 			}
-			v[u] = word;
+			dst[wq] = make_uint4(v[0], v[1], v[2], v[3]);
 		}
-		reinterpret_cast<uint4 *>(p.out + (row_base + pl) * p.ldw)[wq] = make_uint4(v[0], v[1], v[2], v[3]);
+	}
+}
+
+// Phase A of the bit kernels: planes[c][rr][xw] = ballot of (input(c, iy0 + rr, 32*xw + lane - pad) > 0).
+// One warp walks whole plane rows, eight words (eight independent loads per lane) at a time; the only integer
+// division is one per plane row.
+__device__ __forceinline__ void build_bit_planes(const float * img, size_t chan_stride, const PackParams & p,
+		int RR, int PW, int iy0)
+{
+	extern __shared__ uint32_t s_words[];
+	const int lane = threadIdx.x & 31;
+	const int warp = threadIdx.x >> 5;
+	constexpr int NWARPS = PK_THREADS / 32;
+	constexpr int UNROLL = 8;
+	for (int cr = warp; cr < p.C * RR; cr += NWARPS)
+	{
+		const int c = cr / RR;
+		const int rr = cr - c * RR;
+		const int iy = iy0 + rr;
+		const bool row_ok = (iy >= 0 && iy < p.H);
+		const float * row = img + (size_t)c * chan_stride + (size_t)iy * p.W - p.pad + lane;
+		uint32_t * dst = s_words + (size_t)cr * PW;
+		for (int xw0 = 0; xw0 < PW; xw0 += UNROLL)
+		{
+			float v[UNROLL];
+			#pragma unroll
+			for (int u = 0; u < UNROLL; ++u)
+			{
+				const int ix = (xw0 + u) * 32 + lane - p.pad;
+				v[u] = (row_ok && xw0 + u < PW && ix >= 0 && ix < p.W) ? __ldg(row + (xw0 + u) * 32) : 0.0f;
+			}
+			#pragma unroll
+			for (int u = 0; u < UNROLL; ++u)
+			{
+				const uint32_t word = __ballot_sync(0xffffffffu, v[u] > 0);
+				if (lane == 0 && xw0 + u < PW) { dst[xw0 + u] = word; }
+			}
+		}
 	}
 }
 
@@ -183,36 +244,7 @@ pack_input_bits_kernel(const PackParams p)
 	// phase A: one warp ballot per 32 consecutive padded positions of one (channel, row)
 	const int lane = threadIdx.x & 31;
 	const int warp = threadIdx.x >> 5;
-	const int items = p.C * RR * PW;
-	constexpr int NWARPS = PK_THREADS / 32;
-	constexpr int UNROLL = 8;                              // loads in flight per lane before the first ballot
-	for (int base = warp; base < items; base += UNROLL * NWARPS)
-	{
-		float v[UNROLL];
-		#pragma unroll
-		for (int u = 0; u < UNROLL; ++u)
-		{
-			const int it = base + u * NWARPS;
-			const int xw = it % PW;
-			const int cr = it / PW;
-			const int rr = cr % RR;
-			const int c = cr / RR;
-			const int ix = xw * 32 + lane - p.pad;
-			const int iy = iy0 + rr;
-			v[u] = 0.0f;
-			if (it < items && ix >= 0 && ix < p.W && iy >= 0 && iy < p.H)
-			{
-				v[u] = __ldg(img + (size_t)c * chan_stride + (size_t)iy * p.W + ix);
-			}
-		}
-		#pragma unroll
-		for (int u = 0; u < UNROLL; ++u)
-		{
-			const int it = base + u * NWARPS;
-			const uint32_t word = __ballot_sync(0xffffffffu, v[u] > 0);
-			if (lane == 0 && it < items) { s_words[it] = word; }
-		}
-	}
+	build_bit_planes(img, chan_stride, p, RR, PW, iy0);
 	__syncthreads();
 
 	// phase B: thread builds 4 consecutive K-words (bits k0 .. k0+127) of one output row.
@@ -261,6 +293,96 @@ pack_input_bits_kernel(const PackParams p)
 	}
 }
 
+// Stride-1 bit path.  Same bit planes as above; phase B works on 32x32 bit blocks held in registers:
+// a thread gathers, for 32 consecutive K indices, the 32-pixel words "tap (c, ky, kx) of pixels x0 .. x0+31"
+// (one funnel shift each, because with stride 1 those taps are adjacent plane bits), transposes the block with
+// five butterfly stages, and stores one K-word for each of the 32 pixels.  That is about 0.8 instructions per
+// output bit instead of a dozen, which is what lets the small-channel layers approach memory speed.
+__device__ __forceinline__ void transpose32(uint32_t (&A)[32])
+{
+	// out[l] bit k == in[k] bit l  (bit 0 = least significant)
+	uint32_t m = 0x0000ffffu;
+	#pragma unroll
+	for (int j = 16; j != 0; j >>= 1)
+	{
+		#pragma unroll
+		for (int k = 0; k < 32; k = (k + j + 1) & ~j)
+		{
+			const uint32_t t = ((A[k] >> j) ^ A[k + j]) & m;
+			A[k + j] ^= t;
+			A[k] ^= t << j;
+		}
+		m ^= m << (j >> 1);
+	}
+}
+
+__global__ void __launch_bounds__(PK_THREADS)
+pack_input_bits_s1_kernel(const PackParams p)
+{
+	extern __shared__ uint32_t s_words[];
+	const int tile = blockIdx.x % p.tiles_per_image;
+	const int b = blockIdx.x / p.tiles_per_image;
+	const int y0 = tile * p.rows_per_cta;
+	const int y1 = min(y0 + p.rows_per_cta, p.OH);
+	const int RR = (y1 - y0 - 1) + p.ks;
+	const int PW = ((p.W + 2 * p.pad + 31) >> 5) + 1;
+	const size_t chan_stride = (size_t)p.H * p.W;
+	const float * img = p.in + (size_t)b * p.C * chan_stride;
+	const int iy0 = y0 - p.pad;
+
+	// phase A: one warp ballot per 32 consecutive padded positions of one (channel, row)
+	const int lane = threadIdx.x & 31;
+	const int warp = threadIdx.x >> 5;
+	build_bit_planes(img, chan_stride, p, RR, PW, iy0);
+	__syncthreads();
+
+	// phase B: task = (output row yl, 32-pixel chunk pc, K-word kb); consecutive threads take consecutive kb
+	const int chunks = (p.OW + 31) >> 5;
+	const int tasks = (y1 - y0) * chunks * p.ldw;
+	const int taps = p.ks * p.ks;
+	const size_t row_base = (size_t)b * p.OH * p.OW + (size_t)y0 * p.OW;
+	for (int t = threadIdx.x; t < tasks; t += PK_THREADS)
+	{
+		const int kb = t % p.ldw;
+		const int rest = t / p.ldw;
+		const int pc = rest % chunks;
+		const int yl = rest / chunks;
+		const int x0 = pc * 32;
+		uint32_t * dst = p.out + (row_base + (size_t)yl * p.OW + x0) * p.ldw + kb;
+		const int npix = min(32, p.OW - x0);
+		int k = kb * 32;
+		if (k >= p.K)
+		{
+			for (int l = 0; l < npix; ++l) { dst[(size_t)l * p.ldw] = 0u; }
+			continue;
+		}
+		int c = k / taps;
+		int tt = k - c * taps;
+		int ky = tt / p.ks;
+		int kx = tt - ky * p.ks;
+		const uint32_t * plane = s_words + ((size_t)c * RR + yl + ky) * PW + pc;
+		uint32_t A[32];
+		#pragma unroll
+		for (int kk = 0; kk < 32; ++kk)
+		{
+			A[kk] = (k < p.K) ? __funnelshift_r(plane[0], plane[1], kx) : 0u;
+			++k;
+			if (++kx == p.ks)
+			{
+				kx = 0;
+				plane += PW;
+				if (++ky == p.ks) { ky = 0; plane += (size_t)(RR - p.ks) * PW; }
+			}
+		}
+		transpose32(A);
+		#pragma unroll
+		for (int l = 0; l < 32; ++l)
+		{
+			if (l < npix) { dst[(size_t)l * p.ldw] = A[l]; }
+		}
+	}
+}
+
 // ---- channel pack only (stage-level seam) -----------------------------------------------------
 // input [c][hw] -> packed [c/32][hw]; one thread per output word, coalesced along hw.
 __global__ void __launch_bounds__(PK_THREADS)
@@ -306,7 +428,10 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 	p.ks = d.size; p.stride = d.stride; p.pad = d.pad;
 	p.K = d.size * d.size * d.c;
 	p.ldw = aligned_lda(p.K) / 32;
+	p.tab_offset = 0;
+	p.lpp_shift = 0;
 	const bool word_path = (d.c % 32 == 0);
+	if (d.size > 63) { return XNOR_B200_ERR_TOO_LARGE; }             // kernel offsets are kept in 6-bit fields
 	// CTAs to aim for.  Each CTA loads, synchronises, then stores, so overlap of loads and stores comes from
 	// several CTAs sharing an SM.  XNOR_B200_PACK_CTAS_PER_SM overrides the factor (tuning aid).
 	int ctas_per_sm = 4;
@@ -334,10 +459,18 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 		if (row_bytes * (size_t)min(in_rows(1), d.h) > PK_MAX_SMEM) { return XNOR_B200_ERR_TOO_LARGE; }
 		const int strips = (int)min((long long)p.OH, max(1LL, (want_ctas + ctas - 1) / ctas));
 		int rows = (p.OH + strips - 1) / strips;
-		while (rows > 1 && row_bytes * (size_t)min(in_rows(rows), d.h) > PK_MAX_SMEM) { --rows; }
+		const size_t room = PK_MAX_SMEM - (size_t)p.ldw * 4 - 16;            // staged rows share the limit with the K-word table
+		if (row_bytes * (size_t)min(in_rows(1), d.h) > room) { return XNOR_B200_ERR_TOO_LARGE; }
+		while (rows > 1 && row_bytes * (size_t)min(in_rows(rows), d.h) > room) { --rows; }
 		p.rows_per_cta = rows;
 		p.tiles_per_image = (p.OH + rows - 1) / rows;
-		const size_t smem = round_up(row_bytes * (size_t)min(in_rows(rows), d.h), 16);
+		const size_t words_bytes = round_up(row_bytes * (size_t)min(in_rows(rows), d.h), 16);
+		p.tab_offset = (int)(words_bytes / 4);
+		const size_t smem = words_bytes + (size_t)p.ldw * 4;             // + the K-word table (at most ldw entries)
+		const int nq_max = (p.groups > 1) ? max((cb_per_cta * d.size * d.size) >> 2, (p.ldw >> 2) - (((p.groups - 1) * cb_per_cta * d.size * d.size) >> 2))
+		                                  : (p.ldw >> 2);
+		p.lpp_shift = 0;
+		while ((1 << p.lpp_shift) < min(nq_max, 32)) { ++p.lpp_shift; }
 		const long long grid = (long long)d.batch * p.tiles_per_image * p.groups;
 		if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
 		const int vec = ((d.w % 4 == 0) && (((uintptr_t)input & 15u) == 0)) ? 4
@@ -367,14 +500,18 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 		{
 			--rows;
 		}
+		// Phase A of the bit kernels is a chain of dependent load rounds per warp, so short strips (many CTAs in
+		// flight) hide its latency better than long ones; 8 rows keep the halo re-reads at (size-1)/8.
+		rows = min(rows, 8);
 		p.rows_per_cta = rows;
 		p.tiles_per_image = (p.OH + rows - 1) / rows;
 		const size_t smem = round_up(row_bytes * (size_t)in_rows(rows), 16);
 		const long long grid = (long long)d.batch * p.tiles_per_image;
 		if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
-		int rc = ensure_dynamic_smem((const void *)pack_input_bits_kernel, smem > 48 * 1024 ? PK_MAX_SMEM : 0);
+		void (*kern)(const PackParams) = (d.stride == 1) ? pack_input_bits_s1_kernel : pack_input_bits_kernel;
+		int rc = ensure_dynamic_smem((const void *)kern, smem > 48 * 1024 ? PK_MAX_SMEM : 0);
 		if (rc != XNOR_B200_OK) { return rc; }
-		pack_input_bits_kernel<<<(unsigned)grid, PK_THREADS, smem, stream>>>(p);
+		kern<<<(unsigned)grid, PK_THREADS, smem, stream>>>(p);
 	}
 	return check_launch();
 }
