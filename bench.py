@@ -194,7 +194,7 @@ def run_gpu_arm(args) -> None:
     import torch
     import torch.distributed as dist
     import synth
-    from darknet_b200 import capi, cfgs, network
+    from darknet_b200 import capi, cfgs, network, replicas
     from darknet_b200 import layer as L
 
     rank = int(os.environ.get("RANK", "0"))
@@ -261,11 +261,7 @@ def run_gpu_arm(args) -> None:
         return float(sum(a.elapsed_time(b) for a, b in evs))
 
     def max_over_ranks(ms: float) -> float:
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return replicas.max_over_ranks(ms, dev)
 
     sampler = ClockSampler(local) if rank == 0 else None
     timed_steps(args.warmup, False)
