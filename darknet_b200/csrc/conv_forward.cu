@@ -121,7 +121,7 @@ extern "C" size_t xnor_b200_scratch_bytes(const xnor_b200_conv_desc * desc)
 	return round_up(g.packed_input_bytes, 256);
 }
 
-extern "C" int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const float * input,
+static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_pool_desc * pool, const float * input,
 		const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
 		float * output, const float * shortcut_in, float * shortcut_out,
 		void * scratch, size_t scratch_bytes, void * stream)
@@ -136,10 +136,29 @@ extern "C" int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const fl
 	if (shortcut_out != nullptr && shortcut_in == nullptr) { return XNOR_B200_ERR_NULL; }
 
 	cudaStream_t s = (cudaStream_t)stream;
-	rc = launch_pack_input(*desc, input, (uint32_t *)scratch, s);
+	rc = launch_pack_input(*desc, pool, input, (uint32_t *)scratch, s);
 	if (rc != XNOR_B200_OK) { return rc; }
 	return launch_xnor_gemm(desc->n, desc->batch * g.n_out, g.n_out, g.k,
 			(const uint32_t *)align_bit_weights, g.new_lda / 32, (const uint32_t *)scratch, g.new_lda / 32,
 			output, g.n_out, mean_arr, biases, desc->activation == XNOR_B200_LEAKY,
 			shortcut_in, shortcut_out, nullptr, s);
+}
+
+extern "C" int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const float * input,
+		const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
+		float * output, const float * shortcut_in, float * shortcut_out,
+		void * scratch, size_t scratch_bytes, void * stream)
+{
+	return conv_forward_impl(desc, nullptr, input, align_bit_weights, mean_arr, biases, output, shortcut_in, shortcut_out,
+			scratch, scratch_bytes, stream);
+}
+
+extern "C" int xnor_b200_conv_forward_pooled(const xnor_b200_conv_desc * desc, const xnor_b200_pool_desc * pool,
+		const float * input, const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
+		float * output, const float * shortcut_in, float * shortcut_out,
+		void * scratch, size_t scratch_bytes, void * stream)
+{
+	if (pool == nullptr) { return XNOR_B200_ERR_NULL; }
+	return conv_forward_impl(desc, pool, input, align_bit_weights, mean_arr, biases, output, shortcut_in, shortcut_out,
+			scratch, scratch_bytes, stream);
 }

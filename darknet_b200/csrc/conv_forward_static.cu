@@ -74,7 +74,7 @@ extern "C" int xnor_b200_conv_forward_static(const xnor_b200_conv_desc * desc, c
 	// padding words included, and the GEMM reads only those rows.  What the previous call left behind in
 	// the rest of the array is never read.
 	cudaStream_t s = (cudaStream_t)stream;
-	rc = launch_pack_input(*desc, input, (uint32_t *)scratch, s);
+	rc = launch_pack_input(*desc, nullptr, input, (uint32_t *)scratch, s);
 	if (rc != XNOR_B200_OK) { return rc; }
 	return launch_xnor_gemm(desc->n, desc->batch * g.n_out, g.n_out, g.k,
 			(const uint32_t *)align_bit_weights, g.new_lda / 32, (const uint32_t *)scratch, g.new_lda / 32,

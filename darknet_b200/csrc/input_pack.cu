@@ -43,14 +43,40 @@ struct PackParams
 	int K;               // bits per row that carry data
 	int tab_offset;      // word path: offset (in words) of the K-word table behind the staged rows
 	int lpp_shift;       // word path: log2 of the lanes that share one output pixel in phase B
+	// Optional max-pool in front of the convolution (pool_size == 0: none).  H and W above are then the POOLED
+	// sizes the convolution sees, in_h and in_w the sizes of the tensor actually in memory.
+	int pool_size, pool_stride, pool_off;
+	int in_h, in_w;
 };
+
+// sign(maxpool(x)) at pooled position (iy, ix) of one channel plane: the maximum is > 0 exactly when some
+// in-image window element is > 0 (window origin -pad/2, out-of-image elements ignored:
+// src-lib/maxpool_layer_kernels.cu:48-86), so no maximum is ever formed.
+__device__ __forceinline__ bool pooled_positive(const float * __restrict__ plane, const PackParams & p, int iy, int ix)
+{
+	const int py0 = iy * p.pool_stride - p.pool_off;
+	const int px0 = ix * p.pool_stride - p.pool_off;
+	bool pos = false;
+	for (int l = 0; l < p.pool_size; ++l)
+	{
+		const int yy = py0 + l;
+		if (yy < 0 || yy >= p.in_h) { continue; }
+		for (int m = 0; m < p.pool_size; ++m)
+		{
+			const int xx = px0 + m;
+			if (xx >= 0 && xx < p.in_w) { pos = pos || (__ldg(plane + (size_t)yy * p.in_w + xx) > 0); }
+		}
+	}
+	return pos;
+}
 
 // ---- word path -----------------------------------------------------------------------------
 // shared: packed[cb_local][R][W] words, R = input rows of this strip.
 // VEC  = floats per load (4, 2 or 1, as the row pitch and pointer alignment allow);
 // SUBS = threads sharing one output word, each covering 32/SUBS channels (4 on small problems, to put more threads
 //        to work; 1 on large ones, where a thread then keeps 32 independent loads in flight).
-template <int VEC, int SUBS>
+// POOL = the tensor in memory is max-pooled on the fly (always with VEC == 1: pooled pixels are not contiguous).
+template <int VEC, int SUBS, bool POOL = false>
 __global__ void __launch_bounds__(PK_THREADS)
 pack_input_words_kernel(const PackParams p)
 {
@@ -68,8 +94,8 @@ pack_input_words_kernel(const PackParams p)
 	const int cb0 = g * p.cb_per_cta;
 	const int cbn = min(p.cb_per_cta, CB - cb0);
 	const int span = max(R, 0) * p.W;         // contiguous floats per channel
-	const size_t chan_stride = (size_t)p.H * p.W;
-	const float * img = p.in + ((size_t)b * p.C + (size_t)cb0 * 32) * chan_stride + (size_t)iy_lo * p.W;
+	const size_t chan_stride = POOL ? (size_t)p.in_h * p.in_w : (size_t)p.H * p.W;
+	const float * img = p.in + ((size_t)b * p.C + (size_t)cb0 * 32) * chan_stride + (POOL ? 0 : (size_t)iy_lo * p.W);
 
 	// phase A: 32 channels -> one word per input pixel
 	{
@@ -103,6 +129,13 @@ pack_input_words_kernel(const PackParams p)
 					const float2 v = __ldg(reinterpret_cast<const float2 *>(q));
 					w[0] |= (v.x > 0 ? 1u : 0u) << ch;
 					w[1 % VEC] |= (v.y > 0 ? 1u : 0u) << ch;
+				}
+				else if (POOL)
+				{
+					// ev = (staged row, column) of the pooled tensor; q still points at element ev of an unpooled plane
+					const int rl = ev / p.W;
+					const int xl = ev - rl * p.W;
+					w[0] |= (pooled_positive(q - ev, p, iy_lo + rl, xl) ? 1u : 0u) << ch;
 				}
 				else
 				{
@@ -211,7 +244,15 @@ __device__ __forceinline__ void build_bit_planes(const float * img, size_t chan_
 			for (int u = 0; u < UNROLL; ++u)
 			{
 				const int ix = (xw0 + u) * 32 + lane - p.pad;
-				v[u] = (row_ok && xw0 + u < PW && ix >= 0 && ix < p.W) ? __ldg(row + (xw0 + u) * 32) : 0.0f;
+				const bool ok = row_ok && xw0 + u < PW && ix >= 0 && ix < p.W;
+				if (p.pool_size > 0)
+				{
+					v[u] = (ok && pooled_positive(img + (size_t)c * chan_stride, p, iy, ix)) ? 1.0f : 0.0f;
+				}
+				else
+				{
+					v[u] = ok ? __ldg(row + (xw0 + u) * 32) : 0.0f;
+				}
 			}
 			#pragma unroll
 			for (int u = 0; u < UNROLL; ++u)
@@ -237,7 +278,7 @@ pack_input_bits_kernel(const PackParams p)
 	const int y1 = min(y0 + p.rows_per_cta, p.OH);
 	const int RR = (y1 - y0 - 1) * p.stride + p.ks;
 	const int PW = ((p.W + 2 * p.pad + 31) >> 5) + 1;
-	const size_t chan_stride = (size_t)p.H * p.W;
+	const size_t chan_stride = (p.pool_size > 0) ? (size_t)p.in_h * p.in_w : (size_t)p.H * p.W;
 	const float * img = p.in + (size_t)b * p.C * chan_stride;
 	const int iy0 = y0 * p.stride - p.pad;
 
@@ -326,7 +367,7 @@ pack_input_bits_s1_kernel(const PackParams p)
 	const int y1 = min(y0 + p.rows_per_cta, p.OH);
 	const int RR = (y1 - y0 - 1) + p.ks;
 	const int PW = ((p.W + 2 * p.pad + 31) >> 5) + 1;
-	const size_t chan_stride = (size_t)p.H * p.W;
+	const size_t chan_stride = (p.pool_size > 0) ? (size_t)p.in_h * p.in_w : (size_t)p.H * p.W;
 	const float * img = p.in + (size_t)b * p.C * chan_stride;
 	const int iy0 = y0 - p.pad;
 
@@ -417,9 +458,20 @@ float_to_bit_kernel(const float * __restrict__ src, uint32_t * __restrict__ dst,
 	}
 }
 
-int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32_t * t_bit_input, cudaStream_t stream)
+int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
+		uint32_t * t_bit_input, cudaStream_t stream)
 {
 	PackParams p;
+	p.pool_size = 0; p.pool_stride = 1; p.pool_off = 0; p.in_h = d.h; p.in_w = d.w;
+	if (pool != nullptr)
+	{
+		if (pool->size <= 0 || pool->stride <= 0 || pool->pad < 0 || pool->in_h <= 0 || pool->in_w <= 0) { return XNOR_B200_ERR_INVALID; }
+		// the convolution must be described on the pooled tensor (src-lib/maxpool_layer.cpp:129-130)
+		if (d.h != (pool->in_h + pool->pad - pool->size) / pool->stride + 1
+				|| d.w != (pool->in_w + pool->pad - pool->size) / pool->stride + 1) { return XNOR_B200_ERR_INVALID; }
+		p.pool_size = pool->size; p.pool_stride = pool->stride; p.pool_off = pool->pad / 2;
+		p.in_h = pool->in_h; p.in_w = pool->in_w;
+	}
 	p.in = input;
 	p.out = t_bit_input;
 	p.C = d.c; p.H = d.h; p.W = d.w;
@@ -473,7 +525,8 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 		while ((1 << p.lpp_shift) < min(nq_max, 32)) { ++p.lpp_shift; }
 		const long long grid = (long long)d.batch * p.tiles_per_image * p.groups;
 		if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
-		const int vec = ((d.w % 4 == 0) && (((uintptr_t)input & 15u) == 0)) ? 4
+		const int vec = (pool != nullptr) ? 1
+				: ((d.w % 4 == 0) && (((uintptr_t)input & 15u) == 0)) ? 4
 				: ((d.w % 2 == 0) && (((uintptr_t)input & 7u) == 0)) ? 2 : 1;
 		// words per CTA in phase A; below two per thread the channel split keeps more threads busy
 		const long long words_per_cta = (long long)cb_per_cta * min(in_rows(rows), d.h) * d.w;
@@ -481,6 +534,7 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32
 		void (*kern)(const PackParams) =
 				vec == 4 ? (split ? pack_input_words_kernel<4, 4> : pack_input_words_kernel<4, 1>)
 				: vec == 2 ? (split ? pack_input_words_kernel<2, 4> : pack_input_words_kernel<2, 1>)
+				: (pool != nullptr) ? (split ? pack_input_words_kernel<1, 4, true> : pack_input_words_kernel<1, 1, true>)
 				: (split ? pack_input_words_kernel<1, 4> : pack_input_words_kernel<1, 1>);
 		int rc = ensure_dynamic_smem((const void *)kern, smem > 48 * 1024 ? PK_MAX_SMEM : 0);
 		if (rc != XNOR_B200_OK) { return rc; }
@@ -526,7 +580,17 @@ extern "C" int xnor_b200_pack_input(const xnor_b200_conv_desc * desc, const floa
 	int rc = validate_desc(desc);
 	if (rc != XNOR_B200_OK) { return rc; }
 	if (((uintptr_t)t_bit_input & 15u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
-	return launch_pack_input(*desc, input, (uint32_t *)t_bit_input, (cudaStream_t)stream);
+	return launch_pack_input(*desc, nullptr, input, (uint32_t *)t_bit_input, (cudaStream_t)stream);
+}
+
+extern "C" int xnor_b200_pack_input_pooled(const xnor_b200_conv_desc * desc, const xnor_b200_pool_desc * pool,
+		const float * input, uint8_t * t_bit_input, void * stream)
+{
+	if (desc == nullptr || pool == nullptr || input == nullptr || t_bit_input == nullptr) { return XNOR_B200_ERR_NULL; }
+	int rc = validate_desc(desc);
+	if (rc != XNOR_B200_OK) { return rc; }
+	if (((uintptr_t)t_bit_input & 15u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
+	return launch_pack_input(*desc, pool, input, (uint32_t *)t_bit_input, (cudaStream_t)stream);
 }
 
 extern "C" int xnor_b200_repack_input_bin(const float * input, uint32_t * packed, int w, int h, int c, void * stream)

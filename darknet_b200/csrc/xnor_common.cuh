@@ -58,6 +58,8 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 // Sticky device-side status (bounded wait expired in the tensor-core kernel); synchronous copy from the device.
 int read_tc_error(int * out, bool clear);
 
-int launch_pack_input(const xnor_b200_conv_desc & d, const float * input, uint32_t * t_bit_input, cudaStream_t stream);
+// pool == nullptr: the tensor in memory is the convolution input; otherwise it is max-pooled on the fly.
+int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
+		uint32_t * t_bit_input, cudaStream_t stream);
 
 }  // namespace xnor

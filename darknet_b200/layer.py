@@ -104,12 +104,28 @@ def gemm_counts(M, N, K, A, lda, B, ldb) -> torch.Tensor:
     return counts
 
 
-def forward_convolutional_layer_gpu(l: ConvolutionalLayer, x: torch.Tensor) -> torch.Tensor:
-    """The xnor branch of forward_convolutional_layer_gpu (src-lib/convolutional_kernels.cu:204-262), whole batch."""
+def pack_input_pooled(l: ConvolutionalLayer, pool: capi.PoolDesc, x: torch.Tensor) -> torch.Tensor:
+    """pack_input of maxpool(x) without materialising the pooled tensor; x is the maxpool's input."""
+    out = torch.empty(l.batch * l.geom.n_out, l.new_lda // 8, dtype=torch.uint8, device=l.device)
+    capi.check(capi.lib().xnor_b200_pack_input_pooled(C.byref(l.desc), C.byref(pool), x.data_ptr(), out.data_ptr(), _stream()),
+               "xnor_b200_pack_input_pooled")
+    return out
+
+
+def forward_convolutional_layer_gpu(l: ConvolutionalLayer, x: torch.Tensor, pool: Optional[capi.PoolDesc] = None) -> torch.Tensor:
+    """The xnor branch of forward_convolutional_layer_gpu (src-lib/convolutional_kernels.cu:204-262), whole batch.
+    With `pool`, x is the input of a [maxpool] layer that sits directly in front of this convolution."""
     if l.align_bit_weights_gpu is None:
         raise RuntimeError("binary_align_weights() has not been called for this layer")
-    if x.dtype != torch.float32 or not x.is_contiguous() or x.numel() != l.batch * l.c * l.h * l.w:
+    expect = l.batch * l.c * (l.h * l.w if pool is None else pool.in_h * pool.in_w)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.numel() != expect:
         raise ValueError("input must be a contiguous fp32 tensor of batch*c*h*w elements")
+    if pool is not None:
+        capi.check(capi.lib().xnor_b200_conv_forward_pooled(C.byref(l.desc), C.byref(pool), x.data_ptr(), l.align_bit_weights_gpu.data_ptr(),
+                                                           l.mean_arr_gpu.data_ptr(), l.biases_gpu.data_ptr(), l.output_gpu.data_ptr(),
+                                                           _ptr(l.bin_conv_shortcut_in_gpu), _ptr(l.bin_conv_shortcut_out_gpu),
+                                                           l.scratch.data_ptr(), l.scratch.numel(), _stream()), "xnor_b200_conv_forward_pooled")
+        return l.output_gpu
     capi.check(capi.lib().xnor_b200_conv_forward(C.byref(l.desc), x.data_ptr(), l.align_bit_weights_gpu.data_ptr(),
                                                 l.mean_arr_gpu.data_ptr(), l.biases_gpu.data_ptr(), l.output_gpu.data_ptr(),
                                                 _ptr(l.bin_conv_shortcut_in_gpu), _ptr(l.bin_conv_shortcut_out_gpu),

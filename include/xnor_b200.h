@@ -153,6 +153,30 @@ XNOR_B200_API int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const
 		float * output, const float * shortcut_in, float * shortcut_out,
 		void * scratch, size_t scratch_bytes, void * stream);
 
+/* A [maxpool] layer placed directly in front of an xnor convolution (fields of src-lib/maxpool_layer.cpp:85-135:
+ * size, stride, padding; in_h/in_w = the maxpool's input, i.e. the tensor that is actually in memory).  The
+ * convolution descriptor passed with it describes the POOLED tensor: desc.h = (in_h + pad - size)/stride + 1. */
+typedef struct xnor_b200_pool_desc
+{
+	int size, stride, pad;
+	int in_h, in_w;
+} xnor_b200_pool_desc;
+
+/* forward_maxpool_layer_gpu (src-lib/maxpool_layer_kernels.cu:48-86, :107-167) followed by the input-side chain
+ * of xnor_b200_pack_input, in one kernel: the next layer only needs sign(max(window)), which is the OR of the
+ * signs of the in-image window elements, so the pooled tensor is never written or re-read.  Output identical
+ * to xnor_b200_pack_input applied to the maxpool output. */
+XNOR_B200_API int xnor_b200_pack_input_pooled(const xnor_b200_conv_desc * desc, const xnor_b200_pool_desc * pool,
+		const float * input, uint8_t * t_bit_input, void * stream);
+
+/* xnor_b200_conv_forward with the preceding [maxpool] folded into the pack kernel (see above).  Usable when
+ * nothing but this convolution reads the maxpool output (the chains conv -> maxpool -> xnor conv of the tiny
+ * networks). */
+XNOR_B200_API int xnor_b200_conv_forward_pooled(const xnor_b200_conv_desc * desc, const xnor_b200_pool_desc * pool,
+		const float * input, const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
+		float * output, const float * shortcut_in, float * shortcut_out,
+		void * scratch, size_t scratch_bytes, void * stream);
+
 /* Bytes of the library-resident scratch array behind xnor_b200_conv_forward_static. */
 #define XNOR_B200_STATIC_SCRATCH_BYTES (8u << 20)
 
