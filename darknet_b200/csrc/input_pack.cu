@@ -47,6 +47,7 @@ struct PackParams
 	// sizes the convolution sees, in_h and in_w the sizes of the tensor actually in memory.
 	int pool_size, pool_stride, pool_off;
 	int in_h, in_w;
+	int pool_fast;       // 2x2 window, stride 2, origin 0, even in_h/in_w, 8-byte aligned planes: two float2 loads
 };
 
 // sign(maxpool(x)) at pooled position (iy, ix) of one channel plane: the maximum is > 0 exactly when some
@@ -54,6 +55,13 @@ struct PackParams
 // src-lib/maxpool_layer_kernels.cu:48-86), so no maximum is ever formed.
 __device__ __forceinline__ bool pooled_positive(const float * __restrict__ plane, const PackParams & p, int iy, int ix)
 {
+	if (p.pool_fast)
+	{
+		const float2 * r0 = reinterpret_cast<const float2 *>(plane + (size_t)(2 * iy) * p.in_w) + ix;
+		const float2 a = __ldg(r0);
+		const float2 c = __ldg(r0 + (p.in_w >> 1));
+		return (a.x > 0) || (a.y > 0) || (c.x > 0) || (c.y > 0);
+	}
 	const int py0 = iy * p.pool_stride - p.pool_off;
 	const int px0 = ix * p.pool_stride - p.pool_off;
 	bool pos = false;
@@ -462,7 +470,7 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc *
 		uint32_t * t_bit_input, cudaStream_t stream)
 {
 	PackParams p;
-	p.pool_size = 0; p.pool_stride = 1; p.pool_off = 0; p.in_h = d.h; p.in_w = d.w;
+	p.pool_size = 0; p.pool_stride = 1; p.pool_off = 0; p.in_h = d.h; p.in_w = d.w; p.pool_fast = 0;
 	if (pool != nullptr)
 	{
 		if (pool->size <= 0 || pool->stride <= 0 || pool->pad < 0 || pool->in_h <= 0 || pool->in_w <= 0) { return XNOR_B200_ERR_INVALID; }
@@ -471,6 +479,8 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc *
 				|| d.w != (pool->in_w + pool->pad - pool->size) / pool->stride + 1) { return XNOR_B200_ERR_INVALID; }
 		p.pool_size = pool->size; p.pool_stride = pool->stride; p.pool_off = pool->pad / 2;
 		p.in_h = pool->in_h; p.in_w = pool->in_w;
+		p.pool_fast = (pool->size == 2 && pool->stride == 2 && pool->pad / 2 == 0 && pool->in_h % 2 == 0 && pool->in_w % 2 == 0
+				&& (((uintptr_t)input) & 7u) == 0) ? 1 : 0;
 	}
 	p.in = input;
 	p.out = t_bit_input;

@@ -79,6 +79,9 @@ class Layer:
     input_layers: List[int] = field(default_factory=list)
     # shortcut fused into the preceding xnor conv (src-lib/darknet_network.cpp:1799-1813)
     blank: bool = False
+    # maxpool whose only reader is the xnor conv right after it: folded into that conv's pack kernel
+    folded: bool = False
+    pool_desc: Optional[capi.PoolDesc] = None
     output_gpu: Optional[torch.Tensor] = None
 
     @property
@@ -95,6 +98,8 @@ class Network:
     layers: List[Layer]
     device: torch.device
     xnor_launches_per_forward: int = 0
+    folded_maxpools: int = 0
+    fold_maxpool_min_batch: int = 4
 
 
 def parse_network_cfg(path: str, batch: int = 1, device: str = "cuda:0") -> Network:
@@ -237,7 +242,28 @@ def calculate_binary_weights(net: Network) -> None:
                 sc.blank = True
                 sc.output_gpu = torch.empty(net.batch, sc.out_c, sc.out_h, sc.out_w, device=dev)
                 xl.bin_conv_shortcut_out_gpu = sc.output_gpu
+    fold_maxpools(net)
     torch.cuda.synchronize(dev)
+
+
+def fold_maxpools(net: Network) -> None:
+    """Marks every [maxpool] that only feeds the xnor convolution directly after it: the convolution then reads the
+    maxpool's input and pools while packing (xnor_b200_conv_forward_pooled), and the maxpool layer does nothing."""
+    referenced = set()
+    for l in net.layers:
+        if l.type in ("route", "shortcut"):
+            referenced.update(l.input_layers)
+    for j, l in enumerate(net.layers[:-1]):
+        nxt = net.layers[j + 1]
+        # Measured on B200: the folded kernel wins from a few images per call upwards (it reads the unpooled tensor
+        # once instead of writing and re-reading the pooled one) and only for the 2x2/stride-2 window it has a
+        # vectorised path for; at batch 1 the separate maxpool launch is cheaper than the longer pack kernel.
+        fast = l.size == 2 and l.stride == 2 and l.pad // 2 == 0 and l.h % 2 == 0 and l.w % 2 == 0
+        if (l.type == "maxpool" and j not in referenced and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None
+                and fast and net.batch >= net.fold_maxpool_min_batch):
+            l.folded = True
+            nxt.pool_desc = capi.PoolDesc(l.size, l.stride, l.pad, l.h, l.w)
+            net.folded_maxpools += 1
 
 
 # ---- forward -------------------------------------------------------------------------------------
@@ -298,11 +324,12 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
                 nxt = net.layers[l.index + 1] if l.index + 1 < len(net.layers) else None
                 if nxt is not None and nxt.blank:
                     xl.bin_conv_shortcut_in_gpu = net.layers[nxt.input_layers[0]].output_gpu
-                cur = L.forward_convolutional_layer_gpu(xl, cur)
+                cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
             else:
                 cur = _activate(F.conv2d(cur, l.weights_gpu, l.biases_gpu, l.stride, l.pad), l.activation)
         elif l.type == "maxpool":
-            cur = _maxpool(cur, l)
+            if not l.folded:                      # a folded maxpool hands its input on untouched
+                cur = _maxpool(cur, l)
         elif l.type == "route":
             cur = net.layers[l.input_layers[0]].output_gpu if len(l.input_layers) == 1 else \
                 torch.cat([net.layers[i].output_gpu for i in l.input_layers], 1)

@@ -71,3 +71,27 @@ def test_pooled_descriptor_must_match_the_convolution_input():
     x = torch.zeros(1, 32, 24, 24, device="cuda")
     with pytest.raises(capi.XnorError, match="invalid"):
         L.pack_input_pooled(l, bad, x)
+
+
+def test_network_with_folded_maxpools_equals_unfolded(tmp_path):
+    """yolov3-tiny_xnor at a reduced input size: folding the maxpools changes no output bit."""
+    from darknet_b200 import cfgs, network
+    cfg = tmp_path / "net.cfg"
+    cfg.write_text(cfgs.yolov3_tiny_xnor_cfg(96, 96))
+    net_cpu = network.parse_network_cfg(str(cfg), 2, "cpu")
+    w = tmp_path / "net.weights"
+    network.write_synthetic_weights(net_cpu, str(w), seed=5)
+    x = torch.from_numpy(synth.uniform01(9, (2, 3, 96, 96))).cuda()
+    net = network.load_network_custom(str(cfg), str(w), 2)
+    assert net.folded_maxpools == 0                     # below the batch threshold nothing is folded by default
+    net.fold_maxpool_min_batch = 1
+    network.fold_maxpools(net)
+    assert net.folded_maxpools == 5                     # the five 2x2/stride-2 pools; the stride-1 pool stays a layer
+    heads_folded = [h.clone() for h in network.forward_network_gpu(net, x)]
+    for l in net.layers:
+        l.folded = False
+        l.pool_desc = None
+    heads_plain = network.forward_network_gpu(net, x)
+    assert len(heads_folded) == 2
+    for a, b in zip(heads_folded, heads_plain):
+        assert torch.equal(a, b)
