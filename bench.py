@@ -51,6 +51,9 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="images per GPU per step (the metric is quoted at 1)")
     ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
+    ap.add_argument("--workload", default="yolov3-tiny_xnor", choices=["yolov3-tiny_xnor", "tiny-yolo_xnor", "darknet53_448_xnor"],
+                    help="network to run; the default is the configuration the metric is quoted on, the others are the "
+                         "batched BASELINE configurations (use with --batch)")
     return ap.parse_args()
 
 
@@ -212,14 +215,18 @@ def run_gpu_arm(args) -> None:
     with tempfile.TemporaryDirectory() as td:
         cfg_path, w_path = os.path.join(td, "yolov3-tiny_xnor.cfg"), os.path.join(td, "synthetic.weights")
         with open(cfg_path, "w") as fh:
-            fh.write(cfgs.yolov3_tiny_xnor_cfg())
+            fh.write(cfgs.CFGS[args.workload]())
         net0 = network.parse_network_cfg(cfg_path, batch, "cpu")
         network.write_synthetic_weights(net0, w_path, seed=1)
         net = network.load_network_custom(cfg_path, w_path, batch, str(dev))
     rows = network.xnor_layer_shapes(net)
     binops_per_image = sum(r["binops"] for r in rows)
 
-    x_host = torch.from_numpy(synth.uniform01(1 + rank, (batch, 3, 416, 416))).pin_memory()
+    default_workload = (args.workload == "yolov3-tiny_xnor")
+    workload_text = WORKLOAD if default_workload and batch == 1 else \
+        f"{args.workload} forward, {net.h}x{net.w}x3 fp32 input U[0,1), batch {batch} per GPU, seeded random weights"
+    metric_text = METRIC if default_workload else f"images/s {args.workload}@{net.h}"
+    x_host = torch.from_numpy(synth.uniform01(1 + rank, (batch, 3, net.h, net.w))).pin_memory()
     x_dev = x_host.to(dev, non_blocking=True)
     stream = torch.cuda.Stream(dev)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
@@ -281,7 +288,7 @@ def run_gpu_arm(args) -> None:
 
     # ---- roofline of the dominant kernel (XNOR GEMM), rank 0 only ----
     roofline = pack_roofline = large_roofline = cpu_baseline = None
-    if rank == 0:
+    if rank == 0 and default_workload:
         lib = capi.lib()
         xl_layers = [l.xnor_layer for l in net.layers if l.type == "convolutional" and l.xnor]
         inputs = [torch.from_numpy(synth.bell(50 + i, (batch, xl.c, xl.h, xl.w))).to(dev) for i, xl in enumerate(xl_layers)]
@@ -384,10 +391,10 @@ def run_gpu_arm(args) -> None:
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": metric_text, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "global_batch": world * batch, "parallelism": f"replicas x{world} (no collective)",
+            "config": {"workload": workload_text, "global_batch": world * batch, "folded_maxpools": net.folded_maxpools, "parallelism": f"replicas x{world} (no collective)",
                        "l2": "256 MiB buffer written between timed steps", "timing": "per-step CUDA events on the launch stream, CUDA graph replay",
                        "float_layers": "cuDNN/ATen fp32 (outside the path, as in Darknet)",
                        "xnor_binops_per_image": binops_per_image},

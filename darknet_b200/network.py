@@ -272,10 +272,20 @@ def _activate(x: torch.Tensor, a: str) -> torch.Tensor:
     if a == "linear":
         return x
     if a == "leaky":
-        return torch.where(x > 0, x, x * 0.1)
+        return F.leaky_relu(x, 0.1)
     if a == "logistic":
         return torch.sigmoid(x)
     raise ValueError(f"activation {a} not used by the xnor cfgs")
+
+
+def _float_conv_small(net: Network, l: Layer, x: torch.Tensor) -> torch.Tensor:
+    """The few-input-channel float convolution in front of the path: one fused direct-convolution kernel."""
+    import ctypes as C
+    desc = capi.ConvDesc(net.batch, l.c, l.h, l.w, l.n, l.size, l.stride, l.pad, capi.LEAKY if l.activation == "leaky" else capi.LINEAR)
+    out = torch.empty(net.batch, l.n, l.out_h, l.out_w, dtype=torch.float32, device=x.device)
+    capi.check(capi.lib().xnor_b200_float_conv_small(C.byref(desc), x.data_ptr(), l.weights_gpu.data_ptr(), l.biases_gpu.data_ptr(),
+                                                    out.data_ptr(), torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_small")
+    return out
 
 
 def _maxpool(x: torch.Tensor, l: Layer) -> torch.Tensor:
@@ -325,6 +335,8 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
                 if nxt is not None and nxt.blank:
                     xl.bin_conv_shortcut_in_gpu = net.layers[nxt.input_layers[0]].output_gpu
                 cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
+            elif l.c * l.size * l.size <= 128 and l.n <= 256 and l.activation in ("leaky", "linear"):
+                cur = _float_conv_small(net, l, cur)
             else:
                 cur = _activate(F.conv2d(cur, l.weights_gpu, l.biases_gpu, l.stride, l.pad), l.activation)
         elif l.type == "maxpool":

@@ -177,6 +177,15 @@ XNOR_B200_API int xnor_b200_conv_forward_pooled(const xnor_b200_conv_desc * desc
 		float * output, const float * shortcut_in, float * shortcut_out,
 		void * scratch, size_t scratch_bytes, void * stream);
 
+/* The float convolution in front of the path (3 input channels -> 16/32 filters in the xnor networks): the float
+ * branch of forward_convolutional_layer_gpu (src-lib/convolutional_kernels.cu:373-434, cuDNN or im2col + sgemm) +
+ * add_bias_gpu + leaky activate_array_ongpu (src-lib/activation_kernels.cu:34) as one direct-convolution kernel
+ * for layers with c*size*size <= 128.  weights [n][c*size*size] (batch-norm folded), biases [n] or NULL,
+ * output [batch][n][out_h*out_w].  fp32 throughout; sums run over (channel, ky, kx) with fused multiply-adds, so
+ * results agree with cuDNN to rounding (about 1e-6 relative), not bit for bit. */
+XNOR_B200_API int xnor_b200_float_conv_small(const xnor_b200_conv_desc * desc, const float * input, const float * weights,
+		const float * biases, float * output, void * stream);
+
 /* Bytes of the library-resident scratch array behind xnor_b200_conv_forward_static. */
 #define XNOR_B200_STATIC_SCRATCH_BYTES (8u << 20)
 

@@ -1,0 +1,41 @@
+"""The fused few-channel float convolution (layer in front of the xnor path) against cuDNN fp32."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import synth
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from darknet_b200 import capi  # noqa: E402
+
+
+@pytest.mark.parametrize("case", [
+    (2, 3, 40, 56, 16, 3, 1, 1, 1), (1, 3, 33, 17, 32, 3, 1, 1, 0), (2, 3, 20, 20, 16, 3, 2, 1, 1),
+    (1, 4, 12, 12, 8, 5, 1, 2, 1), (1, 1, 9, 9, 3, 1, 1, 0, 0), (1, 3, 416, 416, 16, 3, 1, 1, 1),
+], ids=lambda c: "b%d_c%d_%dx%d_n%d_k%d_s%d_p%d_%d" % c)
+def test_float_conv_small_matches_cudnn(case):
+    torch.backends.cudnn.allow_tf32 = False
+    batch, c, h, w, n, ks, stride, pad, leaky = case
+    x = torch.from_numpy(synth.uniform01(sum(case), (batch, c, h, w))).cuda()
+    wt = torch.from_numpy(synth.bell(sum(case) + 1, (n, c, ks, ks), 0.05)).cuda()
+    b = torch.from_numpy(synth.bell(sum(case) + 2, (n,), 0.01)).cuda()
+    want = torch.nn.functional.conv2d(x.double(), wt.double(), b.double(), stride, pad)
+    if leaky:
+        want = torch.where(want > 0, want, want * 0.1)
+    desc = capi.ConvDesc(batch, c, h, w, n, ks, stride, pad, capi.LEAKY if leaky else capi.LINEAR)
+    out = torch.full(want.shape, float("nan"), dtype=torch.float32, device="cuda")
+    capi.check(capi.lib().xnor_b200_float_conv_small(C.byref(desc), x.data_ptr(), wt.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                                    torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_small")
+    torch.cuda.synchronize()
+    # fp32 accumulation of <= 100 products of magnitude <= 0.2: absolute error far below 1e-5
+    assert torch.isfinite(out).all()
+    assert (out.double() - want).abs().max().item() <= 1e-5
+
+
+def test_float_conv_small_rejects_wide_layers():
+    desc = capi.ConvDesc(1, 64, 8, 8, 8, 3, 1, 1, capi.LINEAR)       # 576 taps
+    z = torch.zeros(8, device="cuda")
+    assert capi.lib().xnor_b200_float_conv_small(C.byref(desc), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None) == 6
