@@ -287,7 +287,7 @@ def run_gpu_arm(args) -> None:
     e2e_value = world * batch * args.steps / (ms_e2e * 1e-3)
 
     # ---- roofline of the dominant kernel (XNOR GEMM), rank 0 only ----
-    roofline = pack_roofline = large_roofline = cpu_baseline = None
+    roofline = pack_roofline = large_roofline = large_pack_roofline = cpu_baseline = None
     if rank == 0 and default_workload:
         lib = capi.lib()
         xl_layers = [l.xnor_layer for l in net.layers if l.type == "convolutional" and l.xnor]
@@ -385,6 +385,21 @@ def run_gpu_arm(args) -> None:
             "peak_source": "measured in this run: back-to-back tcgen05.mma kind::i8 128x256x32 from resident shared memory",
             "vs_int_popc_peak": big_tops / popc_peak_tops, "ms": ms_big,
         }
+        # The pack kernel of the same batch-64 layer (256 channels, 26x26, 3x3): HBM-bound, reported beside the batch-1 figure.
+        from darknet_b200 import layer as L2
+        lp = L2.make_convolutional_layer(64, 26, 26, 256, 512, 3, 1, 1, capi.LEAKY, device=str(dev))
+        xp = torch.from_numpy(synth.bell(77, (64, 256, 26, 26))).to(dev)
+        outp = torch.empty(64 * lp.geom.n_out, lp.new_lda // 8, dtype=torch.uint8, device=dev)
+
+        def big_pack():
+            capi.check(lib.xnor_b200_pack_input(C.byref(lp.desc), xp.data_ptr(), outp.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+        ms_bp = time_launches(big_pack)
+        bp_bytes = 64 * (4 * 256 * 26 * 26 + lp.geom.n_out * lp.new_lda // 8)
+        large_pack_roofline = {
+            "kernel": "pack_input_words_kernel<2,1,0>, batch 64, C=256, 26x26, 3x3", "bound": "hbm", "achieved": bp_bytes / (ms_bp * 1e-3) / 1e9,
+            "peak": hbm_peak, "unit": "GB/s", "frac": bp_bytes / (ms_bp * 1e-3) / 1e9 / hbm_peak, "traffic": None, "ms": ms_bp,
+            "peak_source": pack_roofline["peak_source"],
+        }
         if world == 1:
             ips, kind, cores, sample = time_cpu_reference(args.cpu_baseline_seconds)
             cpu_baseline = {"value": ips, "unit": "images/s", "cores": cores, "kind": kind, "sample": sample}
@@ -399,7 +414,8 @@ def run_gpu_arm(args) -> None:
                        "float_layers": "cuDNN/ATen fp32 (outside the path, as in Darknet)",
                        "xnor_binops_per_image": binops_per_image},
             "xnor_gemm_tops": roofline["achieved"] if roofline else None,
-            "roofline": roofline, "roofline_pack": pack_roofline, "roofline_large_batch": large_roofline, "cpu_baseline": cpu_baseline,
+            "roofline": roofline, "roofline_pack": pack_roofline, "roofline_large_batch": large_roofline, "roofline_pack_large_batch": large_pack_roofline,
+            "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": args.steps * net.xnor_launches_per_forward,

@@ -120,34 +120,51 @@ pack_input_words_kernel(const PackParams p)
 			uint32_t w[VEC];
 			#pragma unroll
 			for (int j = 0; j < VEC; ++j) { w[j] = 0; }
-			#pragma unroll
-			for (int ch = 0; ch < CH; ++ch)
+			if (POOL)
 			{
-				const float * q = src + (size_t)ch * chan_stride;
-				if (VEC == 4)
+				// ev = (staged row, column) of the pooled tensor; src - ev is element 0 of the first unpooled plane
+				const int rl = ev / p.W;
+				const int xl = ev - rl * p.W;
+				#pragma unroll
+				for (int ch = 0; ch < CH; ++ch)
 				{
-					const float4 v = __ldg(reinterpret_cast<const float4 *>(q));
-					w[0] |= (v.x > 0 ? 1u : 0u) << ch;
-					w[1 % VEC] |= (v.y > 0 ? 1u : 0u) << ch;
-					w[2 % VEC] |= (v.z > 0 ? 1u : 0u) << ch;
-					w[3 % VEC] |= (v.w > 0 ? 1u : 0u) << ch;
+					w[0] |= (pooled_positive(src - ev + (size_t)ch * chan_stride, p, iy_lo + rl, xl) ? 1u : 0u) << ch;
 				}
-				else if (VEC == 2)
+			}
+			else
+			{
+				// Loads are issued in explicit batches (all loads of a batch before the first compare) so that a thread
+				// keeps LB independent requests in flight; the kernel is bound by memory latency otherwise.
+				constexpr int LB = (CH < 16) ? CH : 16;
+				#pragma unroll
+				for (int ch0 = 0; ch0 < CH; ch0 += LB)
 				{
-					const float2 v = __ldg(reinterpret_cast<const float2 *>(q));
-					w[0] |= (v.x > 0 ? 1u : 0u) << ch;
-					w[1 % VEC] |= (v.y > 0 ? 1u : 0u) << ch;
-				}
-				else if (POOL)
-				{
-					// ev = (staged row, column) of the pooled tensor; q still points at element ev of an unpooled plane
-					const int rl = ev / p.W;
-					const int xl = ev - rl * p.W;
-					w[0] |= (pooled_positive(q - ev, p, iy_lo + rl, xl) ? 1u : 0u) << ch;
-				}
-				else
-				{
-					w[0] |= (__ldg(q) > 0 ? 1u : 0u) << ch;
+					float v[LB][VEC];
+					#pragma unroll
+					for (int u = 0; u < LB; ++u)
+					{
+						const float * q = src + (size_t)(ch0 + u) * chan_stride;
+						if (VEC == 4)
+						{
+							const float4 t = __ldg(reinterpret_cast<const float4 *>(q));
+							v[u][0] = t.x; v[u][1 % VEC] = t.y; v[u][2 % VEC] = t.z; v[u][3 % VEC] = t.w;
+						}
+						else if (VEC == 2)
+						{
+							const float2 t = __ldg(reinterpret_cast<const float2 *>(q));
+							v[u][0] = t.x; v[u][1 % VEC] = t.y;
+						}
+						else
+						{
+							v[u][0] = __ldg(q);
+						}
+					}
+					#pragma unroll
+					for (int u = 0; u < LB; ++u)
+					{
+						#pragma unroll
+						for (int j = 0; j < VEC; ++j) { w[j] |= (v[u][j] > 0 ? 1u : 0u) << (ch0 + u); }
+					}
 				}
 			}
 			if (SUBS == 1)
@@ -540,7 +557,7 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc *
 				: ((d.w % 2 == 0) && (((uintptr_t)input & 7u) == 0)) ? 2 : 1;
 		// words per CTA in phase A; below two per thread the channel split keeps more threads busy
 		const long long words_per_cta = (long long)cb_per_cta * min(in_rows(rows), d.h) * d.w;
-		const bool split = words_per_cta < 2LL * PK_THREADS * vec;
+		const bool split = words_per_cta < (long long)PK_THREADS * vec;
 		void (*kern)(const PackParams) =
 				vec == 4 ? (split ? pack_input_words_kernel<4, 4> : pack_input_words_kernel<4, 1>)
 				: vec == 2 ? (split ? pack_input_words_kernel<2, 4> : pack_input_words_kernel<2, 1>)
