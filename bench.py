@@ -381,7 +381,9 @@ def run_gpu_arm(args) -> None:
         big_tops = 2.0 * M_ * N_ * K_ / (ms_big * 1e-3) / 1e12
         large_roofline = {
             "kernel": "xnor_gemm_tc_kernel<256> (tcgen05 kind::i8), M=512 N=64x676 K=2304", "bound": "tensor", "achieved": big_tops,
-            "peak": umma_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": big_tops / umma_peak_tops, "traffic": None,
+            "peak": umma_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": big_tops / umma_peak_tops,
+            # dram read + write of one launch of this shape, ncu capture summarised in profiles/xnor_gemm_tc_kernel_m512_n43264_k2304.md
+            "traffic": 44.41e6,
             "peak_source": "measured in this run: back-to-back tcgen05.mma kind::i8 128x256x32 from resident shared memory",
             "vs_int_popc_peak": big_tops / popc_peak_tops, "ms": ms_big,
         }
@@ -397,7 +399,9 @@ def run_gpu_arm(args) -> None:
         bp_bytes = 64 * (4 * 256 * 26 * 26 + lp.geom.n_out * lp.new_lda // 8)
         large_pack_roofline = {
             "kernel": "pack_input_words_kernel<2,1,0>, batch 64, C=256, 26x26, 3x3", "bound": "hbm", "achieved": bp_bytes / (ms_bp * 1e-3) / 1e9,
-            "peak": hbm_peak, "unit": "GB/s", "frac": bp_bytes / (ms_bp * 1e-3) / 1e9 / hbm_peak, "traffic": None, "ms": ms_bp,
+            "peak": hbm_peak, "unit": "GB/s", "frac": bp_bytes / (ms_bp * 1e-3) / 1e9 / hbm_peak,
+            # dram read + write of one launch, ncu capture summarised in profiles/pack_input_words_kernel_b64_c256_26x26.md
+            "traffic": 44.41e6, "ms": ms_bp,
             "peak_source": pack_roofline["peak_source"],
         }
         if world == 1:
