@@ -2,8 +2,8 @@
 //
 // tcgen05.mma has no 1-bit operand kind, and the legacy mma.sync b1 path measures slower than the integer
 // pipe on this GPU.  A binary dot product is nevertheless an integer GEMM: with both operands expanded to
-// bytes holding 0 or 1,
-//     D[j][i] = sum_k b_jk * a_ik = popc(B_j & A_i)            (kind::i8, u8 x u8 -> s32, exact)
+// signed bytes holding 0 or -1,
+//     D[j][i] = sum_k b_jk * a_ik = popc(B_j & A_i)            (kind::i8, s8 x s8 -> s32, exact)
 //     agreeing bits = K - popc(A_i) - popc(B_j) + 2 * D[j][i]
 // so the packed operands stay 1 bit per element in HBM and L2 (the same buffers the integer-pipe kernel reads)
 // and are widened to bytes only inside shared memory, next to the tensor core that consumes them.
@@ -87,14 +87,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t * bar, uint32_t parity, volat
 	return false;
 }
 
-// 16 bits -> 16 bytes of 0/1 (bit j -> byte j).  (x & 15) * 0x204081 puts bit j of the nibble at bit 8j.
+// 16 bits -> 16 bytes, each 0x00 (bit clear) or 0xFF (bit set), with one byte-permute per 4 bytes: PRMT picks
+// every output byte from an 8-byte pool by a 4-bit selector taken from the packed word itself.  The pool
+// alternates 0x00, 0xFF, so only the selector's lowest bit matters, and since 0x00 / 0xFF are their own sign
+// replication the selector's mode bit does not matter either: no masking is needed.  Word q of the result holds
+// bits q, q+4, q+8, q+12 of the group -- a permutation of K inside the 16-byte chunk that is applied identically to
+// both operands and therefore leaves every dot product unchanged.  As signed bytes the values are 0 and -1, and
+// (-1)*(-1) = +1, so the s8 x s8 -> s32 MMA still accumulates popc(a & b).
 __device__ __forceinline__ uint4 expand16(uint32_t bits)
 {
+	constexpr uint32_t POOL = 0xFF00FF00u;
 	uint4 v;
-	v.x = ((bits & 15u) * 0x204081u) & 0x01010101u;
-	v.y = (((bits >> 4) & 15u) * 0x204081u) & 0x01010101u;
-	v.z = (((bits >> 8) & 15u) * 0x204081u) & 0x01010101u;
-	v.w = (((bits >> 12) & 15u) * 0x204081u) & 0x01010101u;
+	v.x = __byte_perm(POOL, POOL, bits);
+	v.y = __byte_perm(POOL, POOL, bits >> 1);
+	v.z = __byte_perm(POOL, POOL, bits >> 2);
+	v.w = __byte_perm(POOL, POOL, bits >> 3);
 	return v;
 }
 
@@ -146,9 +153,8 @@ xnor_gemm_tc_kernel(const TcParams p)
 	__shared__ uint64_t bar_empty[TC_STAGES];
 	__shared__ uint64_t bar_done;
 	__shared__ uint32_t tmem_base_slot;
-	__shared__ int s_pop[S::ROWS];
-	__shared__ float s_mean[NF];
-	__shared__ float s_bias[NF];
+	__shared__ int s_pop[TC_PIX];                            // popc of every pixel row
+	__shared__ int4 s_fil[NF];                               // per filter: {-2 popc(row), mean bits, bias bits, 0}
 	__shared__ int s_failed_storage;
 	volatile int * s_failed = &s_failed_storage;
 
@@ -179,12 +185,6 @@ xnor_gemm_tc_kernel(const TcParams p)
 				:: "r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)NF) : "memory");
 		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 	}
-	for (int i = tid; i < NF; i += S::THREADS)
-	{
-		const int f = f0 + i;
-		s_mean[i] = (f < p.M && p.mean_arr != nullptr) ? __ldg(p.mean_arr + f) : 0.0f;
-		s_bias[i] = (f < p.M && p.bias != nullptr) ? __ldg(p.bias + f) : 0.0f;
-	}
 	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 	__syncthreads();
 	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -195,8 +195,8 @@ xnor_gemm_tc_kernel(const TcParams p)
 		// ---- MMA issuer -------------------------------------------------------------------------
 		if (lane == 0)
 		{
-			// instruction descriptor: D = s32, A = B = u8, both K-major, N = NF, M = 128
-			const uint32_t idesc = (2u << 4) | ((uint32_t)(NF >> 3) << 17) | ((uint32_t)(TC_PIX >> 4) << 24);
+			// instruction descriptor: D = s32, A = B = s8, both K-major, N = NF, M = 128
+			const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NF >> 3) << 17) | ((uint32_t)(TC_PIX >> 4) << 24);
 			bool ok = true;
 			for (int kb = 0; kb < p.kblocks && ok; ++kb)
 			{
@@ -270,7 +270,17 @@ xnor_gemm_tc_kernel(const TcParams p)
 			__syncwarp();
 			if (lane == 0) { mbar_arrive(&bar_full[s]); }
 		}
-		s_pop[r] = pop;
+		if (is_pix)
+		{
+			s_pop[row_in_tile] = pop;
+		}
+		else
+		{
+			const int f = f0 + row_in_tile;
+			const float mean = (f < p.M && p.mean_arr != nullptr) ? __ldg(p.mean_arr + f) : 0.0f;
+			const float bias = (f < p.M && p.bias != nullptr) ? __ldg(p.bias + f) : 0.0f;
+			s_fil[row_in_tile] = make_int4(-2 * pop, __float_as_int(mean), __float_as_int(bias), 0);
+		}
 	}
 
 	// ---- everyone: wait for the accumulators ----------------------------------------------------------
@@ -292,7 +302,12 @@ xnor_gemm_tc_kernel(const TcParams p)
 		const bool col_ok = col < p.n_total;
 		const int img = col_ok ? col / p.n_per_image : 0;
 		const int pix = col_ok ? col - img * p.n_per_image : 0;
-		const int pop_b = s_pop[pix_local];
+		const int k_b = p.K - 2 * s_pop[pix_local];
+		const bool has_bias = (p.bias != nullptr);
+		const size_t pix_off = ((size_t)img * p.M + f0) * p.ldc + pix;    // element (first filter of the tile, this pixel)
+		float * c_pix = (p.C != nullptr) ? p.C + pix_off : nullptr;
+		float * sc_out = (p.shortcut_out != nullptr) ? p.shortcut_out + pix_off : nullptr;
+		const float * sc_in = (p.shortcut_in != nullptr) ? p.shortcut_in + pix_off : nullptr;
 		#pragma unroll 1
 		for (int chunk = share; chunk < NF / 32; chunk += SHARES)
 		{
@@ -308,31 +323,35 @@ xnor_gemm_tc_kernel(const TcParams p)
 				  "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
 				: "r"(taddr) : "memory");
 			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-			if (col_ok)
+			if (!col_ok) { continue; }
+			const int fbase = chunk * 32;
+			if (p.counts != nullptr)
 			{
 				#pragma unroll
 				for (int j = 0; j < 32; ++j)
 				{
-					const int fl = chunk * 32 + j;            // filter within the tile
-					const int f = f0 + fl;
-					if (f < p.M)
+					if (f0 + fbase + j < p.M)
 					{
 						// agreeing bits among the first K
-						const int count = p.K - s_pop[TC_PIX + fl] - pop_b + 2 * (int)d[j];
-						if (p.counts != nullptr)
-						{
-							p.counts[(size_t)f * p.n_total + col] = count;
-						}
-						else
-						{
-							const size_t idx = ((size_t)img * p.M + f) * p.ldc + pix;
-							float v = __fmul_rn((float)(2 * count - p.K), s_mean[fl]);
-							if (p.bias != nullptr) { v = __fadd_rn(v, s_bias[fl]); }
-							if (p.leaky) { v = (v < 0.0f) ? __fmul_rn(v, 0.1f) : v; }
-							p.C[idx] = v;
-							if (p.shortcut_out != nullptr) { p.shortcut_out[idx] = __fadd_rn(__ldg(p.shortcut_in + idx), v); }
-						}
+						p.counts[(size_t)(f0 + fbase + j) * p.n_total + col] = (k_b + s_fil[fbase + j].x + 4 * (int)d[j] + p.K) >> 1;
 					}
+				}
+				continue;
+			}
+			float * out = c_pix + (size_t)fbase * p.ldc;
+			#pragma unroll
+			for (int j = 0; j < 32; ++j)
+			{
+				if (f0 + fbase + j < p.M)
+				{
+					const int4 fi = s_fil[fbase + j];                  // one broadcast 16-byte read per filter
+					// 2*agree - K = (K - 2 popc(b)) - 2 popc(a) + 4 popc(a & b)
+					const int dot = k_b + fi.x + 4 * (int)d[j];
+					float v = __fmul_rn((float)dot, __int_as_float(fi.y));
+					if (has_bias) { v = __fadd_rn(v, __int_as_float(fi.z)); }
+					if (p.leaky) { v = (v < 0.0f) ? __fmul_rn(v, 0.1f) : v; }
+					out[(size_t)j * p.ldc] = v;
+					if (sc_out != nullptr) { sc_out[(size_t)(fbase + j) * p.ldc] = __fadd_rn(__ldg(sc_in + (size_t)(fbase + j) * p.ldc), v); }
 				}
 			}
 		}
