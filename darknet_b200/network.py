@@ -293,8 +293,13 @@ def _maxpool(x: torch.Tensor, l: Layer) -> torch.Tensor:
     lo = l.pad // 2
     need_h = (l.out_h - 1) * l.stride + l.size - lo
     need_w = (l.out_w - 1) * l.stride + l.size - lo
-    x = F.pad(x, (lo, max(need_w - l.w, 0), lo, max(need_h - l.h, 0)), value=float("-inf"))
-    return F.max_pool2d(x, l.size, l.stride)[:, :, :l.out_h, :l.out_w]
+    hi_w, hi_h = max(need_w - l.w, 0), max(need_h - l.h, 0)
+    if lo or hi_w or hi_h:                                       # the common 2x2/stride-2 pool of an even map needs none
+        x = F.pad(x, (lo, hi_w, lo, hi_h), value=float("-inf"))
+    y = F.max_pool2d(x, l.size, l.stride)
+    if y.shape[2] != l.out_h or y.shape[3] != l.out_w:
+        y = y[:, :, :l.out_h, :l.out_w].contiguous()
+    return y
 
 
 def _yolo(x: torch.Tensor, l: Layer) -> torch.Tensor:
@@ -302,6 +307,11 @@ def _yolo(x: torch.Tensor, l: Layer) -> torch.Tensor:
     mask = [int(v) for v in l.opts["mask"].split(",")]
     classes = int(l.opts.get("classes", 20))
     b = x.shape[0]
+    if x.is_cuda and x.is_contiguous() and float(l.opts.get("scale_x_y", 1)) == 1.0:
+        out = torch.empty_like(x)
+        capi.check(capi.lib().xnor_b200_yolo_activate(x.data_ptr(), out.data_ptr(), b, len(mask), classes, l.h * l.w,
+                                                     torch.cuda.current_stream().cuda_stream), "xnor_b200_yolo_activate")
+        return out
     v = x.reshape(b, len(mask), 5 + classes, l.h * l.w).clone()
     v[:, :, 0:2] = torch.sigmoid(v[:, :, 0:2])
     v[:, :, 4:] = torch.sigmoid(v[:, :, 4:])
@@ -337,6 +347,12 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
                 cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
             elif l.c * l.size * l.size <= 128 and l.n <= 256 and l.activation in ("leaky", "linear"):
                 cur = _float_conv_small(net, l, cur)
+            elif l.size == 1 and l.stride == 1 and l.pad == 0:
+                # a 1x1 convolution is a plain matrix product per image (cuBLAS sgemm, fp32)
+                b = cur.shape[0]
+                y = torch.baddbmm(l.biases_gpu.view(1, l.n, 1), l.weights_gpu.view(1, l.n, l.c).expand(b, -1, -1),
+                                  cur.reshape(b, l.c, l.h * l.w))
+                cur = _activate(y.view(b, l.n, l.out_h, l.out_w), l.activation)
             else:
                 cur = _activate(F.conv2d(cur, l.weights_gpu, l.biases_gpu, l.stride, l.pad), l.activation)
         elif l.type == "maxpool":

@@ -186,6 +186,11 @@ XNOR_B200_API int xnor_b200_conv_forward_pooled(const xnor_b200_conv_desc * desc
 XNOR_B200_API int xnor_b200_float_conv_small(const xnor_b200_conv_desc * desc, const float * input, const float * weights,
 		const float * biases, float * output, void * stream);
 
+/* The activation step of forward_yolo_layer_gpu (src-lib/yolo_layer.cpp:1439-1489) behind the path: logistic on the
+ * x, y, objectness and class entries of every anchor, w and h raw, in one pass.  input/output
+ * [batch][anchors][4 + 1 + classes][hw] (may be the same pointer).  Box decoding and NMS stay on the host side. */
+XNOR_B200_API int xnor_b200_yolo_activate(const float * input, float * output, int batch, int anchors, int classes, int hw, void * stream);
+
 /* Bytes of the library-resident scratch array behind xnor_b200_conv_forward_static. */
 #define XNOR_B200_STATIC_SCRATCH_BYTES (8u << 20)
 

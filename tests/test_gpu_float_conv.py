@@ -39,3 +39,16 @@ def test_float_conv_small_rejects_wide_layers():
     desc = capi.ConvDesc(1, 64, 8, 8, 8, 3, 1, 1, capi.LINEAR)       # 576 taps
     z = torch.zeros(8, device="cuda")
     assert capi.lib().xnor_b200_float_conv_small(C.byref(desc), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None) == 6
+
+
+def test_yolo_activate_matches_elementwise_definition():
+    b, anchors, classes, hw = 2, 3, 80, 13 * 13
+    x = torch.from_numpy(synth.bell(3, (b, anchors * (5 + classes), 13, 13), 3.0)).cuda()
+    out = torch.empty_like(x)
+    capi.check(capi.lib().xnor_b200_yolo_activate(x.data_ptr(), out.data_ptr(), b, anchors, classes, hw, None), "yolo")
+    torch.cuda.synchronize()
+    v = x.reshape(b, anchors, 5 + classes, hw).clone()
+    v[:, :, 0:2] = torch.sigmoid(v[:, :, 0:2])
+    v[:, :, 4:] = torch.sigmoid(v[:, :, 4:])
+    assert torch.equal(out.reshape(v.shape)[:, :, 2:4], x.reshape(v.shape)[:, :, 2:4])
+    assert (out.reshape(v.shape) - v).abs().max().item() <= 1e-6
