@@ -24,7 +24,7 @@ EXPORTS = (
     "xnor_b200_repack_input_bin", "xnor_b200_pack_input", "xnor_b200_gemm_bin_mean_transposed",
     "xnor_b200_gemm_counts", "xnor_b200_scratch_bytes", "xnor_b200_conv_forward",
     "xnor_b200_conv_forward_static", "xnor_b200_take_device_status",
-    "xnor_b200_pack_input_pooled", "xnor_b200_conv_forward_pooled", "xnor_b200_float_conv_small", "xnor_b200_yolo_activate",
+    "xnor_b200_pack_input_pooled", "xnor_b200_conv_forward_pooled", "xnor_b200_float_conv_small", "xnor_b200_yolo_activate", "xnor_b200_conv_forward_io",
     "xnor_b200_measure_popc_peak", "xnor_b200_measure_bmma_peak", "xnor_b200_measure_umma_i8_peak",
 )
 
@@ -37,6 +37,12 @@ class ConvDesc(C.Structure):
 class PoolDesc(C.Structure):
     """struct xnor_b200_pool_desc"""
     _fields_ = [(n, C.c_int) for n in ("size", "stride", "pad", "in_h", "in_w")]
+
+
+class ConvIO(C.Structure):
+    """struct xnor_b200_conv_io"""
+    _fields_ = [("input", C.c_void_p), ("input_signs", C.c_void_p), ("pool", C.POINTER(PoolDesc)), ("output", C.c_void_p),
+                ("output_signs", C.c_void_p), ("shortcut_in", C.c_void_p), ("shortcut_out", C.c_void_p)]
 
 
 class ConvGeom(C.Structure):
@@ -88,6 +94,7 @@ def lib() -> C.CDLL:
     L.xnor_b200_conv_forward_pooled.argtypes = [dp, pp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
     L.xnor_b200_float_conv_small.argtypes = [dp, vp, vp, vp, vp, vp]
     L.xnor_b200_yolo_activate.argtypes = [vp, vp, ci, ci, ci, ci, vp]
+    L.xnor_b200_conv_forward_io.argtypes = [dp, C.POINTER(ConvIO), vp, vp, vp, vp, sz, vp]
     L.xnor_b200_conv_forward_static.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
     L.xnor_b200_take_device_status.argtypes = [C.POINTER(ci)]
     L.xnor_b200_measure_popc_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]

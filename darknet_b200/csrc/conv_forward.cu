@@ -124,10 +124,13 @@ extern "C" size_t xnor_b200_scratch_bytes(const xnor_b200_conv_desc * desc)
 static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_pool_desc * pool, const float * input,
 		const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
 		float * output, const float * shortcut_in, float * shortcut_out,
-		void * scratch, size_t scratch_bytes, void * stream)
+		void * scratch, size_t scratch_bytes, void * stream,
+		const uint32_t * input_signs = nullptr, uint32_t * output_signs = nullptr)
 {
-	if (desc == nullptr || input == nullptr || align_bit_weights == nullptr || mean_arr == nullptr
-			|| output == nullptr || scratch == nullptr) { return XNOR_B200_ERR_NULL; }
+	if (desc == nullptr || align_bit_weights == nullptr || mean_arr == nullptr || scratch == nullptr) { return XNOR_B200_ERR_NULL; }
+	if ((input == nullptr) == (input_signs == nullptr) || (output == nullptr) == (output_signs == nullptr)) { return XNOR_B200_ERR_NULL; }
+	if (output_signs != nullptr && (shortcut_out != nullptr || desc->n % 32 != 0)) { return XNOR_B200_ERR_INVALID; }
+	if (input_signs != nullptr && desc->c % 32 != 0) { return XNOR_B200_ERR_INVALID; }
 	xnor_b200_conv_geom g;
 	int rc = xnor_b200_conv_geometry(desc, &g);
 	if (rc != XNOR_B200_OK) { return rc; }
@@ -136,12 +139,23 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_p
 	if (shortcut_out != nullptr && shortcut_in == nullptr) { return XNOR_B200_ERR_NULL; }
 
 	cudaStream_t s = (cudaStream_t)stream;
-	rc = launch_pack_input(*desc, pool, input, (uint32_t *)scratch, s);
+	rc = (input_signs != nullptr)
+			? launch_pack_input(*desc, pool, reinterpret_cast<const float *>(input_signs), (uint32_t *)scratch, s, 1)
+			: launch_pack_input(*desc, pool, input, (uint32_t *)scratch, s, 0);
 	if (rc != XNOR_B200_OK) { return rc; }
 	return launch_xnor_gemm(desc->n, desc->batch * g.n_out, g.n_out, g.k,
 			(const uint32_t *)align_bit_weights, g.new_lda / 32, (const uint32_t *)scratch, g.new_lda / 32,
 			output, g.n_out, mean_arr, biases, desc->activation == XNOR_B200_LEAKY,
-			shortcut_in, shortcut_out, nullptr, s);
+			shortcut_in, shortcut_out, nullptr, s, output_signs);
+}
+
+extern "C" int xnor_b200_conv_forward_io(const xnor_b200_conv_desc * desc, const xnor_b200_conv_io * io,
+		const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
+		void * scratch, size_t scratch_bytes, void * stream)
+{
+	if (io == nullptr) { return XNOR_B200_ERR_NULL; }
+	return conv_forward_impl(desc, io->pool, io->input, align_bit_weights, mean_arr, biases, io->output,
+			io->shortcut_in, io->shortcut_out, scratch, scratch_bytes, stream, io->input_signs, io->output_signs);
 }
 
 extern "C" int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const float * input,

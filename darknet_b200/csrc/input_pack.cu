@@ -78,6 +78,71 @@ __device__ __forceinline__ bool pooled_positive(const float * __restrict__ plane
 	return pos;
 }
 
+// Phase B of the word path, shared by the kernels that stage channel-packed words in shared memory: assembles the
+// packed rows of output rows y0..y1-1 for the channel blocks cb0..cb0+cbn-1 (group g) from s_words[cbl][R][W].
+__device__ __forceinline__ void words_phase_b(const PackParams & p, uint32_t * s_words, int b, int g, int y0, int y1,
+		int iy_lo, int R, int CB, int cb0, int cbn)
+{
+	// phase B: one uint4 (4 K-words) per thread-iteration over this CTA's word range.
+	// A small table maps every K-word of the range to (offset inside the staged rows, ky, kx) once per CTA, so
+	// the per-word work is a table read, two bounds checks and one shared load -- no integer division.
+	const int taps = p.ks * p.ks;
+	const int new_k = CB * taps;
+	const bool last_group = (g == p.groups - 1);
+	const int q_lo = (cb0 * taps) >> 2;                                   // cb0 % 4 == 0 whenever groups > 1
+	const int q_hi = last_group ? (p.ldw >> 2) : (((cb0 + cbn) * taps) >> 2);
+	const int nq = q_hi - q_lo;
+	uint32_t * s_tab = s_words + p.tab_offset;                            // nq*4 entries: off | ky << 20 | kx << 26
+	for (int i = threadIdx.x; i < nq * 4; i += PK_THREADS)
+	{
+		const int wi = q_lo * 4 + i;
+		uint32_t e = 0xffffffffu;                                         // padding word
+		if (wi < new_k)
+		{
+			const int cb = wi / taps;
+			const int t = wi - cb * taps;
+			const int ky = t / p.ks;
+			const int kx = t - ky * p.ks;
+			e = (uint32_t)(((cb - cb0) * R + ky) * p.W + kx) | ((uint32_t)ky << 20) | ((uint32_t)kx << 26);
+		}
+		s_tab[i] = e;
+	}
+	__syncthreads();
+
+	const int pixels = (y1 - y0) * p.OW;
+	const size_t row_base = (size_t)b * p.OH * p.OW + (size_t)y0 * p.OW;
+	const int lpp = 1 << p.lpp_shift;                                     // lanes per pixel: power of two >= min(nq, 32)
+	const int wq_first = threadIdx.x & (lpp - 1);
+	for (int pl = threadIdx.x >> p.lpp_shift; pl < pixels; pl += PK_THREADS >> p.lpp_shift)
+	{
+		const int yl = pl / p.OW;
+		const int x = pl - yl * p.OW;
+		const int iy_base = (y0 + yl) * p.stride - p.pad - iy_lo;   // relative to the staged rows
+		const int ix_base = x * p.stride - p.pad;
+		const int base_off = iy_base * p.W + ix_base;
+		uint4 * dst = reinterpret_cast<uint4 *>(p.out + (row_base + pl) * p.ldw) + q_lo;
+		for (int wq = wq_first; wq < nq; wq += lpp)
+		{
+			const uint4 e4 = reinterpret_cast<const uint4 *>(s_tab)[wq];
+			const uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
+			uint32_t v[4];
+			#pragma unroll
+			for (int u = 0; u < 4; ++u)
+			{
+				uint32_t word = 0;
+				if (e[u] != 0xffffffffu)
+				{
+					const int r = iy_base + (int)((e[u] >> 20) & 63u);
+					const int ix = ix_base + (int)(e[u] >> 26);
+					if (r >= 0 && r < R && ix >= 0 && ix < p.W) { word = s_words[base_off + (int)(e[u] & 0xfffffu)]; }
+				}
+				v[u] = word;
+			}
+			dst[wq] = make_uint4(v[0], v[1], v[2], v[3]);
+		}
+	}
+}
+
 // ---- word path -----------------------------------------------------------------------------
 // shared: packed[cb_local][R][W] words, R = input rows of this strip.
 // VEC  = floats per load (4, 2 or 1, as the row pitch and pointer alignment allow);
@@ -183,64 +248,63 @@ pack_input_words_kernel(const PackParams p)
 	}
 	__syncthreads();
 
-	// phase B: one uint4 (4 K-words) per thread-iteration over this CTA's word range.
-	// A small table maps every K-word of the range to (offset inside the staged rows, ky, kx) once per CTA, so
-	// the per-word work is a table read, two bounds checks and one shared load -- no integer division.
-	const int taps = p.ks * p.ks;
-	const int new_k = CB * taps;
-	const bool last_group = (g == p.groups - 1);
-	const int q_lo = (cb0 * taps) >> 2;                                   // cb0 % 4 == 0 whenever groups > 1
-	const int q_hi = last_group ? (p.ldw >> 2) : (((cb0 + cbn) * taps) >> 2);
-	const int nq = q_hi - q_lo;
-	uint32_t * s_tab = s_words + p.tab_offset;                            // nq*4 entries: off | ky << 20 | kx << 26
-	for (int i = threadIdx.x; i < nq * 4; i += PK_THREADS)
+	words_phase_b(p, s_words, b, g, y0, y1, iy_lo, R, CB, cb0, cbn);
+}
+
+// The same packing when the previous xnor layer already left its output as sign bits, 32 channels per word
+// ([image][C/32][in_h*in_w], written by the sign-only GEMM epilogue): phase A is a copy of words -- or, with a
+// max-pool in between, the OR of the window's words, because sign(max) is the OR of the signs.  The fp32
+// activation tensor and the pooled tensor are never written.
+__global__ void __launch_bounds__(PK_THREADS)
+pack_input_from_signs_kernel(const PackParams p)
+{
+	extern __shared__ uint32_t s_words[];
+	const int g = blockIdx.x % p.groups;
+	const int rest = blockIdx.x / p.groups;
+	const int tile = rest % p.tiles_per_image;
+	const int b = rest / p.tiles_per_image;
+	const int y0 = tile * p.rows_per_cta;
+	const int y1 = min(y0 + p.rows_per_cta, p.OH);
+	const int iy_lo = max(y0 * p.stride - p.pad, 0);
+	const int iy_hi = min((y1 - 1) * p.stride - p.pad + p.ks - 1, p.H - 1);
+	const int R = iy_hi - iy_lo + 1;
+	const int CB = p.C >> 5;
+	const int cb0 = g * p.cb_per_cta;
+	const int cbn = min(p.cb_per_cta, CB - cb0);
+	const int span = max(R, 0) * p.W;
+	const size_t plane = (size_t)p.in_h * p.in_w;
+	const uint32_t * bits = reinterpret_cast<const uint32_t *>(p.in) + ((size_t)b * CB + cb0) * plane;
+	for (int idx = threadIdx.x; idx < cbn * span; idx += PK_THREADS)
 	{
-		const int wi = q_lo * 4 + i;
-		uint32_t e = 0xffffffffu;                                         // padding word
-		if (wi < new_k)
+		const int cbl = idx / span;
+		const int e = idx - cbl * span;
+		const uint32_t * src = bits + (size_t)cbl * plane;
+		uint32_t word = 0;
+		if (p.pool_size == 0)
 		{
-			const int cb = wi / taps;
-			const int t = wi - cb * taps;
-			const int ky = t / p.ks;
-			const int kx = t - ky * p.ks;
-			e = (uint32_t)(((cb - cb0) * R + ky) * p.W + kx) | ((uint32_t)ky << 20) | ((uint32_t)kx << 26);
+			word = __ldg(src + (size_t)iy_lo * p.W + e);
 		}
-		s_tab[i] = e;
+		else
+		{
+			const int rl = e / p.W;
+			const int xl = e - rl * p.W;
+			const int py0 = (iy_lo + rl) * p.pool_stride - p.pool_off;
+			const int px0 = xl * p.pool_stride - p.pool_off;
+			for (int l = 0; l < p.pool_size; ++l)
+			{
+				const int yy = py0 + l;
+				if (yy < 0 || yy >= p.in_h) { continue; }
+				for (int m = 0; m < p.pool_size; ++m)
+				{
+					const int xx = px0 + m;
+					if (xx >= 0 && xx < p.in_w) { word |= __ldg(src + (size_t)yy * p.in_w + xx); }
+				}
+			}
+		}
+		s_words[idx] = word;
 	}
 	__syncthreads();
-
-	const int pixels = (y1 - y0) * p.OW;
-	const size_t row_base = (size_t)b * p.OH * p.OW + (size_t)y0 * p.OW;
-	const int lpp = 1 << p.lpp_shift;                                     // lanes per pixel: power of two >= min(nq, 32)
-	const int wq_first = threadIdx.x & (lpp - 1);
-	for (int pl = threadIdx.x >> p.lpp_shift; pl < pixels; pl += PK_THREADS >> p.lpp_shift)
-	{
-		const int yl = pl / p.OW;
-		const int x = pl - yl * p.OW;
-		const int iy_base = (y0 + yl) * p.stride - p.pad - iy_lo;   // relative to the staged rows
-		const int ix_base = x * p.stride - p.pad;
-		const int base_off = iy_base * p.W + ix_base;
-		uint4 * dst = reinterpret_cast<uint4 *>(p.out + (row_base + pl) * p.ldw) + q_lo;
-		for (int wq = wq_first; wq < nq; wq += lpp)
-		{
-			const uint4 e4 = reinterpret_cast<const uint4 *>(s_tab)[wq];
-			const uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
-			uint32_t v[4];
-			#pragma unroll
-			for (int u = 0; u < 4; ++u)
-			{
-				uint32_t word = 0;
-				if (e[u] != 0xffffffffu)
-				{
-					const int r = iy_base + (int)((e[u] >> 20) & 63u);
-					const int ix = ix_base + (int)(e[u] >> 26);
-					if (r >= 0 && r < R && ix >= 0 && ix < p.W) { word = s_words[base_off + (int)(e[u] & 0xfffffu)]; }
-				}
-				v[u] = word;
-			}
-			dst[wq] = make_uint4(v[0], v[1], v[2], v[3]);
-		}
-	}
+	words_phase_b(p, s_words, b, g, y0, y1, iy_lo, R, CB, cb0, cbn);
 }
 
 // Phase A of the bit kernels: planes[c][rr][xw] = ballot of (input(c, iy0 + rr, 32*xw + lane - pad) > 0).
@@ -484,8 +548,9 @@ float_to_bit_kernel(const float * __restrict__ src, uint32_t * __restrict__ dst,
 }
 
 int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
-		uint32_t * t_bit_input, cudaStream_t stream)
+		uint32_t * t_bit_input, cudaStream_t stream, int from_signs)
 {
+	if (from_signs && d.c % 32 != 0) { return XNOR_B200_ERR_INVALID; }
 	PackParams p;
 	p.pool_size = 0; p.pool_stride = 1; p.pool_off = 0; p.in_h = d.h; p.in_w = d.w; p.pool_fast = 0;
 	if (pool != nullptr)
@@ -563,6 +628,7 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc *
 				: vec == 2 ? (split ? pack_input_words_kernel<2, 4> : pack_input_words_kernel<2, 1>)
 				: (pool != nullptr) ? (split ? pack_input_words_kernel<1, 4, true> : pack_input_words_kernel<1, 1, true>)
 				: (split ? pack_input_words_kernel<1, 4> : pack_input_words_kernel<1, 1>);
+		if (from_signs) { kern = pack_input_from_signs_kernel; }
 		int rc = ensure_dynamic_smem((const void *)kern, smem > 48 * 1024 ? PK_MAX_SMEM : 0);
 		if (rc != XNOR_B200_OK) { return rc; }
 		kern<<<(unsigned)grid, PK_THREADS, smem, stream>>>(p);

@@ -42,24 +42,27 @@ int ensure_dynamic_smem(const void * kernel, size_t bytes);
 
 // Internal launchers shared between translation units --------------------------------------
 
+// signs != nullptr: instead of C, only the sign bits of the output are written, 32 filters per word, laid out
+// [image][M/32][pixel] (requires M % 32 == 0).
 // GEMM with the batch folded into the column index: column j = b*n_per_image + p is written to
 // C[(b*M + i)*ldc + p].  counts != nullptr selects the integer-accumulator output instead of C.
 int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
-		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream);
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs = nullptr);
 
 // Tensor-core (tcgen05, kind::i8 on bytes expanded in shared memory) variant of the same GEMM for large layers.
 bool tc_gemm_eligible(int M, int n_total, int K);
 int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
-		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream);
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs = nullptr);
 // Sticky device-side status (bounded wait expired in the tensor-core kernel); synchronous copy from the device.
 int read_tc_error(int * out, bool clear);
 
 // pool == nullptr: the tensor in memory is the convolution input; otherwise it is max-pooled on the fly.
+// from_signs != 0: `input` is not fp32 but the sign words [image][c/32][in_h*in_w] left by a sign-only GEMM epilogue.
 int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
-		uint32_t * t_bit_input, cudaStream_t stream);
+		uint32_t * t_bit_input, cudaStream_t stream, int from_signs = 0);
 
 }  // namespace xnor

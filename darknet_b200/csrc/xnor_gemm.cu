@@ -52,6 +52,7 @@ struct GemmParams
 	const float * shortcut_in;
 	float * shortcut_out;
 	int32_t * counts;       // when set: write integer agreement counts [M][n_total] instead of C
+	uint32_t * signs;       // when set: write only the sign bits of the output, 32 filters per word: [img][M/32][pixel]
 	int tiles_m, tiles_n;
 };
 
@@ -209,6 +210,51 @@ xnor_gemm_kernel(const GemmParams p)
 		if (blockIdx.z != 0) { return; }
 	}
 
+	// Sign-only epilogue: the next layer binarises this output anyway, so only (value > 0) is kept, packed 32
+	// filters to a word in the channel-packed layout the next pack kernel stages in shared memory.  Bytes go
+	// through shared memory because one thread's register tile holds filters that are TY rows apart.
+	if (p.signs != nullptr)
+	{
+		constexpr int SP = BN + 4;
+		static_assert(BM % 32 == 0 && BM * SP <= STAGES * (BM + BN) * PITCH * 4, "sign staging does not fit the ring");
+		uint8_t * s_sign = reinterpret_cast<uint8_t *>(smem);
+		__syncthreads();                                   // the operand ring (or the parked sums) is dead from here on
+		#pragma unroll
+		for (int i = 0; i < TM; ++i)
+		{
+			const int ml = i * TY + ty;
+			const int m = m0 + ml;
+			const float mean = (m < p.M) ? __ldg(p.mean_arr + m) : 0.0f;
+			const float bias = (m < p.M && p.bias != nullptr) ? __ldg(p.bias + m) : 0.0f;
+			#pragma unroll
+			for (int j = 0; j < TN; ++j)
+			{
+				float v = __fmul_rn((float)(p.K - 2 * acc[i][j]), mean);
+				if (p.bias != nullptr) { v = __fadd_rn(v, bias); }
+				s_sign[ml * SP + j * TX + tx] = (m < p.M && v > 0.0f) ? 1 : 0;
+			}
+		}
+		__syncthreads();
+		const int mwords = p.M >> 5;
+		for (int idx = threadIdx.x; idx < (BM / 32) * BN; idx += NT)
+		{
+			const int wl = idx / BN;
+			const int cl = idx - wl * BN;
+			const int col = n0 + cl;
+			const int mw = (m0 >> 5) + wl;
+			if (col < p.n_total && mw < mwords)
+			{
+				uint32_t word = 0;
+				#pragma unroll
+				for (int k = 0; k < 32; ++k) { word |= (uint32_t)s_sign[(wl * 32 + k) * SP + cl] << k; }
+				const int img = col / p.n_per_image;
+				const int pix = col - img * p.n_per_image;
+				p.signs[((size_t)img * mwords + mw) * p.n_per_image + pix] = word;
+			}
+		}
+		return;
+	}
+
 	// epilogue
 	#pragma unroll
 	for (int j = 0; j < TN; ++j)
@@ -311,9 +357,11 @@ static float estimate_cycles(const TileConfig & c, int M, int n_total, int kw, i
 int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
-		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream)
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs)
 {
+	if (signs != nullptr && M % 32 != 0) { return XNOR_B200_ERR_INVALID; }
 	GemmParams p;
+	p.signs = signs;
 	p.A = A; p.B = B;
 	p.M = M; p.n_total = n_total; p.n_per_image = n_per_image; p.K = K;
 	p.lda_words = lda_words; p.ldb_words = ldb_words;
@@ -329,7 +377,7 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		if (use_tc)
 		{
 			return launch_xnor_gemm_tc(M, n_total, n_per_image, K, A, lda_words, B, ldb_words, C, ldc, mean_arr, bias, leaky,
-					shortcut_in, shortcut_out, counts, stream);
+					shortcut_in, shortcut_out, counts, stream, signs);
 		}
 	}
 

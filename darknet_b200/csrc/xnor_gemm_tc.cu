@@ -52,6 +52,7 @@ struct TcParams
 	const float * shortcut_in;
 	float * shortcut_out;
 	int32_t * counts;
+	uint32_t * signs;       // when set: sign bits of the output only, [img][M/32][pixel]
 	int tiles_f;            // filter tiles (fastest-varying in blockIdx.x)
 };
 
@@ -338,6 +339,24 @@ xnor_gemm_tc_kernel(const TcParams p)
 				}
 				continue;
 			}
+			if (p.signs != nullptr)
+			{
+				// the 32 filters of this chunk are exactly one channel-packed word of this thread's pixel
+				if (f0 + fbase < p.M)
+				{
+					uint32_t word = 0;
+					#pragma unroll
+					for (int j = 0; j < 32; ++j)
+					{
+						const int4 fi = s_fil[fbase + j];
+						float v = __fmul_rn((float)(k_b + fi.x + 4 * (int)d[j]), __int_as_float(fi.y));
+						if (has_bias) { v = __fadd_rn(v, __int_as_float(fi.z)); }
+						word |= (v > 0.0f ? 1u : 0u) << j;
+					}
+					p.signs[((size_t)img * (p.M >> 5) + ((f0 + fbase) >> 5)) * p.n_per_image + pix] = word;
+				}
+				continue;
+			}
 			float * out = c_pix + (size_t)fbase * p.ldc;
 			#pragma unroll
 			for (int j = 0; j < 32; ++j)
@@ -395,9 +414,10 @@ static int launch_tc(TcParams & p, cudaStream_t stream)
 int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
-		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream)
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs)
 {
 	TcParams p;
+	p.signs = signs;
 	p.A = A; p.B = B;
 	p.M = M; p.n_total = n_total; p.n_per_image = n_per_image; p.K = K;
 	p.lda_words = lda_words; p.ldb_words = ldb_words;

@@ -131,3 +131,28 @@ def forward_convolutional_layer_gpu(l: ConvolutionalLayer, x: torch.Tensor, pool
                                                 _ptr(l.bin_conv_shortcut_in_gpu), _ptr(l.bin_conv_shortcut_out_gpu),
                                                 l.scratch.data_ptr(), l.scratch.numel(), _stream()), "xnor_b200_conv_forward")
     return l.output_gpu
+
+
+def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tensor] = None, x_signs: Optional[torch.Tensor] = None,
+                                   pool: Optional[capi.PoolDesc] = None, want_signs: bool = False) -> torch.Tensor:
+    """xnor_b200_conv_forward_io: the layer forward with optional sign-bit input (x_signs: int32 [batch][c/32][in_h*in_w])
+    and optional sign-bit output (returned as int32 [batch][n/32][out_h*out_w] instead of the fp32 tensor)."""
+    if l.align_bit_weights_gpu is None:
+        raise RuntimeError("binary_align_weights() has not been called for this layer")
+    io = capi.ConvIO()
+    io.input = _ptr(x)
+    io.input_signs = _ptr(x_signs)
+    io.pool = C.pointer(pool) if pool is not None else None
+    out = None
+    if want_signs:
+        out = torch.empty(l.batch, l.n // 32, l.geom.n_out, dtype=torch.int32, device=l.device)
+        io.output_signs = out.data_ptr()
+    else:
+        out = l.output_gpu
+        io.output = out.data_ptr()
+        io.shortcut_in = _ptr(l.bin_conv_shortcut_in_gpu)
+        io.shortcut_out = _ptr(l.bin_conv_shortcut_out_gpu)
+    capi.check(capi.lib().xnor_b200_conv_forward_io(C.byref(l.desc), C.byref(io), l.align_bit_weights_gpu.data_ptr(),
+                                                   l.mean_arr_gpu.data_ptr(), l.biases_gpu.data_ptr(), l.scratch.data_ptr(),
+                                                   l.scratch.numel(), _stream()), "xnor_b200_conv_forward_io")
+    return out

@@ -82,6 +82,10 @@ class Layer:
     # maxpool whose only reader is the xnor conv right after it: folded into that conv's pack kernel
     folded: bool = False
     pool_desc: Optional[capi.PoolDesc] = None
+    # xnor conv whose only reader is another xnor conv (directly or through a maxpool): hands over sign bits
+    emit_signs: bool = False
+    sign_source: Optional[int] = None
+    sign_out: Optional[torch.Tensor] = None
     output_gpu: Optional[torch.Tensor] = None
 
     @property
@@ -100,6 +104,8 @@ class Network:
     xnor_launches_per_forward: int = 0
     folded_maxpools: int = 0
     fold_maxpool_min_batch: int = 4
+    sign_chains: bool = True
+    sign_links: int = 0
 
 
 def parse_network_cfg(path: str, batch: int = 1, device: str = "cuda:0") -> Network:
@@ -242,8 +248,41 @@ def calculate_binary_weights(net: Network) -> None:
                 sc.blank = True
                 sc.output_gpu = torch.empty(net.batch, sc.out_c, sc.out_h, sc.out_w, device=dev)
                 xl.bin_conv_shortcut_out_gpu = sc.output_gpu
+    if net.sign_chains:
+        link_sign_chains(net)
     fold_maxpools(net)
     torch.cuda.synchronize(dev)
+
+
+def link_sign_chains(net: Network) -> None:
+    """Finds xnor convolutions whose output is read by nothing but the next xnor convolution -- directly or through
+    one [maxpool] -- and switches the pair to the sign-bit hand-over of xnor_b200_conv_forward_io: the producer
+    writes 1 bit per value, the maxpool becomes an OR inside the consumer's pack kernel, and neither the fp32
+    tensor nor the pooled tensor exists.  These are the bin_output=1 layers of the tiny networks."""
+    referenced = set()
+    for l in net.layers:
+        if l.type in ("route", "shortcut"):
+            referenced.update(l.input_layers)
+    n = len(net.layers)
+    for j, l in enumerate(net.layers):
+        if not (l.type == "convolutional" and l.xnor and l.xnor_layer is not None and l.n % 32 == 0) or j in referenced or j + 1 >= n:
+            continue
+        if net.layers[j + 1].blank:
+            continue
+        k = j + 1
+        pool = None
+        if net.layers[k].type == "maxpool" and k not in referenced and k + 1 < n:
+            pool = net.layers[k]
+            k += 1
+        consumer = net.layers[k]
+        if not (consumer.type == "convolutional" and consumer.xnor and consumer.xnor_layer is not None):
+            continue
+        l.emit_signs = True
+        consumer.sign_source = j
+        if pool is not None:
+            pool.folded = True
+            consumer.pool_desc = capi.PoolDesc(pool.size, pool.stride, pool.pad, pool.h, pool.w)
+        net.sign_links += 1
 
 
 def fold_maxpools(net: Network) -> None:
@@ -259,7 +298,7 @@ def fold_maxpools(net: Network) -> None:
         # once instead of writing and re-reading the pooled one) and only for the 2x2/stride-2 window it has a
         # vectorised path for; at batch 1 the separate maxpool launch is cheaper than the longer pack kernel.
         fast = l.size == 2 and l.stride == 2 and l.pad // 2 == 0 and l.h % 2 == 0 and l.w % 2 == 0
-        if (l.type == "maxpool" and j not in referenced and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None
+        if (l.type == "maxpool" and not l.folded and j not in referenced and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None
                 and fast and net.batch >= net.fold_maxpool_min_batch):
             l.folded = True
             nxt.pool_desc = capi.PoolDesc(l.size, l.stride, l.pad, l.h, l.w)
@@ -344,7 +383,14 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
                 nxt = net.layers[l.index + 1] if l.index + 1 < len(net.layers) else None
                 if nxt is not None and nxt.blank:
                     xl.bin_conv_shortcut_in_gpu = net.layers[nxt.input_layers[0]].output_gpu
-                cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
+                if l.emit_signs or l.sign_source is not None:
+                    src = net.layers[l.sign_source].sign_out if l.sign_source is not None else None
+                    out = L.forward_convolutional_layer_io(xl, x=None if src is not None else cur, x_signs=src,
+                                                           pool=l.pool_desc, want_signs=l.emit_signs)
+                    l.sign_out = out if l.emit_signs else None
+                    cur = None if l.emit_signs else out
+                else:
+                    cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
             elif l.c * l.size * l.size <= 128 and l.n <= 256 and l.activation in ("leaky", "linear"):
                 cur = _float_conv_small(net, l, cur)
             elif l.size == 1 and l.stride == 1 and l.pad == 0:
@@ -380,11 +426,12 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
     return heads
 
 
-def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "cuda:0") -> Network:
+def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "cuda:0", sign_chains: bool = True) -> Network:
     """load_network_custom (src-lib/weights.cpp:665-691): parse, load, fold batch-norm, pack binary weights."""
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
     net = parse_network_cfg(cfg, batch, device)
+    net.sign_chains = sign_chains
     load_weights(net, weights)
     fuse_conv_batchnorm(net)
     calculate_binary_weights(net)

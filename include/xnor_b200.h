@@ -177,6 +177,33 @@ XNOR_B200_API int xnor_b200_conv_forward_pooled(const xnor_b200_conv_desc * desc
 		float * output, const float * shortcut_in, float * shortcut_out,
 		void * scratch, size_t scratch_bytes, void * stream);
 
+/* Operands of xnor_b200_conv_forward_io.  Exactly one of input / input_signs and exactly one of output /
+ * output_signs is non-NULL.
+ *   input_signs   the previous xnor layer's output as sign bits, 32 channels per word, [batch][c/32][h*w] (with
+ *                 `pool`: [batch][c/32][in_h*in_w] of the tensor in front of the maxpool); needs c % 32 == 0
+ *   output_signs  this layer's output as sign bits only, [batch][n/32][out_h*out_w]; needs n % 32 == 0 and no
+ *                 shortcut; the activation plays no role (leaky keeps the sign) */
+typedef struct xnor_b200_conv_io
+{
+	const float * input;
+	const uint32_t * input_signs;
+	const xnor_b200_pool_desc * pool;     /* optional maxpool between the previous layer and this one */
+	float * output;
+	uint32_t * output_signs;
+	const float * shortcut_in;
+	float * shortcut_out;
+} xnor_b200_conv_io;
+
+/* xnor_b200_conv_forward for chains of xnor layers.  A layer marked bin_output=1 feeds nothing but the next
+ * binarised convolution (src-lib/darknet_network.cpp:1794-1797 drops its activation for that reason), which only
+ * looks at the sign of every value: with output_signs the GEMM epilogue writes that sign, 1 bit per value, instead
+ * of the fp32 tensor, and the next layer's pack kernel reads the words (ORing them over the pool window when a
+ * [maxpool] sits in between, src-lib/maxpool_layer_kernels.cu:48-86).  The bits equal what the next layer would
+ * have derived from the fp32 tensor, so every later result is unchanged bit for bit. */
+XNOR_B200_API int xnor_b200_conv_forward_io(const xnor_b200_conv_desc * desc, const xnor_b200_conv_io * io,
+		const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
+		void * scratch, size_t scratch_bytes, void * stream);
+
 /* The float convolution in front of the path (3 input channels -> 16/32 filters in the xnor networks): the float
  * branch of forward_convolutional_layer_gpu (src-lib/convolutional_kernels.cu:373-434, cuDNN or im2col + sgemm) +
  * add_bias_gpu + leaky activate_array_ongpu (src-lib/activation_kernels.cu:34) as one direct-convolution kernel

@@ -1,0 +1,97 @@
+"""Chains of xnor layers that hand over sign bits instead of fp32 tensors (xnor_b200_conv_forward_io).
+
+Layer 1 writes only the sign of its output (1 bit per value, 32 filters per word); layer 2 packs its operand from
+those words, ORing them over a max-pool window when a [maxpool] sits in between.  Every result of layer 2 must be
+bit-identical to the ordinary route (fp32 output -> maxpool -> pack), for both GEMM kernels."""
+import os
+
+import numpy as np
+import pytest
+
+import synth
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+import torch.nn.functional as F  # noqa: E402
+
+from darknet_b200 import capi, layer as L  # noqa: E402
+
+
+def build(batch, c, h, w, n, ks, leaky, seed):
+    x, wt, b = synth.conv_case(seed, batch, c, h, w, n, ks)
+    l = L.make_convolutional_layer(batch, h, w, c, n, ks, 1, ks // 2, capi.LEAKY if leaky else capi.LINEAR)
+    l.load_weights(torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda())
+    L.binary_align_weights(l)
+    return l, torch.from_numpy(x).cuda()
+
+
+@pytest.mark.parametrize("tc", ["0", "1"])
+@pytest.mark.parametrize("case", [
+    # batch, c1, h, w, n1 (= c2), n2, pool (size, stride, pad) or None
+    (2, 32, 16, 16, 64, 48, (2, 2, 1)),
+    (1, 64, 26, 26, 128, 40, None),
+    (2, 16, 24, 24, 32, 24, (2, 2, 1)),          # layer 1 on the bit path (16 channels)
+    (1, 96, 13, 13, 256, 64, (2, 1, 1)),         # stride-1 pool, window clipped at the edge
+    (3, 64, 12, 10, 96, 33, (3, 2, 2)),
+], ids=lambda c: "b%d_c%d_%dx%d_n%d_n%d_%s" % c)
+def test_sign_chain_equals_fp32_chain(case, tc):
+    batch, c1, h, w, n1, n2, pool = case
+    old = os.environ.get("XNOR_B200_GEMM_TC")
+    os.environ["XNOR_B200_GEMM_TC"] = tc
+    try:
+        l1, x = build(batch, c1, h, w, n1, 3, 0, 31 + c1)
+        y1 = L.forward_convolutional_layer_gpu(l1, x).clone()
+        signs = L.forward_convolutional_layer_io(l1, x=x, want_signs=True)
+        # the sign words are the channel-packed signs of the fp32 output
+        bits = (y1 > 0).reshape(batch, n1 // 32, 32, h * w).to(torch.int64)
+        want_words = (bits << torch.arange(32, device="cuda").view(1, 1, 32, 1)).sum(2)
+        assert torch.equal(signs.to(torch.int64) & 0xFFFFFFFF, want_words)
+
+        if pool is None:
+            h2, w2, pd, mid = h, w, None, y1
+        else:
+            ps, pst, pp = pool
+            h2, w2 = (h + pp - ps) // pst + 1, (w + pp - ps) // pst + 1
+            pd = capi.PoolDesc(ps, pst, pp, h, w)
+            lo = pp // 2
+            padded = F.pad(y1, (lo, max((w2 - 1) * pst + ps - lo - w, 0), lo, max((h2 - 1) * pst + ps - lo - h, 0)), value=float("-inf"))
+            mid = F.max_pool2d(padded, ps, pst)[:, :, :h2, :w2].contiguous()
+        l2, _ = build(batch, n1, h2, w2, n2, 3, 1, 77 + n1)
+        want = L.forward_convolutional_layer_gpu(l2, mid).clone()
+        got = L.forward_convolutional_layer_io(l2, x_signs=signs, pool=pd).clone()
+        assert torch.equal(got, want)
+    finally:
+        if old is None:
+            os.environ.pop("XNOR_B200_GEMM_TC", None)
+        else:
+            os.environ["XNOR_B200_GEMM_TC"] = old
+
+
+def test_io_argument_checks():
+    l, x = build(1, 32, 8, 8, 40, 3, 0, 5)               # 40 filters: not a multiple of 32
+    with pytest.raises(capi.XnorError, match="invalid"):
+        L.forward_convolutional_layer_io(l, x=x, want_signs=True)
+    with pytest.raises(capi.XnorError, match="NULL"):
+        L.forward_convolutional_layer_io(l)              # neither kind of input
+
+
+@pytest.mark.parametrize("batch", [1, 4])
+def test_network_with_sign_chains_equals_fp32_network(tmp_path, batch):
+    """yolov3-tiny_xnor at a reduced input size: handing sign bits from one xnor layer to the next (with the
+    maxpool between them turned into an OR) changes no bit of either head."""
+    from darknet_b200 import cfgs, network
+    cfg = tmp_path / "net.cfg"
+    cfg.write_text(cfgs.yolov3_tiny_xnor_cfg(96, 96))
+    net_cpu = network.parse_network_cfg(str(cfg), batch, "cpu")
+    w = tmp_path / "net.weights"
+    network.write_synthetic_weights(net_cpu, str(w), seed=5)
+    x = torch.from_numpy(synth.uniform01(9, (batch, 3, 96, 96))).cuda()
+    linked = network.load_network_custom(str(cfg), str(w), batch)
+    plain = network.load_network_custom(str(cfg), str(w), batch, sign_chains=False)
+    assert linked.sign_links >= 3 and plain.sign_links == 0
+    got = network.forward_network_gpu(linked, x)
+    want = network.forward_network_gpu(plain, x)
+    assert len(got) == len(want) == 2
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
