@@ -83,6 +83,7 @@ class Layer:
     folded: bool = False
     pool_desc: Optional[capi.PoolDesc] = None
     # xnor conv whose only reader is another xnor conv (directly or through a maxpool): hands over sign bits
+    weights_blocked_gpu: Optional[torch.Tensor] = None     # float conv on a small map: weights re-blocked at load time
     emit_signs: bool = False
     sign_source: Optional[int] = None
     sign_out: Optional[torch.Tensor] = None
@@ -105,6 +106,7 @@ class Network:
     folded_maxpools: int = 0
     fold_maxpool_min_batch: int = 4
     sign_chains: bool = True
+    float_map_max_pixels: int = 4096       # batch*out_h*out_w up to which float convs use the cluster split-K kernel
     sign_links: int = 0
 
 
@@ -248,6 +250,7 @@ def calculate_binary_weights(net: Network) -> None:
                 sc.blank = True
                 sc.output_gpu = torch.empty(net.batch, sc.out_c, sc.out_h, sc.out_w, device=dev)
                 xl.bin_conv_shortcut_out_gpu = sc.output_gpu
+    prepare_float_map_convs(net)
     if net.sign_chains:
         link_sign_chains(net)
     fold_maxpools(net)
@@ -327,6 +330,38 @@ def _float_conv_small(net: Network, l: Layer, x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def _map_conv_desc(net: Network, l: Layer) -> capi.ConvDesc:
+    return capi.ConvDesc(net.batch, l.c, l.h, l.w, l.n, l.size, l.stride, l.pad, capi.LEAKY if l.activation == "leaky" else capi.LINEAR)
+
+
+def prepare_float_map_convs(net: Network) -> None:
+    """Re-blocks the weights of the float convolutions that the small-map kernel takes (many channels, stride 1,
+    3x3/pad 1 or 1x1, few output pixels in the whole batch).  Runs after fuse_conv_batchnorm."""
+    import ctypes as C
+    for l in net.layers:
+        if l.type != "convolutional" or l.xnor or l.activation not in ("leaky", "linear"):
+            continue
+        if l.c * l.size * l.size <= 128 or net.batch * l.out_h * l.out_w > net.float_map_max_pixels:
+            continue
+        desc = _map_conv_desc(net, l)
+        nbytes = capi.lib().xnor_b200_float_conv_map_weights_bytes(C.byref(desc))
+        if nbytes == 0:
+            continue
+        l.weights_blocked_gpu = torch.empty(nbytes // 4, dtype=torch.float32, device=l.weights_gpu.device)
+        capi.check(capi.lib().xnor_b200_float_conv_map_prepare(C.byref(desc), l.weights_gpu.data_ptr(), l.weights_blocked_gpu.data_ptr(),
+                                                              torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_map_prepare")
+
+
+def _float_conv_map(net: Network, l: Layer, x: torch.Tensor) -> torch.Tensor:
+    """A many-channel float convolution on a small map: cluster split-K kernel with bias and activation fused."""
+    import ctypes as C
+    desc = _map_conv_desc(net, l)
+    out = torch.empty(net.batch, l.n, l.out_h, l.out_w, dtype=torch.float32, device=x.device)
+    capi.check(capi.lib().xnor_b200_float_conv_map(C.byref(desc), x.data_ptr(), l.weights_blocked_gpu.data_ptr(), l.biases_gpu.data_ptr(),
+                                                  out.data_ptr(), torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_map")
+    return out
+
+
 def _maxpool(x: torch.Tensor, l: Layer) -> torch.Tensor:
     # window origin = -pad/2, out-of-image taps ignored (src-lib/maxpool_layer_kernels.cu:48-86)
     lo = l.pad // 2
@@ -393,6 +428,8 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
                     cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
             elif l.c * l.size * l.size <= 128 and l.n <= 256 and l.activation in ("leaky", "linear"):
                 cur = _float_conv_small(net, l, cur)
+            elif l.weights_blocked_gpu is not None:
+                cur = _float_conv_map(net, l, cur.contiguous())
             elif l.size == 1 and l.stride == 1 and l.pad == 0:
                 # a 1x1 convolution is a plain matrix product per image (cuBLAS sgemm, fp32)
                 b = cur.shape[0]

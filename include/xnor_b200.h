@@ -213,6 +213,19 @@ XNOR_B200_API int xnor_b200_conv_forward_io(const xnor_b200_conv_desc * desc, co
 XNOR_B200_API int xnor_b200_float_conv_small(const xnor_b200_conv_desc * desc, const float * input, const float * weights,
 		const float * biases, float * output, void * stream);
 
+/* The float convolutions behind the path (many channels on a small map: the 3x3 256->512 layer on 13x13 and the
+ * 1x1 layers in front of the yolo heads): the same float branch of forward_convolutional_layer_gpu
+ * (src-lib/convolutional_kernels.cu:373-434) + add_bias_gpu + activate_array_ongpu, for stride 1 and either
+ * size 3 / pad 1 (c % 8 == 0, (h+2)*(w+2) <= 1024) or size 1 / pad 0 (c % 32 == 0).  The channels are split over a
+ * thread-block cluster so that a batch-1 layer still covers the chip; partial sums are added in a fixed order.
+ * Weights are re-blocked once at load time: _weights_bytes gives the size of the blocked copy (0 for a shape the
+ * kernel does not take), _prepare fills it from Darknet's [n][c*size*size] weights (batch-norm folded), and the
+ * forward takes the blocked copy (16-byte aligned).  Results agree with cuDNN to rounding, not bit for bit. */
+XNOR_B200_API size_t xnor_b200_float_conv_map_weights_bytes(const xnor_b200_conv_desc * desc);
+XNOR_B200_API int xnor_b200_float_conv_map_prepare(const xnor_b200_conv_desc * desc, const float * weights, float * blocked, void * stream);
+XNOR_B200_API int xnor_b200_float_conv_map(const xnor_b200_conv_desc * desc, const float * input, const float * blocked_weights,
+		const float * biases, float * output, void * stream);
+
 /* The activation step of forward_yolo_layer_gpu (src-lib/yolo_layer.cpp:1439-1489) behind the path: logistic on the
  * x, y, objectness and class entries of every anchor, w and h raw, in one pass.  input/output
  * [batch][anchors][4 + 1 + classes][hw] (may be the same pointer).  Box decoding and NMS stay on the host side. */

@@ -52,3 +52,52 @@ def test_yolo_activate_matches_elementwise_definition():
     v[:, :, 4:] = torch.sigmoid(v[:, :, 4:])
     assert torch.equal(out.reshape(v.shape)[:, :, 2:4], x.reshape(v.shape)[:, :, 2:4])
     assert (out.reshape(v.shape) - v).abs().max().item() <= 1e-6
+
+
+@pytest.mark.parametrize("case", [
+    # batch, c, h, w, n, size, leaky
+    (1, 256, 13, 13, 512, 3, 1),        # the 3x3 float convolution of yolov3-tiny_xnor (8-way channel split)
+    (1, 512, 13, 13, 255, 1, 0),        # yolo head, filter count not a multiple of 32
+    (1, 256, 26, 26, 255, 1, 0),        # second head: 4 pixel tiles, the last one ragged
+    (2, 64, 26, 26, 40, 3, 1),          # 3x3 on the largest map the kernel stages, two images
+    (3, 32, 7, 5, 33, 1, 1),            # single pipeline stage, no split
+    (2, 8, 9, 11, 64, 3, 0),            # one stage of 8 channels
+    (5, 96, 13, 13, 96, 3, 1),          # channel count that only splits by 4
+], ids=lambda c: "b%d_c%d_%dx%d_n%d_k%d_%d" % c)
+def test_float_conv_map_matches_fp64_convolution(case):
+    batch, c, h, w, n, ks, leaky = case
+    pad = ks // 2
+    x = torch.from_numpy(synth.bell(sum(case), (batch, c, h, w), 1.0)).cuda()
+    wt = torch.from_numpy(synth.bell(sum(case) + 1, (n, c, ks, ks), 0.05)).cuda()
+    b = torch.from_numpy(synth.bell(sum(case) + 2, (n,), 0.01)).cuda()
+    want = torch.nn.functional.conv2d(x.double(), wt.double(), b.double(), 1, pad)
+    if leaky:
+        want = torch.where(want > 0, want, want * 0.1)
+    desc = capi.ConvDesc(batch, c, h, w, n, ks, 1, pad, capi.LEAKY if leaky else capi.LINEAR)
+    lib = capi.lib()
+    nbytes = lib.xnor_b200_float_conv_map_weights_bytes(C.byref(desc))
+    assert nbytes == ((n + 31) // 32) * 32 * c * ks * ks * 4
+    blocked = torch.full((nbytes // 4,), float("nan"), dtype=torch.float32, device="cuda")
+    capi.check(lib.xnor_b200_float_conv_map_prepare(C.byref(desc), wt.data_ptr(), blocked.data_ptr(), None), "prepare")
+    out = torch.full(want.shape, float("nan"), dtype=torch.float32, device="cuda")
+    capi.check(lib.xnor_b200_float_conv_map(C.byref(desc), x.data_ptr(), blocked.data_ptr(), b.data_ptr(), out.data_ptr(), None), "map conv")
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all()
+    # fp32 accumulation of c*k*k products of magnitude about 0.05: error grows like sqrt(K) * 2^-24 * |sum|
+    tol = 2e-5 * max(1.0, want.abs().max().item())
+    assert (out.double() - want).abs().max().item() <= tol
+    # deterministic: the cluster reduction adds the partial sums in rank order
+    out2 = torch.empty_like(out)
+    capi.check(lib.xnor_b200_float_conv_map(C.byref(desc), x.data_ptr(), blocked.data_ptr(), b.data_ptr(), out2.data_ptr(), None), "map conv")
+    assert torch.equal(out, out2)
+
+
+def test_float_conv_map_rejects_other_shapes():
+    lib = capi.lib()
+    for bad in [capi.ConvDesc(1, 64, 13, 13, 32, 3, 2, 1, capi.LINEAR),      # stride 2
+                capi.ConvDesc(1, 60, 13, 13, 32, 3, 1, 1, capi.LINEAR),      # channels not a multiple of 8
+                capi.ConvDesc(1, 64, 40, 40, 32, 3, 1, 1, capi.LINEAR),      # map too large to stage
+                capi.ConvDesc(1, 48, 13, 13, 32, 1, 1, 0, capi.LINEAR)]:     # 1x1 with channels not a multiple of 32
+        assert lib.xnor_b200_float_conv_map_weights_bytes(C.byref(bad)) == 0
+        z = torch.zeros(64, device="cuda")
+        assert lib.xnor_b200_float_conv_map(C.byref(bad), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None) == 1
