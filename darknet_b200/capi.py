@@ -24,7 +24,7 @@ EXPORTS = (
     "xnor_b200_repack_input_bin", "xnor_b200_pack_input", "xnor_b200_gemm_bin_mean_transposed",
     "xnor_b200_gemm_counts", "xnor_b200_scratch_bytes", "xnor_b200_conv_forward",
     "xnor_b200_conv_forward_static", "xnor_b200_take_device_status",
-    "xnor_b200_pack_input_pooled", "xnor_b200_conv_forward_pooled", "xnor_b200_float_conv_small", "xnor_b200_float_conv_map_weights_bytes",
+    "xnor_b200_pack_input_pooled", "xnor_b200_conv_forward_pooled", "xnor_b200_float_conv_small", "xnor_b200_float_conv3_io", "xnor_b200_float_conv_map_weights_bytes",
     "xnor_b200_float_conv_map_prepare", "xnor_b200_float_conv_map", "xnor_b200_yolo_activate", "xnor_b200_conv_forward_io",
     "xnor_b200_measure_popc_peak", "xnor_b200_measure_bmma_peak", "xnor_b200_measure_umma_i8_peak",
 )
@@ -94,6 +94,7 @@ def lib() -> C.CDLL:
     L.xnor_b200_pack_input_pooled.argtypes = [dp, pp, vp, vp, vp]
     L.xnor_b200_conv_forward_pooled.argtypes = [dp, pp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
     L.xnor_b200_float_conv_small.argtypes = [dp, vp, vp, vp, vp, vp]
+    L.xnor_b200_float_conv3_io.argtypes = [dp, ci, vp, vp, vp, vp, vp, vp]
     L.xnor_b200_float_conv_map_weights_bytes.argtypes = [dp]
     L.xnor_b200_float_conv_map_weights_bytes.restype = C.c_size_t
     L.xnor_b200_float_conv_map_prepare.argtypes = [dp, vp, vp, vp]

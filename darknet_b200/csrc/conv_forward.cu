@@ -130,7 +130,7 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_p
 	if (desc == nullptr || align_bit_weights == nullptr || mean_arr == nullptr || scratch == nullptr) { return XNOR_B200_ERR_NULL; }
 	if ((input == nullptr) == (input_signs == nullptr) || (output == nullptr) == (output_signs == nullptr)) { return XNOR_B200_ERR_NULL; }
 	if (output_signs != nullptr && (shortcut_out != nullptr || desc->n % 32 != 0)) { return XNOR_B200_ERR_INVALID; }
-	if (input_signs != nullptr && desc->c % 32 != 0) { return XNOR_B200_ERR_INVALID; }
+	if (input_signs != nullptr && desc->c % 32 != 0 && pool != nullptr) { return XNOR_B200_ERR_INVALID; }
 	xnor_b200_conv_geom g;
 	int rc = xnor_b200_conv_geometry(desc, &g);
 	if (rc != XNOR_B200_OK) { return rc; }

@@ -103,6 +103,155 @@ float_conv_small_kernel(const FloatConvParams p)
 	}
 }
 
+// ---- 3 input channels, 3x3, stride 1, pad 1: a thread computes a 2x2 block of outputs for 8 filters ----------
+// The first layer of every xnor network.  One thread loads the 4x4x3 input patch of its block once (48 values in
+// registers) and reads each weight once per block as part of a 16-byte vector, so the kernel runs at FMA speed
+// instead of one shared-memory load per multiply.  Three ways to finish, chosen by the caller:
+//   * fp32 output at full resolution (bias, leaky/linear);
+//   * the [maxpool] size 2 / stride 2 that follows the layer applied in registers, fp32 output at half resolution
+//     (leaky is monotonic, so max(act(v)) == act(max(v)) value for value);
+//   * only the SIGN of that pooled output, as x-packed bit planes uint32 [image][filter][H/2][ceil(W/2/32)] -- what
+//     a following xnor layer needs and nothing more (max > 0 exactly when one of the four values is > 0).
+// Each output value is formed exactly as in float_conv_small_kernel: fmaf over (channel, ky, kx) from zero, then
+// + bias, so the three variants and that kernel agree bit for bit.
+constexpr int FB_THREADS = 256;          // 8 warps: warp w = block row w of the tile, lane = block column
+constexpr int FB_FILTERS = 8;            // filters per thread (blockIdx.y picks the group)
+
+struct FloatBlockParams
+{
+	const float * in;        // [batch][3][H][W]
+	const float * weights;   // [n][27]
+	const float * biases;    // [n] or nullptr
+	float * out;             // fp32 output (full or pooled) or nullptr
+	uint32_t * planes;       // pooled sign planes or nullptr
+	int H, W, N;
+	int BH, BW;              // 2x2 blocks per column / row: ceil(H/2), ceil(W/2)
+	int xtiles;              // ceil(BW / 32)
+	int pooled;              // 1: one value per block
+	int leaky;
+};
+
+__global__ void __launch_bounds__(FB_THREADS)
+float_conv3_block_kernel(const FloatBlockParams p)
+{
+	__shared__ __align__(16) float s_w[27 * FB_FILTERS];      // [tap][filter of this group]
+	__shared__ float s_b[FB_FILTERS];
+	const int f0 = blockIdx.y * FB_FILTERS;
+	for (int i = threadIdx.x; i < 27 * FB_FILTERS; i += FB_THREADS)
+	{
+		const int k = i / FB_FILTERS;
+		const int f = f0 + (i - k * FB_FILTERS);
+		s_w[i] = (f < p.N) ? p.weights[(size_t)f * 27 + k] : 0.0f;
+	}
+	if (threadIdx.x < FB_FILTERS)
+	{
+		const int f = f0 + threadIdx.x;
+		s_b[threadIdx.x] = (p.biases != nullptr && f < p.N) ? p.biases[f] : 0.0f;
+	}
+	__syncthreads();
+
+	const int lane = threadIdx.x & 31;
+	const int warp = threadIdx.x >> 5;
+	const int xt = blockIdx.x % p.xtiles;
+	const int yt = blockIdx.x / p.xtiles;
+	const int bx = xt * 32 + lane;
+	const int by = yt * 8 + warp;
+	const bool live = (bx < p.BW && by < p.BH);
+	const float * img = p.in + (size_t)blockIdx.z * 3 * p.H * p.W;
+
+	// the 4x4 patch of each channel: rows 2by-1 .. 2by+2, columns 2bx-1 .. 2bx+2
+	float v[3][4][4];
+	#pragma unroll
+	for (int c = 0; c < 3; ++c)
+	{
+		#pragma unroll
+		for (int r = 0; r < 4; ++r)
+		{
+			const int iy = 2 * by - 1 + r;
+			#pragma unroll
+			for (int q = 0; q < 4; ++q)
+			{
+				const int ix = 2 * bx - 1 + q;
+				const bool ok = live && iy >= 0 && iy < p.H && ix >= 0 && ix < p.W;
+				v[c][r][q] = ok ? __ldg(img + ((size_t)c * p.H + iy) * p.W + ix) : 0.0f;
+			}
+		}
+	}
+	float acc[FB_FILTERS][4];              // [filter][2*dy + dx]
+	#pragma unroll
+	for (int f = 0; f < FB_FILTERS; ++f)
+	{
+		#pragma unroll
+		for (int o = 0; o < 4; ++o) { acc[f][o] = 0.0f; }
+	}
+	#pragma unroll
+	for (int c = 0; c < 3; ++c)
+	{
+		#pragma unroll
+		for (int ky = 0; ky < 3; ++ky)
+		{
+			#pragma unroll
+			for (int kx = 0; kx < 3; ++kx)
+			{
+				const int k = (c * 3 + ky) * 3 + kx;
+				const float4 wa = *reinterpret_cast<const float4 *>(s_w + k * FB_FILTERS);
+				const float4 wb = *reinterpret_cast<const float4 *>(s_w + k * FB_FILTERS + 4);
+				const float w[FB_FILTERS] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+				#pragma unroll
+				for (int f = 0; f < FB_FILTERS; ++f)
+				{
+					acc[f][0] = fmaf(v[c][ky][kx], w[f], acc[f][0]);
+					acc[f][1] = fmaf(v[c][ky][kx + 1], w[f], acc[f][1]);
+					acc[f][2] = fmaf(v[c][ky + 1][kx], w[f], acc[f][2]);
+					acc[f][3] = fmaf(v[c][ky + 1][kx + 1], w[f], acc[f][3]);
+				}
+			}
+		}
+	}
+
+	const bool col1 = (2 * bx + 1 < p.W);
+	const bool row1 = (2 * by + 1 < p.H);
+	#pragma unroll
+	for (int f = 0; f < FB_FILTERS; ++f)
+	{
+		const float r0 = acc[f][0] + s_b[f], r1 = acc[f][1] + s_b[f], r2 = acc[f][2] + s_b[f], r3 = acc[f][3] + s_b[f];
+		if (p.planes != nullptr)
+		{
+			// pooled sign: the block lies inside the image whenever it is live (H and W are even in this mode)
+			const uint32_t word = __ballot_sync(0xffffffffu, live && (r0 > 0.0f || r1 > 0.0f || r2 > 0.0f || r3 > 0.0f));
+			if (lane == 0 && by < p.BH && f0 + f < p.N)
+			{
+				p.planes[(((size_t)blockIdx.z * p.N + f0 + f) * p.BH + by) * p.xtiles + xt] = word;
+			}
+			continue;
+		}
+		if (!live || f0 + f >= p.N) { continue; }
+		if (p.pooled)
+		{
+			float m = fmaxf(fmaxf(r0, r1), fmaxf(r2, r3));
+			if (p.leaky) { m = (m > 0.0f) ? m : m * 0.1f; }
+			p.out[(((size_t)blockIdx.z * p.N + f0 + f) * p.BH + by) * p.BW + bx] = m;
+		}
+		else
+		{
+			float a0 = r0, a1 = r1, a2 = r2, a3 = r3;
+			if (p.leaky)
+			{
+				a0 = (a0 > 0.0f) ? a0 : a0 * 0.1f; a1 = (a1 > 0.0f) ? a1 : a1 * 0.1f;
+				a2 = (a2 > 0.0f) ? a2 : a2 * 0.1f; a3 = (a3 > 0.0f) ? a3 : a3 * 0.1f;
+			}
+			float * dst = p.out + (((size_t)blockIdx.z * p.N + f0 + f) * p.H + 2 * by) * p.W + 2 * bx;
+			dst[0] = a0;
+			if (col1) { dst[1] = a1; }
+			if (row1)
+			{
+				dst[p.W] = a2;
+				if (col1) { dst[p.W + 1] = a3; }
+			}
+		}
+	}
+}
+
 }  // namespace xnor
 
 using namespace xnor;
@@ -137,5 +286,30 @@ extern "C" int xnor_b200_float_conv_small(const xnor_b200_conv_desc * desc, cons
 		if (rc != XNOR_B200_OK) { return rc; }
 		float_conv_small_kernel<0, 0><<<grid, FC_THREADS, smem, (cudaStream_t)stream>>>(p);
 	}
+	return check_launch();
+}
+
+extern "C" int xnor_b200_float_conv3_io(const xnor_b200_conv_desc * desc, int pool, const float * input, const float * weights,
+		const float * biases, float * output, uint32_t * output_sign_planes, void * stream)
+{
+	if (desc == nullptr || input == nullptr || weights == nullptr) { return XNOR_B200_ERR_NULL; }
+	if ((output == nullptr) == (output_sign_planes == nullptr)) { return XNOR_B200_ERR_NULL; }
+	int rc = validate_desc(desc);
+	if (rc != XNOR_B200_OK) { return rc; }
+	if (desc->c != 3 || desc->size != 3 || desc->stride != 1 || desc->pad != 1) { return XNOR_B200_ERR_INVALID; }
+	if (pool != 0 && pool != 2) { return XNOR_B200_ERR_INVALID; }
+	if (pool == 2 && (desc->h % 2 != 0 || desc->w % 2 != 0)) { return XNOR_B200_ERR_INVALID; }
+	if (output_sign_planes != nullptr && pool != 2) { return XNOR_B200_ERR_INVALID; }
+	FloatBlockParams p;
+	p.in = input; p.weights = weights; p.biases = biases; p.out = output; p.planes = output_sign_planes;
+	p.H = desc->h; p.W = desc->w; p.N = desc->n;
+	p.BH = (desc->h + 1) / 2; p.BW = (desc->w + 1) / 2;
+	p.xtiles = (p.BW + 31) / 32;
+	p.pooled = (pool == 2) ? 1 : 0;
+	p.leaky = (desc->activation == XNOR_B200_LEAKY) ? 1 : 0;
+	const long long tiles = (long long)p.xtiles * ((p.BH + 7) / 8);
+	const int groups = (desc->n + FB_FILTERS - 1) / FB_FILTERS;
+	if (tiles > 0x7fffffffLL || groups > 65535 || desc->batch > 65535) { return XNOR_B200_ERR_TOO_LARGE; }
+	float_conv3_block_kernel<<<dim3((unsigned)tiles, (unsigned)groups, (unsigned)desc->batch), FB_THREADS, 0, (cudaStream_t)stream>>>(p);
 	return check_launch();
 }

@@ -48,6 +48,7 @@ struct PackParams
 	int pool_size, pool_stride, pool_off;
 	int in_h, in_w;
 	int pool_fast;       // 2x2 window, stride 2, origin 0, even in_h/in_w, 8-byte aligned planes: two float2 loads
+	int from_planes;     // bit path: `in` holds sign planes uint32 [image][C][H][ceil(W/32)] (bit x%32 of word x/32) instead of floats
 };
 
 // sign(maxpool(x)) at pooled position (iy, ix) of one channel plane: the maximum is > 0 exactly when some
@@ -318,6 +319,29 @@ __device__ __forceinline__ void build_bit_planes(const float * img, size_t chan_
 	const int warp = threadIdx.x >> 5;
 	constexpr int NWARPS = PK_THREADS / 32;
 	constexpr int UNROLL = 8;
+	if (p.from_planes)
+	{
+		// the producer already made x-packed sign words; a staged word is two of them shifted by the padding
+		const int GW = (p.W + 31) >> 5;
+		const uint32_t * planes = reinterpret_cast<const uint32_t *>(img);
+		for (int cr = warp; cr < p.C * RR; cr += NWARPS)
+		{
+			const int c = cr / RR;
+			const int rr = cr - c * RR;
+			const int iy = iy0 + rr;
+			const bool row_ok = (iy >= 0 && iy < p.H);
+			const uint32_t * g = planes + ((size_t)c * p.H + (row_ok ? iy : 0)) * GW;
+			for (int xw = lane; xw < PW; xw += 32)
+			{
+				const int first = 32 * xw - p.pad;               // image column of bit 0 of this staged word
+				const int w0 = first >> 5;
+				const uint32_t lo = (row_ok && w0 >= 0 && w0 < GW) ? __ldg(g + w0) : 0u;
+				const uint32_t hi = (row_ok && w0 + 1 >= 0 && w0 + 1 < GW) ? __ldg(g + w0 + 1) : 0u;
+				s_words[(size_t)cr * PW + xw] = __funnelshift_r(lo, hi, first & 31);
+			}
+		}
+		return;
+	}
 	for (int cr = warp; cr < p.C * RR; cr += NWARPS)
 	{
 		const int c = cr / RR;
@@ -368,7 +392,8 @@ pack_input_bits_kernel(const PackParams p)
 	const int RR = (y1 - y0 - 1) * p.stride + p.ks;
 	const int PW = ((p.W + 2 * p.pad + 31) >> 5) + 1;
 	const size_t chan_stride = (p.pool_size > 0) ? (size_t)p.in_h * p.in_w : (size_t)p.H * p.W;
-	const float * img = p.in + (size_t)b * p.C * chan_stride;
+	const float * img = p.from_planes ? p.in + (size_t)b * p.C * p.H * ((p.W + 31) >> 5)       // 4-byte words either way
+	                                  : p.in + (size_t)b * p.C * chan_stride;
 	const int iy0 = y0 * p.stride - p.pad;
 
 	// phase A: one warp ballot per 32 consecutive padded positions of one (channel, row)
@@ -457,7 +482,8 @@ pack_input_bits_s1_kernel(const PackParams p)
 	const int RR = (y1 - y0 - 1) + p.ks;
 	const int PW = ((p.W + 2 * p.pad + 31) >> 5) + 1;
 	const size_t chan_stride = (p.pool_size > 0) ? (size_t)p.in_h * p.in_w : (size_t)p.H * p.W;
-	const float * img = p.in + (size_t)b * p.C * chan_stride;
+	const float * img = p.from_planes ? p.in + (size_t)b * p.C * p.H * ((p.W + 31) >> 5)       // 4-byte words either way
+	                                  : p.in + (size_t)b * p.C * chan_stride;
 	const int iy0 = y0 - p.pad;
 
 	// phase A: one warp ballot per 32 consecutive padded positions of one (channel, row)
@@ -550,8 +576,9 @@ float_to_bit_kernel(const float * __restrict__ src, uint32_t * __restrict__ dst,
 int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
 		uint32_t * t_bit_input, cudaStream_t stream, int from_signs)
 {
-	if (from_signs && d.c % 32 != 0) { return XNOR_B200_ERR_INVALID; }
+	if (from_signs && d.c % 32 != 0 && pool != nullptr) { return XNOR_B200_ERR_INVALID; }     // sign planes are made at the size the convolution sees
 	PackParams p;
+	p.from_planes = (from_signs && d.c % 32 != 0) ? 1 : 0;
 	p.pool_size = 0; p.pool_stride = 1; p.pool_off = 0; p.in_h = d.h; p.in_w = d.w; p.pool_fast = 0;
 	if (pool != nullptr)
 	{

@@ -84,6 +84,8 @@ class Layer:
     pool_desc: Optional[capi.PoolDesc] = None
     # xnor conv whose only reader is another xnor conv (directly or through a maxpool): hands over sign bits
     weights_blocked_gpu: Optional[torch.Tensor] = None     # float conv on a small map: weights re-blocked at load time
+    conv3_pool: int = 0              # first float conv (3 channels, 3x3): 2 = the 2x2/2 maxpool behind it is applied in the kernel
+    emit_planes: bool = False        # ... and only the sign planes of the pooled output are written
     emit_signs: bool = False
     sign_source: Optional[int] = None
     sign_out: Optional[torch.Tensor] = None
@@ -106,6 +108,7 @@ class Network:
     folded_maxpools: int = 0
     fold_maxpool_min_batch: int = 4
     sign_chains: bool = True
+    fuse_first_conv: bool = True
     float_map_max_pixels: int = 4096       # batch*out_h*out_w up to which float convs use the cluster split-K kernel
     sign_links: int = 0
 
@@ -253,6 +256,8 @@ def calculate_binary_weights(net: Network) -> None:
     prepare_float_map_convs(net)
     if net.sign_chains:
         link_sign_chains(net)
+    if net.fuse_first_conv:
+        link_first_conv(net)
     fold_maxpools(net)
     torch.cuda.synchronize(dev)
 
@@ -288,6 +293,34 @@ def link_sign_chains(net: Network) -> None:
         net.sign_links += 1
 
 
+def link_first_conv(net: Network) -> None:
+    """The float 3-channel 3x3 convolution in front of the path: when a 2x2/stride-2 [maxpool] that nothing else reads
+    follows it, the kernel pools in registers; when the layer after that is an xnor convolution (c % 32 != 0, so it
+    takes x-packed sign planes) the kernel writes just those planes (xnor_b200_float_conv3_io)."""
+    referenced = set()
+    for l in net.layers:
+        if l.type in ("route", "shortcut"):
+            referenced.update(l.input_layers)
+    for j, l in enumerate(net.layers):
+        if not (l.type == "convolutional" and not l.xnor and l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1
+                and l.activation in ("leaky", "linear")):
+            continue
+        if j in referenced or j + 1 >= len(net.layers):
+            continue
+        mp = net.layers[j + 1]
+        if not (mp.type == "maxpool" and not mp.folded and mp.size == 2 and mp.stride == 2 and mp.pad // 2 == 0
+                and mp.h % 2 == 0 and mp.w % 2 == 0):
+            continue
+        l.conv3_pool = 2
+        mp.folded = True
+        if net.sign_chains and j + 1 not in referenced and j + 2 < len(net.layers):
+            nxt = net.layers[j + 2]
+            if nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None and nxt.c % 32 != 0 and nxt.pool_desc is None:
+                l.emit_planes = True
+                nxt.sign_source = j
+                net.sign_links += 1
+
+
 def fold_maxpools(net: Network) -> None:
     """Marks every [maxpool] that only feeds the xnor convolution directly after it: the convolution then reads the
     maxpool's input and pools while packing (xnor_b200_conv_forward_pooled), and the maxpool layer does nothing."""
@@ -318,6 +351,21 @@ def _activate(x: torch.Tensor, a: str) -> torch.Tensor:
     if a == "logistic":
         return torch.sigmoid(x)
     raise ValueError(f"activation {a} not used by the xnor cfgs")
+
+
+def _float_conv3(net: Network, l: Layer, x: torch.Tensor) -> torch.Tensor:
+    """The 3-channel 3x3 first convolution: 2x2 blocks per thread, optional fused maxpool, optional sign-plane output."""
+    import ctypes as C
+    desc = capi.ConvDesc(net.batch, l.c, l.h, l.w, l.n, l.size, l.stride, l.pad, capi.LEAKY if l.activation == "leaky" else capi.LINEAR)
+    oh, ow = (l.out_h // 2, l.out_w // 2) if l.conv3_pool else (l.out_h, l.out_w)
+    if l.emit_planes:
+        out = torch.empty(net.batch, l.n, oh, (ow + 31) // 32, dtype=torch.int32, device=x.device)
+    else:
+        out = torch.empty(net.batch, l.n, oh, ow, dtype=torch.float32, device=x.device)
+    capi.check(capi.lib().xnor_b200_float_conv3_io(C.byref(desc), l.conv3_pool, x.data_ptr(), l.weights_gpu.data_ptr(), l.biases_gpu.data_ptr(),
+                                                  None if l.emit_planes else out.data_ptr(), out.data_ptr() if l.emit_planes else None,
+                                                  torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv3_io")
+    return out
 
 
 def _float_conv_small(net: Network, l: Layer, x: torch.Tensor) -> torch.Tensor:
@@ -426,6 +474,10 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
                     cur = None if l.emit_signs else out
                 else:
                     cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
+            elif l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1 and l.activation in ("leaky", "linear"):
+                cur = _float_conv3(net, l, cur.contiguous())
+                if l.emit_planes:
+                    l.sign_out, cur = cur, None
             elif l.c * l.size * l.size <= 128 and l.n <= 256 and l.activation in ("leaky", "linear"):
                 cur = _float_conv_small(net, l, cur)
             elif l.weights_blocked_gpu is not None:
@@ -463,12 +515,14 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
     return heads
 
 
-def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "cuda:0", sign_chains: bool = True) -> Network:
+def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "cuda:0", sign_chains: bool = True,
+                        fuse_first_conv: bool = True) -> Network:
     """load_network_custom (src-lib/weights.cpp:665-691): parse, load, fold batch-norm, pack binary weights."""
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
     net = parse_network_cfg(cfg, batch, device)
     net.sign_chains = sign_chains
+    net.fuse_first_conv = fuse_first_conv
     load_weights(net, weights)
     fuse_conv_batchnorm(net)
     calculate_binary_weights(net)

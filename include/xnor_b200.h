@@ -180,7 +180,10 @@ XNOR_B200_API int xnor_b200_conv_forward_pooled(const xnor_b200_conv_desc * desc
 /* Operands of xnor_b200_conv_forward_io.  Exactly one of input / input_signs and exactly one of output /
  * output_signs is non-NULL.
  *   input_signs   the previous xnor layer's output as sign bits, 32 channels per word, [batch][c/32][h*w] (with
- *                 `pool`: [batch][c/32][in_h*in_w] of the tensor in front of the maxpool); needs c % 32 == 0
+ *                 `pool`: [batch][c/32][in_h*in_w] of the tensor in front of the maxpool) when c % 32 == 0;
+ *                 when c % 32 != 0 (the first xnor layer behind a float convolution): x-packed sign planes
+ *                 [batch][c][h][ceil(w/32)], bit x%32 of word x/32 = "value at column x > 0", no `pool`
+ *                 (xnor_b200_float_conv3_io writes them already pooled)
  *   output_signs  this layer's output as sign bits only, [batch][n/32][out_h*out_w]; needs n % 32 == 0 and no
  *                 shortcut; the activation plays no role (leaky keeps the sign) */
 typedef struct xnor_b200_conv_io
@@ -212,6 +215,18 @@ XNOR_B200_API int xnor_b200_conv_forward_io(const xnor_b200_conv_desc * desc, co
  * results agree with cuDNN to rounding (about 1e-6 relative), not bit for bit. */
 XNOR_B200_API int xnor_b200_float_conv_small(const xnor_b200_conv_desc * desc, const float * input, const float * weights,
 		const float * biases, float * output, void * stream);
+
+/* The same first float layer when it has 3 input channels, size 3, stride 1, pad 1 (all xnor networks), computed as
+ * 2x2 output blocks per thread, optionally with the [maxpool] size 2 / stride 2 that follows it applied in registers
+ * (pool = 2, needs even h and w; pool = 0: none), and optionally reduced to what a following xnor layer reads:
+ *   output              fp32 [batch][n][h][w] (pool 0) or [batch][n][h/2][w/2] (pool 2), bias and activation applied
+ *   output_sign_planes  pool 2 only: sign of the pooled output as x-packed planes [batch][n][h/2][ceil(w/2/32)],
+ *                       the input_signs format of xnor_b200_conv_forward_io for c % 32 != 0
+ * Exactly one of the two is non-NULL.  Every value is formed as in xnor_b200_float_conv_small, so the planes equal
+ * the sign of maxpool(that call's output) bit for bit.  Replaces forward_convolutional_layer_gpu (float branch) +
+ * forward_maxpool_layer_gpu (src-lib/maxpool_layer_kernels.cu:48-86) + the sign step of the next layer. */
+XNOR_B200_API int xnor_b200_float_conv3_io(const xnor_b200_conv_desc * desc, int pool, const float * input, const float * weights,
+		const float * biases, float * output, uint32_t * output_sign_planes, void * stream);
 
 /* The float convolutions behind the path (many channels on a small map: the 3x3 256->512 layer on 13x13 and the
  * 1x1 layers in front of the yolo heads): the same float branch of forward_convolutional_layer_gpu

@@ -101,3 +101,77 @@ def test_float_conv_map_rejects_other_shapes():
         assert lib.xnor_b200_float_conv_map_weights_bytes(C.byref(bad)) == 0
         z = torch.zeros(64, device="cuda")
         assert lib.xnor_b200_float_conv_map(C.byref(bad), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None) == 1
+
+
+def _conv3(desc, pool, x, wt, b, planes=False):
+    n, h, w = desc.n, desc.h, desc.w
+    oh, ow = (h // 2, w // 2) if pool else (h, w)
+    if planes:
+        out = torch.full((desc.batch, n, oh, (ow + 31) // 32), -1, dtype=torch.int32, device="cuda")
+    else:
+        out = torch.full((desc.batch, n, oh, ow), float("nan"), dtype=torch.float32, device="cuda")
+    capi.check(capi.lib().xnor_b200_float_conv3_io(C.byref(desc), pool, x.data_ptr(), wt.data_ptr(), b.data_ptr(),
+                                                  None if planes else out.data_ptr(), out.data_ptr() if planes else None, None), "conv3_io")
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("case", [
+    (2, 40, 56, 16, 1), (1, 34, 18, 32, 0), (1, 66, 130, 20, 1), (1, 416, 416, 16, 1), (3, 8, 70, 8, 1),
+], ids=lambda c: "b%d_%dx%d_n%d_%d" % c)
+def test_float_conv3_io_equals_small_kernel_and_its_pooled_sign(case):
+    """Full-resolution output equals xnor_b200_float_conv_small bit for bit; the pooled output equals max_pool2d of it;
+    the sign planes equal the sign of the pooled output, packed along x."""
+    batch, h, w, n, leaky = case
+    x = torch.from_numpy(synth.bell(sum(case), (batch, 3, h, w), 1.0)).cuda()
+    wt = torch.from_numpy(synth.bell(sum(case) + 1, (n, 3, 3, 3), 0.3)).cuda()
+    b = torch.from_numpy(synth.bell(sum(case) + 2, (n,), 0.1)).cuda()
+    desc = capi.ConvDesc(batch, 3, h, w, n, 3, 1, 1, capi.LEAKY if leaky else capi.LINEAR)
+    ref = torch.empty(batch, n, h, w, device="cuda")
+    capi.check(capi.lib().xnor_b200_float_conv_small(C.byref(desc), x.data_ptr(), wt.data_ptr(), b.data_ptr(), ref.data_ptr(), None), "small")
+    full = _conv3(desc, 0, x, wt, b)
+    assert torch.equal(full, ref)
+    pooled = _conv3(desc, 2, x, wt, b)
+    want = torch.nn.functional.max_pool2d(ref, 2, 2)
+    assert torch.equal(pooled, want)
+    planes = _conv3(desc, 2, x, wt, b, planes=True).cpu().numpy().view(np.uint32)
+    pos = (want > 0).cpu().numpy()
+    ow = w // 2
+    padded = np.zeros(pos.shape[:3] + (((ow + 31) // 32) * 32,), dtype=bool)
+    padded[..., :ow] = pos
+    bits = padded.reshape(pos.shape[:3] + (-1, 32))
+    words = (bits.astype(np.uint64) << np.arange(32, dtype=np.uint64)).sum(-1).astype(np.uint32)
+    assert np.array_equal(planes, words)
+
+
+def test_float_conv3_planes_feed_the_bit_path_xnor_layer():
+    """conv 3->16 + maxpool + xnor conv 16->32: the xnor layer fed the sign planes gives the bits it gives on the fp32 tensor."""
+    from darknet_b200 import layer as L
+    batch, h, w = 2, 36, 76
+    x = torch.from_numpy(synth.bell(5, (batch, 3, h, w), 1.0)).cuda()
+    wt = torch.from_numpy(synth.bell(6, (16, 3, 3, 3), 0.3)).cuda()
+    b = torch.from_numpy(synth.bell(7, (16,), 0.1)).cuda()
+    desc = capi.ConvDesc(batch, 3, h, w, 16, 3, 1, 1, capi.LEAKY)
+    pooled = _conv3(desc, 2, x, wt, b)
+    planes = _conv3(desc, 2, x, wt, b, planes=True)
+    for stride in (1, 2):
+        l = L.make_convolutional_layer(batch, h // 2, w // 2, 16, 32, 3, stride, 1, capi.LEAKY)
+        l.load_weights(torch.from_numpy(synth.bell(8, (32, 16 * 9), 0.05)).cuda(), torch.from_numpy(synth.bell(9, (32,), 0.01)).cuda())
+        L.binary_align_weights(l)
+        want = L.forward_convolutional_layer_gpu(l, pooled).clone()
+        got = L.forward_convolutional_layer_io(l, x_signs=planes)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+
+
+def test_float_conv3_io_argument_checks():
+    lib = capi.lib()
+    z = torch.zeros(4096, device="cuda")
+    ok = capi.ConvDesc(1, 3, 8, 8, 8, 3, 1, 1, capi.LINEAR)
+    odd = capi.ConvDesc(1, 3, 9, 8, 8, 3, 1, 1, capi.LINEAR)
+    four = capi.ConvDesc(1, 4, 8, 8, 8, 3, 1, 1, capi.LINEAR)
+    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, None) == 2        # no output
+    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, z.data_ptr(), None) == 1  # planes need the pool
+    assert lib.xnor_b200_float_conv3_io(C.byref(odd), 2, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 1  # odd height
+    assert lib.xnor_b200_float_conv3_io(C.byref(four), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 1
+    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 3, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 1

@@ -67,7 +67,7 @@ def test_network_heads_match_cpu_oracle_network(port, tmp_path, name, size):
 
     # the per-layer check needs every fp32 tensor, so this network keeps them; the default network hands sign bits
     # from layer to layer where it can and must reach the same heads bit for bit
-    net = network.load_network_custom(str(cfg), str(w), 1, sign_chains=False)
+    net = network.load_network_custom(str(cfg), str(w), 1, sign_chains=False, fuse_first_conv=False)
     heads_gpu = [h.cpu() for h in network.forward_network_gpu(net, x.cuda())]
     linked = network.load_network_custom(str(cfg), str(w), 1)
     for a, b in zip(heads_gpu, network.forward_network_gpu(linked, x.cuda())):

@@ -82,7 +82,7 @@ def test_network_with_folded_maxpools_equals_unfolded(tmp_path):
     w = tmp_path / "net.weights"
     network.write_synthetic_weights(net_cpu, str(w), seed=5)
     x = torch.from_numpy(synth.uniform01(9, (2, 3, 96, 96))).cuda()
-    net = network.load_network_custom(str(cfg), str(w), 2, sign_chains=False)
+    net = network.load_network_custom(str(cfg), str(w), 2, sign_chains=False, fuse_first_conv=False)
     assert net.folded_maxpools == 0                     # below the batch threshold nothing is folded by default
     net.fold_maxpool_min_batch = 1
     network.fold_maxpools(net)

@@ -88,8 +88,9 @@ def test_network_with_sign_chains_equals_fp32_network(tmp_path, batch):
     network.write_synthetic_weights(net_cpu, str(w), seed=5)
     x = torch.from_numpy(synth.uniform01(9, (batch, 3, 96, 96))).cuda()
     linked = network.load_network_custom(str(cfg), str(w), batch)
-    plain = network.load_network_custom(str(cfg), str(w), batch, sign_chains=False)
-    assert linked.sign_links >= 3 and plain.sign_links == 0
+    plain = network.load_network_custom(str(cfg), str(w), batch, sign_chains=False, fuse_first_conv=False)
+    assert linked.sign_links >= 4 and plain.sign_links == 0
+    assert linked.layers[0].emit_planes and linked.layers[0].conv3_pool == 2
     got = network.forward_network_gpu(linked, x)
     want = network.forward_network_gpu(plain, x)
     assert len(got) == len(want) == 2
