@@ -40,10 +40,17 @@ class PoolDesc(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("size", "stride", "pad", "in_h", "in_w")]
 
 
+class SignSink(C.Structure):
+    """struct xnor_b200_sign_sink"""
+    _fields_ = [("consumer", C.POINTER(ConvDesc)), ("consumer_scratch", C.c_void_p), ("channel_offset", C.c_int), ("pool", C.c_int),
+                ("upsample", C.c_int), ("consumer_window_major", C.c_int)]
+
+
 class ConvIO(C.Structure):
     """struct xnor_b200_conv_io"""
     _fields_ = [("input", C.c_void_p), ("input_signs", C.c_void_p), ("pool", C.POINTER(PoolDesc)), ("output", C.c_void_p),
-                ("output_signs", C.c_void_p), ("shortcut_in", C.c_void_p), ("shortcut_out", C.c_void_p)]
+                ("output_signs", C.c_void_p), ("shortcut_in", C.c_void_p), ("shortcut_out", C.c_void_p),
+                ("input_packed", C.c_int), ("window_major", C.c_int), ("sinks", C.POINTER(SignSink)), ("n_sinks", C.c_int)]
 
 
 class ConvGeom(C.Structure):

@@ -121,32 +121,97 @@ extern "C" size_t xnor_b200_scratch_bytes(const xnor_b200_conv_desc * desc)
 	return round_up(g.packed_input_bytes, 256);
 }
 
-static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_pool_desc * pool, const float * input,
+// Fills the kernel-side description of one sign sink; checks that the tensor this layer produces (after the optional
+// pool / upsample) is exactly the consumer's input.
+static int make_sink(const xnor_b200_conv_desc * desc, const xnor_b200_conv_geom & g, const xnor_b200_sign_sink & in, SinkParams * out)
+{
+	const xnor_b200_conv_desc * c = in.consumer;
+	if (c == nullptr || in.consumer_scratch == nullptr) { return XNOR_B200_ERR_NULL; }
+	int rc = validate_desc(c);
+	if (rc != XNOR_B200_OK) { return rc; }
+	if (c->c % 32 != 0 || c->stride != 1 || 2 * c->pad != c->size - 1 || c->batch != desc->batch) { return XNOR_B200_ERR_INVALID; }
+	if (in.channel_offset < 0 || in.channel_offset % 32 != 0 || in.channel_offset + desc->n > c->c) { return XNOR_B200_ERR_INVALID; }
+	if ((in.pool != 0 && in.pool != 2) || (in.upsample != 0 && in.upsample != 1 && in.upsample != 2)) { return XNOR_B200_ERR_INVALID; }
+	if (in.pool == 2 && in.upsample == 2) { return XNOR_B200_ERR_INVALID; }
+	int h = g.out_h, w = g.out_w;
+	if (in.pool == 2)
+	{
+		if (h % 2 != 0 || w % 2 != 0) { return XNOR_B200_ERR_INVALID; }
+		h /= 2; w /= 2;
+	}
+	if (in.upsample == 2) { h *= 2; w *= 2; }
+	if (h != c->h || w != c->w) { return XNOR_B200_ERR_INVALID; }
+	if (in.consumer_window_major && (c->h % 2 != 0 || c->w % 2 != 0)) { return XNOR_B200_ERR_INVALID; }
+	if ((((uintptr_t)in.consumer_scratch) & 255u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
+	out->operand = (uint32_t *)in.consumer_scratch;
+	out->ldw = aligned_lda(c->size * c->size * c->c) / 32;
+	out->out_h = c->h; out->out_w = c->w; out->n_out = c->h * c->w;
+	out->ks = c->size; out->pad = c->pad; out->taps = c->size * c->size;
+	out->cb_offset = in.channel_offset / 32;
+	out->pool = in.pool;
+	out->up = (in.upsample == 2) ? 2 : 1;
+	out->win_w = in.consumer_window_major ? c->w / 2 : 0;
+	return XNOR_B200_OK;
+}
+
+static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_conv_io & io,
 		const uint8_t * align_bit_weights, const float * mean_arr, const float * biases,
-		float * output, const float * shortcut_in, float * shortcut_out,
-		void * scratch, size_t scratch_bytes, void * stream,
-		const uint32_t * input_signs = nullptr, uint32_t * output_signs = nullptr)
+		void * scratch, size_t scratch_bytes, void * stream)
 {
 	if (desc == nullptr || align_bit_weights == nullptr || mean_arr == nullptr || scratch == nullptr) { return XNOR_B200_ERR_NULL; }
-	if ((input == nullptr) == (input_signs == nullptr) || (output == nullptr) == (output_signs == nullptr)) { return XNOR_B200_ERR_NULL; }
-	if (output_signs != nullptr && (shortcut_out != nullptr || desc->n % 32 != 0)) { return XNOR_B200_ERR_INVALID; }
-	if (input_signs != nullptr && desc->c % 32 != 0 && pool != nullptr) { return XNOR_B200_ERR_INVALID; }
+	const int n_in = (io.input != nullptr) + (io.input_signs != nullptr) + (io.input_packed != 0);
+	if (n_in != 1) { return XNOR_B200_ERR_NULL; }
+	if (io.n_sinks < 0 || io.n_sinks > 2 || (io.n_sinks > 0 && io.sinks == nullptr)) { return XNOR_B200_ERR_INVALID; }
+	if (io.output != nullptr && io.output_signs != nullptr) { return XNOR_B200_ERR_INVALID; }
+	if (io.output == nullptr && io.output_signs == nullptr && io.n_sinks == 0) { return XNOR_B200_ERR_NULL; }
+	if ((io.output_signs != nullptr || io.n_sinks > 0) && desc->n % 32 != 0) { return XNOR_B200_ERR_INVALID; }
+	if (io.output_signs != nullptr && io.shortcut_out != nullptr) { return XNOR_B200_ERR_INVALID; }
+	if (io.input_signs != nullptr && desc->c % 32 != 0 && io.pool != nullptr) { return XNOR_B200_ERR_INVALID; }
+	if (io.input_packed && io.pool != nullptr) { return XNOR_B200_ERR_INVALID; }
 	xnor_b200_conv_geom g;
 	int rc = xnor_b200_conv_geometry(desc, &g);
 	if (rc != XNOR_B200_OK) { return rc; }
 	if (scratch_bytes < round_up(g.packed_input_bytes, 256)) { return XNOR_B200_ERR_SCRATCH; }
 	if ((((uintptr_t)scratch) & 255u) != 0 || (((uintptr_t)align_bit_weights) & 15u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
-	if (shortcut_out != nullptr && shortcut_in == nullptr) { return XNOR_B200_ERR_NULL; }
+	if (io.shortcut_out != nullptr && (io.shortcut_in == nullptr || io.output == nullptr)) { return XNOR_B200_ERR_NULL; }
+	if (io.window_major && (g.out_h % 2 != 0 || g.out_w % 2 != 0)) { return XNOR_B200_ERR_INVALID; }
+
+	GemmExtra extra = GemmExtra();
+	extra.win_w = io.window_major ? g.out_w / 2 : 0;
+	extra.out_w = g.out_w;
+	extra.n_sinks = io.n_sinks;
+	for (int i = 0; i < io.n_sinks; ++i)
+	{
+		rc = make_sink(desc, g, io.sinks[i], &extra.sinks[i]);
+		if (rc != XNOR_B200_OK) { return rc; }
+		if (io.sinks[i].pool == 2 && !io.window_major) { return XNOR_B200_ERR_INVALID; }
+	}
 
 	cudaStream_t s = (cudaStream_t)stream;
-	rc = (input_signs != nullptr)
-			? launch_pack_input(*desc, pool, reinterpret_cast<const float *>(input_signs), (uint32_t *)scratch, s, 1)
-			: launch_pack_input(*desc, pool, input, (uint32_t *)scratch, s, 0);
-	if (rc != XNOR_B200_OK) { return rc; }
+	if (!io.input_packed)
+	{
+		rc = (io.input_signs != nullptr)
+				? launch_pack_input(*desc, io.pool, reinterpret_cast<const float *>(io.input_signs), (uint32_t *)scratch, s, 1, io.window_major)
+				: launch_pack_input(*desc, io.pool, io.input, (uint32_t *)scratch, s, 0, io.window_major);
+		if (rc != XNOR_B200_OK) { return rc; }
+	}
+	const bool extras = (extra.win_w > 0 || extra.n_sinks > 0);
 	return launch_xnor_gemm(desc->n, desc->batch * g.n_out, g.n_out, g.k,
 			(const uint32_t *)align_bit_weights, g.new_lda / 32, (const uint32_t *)scratch, g.new_lda / 32,
-			output, g.n_out, mean_arr, biases, desc->activation == XNOR_B200_LEAKY,
-			shortcut_in, shortcut_out, nullptr, s, output_signs);
+			io.output, g.n_out, mean_arr, biases, desc->activation == XNOR_B200_LEAKY,
+			io.shortcut_in, io.shortcut_out, nullptr, s, io.output_signs, extras ? &extra : nullptr);
+}
+
+static xnor_b200_conv_io plain_io(const float * input, const xnor_b200_pool_desc * pool, float * output,
+		const float * shortcut_in, float * shortcut_out)
+{
+	xnor_b200_conv_io io = {};
+	io.input = input;
+	io.pool = pool;
+	io.output = output;
+	io.shortcut_in = shortcut_in;
+	io.shortcut_out = shortcut_out;
+	return io;
 }
 
 extern "C" int xnor_b200_conv_forward_io(const xnor_b200_conv_desc * desc, const xnor_b200_conv_io * io,
@@ -154,8 +219,7 @@ extern "C" int xnor_b200_conv_forward_io(const xnor_b200_conv_desc * desc, const
 		void * scratch, size_t scratch_bytes, void * stream)
 {
 	if (io == nullptr) { return XNOR_B200_ERR_NULL; }
-	return conv_forward_impl(desc, io->pool, io->input, align_bit_weights, mean_arr, biases, io->output,
-			io->shortcut_in, io->shortcut_out, scratch, scratch_bytes, stream, io->input_signs, io->output_signs);
+	return conv_forward_impl(desc, *io, align_bit_weights, mean_arr, biases, scratch, scratch_bytes, stream);
 }
 
 extern "C" int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const float * input,
@@ -163,7 +227,8 @@ extern "C" int xnor_b200_conv_forward(const xnor_b200_conv_desc * desc, const fl
 		float * output, const float * shortcut_in, float * shortcut_out,
 		void * scratch, size_t scratch_bytes, void * stream)
 {
-	return conv_forward_impl(desc, nullptr, input, align_bit_weights, mean_arr, biases, output, shortcut_in, shortcut_out,
+	if (input == nullptr || output == nullptr) { return XNOR_B200_ERR_NULL; }
+	return conv_forward_impl(desc, plain_io(input, nullptr, output, shortcut_in, shortcut_out), align_bit_weights, mean_arr, biases,
 			scratch, scratch_bytes, stream);
 }
 
@@ -173,6 +238,7 @@ extern "C" int xnor_b200_conv_forward_pooled(const xnor_b200_conv_desc * desc, c
 		void * scratch, size_t scratch_bytes, void * stream)
 {
 	if (pool == nullptr) { return XNOR_B200_ERR_NULL; }
-	return conv_forward_impl(desc, pool, input, align_bit_weights, mean_arr, biases, output, shortcut_in, shortcut_out,
+	if (input == nullptr || output == nullptr) { return XNOR_B200_ERR_NULL; }
+	return conv_forward_impl(desc, plain_io(input, pool, output, shortcut_in, shortcut_out), align_bit_weights, mean_arr, biases,
 			scratch, scratch_bytes, stream);
 }

@@ -48,8 +48,18 @@ struct PackParams
 	int pool_size, pool_stride, pool_off;
 	int in_h, in_w;
 	int pool_fast;       // 2x2 window, stride 2, origin 0, even in_h/in_w, 8-byte aligned planes: two float2 loads
+	int win_w;           // > 0: output rows of an image in 2x2-window-major pixel order (OW / 2), see out_row()
 	int from_planes;     // bit path: `in` holds sign planes uint32 [image][C][H][ceil(W/32)] (bit x%32 of word x/32) instead of floats
 };
+
+// Row of the packed operand that belongs to output pixel (oy, ox) of image b.  Row-major by default; window-major
+// (the four pixels of a 2x2 pool window on consecutive rows) when the layer's GEMM epilogue pools its output.
+__device__ __forceinline__ size_t out_row(const PackParams & p, int b, int oy, int ox)
+{
+	const size_t img = (size_t)b * p.OH * p.OW;
+	if (p.win_w > 0) { return img + ((size_t)(oy >> 1) * p.win_w + (ox >> 1)) * 4 + (oy & 1) * 2 + (ox & 1); }
+	return img + (size_t)oy * p.OW + ox;
+}
 
 // sign(maxpool(x)) at pooled position (iy, ix) of one channel plane: the maximum is > 0 exactly when some
 // in-image window element is > 0 (window origin -pad/2, out-of-image elements ignored:
@@ -111,7 +121,6 @@ __device__ __forceinline__ void words_phase_b(const PackParams & p, uint32_t * s
 	__syncthreads();
 
 	const int pixels = (y1 - y0) * p.OW;
-	const size_t row_base = (size_t)b * p.OH * p.OW + (size_t)y0 * p.OW;
 	const int lpp = 1 << p.lpp_shift;                                     // lanes per pixel: power of two >= min(nq, 32)
 	const int wq_first = threadIdx.x & (lpp - 1);
 	for (int pl = threadIdx.x >> p.lpp_shift; pl < pixels; pl += PK_THREADS >> p.lpp_shift)
@@ -121,7 +130,7 @@ __device__ __forceinline__ void words_phase_b(const PackParams & p, uint32_t * s
 		const int iy_base = (y0 + yl) * p.stride - p.pad - iy_lo;   // relative to the staged rows
 		const int ix_base = x * p.stride - p.pad;
 		const int base_off = iy_base * p.W + ix_base;
-		uint4 * dst = reinterpret_cast<uint4 *>(p.out + (row_base + pl) * p.ldw) + q_lo;
+		uint4 * dst = reinterpret_cast<uint4 *>(p.out + out_row(p, b, y0 + yl, x) * p.ldw) + q_lo;
 		for (int wq = wq_first; wq < nq; wq += lpp)
 		{
 			const uint4 e4 = reinterpret_cast<const uint4 *>(s_tab)[wq];
@@ -408,7 +417,6 @@ pack_input_bits_kernel(const PackParams p)
 	const int pixels = (y1 - y0) * p.OW;
 	const int n_groups = p.C * p.ks;
 	const uint32_t tap_mask = (p.ks >= 32) ? 0xffffffffu : ((1u << p.ks) - 1u);
-	const size_t row_base = (size_t)b * p.OH * p.OW + (size_t)y0 * p.OW;
 	for (int q = threadIdx.x; q < pixels * ldq; q += PK_THREADS)
 	{
 		const int pl = q / ldq;
@@ -444,7 +452,7 @@ pack_input_bits_kernel(const PackParams p)
 			if (++ky == p.ks) { ky = 0; plane += (size_t)RR * PW; }
 		}
 		if (outw < 4 && fill > 0) { v[outw] = (uint32_t)buf; }
-		reinterpret_cast<uint4 *>(p.out + (row_base + pl) * p.ldw)[wq] = make_uint4(v[0], v[1], v[2], v[3]);
+		reinterpret_cast<uint4 *>(p.out + out_row(p, b, y0 + yl, x) * p.ldw)[wq] = make_uint4(v[0], v[1], v[2], v[3]);
 	}
 }
 
@@ -496,7 +504,6 @@ pack_input_bits_s1_kernel(const PackParams p)
 	const int chunks = (p.OW + 31) >> 5;
 	const int tasks = (y1 - y0) * chunks * p.ldw;
 	const int taps = p.ks * p.ks;
-	const size_t row_base = (size_t)b * p.OH * p.OW + (size_t)y0 * p.OW;
 	for (int t = threadIdx.x; t < tasks; t += PK_THREADS)
 	{
 		const int kb = t % p.ldw;
@@ -504,12 +511,14 @@ pack_input_bits_s1_kernel(const PackParams p)
 		const int pc = rest % chunks;
 		const int yl = rest / chunks;
 		const int x0 = pc * 32;
-		uint32_t * dst = p.out + (row_base + (size_t)yl * p.OW + x0) * p.ldw + kb;
+		uint32_t * dst = p.out + kb;
+		const bool win = (p.win_w > 0);
+		const size_t r0 = out_row(p, b, y0 + yl, x0);      // x0 is a multiple of 32: the 32 pixels are 16 window halves in a row
 		const int npix = min(32, p.OW - x0);
 		int k = kb * 32;
 		if (k >= p.K)
 		{
-			for (int l = 0; l < npix; ++l) { dst[(size_t)l * p.ldw] = 0u; }
+			for (int l = 0; l < npix; ++l) { dst[(r0 + (win ? (size_t)((l >> 1) * 4 + (l & 1)) : (size_t)l)) * p.ldw] = 0u; }
 			continue;
 		}
 		int c = k / taps;
@@ -534,7 +543,7 @@ pack_input_bits_s1_kernel(const PackParams p)
 		#pragma unroll
 		for (int l = 0; l < 32; ++l)
 		{
-			if (l < npix) { dst[(size_t)l * p.ldw] = A[l]; }
+			if (l < npix) { dst[(r0 + (win ? (size_t)((l >> 1) * 4 + (l & 1)) : (size_t)l)) * p.ldw] = A[l]; }
 		}
 	}
 }
@@ -574,11 +583,12 @@ float_to_bit_kernel(const float * __restrict__ src, uint32_t * __restrict__ dst,
 }
 
 int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
-		uint32_t * t_bit_input, cudaStream_t stream, int from_signs)
+		uint32_t * t_bit_input, cudaStream_t stream, int from_signs, int window_major)
 {
 	if (from_signs && d.c % 32 != 0 && pool != nullptr) { return XNOR_B200_ERR_INVALID; }     // sign planes are made at the size the convolution sees
 	PackParams p;
 	p.from_planes = (from_signs && d.c % 32 != 0) ? 1 : 0;
+	p.win_w = 0;
 	p.pool_size = 0; p.pool_stride = 1; p.pool_off = 0; p.in_h = d.h; p.in_w = d.w; p.pool_fast = 0;
 	if (pool != nullptr)
 	{
@@ -596,6 +606,11 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc *
 	p.C = d.c; p.H = d.h; p.W = d.w;
 	p.OH = conv_out_dim(d.h, d.size, d.stride, d.pad);
 	p.OW = conv_out_dim(d.w, d.size, d.stride, d.pad);
+	if (window_major)
+	{
+		if (p.OH % 2 != 0 || p.OW % 2 != 0) { return XNOR_B200_ERR_INVALID; }
+		p.win_w = p.OW / 2;
+	}
 	p.ks = d.size; p.stride = d.stride; p.pad = d.pad;
 	p.K = d.size * d.size * d.c;
 	p.ldw = aligned_lda(p.K) / 32;

@@ -42,6 +42,32 @@ int ensure_dynamic_smem(const void * kernel, size_t bytes);
 
 // Internal launchers shared between translation units --------------------------------------
 
+// A consumer of sign bits that the GEMM epilogue feeds directly: the packed activation operand (t_bit_input) of a
+// following xnor layer with c % 32 == 0, stride 1.  Word (channel block, pixel) of this layer's output sign tensor is
+// stored at every (row, K-word) of that operand where the consumer's im2col would have put it.
+struct SinkParams
+{
+	uint32_t * operand;    // consumer's packed rows [image * n_out + row][ldw]
+	int ldw;               // words per row
+	int out_h, out_w;      // consumer's output map (= its input map: stride 1, "same" padding or 1x1)
+	int n_out;
+	int ks, pad, taps;
+	int cb_offset;         // first 32-channel block of the consumer's input that this producer fills (route concat)
+	int pool;              // 2: a 2x2 / stride-2 max-pool lies in between (OR of the four words); 0: none
+	int up;                // 2: a nearest-neighbour x2 upsample lies in between; 1: none
+	int win_w;             // consumer's rows are in 2x2-window-major order (out_w / 2), 0: row-major
+};
+
+// Optional extras of the integer GEMM.  win_w > 0: the columns of an image are this layer's pixels in
+// 2x2-window-major order (index ((y/2)*win_w + x/2)*4 + (y%2)*2 + x%2), so four consecutive columns are one pool window.
+struct GemmExtra
+{
+	int win_w;
+	int out_w;
+	int n_sinks;
+	SinkParams sinks[2];
+};
+
 // signs != nullptr: instead of C, only the sign bits of the output are written, 32 filters per word, laid out
 // [image][M/32][pixel] (requires M % 32 == 0).
 // GEMM with the batch folded into the column index: column j = b*n_per_image + p is written to
@@ -49,7 +75,8 @@ int ensure_dynamic_smem(const void * kernel, size_t bytes);
 int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
-		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs = nullptr);
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs = nullptr,
+		const GemmExtra * extra = nullptr);
 
 // Tensor-core (tcgen05, kind::i8 on bytes expanded in shared memory) variant of the same GEMM for large layers.
 bool tc_gemm_eligible(int M, int n_total, int K);
@@ -63,6 +90,6 @@ int read_tc_error(int * out, bool clear);
 // pool == nullptr: the tensor in memory is the convolution input; otherwise it is max-pooled on the fly.
 // from_signs != 0: `input` is not fp32 but the sign words [image][c/32][in_h*in_w] left by a sign-only GEMM epilogue.
 int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
-		uint32_t * t_bit_input, cudaStream_t stream, int from_signs = 0);
+		uint32_t * t_bit_input, cudaStream_t stream, int from_signs = 0, int window_major = 0);
 
 }  // namespace xnor

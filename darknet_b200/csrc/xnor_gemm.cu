@@ -54,7 +54,32 @@ struct GemmParams
 	int32_t * counts;       // when set: write integer agreement counts [M][n_total] instead of C
 	uint32_t * signs;       // when set: write only the sign bits of the output, 32 filters per word: [img][M/32][pixel]
 	int tiles_m, tiles_n;
+	GemmExtra x;            // window-major column order and direct sign sinks (all zero: none)
 };
+
+// Pixel (row-major index inside the image) of column `pixcol` of an image.
+__device__ __forceinline__ int col_to_pixel(const GemmParams & p, int pixcol)
+{
+	if (p.x.win_w == 0) { return pixcol; }
+	const int q = pixcol >> 2;
+	const int wy = q / p.x.win_w;
+	const int wx = q - wy * p.x.win_w;
+	return (2 * wy + ((pixcol >> 1) & 1)) * p.x.out_w + 2 * wx + (pixcol & 1);
+}
+
+// Stores sign word `word` of consumer-input pixel (iy, ix), channel block cb, at the place of the consumer's packed
+// operand where its im2col puts tap (ky, kx): K-word cb*taps + ky*ks + kx of output pixel (iy + pad - ky, ix + pad - kx).
+__device__ __forceinline__ void sink_store_tap(const SinkParams & s, int img, int iy, int ix, int cb, int tap, uint32_t word)
+{
+	const int ky = tap / s.ks;
+	const int kx = tap - ky * s.ks;
+	const int oy = iy + s.pad - ky;
+	const int ox = ix + s.pad - kx;
+	if (oy < 0 || oy >= s.out_h || ox < 0 || ox >= s.out_w) { return; }
+	const size_t row = (s.win_w > 0) ? ((size_t)(oy >> 1) * s.win_w + (ox >> 1)) * 4 + (oy & 1) * 2 + (ox & 1)
+	                                 : (size_t)oy * s.out_w + ox;
+	s.operand[((size_t)img * s.n_out + row) * s.ldw + (size_t)(s.cb_offset + cb) * s.taps + tap] = word;
+}
 
 __device__ __forceinline__ void cp_async_16(uint32_t * smem_dst, const uint32_t * gmem_src, bool valid)
 {
@@ -213,10 +238,10 @@ xnor_gemm_kernel(const GemmParams p)
 	// Sign-only epilogue: the next layer binarises this output anyway, so only (value > 0) is kept, packed 32
 	// filters to a word in the channel-packed layout the next pack kernel stages in shared memory.  Bytes go
 	// through shared memory because one thread's register tile holds filters that are TY rows apart.
-	if (p.signs != nullptr)
+	if (p.signs != nullptr || p.x.n_sinks > 0)
 	{
 		constexpr int SP = BN + 4;
-		static_assert(BM % 32 == 0 && BM * SP <= STAGES * (BM + BN) * PITCH * 4, "sign staging does not fit the ring");
+		static_assert(BM % 32 == 0 && BN % 4 == 0 && BM * SP + (BM / 32) * BN * 4 <= STAGES * (BM + BN) * PITCH * 4, "sign staging does not fit the ring");
 		uint8_t * s_sign = reinterpret_cast<uint8_t *>(smem);
 		__syncthreads();                                   // the operand ring (or the parked sums) is dead from here on
 		#pragma unroll
@@ -235,24 +260,68 @@ xnor_gemm_kernel(const GemmParams p)
 			}
 		}
 		__syncthreads();
+		// one thread per (32-filter word, column): assemble the word, keep it in shared memory for the sinks
 		const int mwords = p.M >> 5;
+		uint32_t * s_wd = smem + (BM * SP) / 4;                                  // [(BM/32)][BN], behind the sign bytes
 		for (int idx = threadIdx.x; idx < (BM / 32) * BN; idx += NT)
 		{
 			const int wl = idx / BN;
 			const int cl = idx - wl * BN;
+			uint32_t word = 0;
+			#pragma unroll
+			for (int k = 0; k < 32; ++k) { word |= (uint32_t)s_sign[(wl * 32 + k) * SP + cl] << k; }
+			s_wd[idx] = word;
 			const int col = n0 + cl;
 			const int mw = (m0 >> 5) + wl;
-			if (col < p.n_total && mw < mwords)
+			if (p.signs != nullptr && col < p.n_total && mw < mwords)
 			{
-				uint32_t word = 0;
-				#pragma unroll
-				for (int k = 0; k < 32; ++k) { word |= (uint32_t)s_sign[(wl * 32 + k) * SP + cl] << k; }
 				const int img = col / p.n_per_image;
-				const int pix = col - img * p.n_per_image;
-				p.signs[((size_t)img * mwords + mw) * p.n_per_image + pix] = word;
+				p.signs[((size_t)img * mwords + mw) * p.n_per_image + col_to_pixel(p, col - img * p.n_per_image)] = word;
 			}
 		}
-		return;
+		if (p.x.n_sinks > 0) { __syncthreads(); }
+		// sinks: one task per (word, column or window, copy, tap), spread over the whole CTA
+		#pragma unroll
+		for (int si = 0; si < 2; ++si)
+		{
+			if (si >= p.x.n_sinks) { break; }
+			const SinkParams & s = p.x.sinks[si];
+			const int cols = (s.pool != 0) ? BN / 4 : BN;
+			const int copies = (s.up == 2) ? 4 : 1;
+			const int tasks = (BM / 32) * cols * copies * s.taps;
+			for (int t = threadIdx.x; t < tasks; t += NT)
+			{
+				int r = t;
+				const int cg_ = r % cols;  r /= cols;
+				const int tap = r % s.taps; r /= s.taps;
+				const int cp = r % copies;
+				const int wl = r / copies;
+				const int mw = (m0 >> 5) + wl;
+				if (mw >= mwords) { continue; }
+				if (s.pool != 0)
+				{
+					const int col = n0 + cg_ * 4;
+					if (col >= p.n_total) { continue; }
+					const uint4 w4 = *reinterpret_cast<const uint4 *>(s_wd + wl * BN + cg_ * 4);
+					const int img = col / p.n_per_image;
+					const int q = (col - img * p.n_per_image) >> 2;      // window index: the four columns are one 2x2 window
+					const int wy = q / p.x.win_w;
+					sink_store_tap(s, img, wy, q - wy * p.x.win_w, mw, tap, w4.x | w4.y | w4.z | w4.w);
+				}
+				else
+				{
+					const int col = n0 + cg_;
+					if (col >= p.n_total) { continue; }
+					const int img = col / p.n_per_image;
+					const int pix = col_to_pixel(p, col - img * p.n_per_image);
+					int oy = pix / p.x.out_w;
+					int ox = pix - oy * p.x.out_w;
+					if (s.up == 2) { oy = 2 * oy + (cp >> 1); ox = 2 * ox + (cp & 1); }
+					sink_store_tap(s, img, oy, ox, mw, tap, s_wd[wl * BN + cg_]);
+				}
+			}
+		}
+		if (p.C == nullptr) { return; }
 	}
 
 	// epilogue
@@ -262,7 +331,7 @@ xnor_gemm_kernel(const GemmParams p)
 		const int col = n0 + j * TX + tx;
 		if (col >= p.n_total) { continue; }
 		const int img = col / p.n_per_image;
-		const int pix = col - img * p.n_per_image;
+		const int pix = col_to_pixel(p, col - img * p.n_per_image);
 		#pragma unroll
 		for (int i = 0; i < TM; ++i)
 		{
@@ -357,10 +426,25 @@ static float estimate_cycles(const TileConfig & c, int M, int n_total, int kw, i
 int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
-		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs)
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs,
+		const GemmExtra * extra)
 {
-	if (signs != nullptr && M % 32 != 0) { return XNOR_B200_ERR_INVALID; }
+	const bool extras = (extra != nullptr && (extra->win_w > 0 || extra->n_sinks > 0));
+	if ((signs != nullptr || (extra != nullptr && extra->n_sinks > 0)) && M % 32 != 0) { return XNOR_B200_ERR_INVALID; }
+	if (extras && counts != nullptr) { return XNOR_B200_ERR_INVALID; }
+	if (extras && n_per_image % 4 != 0 && (extra->win_w > 0)) { return XNOR_B200_ERR_INVALID; }
+	if (extras)
+	{
+		if (extra->n_sinks < 0 || extra->n_sinks > 2) { return XNOR_B200_ERR_INVALID; }
+		for (int i = 0; i < extra->n_sinks; ++i)
+		{
+			if (extra->sinks[i].pool != 0 && extra->win_w <= 0) { return XNOR_B200_ERR_INVALID; }   // a window must be four consecutive columns
+		}
+	}
 	GemmParams p;
+	p.x = GemmExtra();
+	if (extra != nullptr) { p.x = *extra; }
+	if (p.x.out_w <= 0) { p.x.out_w = 1; }
 	p.signs = signs;
 	p.A = A; p.B = B;
 	p.M = M; p.n_total = n_total; p.n_per_image = n_per_image; p.K = K;
@@ -374,7 +458,7 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	{
 		const char * tc = std::getenv("XNOR_B200_GEMM_TC");
 		const bool use_tc = (tc != nullptr) ? (tc[0] == '1') : tc_gemm_eligible(M, n_total, K);
-		if (use_tc)
+		if (use_tc && !extras)                                                   // sinks and window order live in this kernel only
 		{
 			return launch_xnor_gemm_tc(M, n_total, n_per_image, K, A, lda_words, B, ldb_words, C, ldc, mean_arr, bias, leaky,
 					shortcut_in, shortcut_out, counts, stream, signs);

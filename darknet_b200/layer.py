@@ -49,7 +49,9 @@ class ConvolutionalLayer:
         self.mean_arr_gpu = torch.zeros(n, dtype=torch.float32, device=self.device)
         self.align_bit_weights_gpu: Optional[torch.Tensor] = None
         self.output_gpu = torch.empty(batch, n, g.out_h, g.out_w, dtype=torch.float32, device=self.device)
-        self.scratch = torch.empty(capi.lib().xnor_b200_scratch_bytes(C.byref(self.desc)), dtype=torch.uint8, device=self.device)
+        # zero-filled: when producers write this operand through sinks, padding taps and row tails are never written
+        self.scratch = torch.zeros(capi.lib().xnor_b200_scratch_bytes(C.byref(self.desc)), dtype=torch.uint8, device=self.device)
+        self.window_major = False      # operand rows in 2x2-window-major pixel order (set when a sink of this layer pools)
         self.bin_conv_shortcut_in_gpu: Optional[torch.Tensor] = None
         self.bin_conv_shortcut_out_gpu: Optional[torch.Tensor] = None
 
@@ -133,25 +135,50 @@ def forward_convolutional_layer_gpu(l: ConvolutionalLayer, x: torch.Tensor, pool
     return l.output_gpu
 
 
+class Sink:
+    """One direct consumer of a layer's sign bits (struct xnor_b200_sign_sink): `consumer` is the ConvolutionalLayer
+    whose scratch the bits are written into, already in its packed-operand layout."""
+
+    def __init__(self, consumer: "ConvolutionalLayer", channel_offset: int = 0, pool: int = 0, upsample: int = 0) -> None:
+        self.consumer, self.channel_offset, self.pool, self.upsample = consumer, channel_offset, pool, upsample
+
+
 def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tensor] = None, x_signs: Optional[torch.Tensor] = None,
-                                   pool: Optional[capi.PoolDesc] = None, want_signs: bool = False) -> torch.Tensor:
-    """xnor_b200_conv_forward_io: the layer forward with optional sign-bit input (x_signs: int32 [batch][c/32][in_h*in_w])
-    and optional sign-bit output (returned as int32 [batch][n/32][out_h*out_w] instead of the fp32 tensor)."""
+                                   pool: Optional[capi.PoolDesc] = None, want_signs: bool = False, packed: bool = False,
+                                   sinks=(), want_output: Optional[bool] = None) -> Optional[torch.Tensor]:
+    """xnor_b200_conv_forward_io.  Input: fp32 `x`, sign words / planes `x_signs`, or `packed` (the producers' sinks have
+    filled l.scratch).  Output: the fp32 tensor (default when there are no sinks, or with want_output), the sign words
+    int32 [batch][n/32][out_h*out_w] (want_signs), and/or the consumers' operands (sinks)."""
     if l.align_bit_weights_gpu is None:
         raise RuntimeError("binary_align_weights() has not been called for this layer")
     io = capi.ConvIO()
     io.input = _ptr(x)
     io.input_signs = _ptr(x_signs)
     io.pool = C.pointer(pool) if pool is not None else None
+    io.input_packed = int(packed)
+    io.window_major = int(l.window_major)
+    if want_output is None:
+        want_output = not want_signs and not sinks
     out = None
     if want_signs:
         out = torch.empty(l.batch, l.n // 32, l.geom.n_out, dtype=torch.int32, device=l.device)
         io.output_signs = out.data_ptr()
-    else:
+    elif want_output:
         out = l.output_gpu
         io.output = out.data_ptr()
         io.shortcut_in = _ptr(l.bin_conv_shortcut_in_gpu)
         io.shortcut_out = _ptr(l.bin_conv_shortcut_out_gpu)
+    if sinks:
+        arr = (capi.SignSink * len(sinks))()
+        for i, s in enumerate(sinks):
+            arr[i].consumer = C.pointer(s.consumer.desc)
+            arr[i].consumer_scratch = s.consumer.scratch.data_ptr()
+            arr[i].channel_offset = s.channel_offset
+            arr[i].pool = s.pool
+            arr[i].upsample = s.upsample
+            arr[i].consumer_window_major = int(s.consumer.window_major)
+        io.sinks = arr
+        io.n_sinks = len(sinks)
     capi.check(capi.lib().xnor_b200_conv_forward_io(C.byref(l.desc), C.byref(io), l.align_bit_weights_gpu.data_ptr(),
                                                    l.mean_arr_gpu.data_ptr(), l.biases_gpu.data_ptr(), l.scratch.data_ptr(),
                                                    l.scratch.numel(), _stream()), "xnor_b200_conv_forward_io")

@@ -87,6 +87,11 @@ class Layer:
     conv3_pool: int = 0              # first float conv (3 channels, 3x3): 2 = the 2x2/2 maxpool behind it is applied in the kernel
     emit_planes: bool = False        # ... and only the sign planes of the pooled output are written
     emit_signs: bool = False
+    # direct sign sinks (xnor_b200_sign_sink): this xnor conv's epilogue fills the packed operand of later xnor convs
+    sinks: List = field(default_factory=list)      # of L.Sink
+    packed_input: bool = False       # xnor conv: every input channel arrives through producers' sinks
+    need_fp32: bool = True           # somebody still reads this layer's fp32 output
+    skip: bool = False               # maxpool / upsample / route that only sat between a sink producer and its consumer
     sign_source: Optional[int] = None
     sign_out: Optional[torch.Tensor] = None
     output_gpu: Optional[torch.Tensor] = None
@@ -111,6 +116,8 @@ class Network:
     fuse_first_conv: bool = True
     float_map_max_pixels: int = 4096       # batch*out_h*out_w up to which float convs use the cluster split-K kernel
     sign_links: int = 0
+    sink_max_batch: int = 2                # direct sinks keep a layer on the integer GEMM kernel: used at small batch only
+    sink_links: int = 0
 
 
 def parse_network_cfg(path: str, batch: int = 1, device: str = "cuda:0") -> Network:
@@ -255,11 +262,98 @@ def calculate_binary_weights(net: Network) -> None:
                 xl.bin_conv_shortcut_out_gpu = sc.output_gpu
     prepare_float_map_convs(net)
     if net.sign_chains:
+        link_sinks(net)
         link_sign_chains(net)
     if net.fuse_first_conv:
         link_first_conv(net)
     fold_maxpools(net)
     torch.cuda.synchronize(dev)
+
+
+def _readers(net: Network) -> Dict[int, List[int]]:
+    """Layer index -> indices of the layers that read its output."""
+    out: Dict[int, List[int]] = {i: [] for i in range(len(net.layers))}
+    for k, l in enumerate(net.layers):
+        if l.type == "route":
+            for i in l.input_layers:
+                out[i].append(k)
+            continue
+        if k > 0:
+            out[k - 1].append(k)
+        if l.type == "shortcut":
+            for i in l.input_layers:
+                out[i].append(k)
+    return out
+
+
+def link_sinks(net: Network) -> None:
+    """Finds xnor convolutions whose whole input comes from other xnor convolutions through nothing but a 2x2/stride-2
+    [maxpool], a stride-2 [upsample] or a [route]: those producers then write the consumer's packed operand from their
+    GEMM epilogue (sign sinks), the consumer runs without a pack kernel, and the layers in between are skipped when
+    nobody else reads them.  A producer keeps its fp32 output only if some other layer reads it."""
+    if net.batch > net.sink_max_batch:
+        return
+    layers = net.layers
+    readers = _readers(net)
+
+    def resolve(k: int, pool: int, up: int):
+        """Input expression of a consumer, walked backwards from layer k: [(producer, channel offset, pool, up, via)]."""
+        l = layers[k]
+        if l.type == "convolutional":
+            if l.xnor and l.xnor_layer is not None and l.n % 32 == 0 and not (k + 1 < len(layers) and layers[k + 1].blank):
+                return [(k, 0, pool, up, [])]
+            return None
+        if l.type == "maxpool" and pool == 0 and up == 0 and k > 0:
+            if l.size == 2 and l.stride == 2 and l.pad // 2 == 0 and l.h % 2 == 0 and l.w % 2 == 0 and not l.folded:
+                r = resolve(k - 1, 2, 0)
+                return None if r is None else [(p, o, pl, u, via + [k]) for p, o, pl, u, via in r]
+            return None
+        if l.type == "upsample" and pool == 0 and up == 0 and l.stride == 2 and k > 0:
+            r = resolve(k - 1, 0, 2)
+            return None if r is None else [(p, o, pl, u, via + [k]) for p, o, pl, u, via in r]
+        if l.type == "route":
+            parts, off = [], 0
+            for i in l.input_layers:
+                r = resolve(i, pool, up)
+                if r is None or off % 32 != 0:
+                    return None
+                parts += [(p, o + off, pl, u, via + [k]) for p, o, pl, u, via in r]
+                off += layers[i].out_c
+            return parts
+        return None
+
+    for k, c in enumerate(layers):
+        if not (c.type == "convolutional" and c.xnor and c.xnor_layer is not None and c.c % 32 == 0 and c.stride == 1
+                and 2 * c.pad == c.size - 1 and k > 0 and c.pool_desc is None and c.sign_source is None):
+            continue
+        expr = resolve(k - 1, 0, 0)
+        if expr is None:
+            continue
+        if any(len(layers[p].sinks) >= 2 for p, *_ in expr):
+            continue
+        c.packed_input = True
+        for p, off, pool, up, via in expr:
+            layers[p].sinks.append(L.Sink(c.xnor_layer, off, pool, up))
+            if pool == 2:
+                layers[p].xnor_layer.window_major = True
+            net.sink_links += 1
+    # which fp32 tensors are still read: walk backwards, a packed consumer reads none
+    for k in range(len(layers) - 1, -1, -1):
+        l = layers[k]
+        if not readers[k]:
+            l.need_fp32 = True                       # network output
+            continue
+        need = False
+        for r in readers[k]:
+            rl = layers[r]
+            if rl.type == "convolutional" and rl.packed_input:
+                continue
+            if rl.type in ("maxpool", "upsample", "route") and not rl.need_fp32:
+                continue
+            need = True
+        l.need_fp32 = need
+        if l.type in ("maxpool", "upsample", "route") and not need:
+            l.skip = True
 
 
 def link_sign_chains(net: Network) -> None:
@@ -275,6 +369,8 @@ def link_sign_chains(net: Network) -> None:
     for j, l in enumerate(net.layers):
         if not (l.type == "convolutional" and l.xnor and l.xnor_layer is not None and l.n % 32 == 0) or j in referenced or j + 1 >= n:
             continue
+        if l.sinks:
+            continue
         if net.layers[j + 1].blank:
             continue
         k = j + 1
@@ -283,7 +379,7 @@ def link_sign_chains(net: Network) -> None:
             pool = net.layers[k]
             k += 1
         consumer = net.layers[k]
-        if not (consumer.type == "convolutional" and consumer.xnor and consumer.xnor_layer is not None):
+        if not (consumer.type == "convolutional" and consumer.xnor and consumer.xnor_layer is not None) or consumer.packed_input:
             continue
         l.emit_signs = True
         consumer.sign_source = j
@@ -466,12 +562,14 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
                 nxt = net.layers[l.index + 1] if l.index + 1 < len(net.layers) else None
                 if nxt is not None and nxt.blank:
                     xl.bin_conv_shortcut_in_gpu = net.layers[nxt.input_layers[0]].output_gpu
-                if l.emit_signs or l.sign_source is not None:
+                if l.emit_signs or l.sign_source is not None or l.sinks or l.packed_input or xl.window_major:
                     src = net.layers[l.sign_source].sign_out if l.sign_source is not None else None
-                    out = L.forward_convolutional_layer_io(xl, x=None if src is not None else cur, x_signs=src,
-                                                           pool=l.pool_desc, want_signs=l.emit_signs)
+                    want_fp32 = not l.emit_signs and (l.need_fp32 or not l.sinks)
+                    out = L.forward_convolutional_layer_io(xl, x=None if (src is not None or l.packed_input) else cur, x_signs=src,
+                                                           pool=l.pool_desc, want_signs=l.emit_signs, packed=l.packed_input,
+                                                           sinks=l.sinks, want_output=want_fp32)
                     l.sign_out = out if l.emit_signs else None
-                    cur = None if l.emit_signs else out
+                    cur = out if want_fp32 else None
                 else:
                     cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
             elif l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1 and l.activation in ("leaky", "linear"):
@@ -490,6 +588,8 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
                 cur = _activate(y.view(b, l.n, l.out_h, l.out_w), l.activation)
             else:
                 cur = _activate(F.conv2d(cur, l.weights_gpu, l.biases_gpu, l.stride, l.pad), l.activation)
+        elif l.skip:
+            cur = None                            # only sat between a sink producer and its consumer
         elif l.type == "maxpool":
             if not l.folded:                      # a folded maxpool hands its input on untouched
                 cur = _maxpool(cur, l)

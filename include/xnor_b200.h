@@ -177,8 +177,8 @@ XNOR_B200_API int xnor_b200_conv_forward_pooled(const xnor_b200_conv_desc * desc
 		float * output, const float * shortcut_in, float * shortcut_out,
 		void * scratch, size_t scratch_bytes, void * stream);
 
-/* Operands of xnor_b200_conv_forward_io.  Exactly one of input / input_signs and exactly one of output /
- * output_signs is non-NULL.
+/* Operands of xnor_b200_conv_forward_io.  Exactly one of input / input_signs / input_packed is given; at least one
+ * of output, output_signs and sinks, and not both output and output_signs.
  *   input_signs   the previous xnor layer's output as sign bits, 32 channels per word, [batch][c/32][h*w] (with
  *                 `pool`: [batch][c/32][in_h*in_w] of the tensor in front of the maxpool) when c % 32 == 0;
  *                 when c % 32 != 0 (the first xnor layer behind a float convolution): x-packed sign planes
@@ -186,6 +186,23 @@ XNOR_B200_API int xnor_b200_conv_forward_pooled(const xnor_b200_conv_desc * desc
  *                 (xnor_b200_float_conv3_io writes them already pooled)
  *   output_signs  this layer's output as sign bits only, [batch][n/32][out_h*out_w]; needs n % 32 == 0 and no
  *                 shortcut; the activation plays no role (leaky keeps the sign) */
+/* A following xnor layer that this layer feeds directly: the GEMM epilogue stores every 32-filter sign word at each
+ * place of the consumer's packed activation operand (its scratch buffer) where the consumer's own im2col + bit-pack
+ * would have put it, so the consumer needs no pack kernel, and a [maxpool] size 2 / stride 2, an [upsample] stride 2
+ * or a [route] concatenation between the two layers needs no kernel either.  The consumer must have c % 32 == 0,
+ * stride 1 and size 3 / pad 1 or size 1 / pad 0, and the same batch.  consumer_scratch must have been zero-filled once
+ * (cudaMemset) before the first forward and be written by nothing else: padding taps and the alignment tail of every
+ * row are the zeros nobody ever overwrites. */
+typedef struct xnor_b200_sign_sink
+{
+	const xnor_b200_conv_desc * consumer;
+	void * consumer_scratch;       /* the scratch the consumer is later run with (input_packed = 1) */
+	int channel_offset;            /* first input channel of the consumer that this layer provides (multiple of 32) */
+	int pool;                      /* 2: a 2x2 / stride-2 max-pool lies in between (this layer then needs window_major = 1); 0: none */
+	int upsample;                  /* 2: a nearest-neighbour x2 upsample lies in between; 0 or 1: none */
+	int consumer_window_major;     /* the consumer is run with window_major = 1 */
+} xnor_b200_sign_sink;
+
 typedef struct xnor_b200_conv_io
 {
 	const float * input;
@@ -195,6 +212,12 @@ typedef struct xnor_b200_conv_io
 	uint32_t * output_signs;
 	const float * shortcut_in;
 	float * shortcut_out;
+	int input_packed;                     /* 1: the producers' sinks have already filled this layer's scratch; no input pointer */
+	int window_major;                     /* 1: the rows of this layer's packed operand (= the columns of its GEMM) are its output
+	                                         pixels in 2x2-window-major order, ((y/2)*(w/2) + x/2)*4 + (y%2)*2 + x%2, so that a
+	                                         pooled sink finds each window in four consecutive columns; outputs are unaffected */
+	const xnor_b200_sign_sink * sinks;    /* up to 2 direct consumers; may be combined with `output` (fp32 for a [route]) */
+	int n_sinks;
 } xnor_b200_conv_io;
 
 /* xnor_b200_conv_forward for chains of xnor layers.  A layer marked bin_output=1 feeds nothing but the next

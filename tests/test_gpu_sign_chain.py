@@ -89,7 +89,14 @@ def test_network_with_sign_chains_equals_fp32_network(tmp_path, batch):
     x = torch.from_numpy(synth.uniform01(9, (batch, 3, 96, 96))).cuda()
     linked = network.load_network_custom(str(cfg), str(w), batch)
     plain = network.load_network_custom(str(cfg), str(w), batch, sign_chains=False, fuse_first_conv=False)
-    assert linked.sign_links >= 4 and plain.sign_links == 0
+    assert plain.sign_links == 0 and plain.sink_links == 0
+    if batch <= linked.sink_max_batch:
+        # 2->4, 4->6, 6->8, 8->10 through maxpools, 12->13 directly, 13->18 through a route, 18->21 through upsample+route, 8->21 through the route
+        assert linked.sink_links == 8 and linked.sign_links >= 2
+        assert [l.index for l in linked.layers if l.skip] == [3, 5, 7, 9, 17, 19, 20]
+        assert not linked.layers[8].need_fp32 and linked.layers[13].need_fp32
+    else:
+        assert linked.sink_links == 0 and linked.sign_links >= 4
     assert linked.layers[0].emit_planes and linked.layers[0].conv3_pool == 2
     got = network.forward_network_gpu(linked, x)
     want = network.forward_network_gpu(plain, x)
