@@ -45,6 +45,8 @@ struct FloatMapParams
 	int splits;              // cluster size along z
 	int chans_per_split;
 	int leaky;
+	int yolo_entries;        // > 0: the layer feeds a [yolo] head with this many entries per anchor (4 + 1 + classes): logistic on
+	                         //      every entry but w, h (entries 2, 3), as forward_yolo_layer_gpu does right after this layer
 };
 
 __device__ __forceinline__ void cp_async_4z(float * smem_dst, const float * gmem_src, bool valid)
@@ -266,6 +268,11 @@ float_conv_map_kernel(const FloatMapParams p)
 		{
 			if (p.bias != nullptr) { sum += p.bias[f]; }
 			if (p.leaky) { sum = (sum > 0.0f) ? sum : sum * 0.1f; }
+			if (p.yolo_entries > 0)
+			{
+				const int e = f % p.yolo_entries;
+				if (e != 2 && e != 3) { sum = 1.0f / (1.0f + expf(-sum)); }
+			}
 			p.out[((size_t)img * p.N + f) * HW + q] = sum;
 		}
 	}
@@ -413,6 +420,13 @@ extern "C" int xnor_b200_float_conv_map_prepare(const xnor_b200_conv_desc * desc
 extern "C" int xnor_b200_float_conv_map(const xnor_b200_conv_desc * desc, const float * input, const float * blocked_weights,
 		const float * biases, float * output, void * stream)
 {
+	return xnor_b200_float_conv_map_yolo(desc, input, blocked_weights, biases, output, 0, stream);
+}
+
+extern "C" int xnor_b200_float_conv_map_yolo(const xnor_b200_conv_desc * desc, const float * input, const float * blocked_weights,
+		const float * biases, float * output, int yolo_entries, void * stream)
+{
+	if (yolo_entries < 0 || (yolo_entries > 0 && (yolo_entries < 5 || desc == nullptr || desc->n % yolo_entries != 0))) { return XNOR_B200_ERR_INVALID; }
 	if (desc == nullptr || input == nullptr || blocked_weights == nullptr || output == nullptr) { return XNOR_B200_ERR_NULL; }
 	int rc = validate_desc(desc);
 	if (rc != XNOR_B200_OK) { return rc; }
@@ -424,6 +438,7 @@ extern "C" int xnor_b200_float_conv_map(const xnor_b200_conv_desc * desc, const 
 	p.C = desc->c; p.H = desc->h; p.W = desc->w; p.N = desc->n;
 	p.K = desc->c * desc->size * desc->size;
 	p.leaky = (desc->activation == XNOR_B200_LEAKY) ? 1 : 0;
+	p.yolo_entries = yolo_entries;
 	// channels per pipeline stage: 16 for 3x3 on the small pitch when the channel count allows (half the barriers)
 	if (desc->size == 1) { return launch_float_map_best<1, 16, 32>(desc, p, (cudaStream_t)stream); }
 	if (desc->h <= 14 && desc->w <= 14)

@@ -84,6 +84,10 @@ class Layer:
     pool_desc: Optional[capi.PoolDesc] = None
     # xnor conv whose only reader is another xnor conv (directly or through a maxpool): hands over sign bits
     weights_blocked_gpu: Optional[torch.Tensor] = None     # float conv on a small map: weights re-blocked at load time
+    branch_start: bool = False       # first / last layer of a head branch that runs on the side stream
+    branch_end: bool = False
+    yolo_entries: int = 0            # float conv in front of a [yolo] layer: the head's logistic step runs in the conv epilogue
+    yolo_done: bool = False          # [yolo] layer whose activation the previous layer already applied
     conv3_pool: int = 0              # first float conv (3 channels, 3x3): 2 = the 2x2/2 maxpool behind it is applied in the kernel
     emit_planes: bool = False        # ... and only the sign planes of the pooled output are written
     emit_signs: bool = False
@@ -116,6 +120,8 @@ class Network:
     fuse_first_conv: bool = True
     float_map_max_pixels: int = 4096       # batch*out_h*out_w up to which float convs use the cluster split-K kernel
     sign_links: int = 0
+    side_branches: bool = True             # a head branch that nothing later reads runs on a second stream
+    side_stream: Optional[torch.cuda.Stream] = None
     sink_max_batch: int = 2                # direct sinks keep a layer on the integer GEMM kernel: used at small batch only
     sink_links: int = 0
 
@@ -261,6 +267,7 @@ def calculate_binary_weights(net: Network) -> None:
                 sc.output_gpu = torch.empty(net.batch, sc.out_c, sc.out_h, sc.out_w, device=dev)
                 xl.bin_conv_shortcut_out_gpu = sc.output_gpu
     prepare_float_map_convs(net)
+    link_branches(net)
     if net.sign_chains:
         link_sinks(net)
         link_sign_chains(net)
@@ -284,6 +291,24 @@ def _readers(net: Network) -> Dict[int, List[int]]:
             for i in l.input_layers:
                 out[i].append(k)
     return out
+
+
+def link_branches(net: Network) -> None:
+    """A [route] with one input i < k-1 starts a second branch at layer i; when nothing at or behind the route reads the
+    layers i+1 .. k-1 (they end in a detection head), those layers are independent of everything that follows and run
+    on a side stream, concurrently with the rest of the network.  Every kernel of a batch-1 forward fills a fraction of
+    the GPU, so the two branches overlap almost completely."""
+    if not net.side_branches:
+        return
+    readers = _readers(net)
+    for k, r in enumerate(net.layers):
+        if r.type != "route" or len(r.input_layers) != 1 or r.input_layers[0] >= k - 1:
+            continue
+        i = r.input_layers[0]
+        inside = set(range(i + 1, k))
+        if all(set(readers[j]) <= inside for j in inside) and not any(net.layers[j].branch_start for j in inside):
+            net.layers[i + 1].branch_start = True
+            net.layers[k - 1].branch_end = True
 
 
 def link_sinks(net: Network) -> None:
@@ -491,6 +516,11 @@ def prepare_float_map_convs(net: Network) -> None:
         nbytes = capi.lib().xnor_b200_float_conv_map_weights_bytes(C.byref(desc))
         if nbytes == 0:
             continue
+        nxt = net.layers[l.index + 1] if l.index + 1 < len(net.layers) else None
+        if (nxt is not None and nxt.type == "yolo" and l.activation == "linear" and float(nxt.opts.get("scale_x_y", 1)) == 1.0
+                and l.n % (5 + int(nxt.opts.get("classes", 20))) == 0):
+            l.yolo_entries = 5 + int(nxt.opts.get("classes", 20))
+            nxt.yolo_done = True
         l.weights_blocked_gpu = torch.empty(nbytes // 4, dtype=torch.float32, device=l.weights_gpu.device)
         capi.check(capi.lib().xnor_b200_float_conv_map_prepare(C.byref(desc), l.weights_gpu.data_ptr(), l.weights_blocked_gpu.data_ptr(),
                                                               torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_map_prepare")
@@ -501,8 +531,9 @@ def _float_conv_map(net: Network, l: Layer, x: torch.Tensor) -> torch.Tensor:
     import ctypes as C
     desc = _map_conv_desc(net, l)
     out = torch.empty(net.batch, l.n, l.out_h, l.out_w, dtype=torch.float32, device=x.device)
-    capi.check(capi.lib().xnor_b200_float_conv_map(C.byref(desc), x.data_ptr(), l.weights_blocked_gpu.data_ptr(), l.biases_gpu.data_ptr(),
-                                                  out.data_ptr(), torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_map")
+    capi.check(capi.lib().xnor_b200_float_conv_map_yolo(C.byref(desc), x.data_ptr(), l.weights_blocked_gpu.data_ptr(), l.biases_gpu.data_ptr(),
+                                                       out.data_ptr(), l.yolo_entries, torch.cuda.current_stream().cuda_stream),
+               "xnor_b200_float_conv_map_yolo")
     return out
 
 
@@ -555,7 +586,18 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
     network's head layers (yolo / region / softmax)."""
     heads: List[torch.Tensor] = []
     cur = x
+    side_ctx = None
+    joins: List[torch.cuda.Event] = []
     for l in net.layers:
+        if l.branch_start and x.is_cuda:
+            # fork: the side stream picks up after the layer that feeds both branches
+            if net.side_stream is None:
+                net.side_stream = torch.cuda.Stream(x.device)
+            fork = torch.cuda.Event()
+            fork.record(torch.cuda.current_stream())
+            net.side_stream.wait_event(fork)
+            side_ctx = torch.cuda.stream(net.side_stream)
+            side_ctx.__enter__()
         if l.type == "convolutional":
             if l.xnor:
                 xl = l.xnor_layer
@@ -606,23 +648,32 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
             cur = torch.softmax(cur.reshape(cur.shape[0], -1), 1).reshape(cur.shape)
             heads.append(cur)
         elif l.type == "yolo":
-            cur = _yolo(cur, l)
+            cur = cur if l.yolo_done else _yolo(cur, l)
             heads.append(cur)
         elif l.type == "region":
             cur = _region(cur, l)
             heads.append(cur)
         l.output_gpu = cur
+        if l.branch_end and side_ctx is not None:
+            done = torch.cuda.Event()
+            done.record(net.side_stream)
+            joins.append(done)
+            side_ctx.__exit__(None, None, None)
+            side_ctx = None
+    for done in joins:                                # join: the caller's stream sees both branches finished
+        torch.cuda.current_stream().wait_event(done)
     return heads
 
 
 def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "cuda:0", sign_chains: bool = True,
-                        fuse_first_conv: bool = True) -> Network:
+                        fuse_first_conv: bool = True, side_branches: bool = True) -> Network:
     """load_network_custom (src-lib/weights.cpp:665-691): parse, load, fold batch-norm, pack binary weights."""
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
     net = parse_network_cfg(cfg, batch, device)
     net.sign_chains = sign_chains
     net.fuse_first_conv = fuse_first_conv
+    net.side_branches = side_branches
     load_weights(net, weights)
     fuse_conv_batchnorm(net)
     calculate_binary_weights(net)

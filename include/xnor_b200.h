@@ -263,6 +263,10 @@ XNOR_B200_API size_t xnor_b200_float_conv_map_weights_bytes(const xnor_b200_conv
 XNOR_B200_API int xnor_b200_float_conv_map_prepare(const xnor_b200_conv_desc * desc, const float * weights, float * blocked, void * stream);
 XNOR_B200_API int xnor_b200_float_conv_map(const xnor_b200_conv_desc * desc, const float * input, const float * blocked_weights,
 		const float * biases, float * output, void * stream);
+/* Same, for the convolution right in front of a [yolo] layer: yolo_entries = 4 + 1 + classes (n must be a multiple of
+ * it) also applies that layer's activation step (xnor_b200_yolo_activate below) to the result; 0 = plain call. */
+XNOR_B200_API int xnor_b200_float_conv_map_yolo(const xnor_b200_conv_desc * desc, const float * input, const float * blocked_weights,
+		const float * biases, float * output, int yolo_entries, void * stream);
 
 /* The activation step of forward_yolo_layer_gpu (src-lib/yolo_layer.cpp:1439-1489) behind the path: logistic on the
  * x, y, objectness and class entries of every anchor, w and h raw, in one pass.  input/output

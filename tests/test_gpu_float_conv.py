@@ -175,3 +175,24 @@ def test_float_conv3_io_argument_checks():
     assert lib.xnor_b200_float_conv3_io(C.byref(odd), 2, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 1  # odd height
     assert lib.xnor_b200_float_conv3_io(C.byref(four), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 1
     assert lib.xnor_b200_float_conv3_io(C.byref(ok), 3, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 1
+
+
+def test_float_conv_map_yolo_equals_conv_then_yolo_activate():
+    batch, c, h, w, classes = 2, 64, 13, 13, 80
+    n = 3 * (5 + classes)
+    x = torch.from_numpy(synth.bell(71, (batch, c, h, w), 1.0)).cuda()
+    wt = torch.from_numpy(synth.bell(72, (n, c, 1, 1), 0.2)).cuda()
+    b = torch.from_numpy(synth.bell(73, (n,), 0.5)).cuda()
+    desc = capi.ConvDesc(batch, c, h, w, n, 1, 1, 0, capi.LINEAR)
+    lib = capi.lib()
+    blocked = torch.empty(lib.xnor_b200_float_conv_map_weights_bytes(C.byref(desc)) // 4, device="cuda")
+    capi.check(lib.xnor_b200_float_conv_map_prepare(C.byref(desc), wt.data_ptr(), blocked.data_ptr(), None), "prepare")
+    raw = torch.empty(batch, n, h, w, device="cuda")
+    capi.check(lib.xnor_b200_float_conv_map(C.byref(desc), x.data_ptr(), blocked.data_ptr(), b.data_ptr(), raw.data_ptr(), None), "map")
+    want = torch.empty_like(raw)
+    capi.check(lib.xnor_b200_yolo_activate(raw.data_ptr(), want.data_ptr(), batch, 3, classes, h * w, None), "yolo")
+    got = torch.empty_like(raw)
+    capi.check(lib.xnor_b200_float_conv_map_yolo(C.byref(desc), x.data_ptr(), blocked.data_ptr(), b.data_ptr(), got.data_ptr(), 5 + classes, None), "map yolo")
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert lib.xnor_b200_float_conv_map_yolo(C.byref(desc), x.data_ptr(), blocked.data_ptr(), b.data_ptr(), got.data_ptr(), 7, None) == 1

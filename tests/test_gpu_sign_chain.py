@@ -88,7 +88,8 @@ def test_network_with_sign_chains_equals_fp32_network(tmp_path, batch):
     network.write_synthetic_weights(net_cpu, str(w), seed=5)
     x = torch.from_numpy(synth.uniform01(9, (batch, 3, 96, 96))).cuda()
     linked = network.load_network_custom(str(cfg), str(w), batch)
-    plain = network.load_network_custom(str(cfg), str(w), batch, sign_chains=False, fuse_first_conv=False)
+    plain = network.load_network_custom(str(cfg), str(w), batch, sign_chains=False, fuse_first_conv=False, side_branches=False)
+    assert linked.layers[14].branch_start and linked.layers[16].branch_end and not plain.layers[14].branch_start
     assert plain.sign_links == 0 and plain.sink_links == 0
     if batch <= linked.sink_max_batch:
         # 2->4, 4->6, 6->8, 8->10 through maxpools, 12->13 directly, 13->18 through a route, 18->21 through upsample+route, 8->21 through the route
