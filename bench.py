@@ -240,6 +240,12 @@ def run_gpu_arm(args) -> None:
     with torch.cuda.graph(graph, stream=stream):
         heads = network.forward_network_gpu(net, x_dev)
     head_host = [torch.empty(h.shape, dtype=h.dtype).pin_memory() for h in heads]
+    # the end-to-end step as one graph: input copy from pinned memory, forward, every head copied to pinned memory on
+    # the stream that produced it
+    graph_e2e = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph_e2e, stream=stream):
+        x_dev.copy_(x_host, non_blocking=True)
+        heads_e2e = network.forward_network_gpu(net, x_dev, head_host)
     h2d_bytes = x_host.numel() * 4
     d2h_bytes = sum(h.numel() * 4 for h in heads)
 
@@ -258,11 +264,9 @@ def run_gpu_arm(args) -> None:
                 flush.fill_(1)
                 a.record(stream)
                 if end_to_end:
-                    x_dev.copy_(x_host, non_blocking=True)
-                graph.replay()
-                if end_to_end:
-                    for hh, hd in zip(head_host, heads):
-                        hh.copy_(hd, non_blocking=True)
+                    graph_e2e.replay()
+                else:
+                    graph.replay()
                 b.record(stream)
         stream.synchronize()
         return float(sum(a.elapsed_time(b) for a, b in evs))
@@ -281,6 +285,9 @@ def run_gpu_arm(args) -> None:
     ms_e2e = timed_steps(args.steps, True)
     barrier()
     ms_e2e = max_over_ranks(ms_e2e)
+    for hh, hd in zip(head_host, heads_e2e):           # the pinned host copies are the device heads of the last step
+        if not torch.equal(hh, hd.cpu()):
+            raise SystemExit("bench: host copy of a head differs from the device tensor")
     clocks = sampler.stop() if sampler else None
 
     value = world * batch * args.steps / (ms_total * 1e-3)
@@ -340,7 +347,7 @@ def run_gpu_arm(args) -> None:
         bmma_peak_tops = g_.value / 1e3
         achieved = binops_per_image * batch / (ms_gemm * 1e-3) / 1e12
         roofline = {
-            "kernel": "xnor_gemm_kernel (9 launches = the xnor layers of one forward)",
+            "kernel": "xnor_gemm_kernel (9 launches = the xnor layers of one forward, stand-alone calls with fp32 epilogue)",
             "bound": "int_popc", "achieved": achieved, "peak": popc_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)",
             "frac": achieved / popc_peak_tops, "traffic": None,
             "peak_source": "measured in this run: register-resident XOR+POPC+ADD loop on all SMs",
@@ -355,7 +362,7 @@ def run_gpu_arm(args) -> None:
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
         pack_gbs = pack_bytes / (ms_pack * 1e-3) / 1e9
         pack_roofline = {
-            "kernel": "pack_input_*_kernel (9 launches)", "bound": "hbm", "achieved": pack_gbs, "peak": hbm_peak, "unit": "GB/s",
+            "kernel": "pack_input_*_kernel (9 launches: every xnor layer's stand-alone xnor_b200_pack_input; the linked forward replaces most of them by sign sinks)", "bound": "hbm", "achieved": pack_gbs, "peak": hbm_peak, "unit": "GB/s",
             "frac": pack_gbs / hbm_peak, "traffic": None, "ms_per_forward": ms_pack,
             "peak_source": "MEASURED_PEAKS.json (of measured)" if peaks else "fallback 6650 GB/s (of fallback)",
         }
@@ -413,16 +420,17 @@ def run_gpu_arm(args) -> None:
             "metric": metric_text, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u32", "data": "synthetic",
-            "config": {"workload": workload_text, "global_batch": world * batch, "folded_maxpools": net.folded_maxpools, "parallelism": f"replicas x{world} (no collective)",
+            "config": {"workload": workload_text, "global_batch": world * batch, "folded_maxpools": net.folded_maxpools, "sign_sinks": net.sink_links, "sign_links": net.sign_links,
+                       "side_branch": any(l.branch_start for l in net.layers), "parallelism": f"replicas x{world} (no collective)",
                        "l2": "256 MiB buffer written between timed steps", "timing": "per-step CUDA events on the launch stream, CUDA graph replay",
-                       "float_layers": "cuDNN/ATen fp32 (outside the path, as in Darknet)",
+                       "float_layers": "this library's fp32 kernels at small batch (first conv + pool + sign, small-map convs with the yolo activation), cuDNN/ATen otherwise",
                        "xnor_binops_per_image": binops_per_image},
             "xnor_gemm_tops": roofline["achieved"] if roofline else None,
             "roofline": roofline, "roofline_pack": pack_roofline, "roofline_large_batch": large_roofline, "roofline_pack_large_batch": large_pack_roofline,
             "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": args.steps * net.xnor_launches_per_forward,
+            "gpu_launches": args.steps * network.own_launches_per_forward(net),
             "clocks": clocks,
         }
         print(json.dumps(line))

@@ -581,9 +581,11 @@ def _region(x: torch.Tensor, l: Layer) -> torch.Tensor:
     return v.reshape(b, -1, l.h, l.w)
 
 
-def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
+def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
     """The layer loop of forward_network_gpu (src-lib/network_kernels.cu:30-65).  Returns the outputs of the
-    network's head layers (yolo / region / softmax)."""
+    network's head layers (yolo / region / softmax).  heads_host: pinned host tensors, one per head; each head is
+    copied there as soon as it exists, on the stream that made it (Darknet's yolo layer pulls its output to the host
+    in every forward, src-lib/yolo_layer.cpp:1439-1489), so the copy of an early head overlaps the rest of the network."""
     heads: List[torch.Tensor] = []
     cur = x
     side_ctx = None
@@ -647,12 +649,18 @@ def forward_network_gpu(net: Network, x: torch.Tensor) -> List[torch.Tensor]:
         elif l.type == "softmax":
             cur = torch.softmax(cur.reshape(cur.shape[0], -1), 1).reshape(cur.shape)
             heads.append(cur)
+            if heads_host is not None:
+                heads_host[len(heads) - 1].copy_(cur, non_blocking=True)
         elif l.type == "yolo":
             cur = cur if l.yolo_done else _yolo(cur, l)
             heads.append(cur)
+            if heads_host is not None:
+                heads_host[len(heads) - 1].copy_(cur, non_blocking=True)
         elif l.type == "region":
             cur = _region(cur, l)
             heads.append(cur)
+            if heads_host is not None:
+                heads_host[len(heads) - 1].copy_(cur, non_blocking=True)
         l.output_gpu = cur
         if l.branch_end and side_ctx is not None:
             done = torch.cuda.Event()
@@ -678,6 +686,20 @@ def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "c
     fuse_conv_batchnorm(net)
     calculate_binary_weights(net)
     return net
+
+
+def own_launches_per_forward(net: Network) -> int:
+    """Kernels of libxnor_b200.so that one forward launches, after every fusion that load_network_custom set up."""
+    n = 0
+    for l in net.layers:
+        if l.type == "convolutional":
+            if l.xnor:
+                n += 1 if l.packed_input else 2                   # GEMM (+ pack kernel)
+            elif (l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1) or l.c * l.size * l.size <= 128 or l.weights_blocked_gpu is not None:
+                n += 1
+        elif l.type == "yolo" and not l.yolo_done:
+            n += 1
+    return n
 
 
 def xnor_layer_shapes(net: Network) -> List[dict]:
