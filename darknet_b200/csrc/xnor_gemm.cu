@@ -353,6 +353,123 @@ xnor_gemm_kernel(const GemmParams p)
 	}
 }
 
+// ---- short-K kernel ---------------------------------------------------------------------------
+// Layers with very short rows (K <= 256 bits: 16 channels x 3x3, or a 1x1 layer over <= 256 channels) on a small batch.  The tiled kernel above
+// spends ~110 instructions per output on them (ring management, staging, per-output index arithmetic) for ~15 that
+// are arithmetic.  Here a thread keeps the packed row of ONE pixel in registers and walks the 32 filters of its
+// filter group, whose packed rows sit in shared memory and are read as broadcasts: per (pixel, filter) KW4 16-byte
+// loads, 4*KW4 XOR + POPC + ADD, one multiply-add for the value.  The thread ends up holding the complete sign word of
+// its pixel, so the sign outputs and sinks need no staging: a pooled sink is an OR over the four lanes of a window.
+constexpr int SK_THREADS = 128;
+
+// FPT = filters per thread (32: a thread owns the whole sign word of its pixel; 8: four neighbouring lanes share a
+// pixel and combine their byte of the word with two shuffles -- used when there are too few pixels to fill the GPU).
+template <int KW4, int FPT>
+__global__ void __launch_bounds__(SK_THREADS)
+xnor_gemm_smallk_kernel(const GemmParams p)
+{
+	constexpr int SUBS = 32 / FPT;
+	__shared__ __align__(16) uint32_t s_a[32 * KW4 * 4];
+	const int m0 = blockIdx.y * 32;
+	for (int i = threadIdx.x; i < 32 * KW4; i += SK_THREADS)
+	{
+		const int f = i / KW4;
+		const int q = i - f * KW4;
+		uint4 v = make_uint4(0u, 0u, 0u, 0u);
+		if (m0 + f < p.M) { v = __ldg(reinterpret_cast<const uint4 *>(p.A + (size_t)(m0 + f) * p.lda_words) + q); }
+		reinterpret_cast<uint4 *>(s_a)[i] = v;
+	}
+	const int sub = threadIdx.x % SUBS;
+	const int col = blockIdx.x * (SK_THREADS / SUBS) + threadIdx.x / SUBS;
+	const bool live = (col < p.n_total);
+	uint4 b[KW4];
+	#pragma unroll
+	for (int q = 0; q < KW4; ++q)
+	{
+		b[q] = live ? __ldg(reinterpret_cast<const uint4 *>(p.B + (size_t)col * p.ldb_words) + q) : make_uint4(0u, 0u, 0u, 0u);
+	}
+	const int img = live ? col / p.n_per_image : 0;
+	const int pixcol = live ? col - img * p.n_per_image : 0;
+	const int pix = col_to_pixel(p, pixcol);
+	__syncthreads();
+
+	uint32_t word = 0;
+	#pragma unroll 4
+	for (int ff = 0; ff < FPT; ++ff)
+	{
+		const int f = sub * FPT + ff;
+		const int m = m0 + f;
+		if (m >= p.M) { break; }
+		int cnt = 0;
+		#pragma unroll
+		for (int q = 0; q < KW4; ++q)
+		{
+			const uint4 a = reinterpret_cast<const uint4 *>(s_a)[f * KW4 + q];
+			cnt += __popc(a.x ^ b[q].x) + __popc(a.y ^ b[q].y) + __popc(a.z ^ b[q].z) + __popc(a.w ^ b[q].w);
+		}
+		float v = __fmul_rn((float)(p.K - 2 * cnt), __ldg(p.mean_arr + m));
+		if (p.bias != nullptr) { v = __fadd_rn(v, __ldg(p.bias + m)); }
+		word |= (v > 0.0f ? 1u : 0u) << f;
+		if (p.C != nullptr && live)
+		{
+			if (p.leaky) { v = (v < 0.0f) ? __fmul_rn(v, 0.1f) : v; }
+			p.C[((size_t)img * p.M + m) * p.ldc + pix] = v;
+		}
+	}
+	if (p.signs == nullptr && p.x.n_sinks == 0) { return; }
+	#pragma unroll
+	for (int o = 1; o < SUBS; o <<= 1) { word |= __shfl_xor_sync(0xffffffffu, word, o); }
+	const int mwords = p.M >> 5;
+	const int mw = blockIdx.y;
+	if (p.signs != nullptr && live && sub == 0) { p.signs[((size_t)img * mwords + mw) * p.n_per_image + pix] = word; }
+	#pragma unroll
+	for (int si = 0; si < 2; ++si)
+	{
+		if (si >= p.x.n_sinks) { break; }
+		const SinkParams & s = p.x.sinks[si];
+		if (s.pool != 0)
+		{
+			// window-major columns: the lanes of columns 4w .. 4w+3 hold one 2x2 window and share the taps of its pooled word
+			uint32_t w = live ? word : 0u;
+			w |= __shfl_xor_sync(0xffffffffu, w, SUBS);
+			w |= __shfl_xor_sync(0xffffffffu, w, 2 * SUBS);
+			if (!live) { continue; }
+			const int q = pixcol >> 2;
+			const int wy = q / p.x.win_w;
+			const int wx = q - wy * p.x.win_w;
+			for (int tap = (col & 3) * SUBS + sub; tap < s.taps; tap += 4 * SUBS) { sink_store_tap(s, img, wy, wx, mw, tap, w); }
+		}
+		else if (live)
+		{
+			const int oy = pix / p.x.out_w;
+			const int ox = pix - oy * p.x.out_w;
+			const int copies = (s.up == 2) ? 4 : 1;
+			for (int t = sub; t < copies * s.taps; t += SUBS)
+			{
+				const int cp = t / s.taps;
+				const int tap = t - cp * s.taps;
+				const int iy = (s.up == 2) ? 2 * oy + (cp >> 1) : oy;
+				const int ix = (s.up == 2) ? 2 * ox + (cp & 1) : ox;
+				sink_store_tap(s, img, iy, ix, mw, tap, word);
+			}
+		}
+	}
+}
+
+template <int KW4>
+static int launch_smallk(const GemmParams & p, cudaStream_t stream)
+{
+	const int gy = (p.M + 31) / 32;
+	// enough pixels to give every SM a few hundred threads: one pixel per thread, else four lanes per pixel
+	const bool wide = ((long long)p.n_total * gy >= (long long)sm_count() * 256);
+	const int cols_per_cta = wide ? SK_THREADS : SK_THREADS / 4;
+	const long long gx = ((long long)p.n_total + cols_per_cta - 1) / cols_per_cta;
+	if (gx > 0x7fffffffLL || gy > 65535) { return XNOR_B200_ERR_TOO_LARGE; }
+	if (wide) { xnor_gemm_smallk_kernel<KW4, 32><<<dim3((unsigned)gx, (unsigned)gy, 1), SK_THREADS, 0, stream>>>(p); }
+	else { xnor_gemm_smallk_kernel<KW4, 8><<<dim3((unsigned)gx, (unsigned)gy, 1), SK_THREADS, 0, stream>>>(p); }
+	return check_launch();
+}
+
 // ---- configurations ----------------------------------------------------------------------------
 
 struct TileConfig
@@ -462,6 +579,21 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		{
 			return launch_xnor_gemm_tc(M, n_total, n_per_image, K, A, lda_words, B, ldb_words, C, ldc, mean_arr, bias, leaky,
 					shortcut_in, shortcut_out, counts, stream, signs);
+		}
+	}
+
+	// Short rows on a small problem: one pixel per thread, no tiling (latency, not throughput, is the issue there).
+	if (counts == nullptr && shortcut_out == nullptr && p.kw <= 8 && (long long)M * n_total <= (4ll << 20)
+			&& std::getenv("XNOR_B200_GEMM_FORCE") == nullptr && (((uintptr_t)A | (uintptr_t)B) & 15u) == 0
+			&& lda_words % 4 == 0 && ldb_words % 4 == 0)
+	{
+		switch (p.kw / 4)
+		{
+			case 1: return launch_smallk<1>(p, stream);
+			case 2: return launch_smallk<2>(p, stream);
+			case 3: return launch_smallk<3>(p, stream);
+			case 4: return launch_smallk<4>(p, stream);
+			default: return launch_smallk<5>(p, stream);
 		}
 	}
 
