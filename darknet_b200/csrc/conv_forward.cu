@@ -188,14 +188,22 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_c
 	}
 
 	cudaStream_t s = (cudaStream_t)stream;
-	if (!io.input_packed)
+	// First xnor layer fed with sign planes, short rows, small problem: the GEMM builds its rows from the planes itself.
+	const bool rows_from_planes = (io.input_signs != nullptr && desc->c % 32 != 0
+			&& gemm_takes_planes(desc->n, desc->batch * g.n_out, desc->c, desc->size, desc->stride, desc->pad));
+	if (rows_from_planes)
+	{
+		extra.planes = io.input_signs;
+		extra.pl_c = desc->c; extra.pl_h = desc->h; extra.pl_w = desc->w;
+	}
+	else if (!io.input_packed)
 	{
 		rc = (io.input_signs != nullptr)
 				? launch_pack_input(*desc, io.pool, reinterpret_cast<const float *>(io.input_signs), (uint32_t *)scratch, s, 1, io.window_major)
 				: launch_pack_input(*desc, io.pool, io.input, (uint32_t *)scratch, s, 0, io.window_major);
 		if (rc != XNOR_B200_OK) { return rc; }
 	}
-	const bool extras = (extra.win_w > 0 || extra.n_sinks > 0);
+	const bool extras = (extra.win_w > 0 || extra.n_sinks > 0 || extra.planes != nullptr);
 	return launch_xnor_gemm(desc->n, desc->batch * g.n_out, g.n_out, g.k,
 			(const uint32_t *)align_bit_weights, g.new_lda / 32, (const uint32_t *)scratch, g.new_lda / 32,
 			io.output, g.n_out, mean_arr, biases, desc->activation == XNOR_B200_LEAKY,

@@ -66,7 +66,14 @@ struct GemmExtra
 	int out_w;
 	int n_sinks;
 	SinkParams sinks[2];
+	// Short-K kernel only: build the B rows on the fly from x-packed sign planes [image][pl_c][pl_h][ceil(pl_w/32)]
+	// (3x3, stride 1, pad 1 over pl_c channels, K order [c][ky][kx]) instead of reading a packed operand.
+	const uint32_t * planes;
+	int pl_c, pl_h, pl_w;
 };
+
+// True when launch_xnor_gemm would run such a layer on the short-K kernel, i.e. when `planes` may be used.
+bool gemm_takes_planes(int M, int n_total, int c, int size, int stride, int pad);
 
 // signs != nullptr: instead of C, only the sign bits of the output are written, 32 filters per word, laid out
 // [image][M/32][pixel] (requires M % 32 == 0).

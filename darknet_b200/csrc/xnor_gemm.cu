@@ -382,15 +382,62 @@ xnor_gemm_smallk_kernel(const GemmParams p)
 	const int sub = threadIdx.x % SUBS;
 	const int col = blockIdx.x * (SK_THREADS / SUBS) + threadIdx.x / SUBS;
 	const bool live = (col < p.n_total);
-	uint4 b[KW4];
-	#pragma unroll
-	for (int q = 0; q < KW4; ++q)
-	{
-		b[q] = live ? __ldg(reinterpret_cast<const uint4 *>(p.B + (size_t)col * p.ldb_words) + q) : make_uint4(0u, 0u, 0u, 0u);
-	}
 	const int img = live ? col / p.n_per_image : 0;
 	const int pixcol = live ? col - img * p.n_per_image : 0;
 	const int pix = col_to_pixel(p, pixcol);
+	uint4 b[KW4];
+	if (FPT == 8 && KW4 <= 2 && p.x.planes != nullptr)
+	{
+		// The packed row of this pixel straight from the sign planes: bits (c*3 + ky)*3 + kx = plane c, row y + ky - 1,
+		// columns x - 1 .. x + 1 (zero outside the image; bits behind the last column are zero in the planes).  The four
+		// lanes of a pixel split the work by kernel row: lane ky gathers its 3 bits of every channel at bit c*9, shifts
+		// the whole row left by 3*ky, and an OR across the four lanes (lane 3 adds nothing) gives everyone the full row.
+		uint32_t w[KW4 * 4 + 1];
+		#pragma unroll
+		for (int i = 0; i < KW4 * 4 + 1; ++i) { w[i] = 0u; }
+		const int y = pix / p.x.pl_w;
+		const int x = pix - y * p.x.pl_w;
+		const int gw = (p.x.pl_w + 31) >> 5;
+		const int w0 = (x - 1) >> 5;                       // -1 for x == 0: that word reads as zero
+		const int sh = (x - 1) & 31;
+		const int iy = y + sub - 1;
+		const bool row_ok = live && sub < 3 && iy >= 0 && iy < p.x.pl_h;
+		const uint32_t * rows = p.x.planes + ((size_t)img * p.x.pl_c * p.x.pl_h + (row_ok ? iy : 0)) * gw;
+		#pragma unroll
+		for (int c = 0; c < KW4 * 128 / 9; ++c)
+		{
+			if (c < p.x.pl_c && row_ok)
+			{
+				const uint32_t * row = rows + (size_t)c * p.x.pl_h * gw;
+				const uint32_t lo = (w0 >= 0) ? __ldg(row + w0) : 0u;
+				const uint32_t hi = (w0 + 1 < gw) ? __ldg(row + w0 + 1) : 0u;
+				const uint32_t bits = __funnelshift_r(lo, hi, sh) & 7u;
+				const int o = c * 9;                           // compile-time after unrolling
+				w[o >> 5] |= bits << (o & 31);
+				if ((o & 31) > 29) { w[(o >> 5) + 1] |= bits >> (32 - (o & 31)); }
+			}
+		}
+		const int lsh = 3 * sub;                               // 0, 3, 6 (9 for the idle lane, whose words are zero)
+		#pragma unroll
+		for (int i = KW4 * 4; i > 0; --i) { w[i] = __funnelshift_l(w[i - 1], w[i], lsh); }
+		w[0] <<= lsh;
+		#pragma unroll
+		for (int i = 0; i < KW4 * 4; ++i)
+		{
+			w[i] |= __shfl_xor_sync(0xffffffffu, w[i], 1);
+			w[i] |= __shfl_xor_sync(0xffffffffu, w[i], 2);
+		}
+		#pragma unroll
+		for (int q = 0; q < KW4; ++q) { b[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]); }
+	}
+	else
+	{
+		#pragma unroll
+		for (int q = 0; q < KW4; ++q)
+		{
+			b[q] = live ? __ldg(reinterpret_cast<const uint4 *>(p.B + (size_t)col * p.ldb_words) + q) : make_uint4(0u, 0u, 0u, 0u);
+		}
+	}
 	__syncthreads();
 
 	uint32_t word = 0;
@@ -461,7 +508,7 @@ static int launch_smallk(const GemmParams & p, cudaStream_t stream)
 {
 	const int gy = (p.M + 31) / 32;
 	// enough pixels to give every SM a few hundred threads: one pixel per thread, else four lanes per pixel
-	const bool wide = ((long long)p.n_total * gy >= (long long)sm_count() * 256);
+	const bool wide = ((long long)p.n_total * gy >= (long long)sm_count() * 256) && p.x.planes == nullptr;   // rows from planes: four lanes share the gathering
 	const int cols_per_cta = wide ? SK_THREADS : SK_THREADS / 4;
 	const long long gx = ((long long)p.n_total + cols_per_cta - 1) / cols_per_cta;
 	if (gx > 0x7fffffffLL || gy > 65535) { return XNOR_B200_ERR_TOO_LARGE; }
@@ -540,13 +587,26 @@ static float estimate_cycles(const TileConfig & c, int M, int n_total, int kw, i
 	return per_sm * (cta_cycles + store_cycles) + 700.0f * ((per_sm + c.max_resident - 1) / c.max_resident) + fixed;
 }
 
+static bool short_k_problem(int M, int n_total, int kw)
+{
+	return kw <= 8 && (long long)M * n_total <= (4ll << 20) && std::getenv("XNOR_B200_GEMM_FORCE") == nullptr
+			&& std::getenv("XNOR_B200_GEMM_TC") == nullptr;
+}
+
+bool gemm_takes_planes(int M, int n_total, int c, int size, int stride, int pad)
+{
+	const int K = c * size * size;
+	return size == 3 && stride == 1 && pad == 1 && c % 32 != 0 && K <= 256
+			&& short_k_problem(M, n_total, (int)round_up((size_t)(K + 31) / 32, 4));
+}
+
 int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
 		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs,
 		const GemmExtra * extra)
 {
-	const bool extras = (extra != nullptr && (extra->win_w > 0 || extra->n_sinks > 0));
+	const bool extras = (extra != nullptr && (extra->win_w > 0 || extra->n_sinks > 0 || extra->planes != nullptr));
 	if ((signs != nullptr || (extra != nullptr && extra->n_sinks > 0)) && M % 32 != 0) { return XNOR_B200_ERR_INVALID; }
 	if (extras && counts != nullptr) { return XNOR_B200_ERR_INVALID; }
 	if (extras && n_per_image % 4 != 0 && (extra->win_w > 0)) { return XNOR_B200_ERR_INVALID; }
@@ -583,9 +643,9 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	}
 
 	// Short rows on a small problem: one pixel per thread, no tiling (latency, not throughput, is the issue there).
-	if (counts == nullptr && shortcut_out == nullptr && p.kw <= 8 && (long long)M * n_total <= (4ll << 20)
-			&& std::getenv("XNOR_B200_GEMM_FORCE") == nullptr && (((uintptr_t)A | (uintptr_t)B) & 15u) == 0
-			&& lda_words % 4 == 0 && ldb_words % 4 == 0)
+	const bool from_planes = (p.x.planes != nullptr);
+	if (counts == nullptr && shortcut_out == nullptr && short_k_problem(M, n_total, p.kw)
+			&& (((uintptr_t)A | (uintptr_t)B) & 15u) == 0 && lda_words % 4 == 0 && ldb_words % 4 == 0)
 	{
 		switch (p.kw / 4)
 		{
@@ -596,6 +656,8 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 			default: return launch_smallk<5>(p, stream);
 		}
 	}
+
+	if (from_planes) { return XNOR_B200_ERR_INVALID; }      // only the short-K kernel builds rows from planes
 
 	const int sms = sm_count();
 	int best_cfg = 0, best_split = 1;
