@@ -75,6 +75,32 @@ struct GemmExtra
 // True when launch_xnor_gemm would run such a layer on the short-K kernel, i.e. when `planes` may be used.
 bool gemm_takes_planes(int M, int n_total, int c, int size, int stride, int pad);
 
+#ifdef __CUDACC__
+// Pixel (row-major index inside the image) of column `pixcol` of an image.
+__device__ __forceinline__ int col_to_pixel(const GemmExtra & x, int pixcol)
+{
+	if (x.win_w == 0) { return pixcol; }
+	const int q = pixcol >> 2;
+	const int wy = q / x.win_w;
+	const int wx = q - wy * x.win_w;
+	return (2 * wy + ((pixcol >> 1) & 1)) * x.out_w + 2 * wx + (pixcol & 1);
+}
+
+// Stores sign word `word` of consumer-input pixel (iy, ix), channel block cb, at the place of the consumer's packed
+// operand where its im2col puts tap (ky, kx): K-word cb*taps + ky*ks + kx of output pixel (iy + pad - ky, ix + pad - kx).
+__device__ __forceinline__ void sink_store_tap(const SinkParams & s, int img, int iy, int ix, int cb, int tap, uint32_t word)
+{
+	const int ky = tap / s.ks;
+	const int kx = tap - ky * s.ks;
+	const int oy = iy + s.pad - ky;
+	const int ox = ix + s.pad - kx;
+	if (oy < 0 || oy >= s.out_h || ox < 0 || ox >= s.out_w) { return; }
+	const size_t row = (s.win_w > 0) ? ((size_t)(oy >> 1) * s.win_w + (ox >> 1)) * 4 + (oy & 1) * 2 + (ox & 1)
+	                                 : (size_t)oy * s.out_w + ox;
+	s.operand[((size_t)img * s.n_out + row) * s.ldw + (size_t)(s.cb_offset + cb) * s.taps + tap] = word;
+}
+#endif
+
 // signs != nullptr: instead of C, only the sign bits of the output are written, 32 filters per word, laid out
 // [image][M/32][pixel] (requires M % 32 == 0).
 // GEMM with the batch folded into the column index: column j = b*n_per_image + p is written to
@@ -90,7 +116,8 @@ bool tc_gemm_eligible(int M, int n_total, int K);
 int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
-		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs = nullptr);
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs = nullptr,
+		const GemmExtra * extra = nullptr);
 // Sticky device-side status (bounded wait expired in the tensor-core kernel); synchronous copy from the device.
 int read_tc_error(int * out, bool clear);
 

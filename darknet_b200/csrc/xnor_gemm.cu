@@ -57,30 +57,6 @@ struct GemmParams
 	GemmExtra x;            // window-major column order and direct sign sinks (all zero: none)
 };
 
-// Pixel (row-major index inside the image) of column `pixcol` of an image.
-__device__ __forceinline__ int col_to_pixel(const GemmParams & p, int pixcol)
-{
-	if (p.x.win_w == 0) { return pixcol; }
-	const int q = pixcol >> 2;
-	const int wy = q / p.x.win_w;
-	const int wx = q - wy * p.x.win_w;
-	return (2 * wy + ((pixcol >> 1) & 1)) * p.x.out_w + 2 * wx + (pixcol & 1);
-}
-
-// Stores sign word `word` of consumer-input pixel (iy, ix), channel block cb, at the place of the consumer's packed
-// operand where its im2col puts tap (ky, kx): K-word cb*taps + ky*ks + kx of output pixel (iy + pad - ky, ix + pad - kx).
-__device__ __forceinline__ void sink_store_tap(const SinkParams & s, int img, int iy, int ix, int cb, int tap, uint32_t word)
-{
-	const int ky = tap / s.ks;
-	const int kx = tap - ky * s.ks;
-	const int oy = iy + s.pad - ky;
-	const int ox = ix + s.pad - kx;
-	if (oy < 0 || oy >= s.out_h || ox < 0 || ox >= s.out_w) { return; }
-	const size_t row = (s.win_w > 0) ? ((size_t)(oy >> 1) * s.win_w + (ox >> 1)) * 4 + (oy & 1) * 2 + (ox & 1)
-	                                 : (size_t)oy * s.out_w + ox;
-	s.operand[((size_t)img * s.n_out + row) * s.ldw + (size_t)(s.cb_offset + cb) * s.taps + tap] = word;
-}
-
 __device__ __forceinline__ void cp_async_16(uint32_t * smem_dst, const uint32_t * gmem_src, bool valid)
 {
 	const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -276,7 +252,7 @@ xnor_gemm_kernel(const GemmParams p)
 			if (p.signs != nullptr && col < p.n_total && mw < mwords)
 			{
 				const int img = col / p.n_per_image;
-				p.signs[((size_t)img * mwords + mw) * p.n_per_image + col_to_pixel(p, col - img * p.n_per_image)] = word;
+				p.signs[((size_t)img * mwords + mw) * p.n_per_image + col_to_pixel(p.x, col - img * p.n_per_image)] = word;
 			}
 		}
 		if (p.x.n_sinks > 0) { __syncthreads(); }
@@ -313,7 +289,7 @@ xnor_gemm_kernel(const GemmParams p)
 					const int col = n0 + cg_;
 					if (col >= p.n_total) { continue; }
 					const int img = col / p.n_per_image;
-					const int pix = col_to_pixel(p, col - img * p.n_per_image);
+					const int pix = col_to_pixel(p.x, col - img * p.n_per_image);
 					int oy = pix / p.x.out_w;
 					int ox = pix - oy * p.x.out_w;
 					if (s.up == 2) { oy = 2 * oy + (cp >> 1); ox = 2 * ox + (cp & 1); }
@@ -331,7 +307,7 @@ xnor_gemm_kernel(const GemmParams p)
 		const int col = n0 + j * TX + tx;
 		if (col >= p.n_total) { continue; }
 		const int img = col / p.n_per_image;
-		const int pix = col_to_pixel(p, col - img * p.n_per_image);
+		const int pix = col_to_pixel(p.x, col - img * p.n_per_image);
 		#pragma unroll
 		for (int i = 0; i < TM; ++i)
 		{
@@ -384,7 +360,7 @@ xnor_gemm_smallk_kernel(const GemmParams p)
 	const bool live = (col < p.n_total);
 	const int img = live ? col / p.n_per_image : 0;
 	const int pixcol = live ? col - img * p.n_per_image : 0;
-	const int pix = col_to_pixel(p, pixcol);
+	const int pix = col_to_pixel(p.x, pixcol);
 	uint4 b[KW4];
 	if (FPT == 8 && KW4 <= 2 && p.x.planes != nullptr)
 	{
@@ -635,10 +611,10 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	{
 		const char * tc = std::getenv("XNOR_B200_GEMM_TC");
 		const bool use_tc = (tc != nullptr) ? (tc[0] == '1') : tc_gemm_eligible(M, n_total, K);
-		if (use_tc && !extras)                                                   // sinks and window order live in this kernel only
+		if (use_tc && !(extra != nullptr && extra->planes != nullptr))
 		{
 			return launch_xnor_gemm_tc(M, n_total, n_per_image, K, A, lda_words, B, ldb_words, C, ldc, mean_arr, bias, leaky,
-					shortcut_in, shortcut_out, counts, stream, signs);
+					shortcut_in, shortcut_out, counts, stream, signs, extras ? extra : nullptr);
 		}
 	}
 

@@ -54,6 +54,7 @@ struct TcParams
 	int32_t * counts;
 	uint32_t * signs;       // when set: sign bits of the output only, [img][M/32][pixel]
 	int tiles_f;            // filter tiles (fastest-varying in blockIdx.x)
+	GemmExtra x;            // window-major column order and direct sign sinks (all zero: none)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -302,7 +303,8 @@ xnor_gemm_tc_kernel(const TcParams p)
 		const int col = n0 + pix_local;                       // global pixel (column of C)
 		const bool col_ok = col < p.n_total;
 		const int img = col_ok ? col / p.n_per_image : 0;
-		const int pix = col_ok ? col - img * p.n_per_image : 0;
+		const int pixcol = col_ok ? col - img * p.n_per_image : 0;
+		const int pix = col_to_pixel(p.x, pixcol);
 		const int k_b = p.K - 2 * s_pop[pix_local];
 		const bool has_bias = (p.bias != nullptr);
 		const size_t pix_off = ((size_t)img * p.M + f0) * p.ldc + pix;    // element (first filter of the tile, this pixel)
@@ -324,8 +326,58 @@ xnor_gemm_tc_kernel(const TcParams p)
 				  "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
 				: "r"(taddr) : "memory");
 			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-			if (!col_ok) { continue; }
 			const int fbase = chunk * 32;
+			if (p.signs != nullptr || p.x.n_sinks > 0)
+			{
+				// the 32 filters of this chunk are exactly one channel-packed word of this thread's pixel
+				uint32_t word = 0;
+				if (col_ok && f0 + fbase < p.M)
+				{
+					#pragma unroll
+					for (int j = 0; j < 32; ++j)
+					{
+						const int4 fi = s_fil[fbase + j];
+						float v = __fmul_rn((float)(k_b + fi.x + 4 * (int)d[j]), __int_as_float(fi.y));
+						if (has_bias) { v = __fadd_rn(v, __int_as_float(fi.z)); }
+						word |= (v > 0.0f ? 1u : 0u) << j;
+					}
+				}
+				const int mw = (f0 + fbase) >> 5;
+				const bool word_ok = col_ok && f0 + fbase < p.M;
+				if (p.signs != nullptr && word_ok) { p.signs[((size_t)img * (p.M >> 5) + mw) * p.n_per_image + pix] = word; }
+				#pragma unroll
+				for (int si = 0; si < 2; ++si)
+				{
+					if (si >= p.x.n_sinks) { break; }
+					const SinkParams & sk = p.x.sinks[si];
+					if (sk.pool != 0)
+					{
+						// window-major columns: lanes 4w .. 4w+3 hold one 2x2 window and share the taps of its pooled word
+						uint32_t w = word;
+						w |= __shfl_xor_sync(0xffffffffu, w, 1);
+						w |= __shfl_xor_sync(0xffffffffu, w, 2);
+						if (!word_ok) { continue; }
+						const int q = pixcol >> 2;
+						const int wy = q / p.x.win_w;
+						const int wx = q - wy * p.x.win_w;
+						for (int tap = col & 3; tap < sk.taps; tap += 4) { sink_store_tap(sk, img, wy, wx, mw, tap, w); }
+					}
+					else if (word_ok)
+					{
+						const int oy = pix / p.x.out_w;
+						const int ox = pix - oy * p.x.out_w;
+						const int copies = (sk.up == 2) ? 4 : 1;
+						for (int t = 0; t < copies * sk.taps; ++t)
+						{
+							const int cp = t / sk.taps;
+							const int tap = t - cp * sk.taps;
+							sink_store_tap(sk, img, (sk.up == 2) ? 2 * oy + (cp >> 1) : oy, (sk.up == 2) ? 2 * ox + (cp & 1) : ox, mw, tap, word);
+						}
+					}
+				}
+				if (p.C == nullptr) { continue; }
+			}
+			if (!col_ok) { continue; }
 			if (p.counts != nullptr)
 			{
 				#pragma unroll
@@ -336,24 +388,6 @@ xnor_gemm_tc_kernel(const TcParams p)
 						// agreeing bits among the first K
 						p.counts[(size_t)(f0 + fbase + j) * p.n_total + col] = (k_b + s_fil[fbase + j].x + 4 * (int)d[j] + p.K) >> 1;
 					}
-				}
-				continue;
-			}
-			if (p.signs != nullptr)
-			{
-				// the 32 filters of this chunk are exactly one channel-packed word of this thread's pixel
-				if (f0 + fbase < p.M)
-				{
-					uint32_t word = 0;
-					#pragma unroll
-					for (int j = 0; j < 32; ++j)
-					{
-						const int4 fi = s_fil[fbase + j];
-						float v = __fmul_rn((float)(k_b + fi.x + 4 * (int)d[j]), __int_as_float(fi.y));
-						if (has_bias) { v = __fadd_rn(v, __int_as_float(fi.z)); }
-						word |= (v > 0.0f ? 1u : 0u) << j;
-					}
-					p.signs[((size_t)img * (p.M >> 5) + ((f0 + fbase) >> 5)) * p.n_per_image + pix] = word;
 				}
 				continue;
 			}
@@ -390,12 +424,23 @@ xnor_gemm_tc_kernel(const TcParams p)
 
 bool tc_gemm_eligible(int M, int n_total, int K)
 {
-	// Needs enough filters to fill the N side of the MMA, enough K to amortise the TMEM round trip, and at
-	// least about one tile per SM; everything else stays on the integer-pipe kernel.
+	// Needs enough filters to fill the N side of the MMA and enough K to amortise the TMEM round trip; beyond that the
+	// faster of two estimates fitted to measurements on B200 (batch 8..64 layer shapes) decides:
+	//   tensor-core kernel: ~14 us of fixed cost (launch with 100+ KB of shared memory, TMEM allocation, pipeline fill,
+	//                       drain) + per tile 0.6 us per 128-bit K block and 4 us of epilogue (half of both for 128-filter
+	//                       tiles), times the tiles the busiest SM gets (co-resident CTAs share the SM's shared-memory bandwidth);
+	//   integer kernel:     ~4 us + binary ops at 250 T/s.
 	if (M < 96 || K < 256) { return false; }
 	const int nf = (M > 128) ? 256 : 128;
 	const long long tiles = (long long)((M + nf - 1) / nf) * ((n_total + TC_PIX - 1) / TC_PIX);
-	return tiles >= sm_count();
+	const double kb = (double)((K + 127) / 128);
+	const double per_tile = (nf == 256) ? 0.6 * kb + 4.0 : 0.33 * kb + 2.5;
+	double load = (double)tiles / (double)sm_count();
+	if (nf == 256) { load = (double)((tiles + sm_count() - 1) / sm_count()); }
+	if (load < 1.0) { load = 1.0; }
+	const double t_tc = 14.0 + per_tile * load;
+	const double t_int = 4.0 + 2.0 * (double)M * (double)n_total * (double)K / 250.0e6;
+	return t_tc < t_int;
 }
 
 template <int NF>
@@ -414,9 +459,14 @@ static int launch_tc(TcParams & p, cudaStream_t stream)
 int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 		const uint32_t * A, int lda_words, const uint32_t * B, int ldb_words,
 		float * C, int ldc, const float * mean_arr, const float * bias, int leaky,
-		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs)
+		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs,
+		const GemmExtra * extra)
 {
 	TcParams p;
+	p.x = GemmExtra();
+	if (extra != nullptr) { p.x = *extra; }
+	if (p.x.out_w <= 0) { p.x.out_w = 1; }
+	if (p.x.planes != nullptr) { return XNOR_B200_ERR_INVALID; }
 	p.signs = signs;
 	p.A = A; p.B = B;
 	p.M = M; p.n_total = n_total; p.n_per_image = n_per_image; p.K = K;

@@ -17,6 +17,8 @@ Only the section types and keys that occur in the three shipped xnor cfgs are un
 """
 from __future__ import annotations
 
+import os
+
 import math
 import struct
 from dataclasses import dataclass, field
@@ -122,7 +124,7 @@ class Network:
     sign_links: int = 0
     side_branches: bool = True             # a head branch that nothing later reads runs on a second stream
     side_stream: Optional[torch.cuda.Stream] = None
-    sink_max_batch: int = 2                # direct sinks keep a layer on the integer GEMM kernel: used at small batch only
+    sink_max_batch: int = 1 << 30          # batch up to which direct sign sinks are linked (both GEMM kernels have them)
     sink_links: int = 0
 
 
@@ -455,7 +457,7 @@ def fold_maxpools(net: Network) -> None:
         # once instead of writing and re-reading the pooled one) and only for the 2x2/stride-2 window it has a
         # vectorised path for; at batch 1 the separate maxpool launch is cheaper than the longer pack kernel.
         fast = l.size == 2 and l.stride == 2 and l.pad // 2 == 0 and l.h % 2 == 0 and l.w % 2 == 0
-        if (l.type == "maxpool" and not l.folded and j not in referenced and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None
+        if (l.type == "maxpool" and not l.folded and not l.skip and j not in referenced and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None
                 and fast and net.batch >= net.fold_maxpool_min_batch):
             l.folded = True
             nxt.pool_desc = capi.PoolDesc(l.size, l.stride, l.pad, l.h, l.w)
@@ -682,6 +684,8 @@ def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "c
     net.sign_chains = sign_chains
     net.fuse_first_conv = fuse_first_conv
     net.side_branches = side_branches
+    if os.environ.get("XNOR_B200_SINK_MAX_BATCH"):            # tuning aid: batch up to which sign sinks are linked
+        net.sink_max_batch = int(os.environ["XNOR_B200_SINK_MAX_BATCH"])
     load_weights(net, weights)
     fuse_conv_batchnorm(net)
     calculate_binary_weights(net)

@@ -16,6 +16,17 @@ import torch.nn.functional as F  # noqa: E402
 from darknet_b200 import capi, layer as L  # noqa: E402
 
 
+@pytest.fixture(autouse=True, params=["auto", "tensor-core"])
+def gemm_kernel(request, monkeypatch):
+    """Every test runs once with the library's own kernel choice (integer / short-K kernels at these sizes) and once
+    with every GEMM forced onto the tcgen05 kernel, which has its own sink epilogue."""
+    if request.param == "tensor-core":
+        monkeypatch.setenv("XNOR_B200_GEMM_TC", "1")
+    else:
+        monkeypatch.delenv("XNOR_B200_GEMM_TC", raising=False)
+    return request.param
+
+
 def make(batch, c, h, w, n, ks, seed, act=capi.LINEAR):
     l = L.make_convolutional_layer(batch, h, w, c, n, ks, 1, ks // 2, act)
     l.load_weights(torch.from_numpy(synth.bell(seed, (n, c * ks * ks), 0.05)).cuda(), torch.from_numpy(synth.bell(seed + 1, (n,), 0.3)).cuda())
