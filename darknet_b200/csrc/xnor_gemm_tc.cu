@@ -146,7 +146,7 @@ struct TcShape
 };
 
 template <int NF>
-__global__ void __launch_bounds__(TcShape<NF>::THREADS)
+__global__ void __launch_bounds__(TcShape<NF>::THREADS, (NF == 128) ? 3 : 2)      // co-resident CTAs: one epilogue overlaps another main loop
 xnor_gemm_tc_kernel(const TcParams p)
 {
 	using S = TcShape<NF>;

