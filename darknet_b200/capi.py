@@ -25,7 +25,7 @@ EXPORTS = (
     "xnor_b200_gemm_counts", "xnor_b200_scratch_bytes", "xnor_b200_conv_forward",
     "xnor_b200_conv_forward_static", "xnor_b200_take_device_status",
     "xnor_b200_pack_input_pooled", "xnor_b200_conv_forward_pooled", "xnor_b200_float_conv_small", "xnor_b200_float_conv3_io", "xnor_b200_float_conv_map_weights_bytes",
-    "xnor_b200_float_conv_map_prepare", "xnor_b200_float_conv_map", "xnor_b200_float_conv_map_yolo", "xnor_b200_yolo_activate", "xnor_b200_conv_forward_io",
+    "xnor_b200_float_conv_map_prepare", "xnor_b200_float_conv_map", "xnor_b200_float_conv_map_yolo", "xnor_b200_yolo_activate", "xnor_b200_conv_forward_io", "xnor_b200_conv_takes_masks", "xnor_b200_tap_major_weights",
     "xnor_b200_measure_popc_peak", "xnor_b200_measure_bmma_peak", "xnor_b200_measure_umma_i8_peak",
 )
 
@@ -50,7 +50,8 @@ class ConvIO(C.Structure):
     """struct xnor_b200_conv_io"""
     _fields_ = [("input", C.c_void_p), ("input_signs", C.c_void_p), ("pool", C.POINTER(PoolDesc)), ("output", C.c_void_p),
                 ("output_signs", C.c_void_p), ("shortcut_in", C.c_void_p), ("shortcut_out", C.c_void_p),
-                ("input_packed", C.c_int), ("window_major", C.c_int), ("sinks", C.POINTER(SignSink)), ("n_sinks", C.c_int)]
+                ("input_packed", C.c_int), ("window_major", C.c_int), ("sinks", C.POINTER(SignSink)), ("n_sinks", C.c_int),
+                ("input_masks", C.c_void_p), ("tap_major_weights", C.c_int)]
 
 
 class ConvGeom(C.Structure):
@@ -101,7 +102,9 @@ def lib() -> C.CDLL:
     L.xnor_b200_pack_input_pooled.argtypes = [dp, pp, vp, vp, vp]
     L.xnor_b200_conv_forward_pooled.argtypes = [dp, pp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
     L.xnor_b200_float_conv_small.argtypes = [dp, vp, vp, vp, vp, vp]
-    L.xnor_b200_float_conv3_io.argtypes = [dp, ci, vp, vp, vp, vp, vp, vp]
+    L.xnor_b200_float_conv3_io.argtypes = [dp, ci, vp, vp, vp, vp, vp, vp, vp]
+    L.xnor_b200_conv_takes_masks.argtypes = [dp]
+    L.xnor_b200_tap_major_weights.argtypes = [dp, vp, vp, vp]
     L.xnor_b200_float_conv_map_weights_bytes.argtypes = [dp]
     L.xnor_b200_float_conv_map_weights_bytes.restype = C.c_size_t
     L.xnor_b200_float_conv_map_prepare.argtypes = [dp, vp, vp, vp]

@@ -159,7 +159,7 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_c
 		void * scratch, size_t scratch_bytes, void * stream)
 {
 	if (desc == nullptr || align_bit_weights == nullptr || mean_arr == nullptr || scratch == nullptr) { return XNOR_B200_ERR_NULL; }
-	const int n_in = (io.input != nullptr) + (io.input_signs != nullptr) + (io.input_packed != 0);
+	const int n_in = (io.input != nullptr) + (io.input_signs != nullptr) + (io.input_packed != 0) + (io.input_masks != nullptr);
 	if (n_in != 1) { return XNOR_B200_ERR_NULL; }
 	if (io.n_sinks < 0 || io.n_sinks > 2 || (io.n_sinks > 0 && io.sinks == nullptr)) { return XNOR_B200_ERR_INVALID; }
 	if (io.output != nullptr && io.output_signs != nullptr) { return XNOR_B200_ERR_INVALID; }
@@ -191,7 +191,14 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_c
 	// First xnor layer fed with sign planes, short rows, small problem: the GEMM builds its rows from the planes itself.
 	const bool rows_from_planes = (io.input_signs != nullptr && desc->c % 32 != 0
 			&& gemm_takes_planes(desc->n, desc->batch * g.n_out, desc->c, desc->size, desc->stride, desc->pad));
-	if (rows_from_planes)
+	if (io.input_masks != nullptr)
+	{
+		// channel masks + tap-major weights: only the short-K kernel reads them
+		if (!xnor_b200_conv_takes_masks(desc) || !io.tap_major_weights || io.pool != nullptr) { return XNOR_B200_ERR_INVALID; }
+		extra.masks = io.input_masks;
+		extra.pl_c = desc->c; extra.pl_h = desc->h; extra.pl_w = desc->w;
+	}
+	else if (rows_from_planes)
 	{
 		extra.planes = io.input_signs;
 		extra.pl_c = desc->c; extra.pl_h = desc->h; extra.pl_w = desc->w;
@@ -203,11 +210,19 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_c
 				: launch_pack_input(*desc, io.pool, io.input, (uint32_t *)scratch, s, 0, io.window_major);
 		if (rc != XNOR_B200_OK) { return rc; }
 	}
-	const bool extras = (extra.win_w > 0 || extra.n_sinks > 0 || extra.planes != nullptr);
+	const bool extras = (extra.win_w > 0 || extra.n_sinks > 0 || extra.planes != nullptr || extra.masks != nullptr);
 	return launch_xnor_gemm(desc->n, desc->batch * g.n_out, g.n_out, g.k,
 			(const uint32_t *)align_bit_weights, g.new_lda / 32, (const uint32_t *)scratch, g.new_lda / 32,
 			io.output, g.n_out, mean_arr, biases, desc->activation == XNOR_B200_LEAKY,
 			io.shortcut_in, io.shortcut_out, nullptr, s, io.output_signs, extras ? &extra : nullptr);
+}
+
+extern "C" int xnor_b200_conv_takes_masks(const xnor_b200_conv_desc * desc)
+{
+	if (desc == nullptr || validate_desc(desc) != XNOR_B200_OK) { return 0; }
+	const int n_out = conv_out_dim(desc->h, desc->size, desc->stride, desc->pad) * conv_out_dim(desc->w, desc->size, desc->stride, desc->pad);
+	return ((desc->c == 8 || desc->c == 16)
+			&& gemm_takes_planes(desc->n, desc->batch * n_out, desc->c, desc->size, desc->stride, desc->pad)) ? 1 : 0;
 }
 
 static xnor_b200_conv_io plain_io(const float * input, const xnor_b200_pool_desc * pool, float * output,

@@ -124,6 +124,7 @@ struct FloatBlockParams
 	const float * biases;    // [n] or nullptr
 	float * out;             // fp32 output (full or pooled) or nullptr
 	uint32_t * planes;       // pooled sign planes or nullptr
+	uint8_t * masks;         // pooled sign masks [image][H/2][W/2][ceil(N/8)] (bit f%8 of byte f/8) or nullptr
 	int H, W, N;
 	int BH, BW;              // 2x2 blocks per column / row: ceil(H/2), ceil(W/2)
 	int xtiles;              // ceil(BW / 32)
@@ -211,6 +212,19 @@ float_conv3_block_kernel(const FloatBlockParams p)
 
 	const bool col1 = (2 * bx + 1 < p.W);
 	const bool row1 = (2 * by + 1 < p.H);
+	if (p.masks != nullptr)
+	{
+		// pooled sign of this thread's 8 filters as one byte of the pixel's channel mask
+		uint32_t m = 0;
+		#pragma unroll
+		for (int f = 0; f < FB_FILTERS; ++f)
+		{
+			const float r0 = acc[f][0] + s_b[f], r1 = acc[f][1] + s_b[f], r2 = acc[f][2] + s_b[f], r3 = acc[f][3] + s_b[f];
+			m |= ((f0 + f < p.N) && (r0 > 0.0f || r1 > 0.0f || r2 > 0.0f || r3 > 0.0f) ? 1u : 0u) << f;
+		}
+		if (live) { p.masks[(((size_t)blockIdx.z * p.BH + by) * p.BW + bx) * gridDim.y + blockIdx.y] = (uint8_t)m; }
+		return;
+	}
 	#pragma unroll
 	for (int f = 0; f < FB_FILTERS; ++f)
 	{
@@ -290,18 +304,18 @@ extern "C" int xnor_b200_float_conv_small(const xnor_b200_conv_desc * desc, cons
 }
 
 extern "C" int xnor_b200_float_conv3_io(const xnor_b200_conv_desc * desc, int pool, const float * input, const float * weights,
-		const float * biases, float * output, uint32_t * output_sign_planes, void * stream)
+		const float * biases, float * output, uint32_t * output_sign_planes, uint8_t * output_sign_masks, void * stream)
 {
 	if (desc == nullptr || input == nullptr || weights == nullptr) { return XNOR_B200_ERR_NULL; }
-	if ((output == nullptr) == (output_sign_planes == nullptr)) { return XNOR_B200_ERR_NULL; }
+	if ((output != nullptr) + (output_sign_planes != nullptr) + (output_sign_masks != nullptr) != 1) { return XNOR_B200_ERR_NULL; }
 	int rc = validate_desc(desc);
 	if (rc != XNOR_B200_OK) { return rc; }
 	if (desc->c != 3 || desc->size != 3 || desc->stride != 1 || desc->pad != 1) { return XNOR_B200_ERR_INVALID; }
 	if (pool != 0 && pool != 2) { return XNOR_B200_ERR_INVALID; }
 	if (pool == 2 && (desc->h % 2 != 0 || desc->w % 2 != 0)) { return XNOR_B200_ERR_INVALID; }
-	if (output_sign_planes != nullptr && pool != 2) { return XNOR_B200_ERR_INVALID; }
+	if ((output_sign_planes != nullptr || output_sign_masks != nullptr) && pool != 2) { return XNOR_B200_ERR_INVALID; }
 	FloatBlockParams p;
-	p.in = input; p.weights = weights; p.biases = biases; p.out = output; p.planes = output_sign_planes;
+	p.in = input; p.weights = weights; p.biases = biases; p.out = output; p.planes = output_sign_planes; p.masks = output_sign_masks;
 	p.H = desc->h; p.W = desc->w; p.N = desc->n;
 	p.BH = (desc->h + 1) / 2; p.BW = (desc->w + 1) / 2;
 	p.xtiles = (p.BW + 31) / 32;

@@ -92,9 +92,45 @@ weights_pack_kernel(const float * __restrict__ weights, int K, int taps, int lda
 	}
 }
 
+// Bit k' = t*C + c of a tap-major row is bit c*taps + t of the reference-order row ([c][tap], c % 32 != 0 layers).
+__global__ void tap_major_weights_kernel(const uint32_t * __restrict__ in, uint32_t * __restrict__ out, int n, int C, int taps, int lda_words)
+{
+	const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+	if (idx >= n * lda_words) { return; }
+	const int f = idx / lda_words;
+	const int w = idx - f * lda_words;
+	const uint32_t * row = in + (size_t)f * lda_words;
+	uint32_t v = 0;
+	for (int b = 0; b < 32; ++b)
+	{
+		const int k = w * 32 + b;
+		if (k >= C * taps) { break; }
+		const int t = k / C;
+		const int c = k - t * C;
+		const int src = c * taps + t;
+		v |= ((row[src >> 5] >> (src & 31)) & 1u) << b;
+	}
+	out[idx] = v;
+}
+
 }  // namespace xnor
 
 using namespace xnor;
+
+extern "C" int xnor_b200_tap_major_weights(const xnor_b200_conv_desc * desc, const uint8_t * align_bit_weights, uint8_t * tap_major, void * stream)
+{
+	if (desc == nullptr || align_bit_weights == nullptr || tap_major == nullptr) { return XNOR_B200_ERR_NULL; }
+	int rc = validate_desc(desc);
+	if (rc != XNOR_B200_OK) { return rc; }
+	if (desc->c % 32 == 0) { return XNOR_B200_ERR_INVALID; }          // the c % 32 == 0 layout is tap-major inside each 32-channel block already
+	if ((((uintptr_t)align_bit_weights | (uintptr_t)tap_major) & 15u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
+	const int taps = desc->size * desc->size;
+	const int lda_words = aligned_lda(taps * desc->c) / 32;
+	const int total = desc->n * lda_words;
+	tap_major_weights_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const uint32_t *)align_bit_weights, (uint32_t *)tap_major,
+			desc->n, desc->c, taps, lda_words);
+	return check_launch();
+}
 
 extern "C" int xnor_b200_binarize_weights(const float * weights, int n, int size, float * binary, float * mean_arr, void * stream)
 {

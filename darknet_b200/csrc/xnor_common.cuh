@@ -70,6 +70,9 @@ struct GemmExtra
 	// (3x3, stride 1, pad 1 over pl_c channels, K order [c][ky][kx]) instead of reading a packed operand.
 	const uint32_t * planes;
 	int pl_c, pl_h, pl_w;
+	// Same, from channel masks [image][pl_h][pl_w][pl_c/8] bytes (bit c%8 of byte c/8), pl_c 8 or 16, with the rows and the
+	// weights in TAP-major K order (bit t*pl_c + c): a row is then nine neighbouring masks side by side.
+	const uint8_t * masks;
 };
 
 // True when launch_xnor_gemm would run such a layer on the short-K kernel, i.e. when `planes` may be used.

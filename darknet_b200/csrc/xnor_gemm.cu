@@ -362,7 +362,36 @@ xnor_gemm_smallk_kernel(const GemmParams p)
 	const int pixcol = live ? col - img * p.n_per_image : 0;
 	const int pix = col_to_pixel(p.x, pixcol);
 	uint4 b[KW4];
-	if (FPT == 8 && KW4 <= 2 && p.x.planes != nullptr)
+	if (FPT == 8 && KW4 <= 2 && p.x.masks != nullptr)
+	{
+		// Tap-major rows: bits [t*C, t*C + C) are the channel mask of the pixel under tap t (zero outside the image).
+		// C is 8 or 16, so a mask never straddles a word.
+		uint32_t w[KW4 * 4];
+		#pragma unroll
+		for (int i = 0; i < KW4 * 4; ++i) { w[i] = 0u; }
+		const int y = pix / p.x.pl_w;
+		const int x = pix - y * p.x.pl_w;
+		const int C = p.x.pl_c;
+		const uint8_t * img_masks = p.x.masks + (size_t)img * p.x.pl_h * p.x.pl_w * (C >> 3);
+		#pragma unroll
+		for (int t = 0; t < 9; ++t)
+		{
+			const int iy = y + t / 3 - 1;
+			const int ix = x + t % 3 - 1;
+			uint32_t m = 0u;
+			if (live && iy >= 0 && iy < p.x.pl_h && ix >= 0 && ix < p.x.pl_w)
+			{
+				const size_t e = (size_t)iy * p.x.pl_w + ix;
+				m = (C == 16) ? (uint32_t)__ldg(reinterpret_cast<const uint16_t *>(img_masks) + e) : (uint32_t)__ldg(img_masks + e);
+			}
+			// bit offset t*C: compile-time for each of the two channel counts
+			if (C == 16) { if (t * 16 < KW4 * 128) { w[(t * 16) >> 5] |= m << ((t * 16) & 31); } }
+			else         { if (t * 8 < KW4 * 128) { w[(t * 8) >> 5] |= m << ((t * 8) & 31); } }
+		}
+		#pragma unroll
+		for (int q = 0; q < KW4; ++q) { b[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]); }
+	}
+	else if (FPT == 8 && KW4 <= 2 && p.x.planes != nullptr)
 	{
 		// The packed row of this pixel straight from the sign planes: bits (c*3 + ky)*3 + kx = plane c, row y + ky - 1,
 		// columns x - 1 .. x + 1 (zero outside the image; bits behind the last column are zero in the planes).  The four
@@ -484,7 +513,7 @@ static int launch_smallk(const GemmParams & p, cudaStream_t stream)
 {
 	const int gy = (p.M + 31) / 32;
 	// enough pixels to give every SM a few hundred threads: one pixel per thread, else four lanes per pixel
-	const bool wide = ((long long)p.n_total * gy >= (long long)sm_count() * 256) && p.x.planes == nullptr;   // rows from planes: four lanes share the gathering
+	const bool wide = ((long long)p.n_total * gy >= (long long)sm_count() * 256) && p.x.planes == nullptr && p.x.masks == nullptr;   // rows from planes / masks: built in the four-lane variant
 	const int cols_per_cta = wide ? SK_THREADS : SK_THREADS / 4;
 	const long long gx = ((long long)p.n_total + cols_per_cta - 1) / cols_per_cta;
 	if (gx > 0x7fffffffLL || gy > 65535) { return XNOR_B200_ERR_TOO_LARGE; }
@@ -582,7 +611,7 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs,
 		const GemmExtra * extra)
 {
-	const bool extras = (extra != nullptr && (extra->win_w > 0 || extra->n_sinks > 0 || extra->planes != nullptr));
+	const bool extras = (extra != nullptr && (extra->win_w > 0 || extra->n_sinks > 0 || extra->planes != nullptr || extra->masks != nullptr));
 	if ((signs != nullptr || (extra != nullptr && extra->n_sinks > 0)) && M % 32 != 0) { return XNOR_B200_ERR_INVALID; }
 	if (extras && counts != nullptr) { return XNOR_B200_ERR_INVALID; }
 	if (extras && n_per_image % 4 != 0 && (extra->win_w > 0)) { return XNOR_B200_ERR_INVALID; }
@@ -611,7 +640,7 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	{
 		const char * tc = std::getenv("XNOR_B200_GEMM_TC");
 		const bool use_tc = (tc != nullptr) ? (tc[0] == '1') : tc_gemm_eligible(M, n_total, K);
-		if (use_tc && !(extra != nullptr && extra->planes != nullptr))
+		if (use_tc && !(extra != nullptr && (extra->planes != nullptr || extra->masks != nullptr)))
 		{
 			return launch_xnor_gemm_tc(M, n_total, n_per_image, K, A, lda_words, B, ldb_words, C, ldc, mean_arr, bias, leaky,
 					shortcut_in, shortcut_out, counts, stream, signs, extras ? extra : nullptr);
@@ -619,7 +648,7 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	}
 
 	// Short rows on a small problem: one pixel per thread, no tiling (latency, not throughput, is the issue there).
-	const bool from_planes = (p.x.planes != nullptr);
+	const bool from_planes = (p.x.planes != nullptr || p.x.masks != nullptr);
 	if (counts == nullptr && shortcut_out == nullptr && short_k_problem(M, n_total, p.kw)
 			&& (((uintptr_t)A | (uintptr_t)B) & 15u) == 0 && lda_words % 4 == 0 && ldb_words % 4 == 0)
 	{

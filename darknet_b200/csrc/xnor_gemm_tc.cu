@@ -466,7 +466,7 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	p.x = GemmExtra();
 	if (extra != nullptr) { p.x = *extra; }
 	if (p.x.out_w <= 0) { p.x.out_w = 1; }
-	if (p.x.planes != nullptr) { return XNOR_B200_ERR_INVALID; }
+	if (p.x.planes != nullptr || p.x.masks != nullptr) { return XNOR_B200_ERR_INVALID; }
 	p.signs = signs;
 	p.A = A; p.B = B;
 	p.M = M; p.n_total = n_total; p.n_per_image = n_per_image; p.K = K;

@@ -48,6 +48,7 @@ class ConvolutionalLayer:
         self.biases_gpu = torch.zeros(n, dtype=torch.float32, device=self.device)
         self.mean_arr_gpu = torch.zeros(n, dtype=torch.float32, device=self.device)
         self.align_bit_weights_gpu: Optional[torch.Tensor] = None
+        self.tap_major_weights_gpu: Optional[torch.Tensor] = None    # xnor_b200_tap_major_weights copy, for channel-mask input
         self.output_gpu = torch.empty(batch, n, g.out_h, g.out_w, dtype=torch.float32, device=self.device)
         # zero-filled: when producers write this operand through sinks, padding taps and row tails are never written
         self.scratch = torch.zeros(capi.lib().xnor_b200_scratch_bytes(C.byref(self.desc)), dtype=torch.uint8, device=self.device)
@@ -145,7 +146,7 @@ class Sink:
 
 def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tensor] = None, x_signs: Optional[torch.Tensor] = None,
                                    pool: Optional[capi.PoolDesc] = None, want_signs: bool = False, packed: bool = False,
-                                   sinks=(), want_output: Optional[bool] = None) -> Optional[torch.Tensor]:
+                                   sinks=(), want_output: Optional[bool] = None, x_masks: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """xnor_b200_conv_forward_io.  Input: fp32 `x`, sign words / planes `x_signs`, or `packed` (the producers' sinks have
     filled l.scratch).  Output: the fp32 tensor (default when there are no sinks, or with want_output), the sign words
     int32 [batch][n/32][out_h*out_w] (want_signs), and/or the consumers' operands (sinks)."""
@@ -157,6 +158,13 @@ def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tens
     io.pool = C.pointer(pool) if pool is not None else None
     io.input_packed = int(packed)
     io.window_major = int(l.window_major)
+    weights = l.align_bit_weights_gpu
+    if x_masks is not None:
+        if l.tap_major_weights_gpu is None:
+            tap_major_weights(l)
+        io.input_masks = x_masks.data_ptr()
+        io.tap_major_weights = 1
+        weights = l.tap_major_weights_gpu
     if want_output is None:
         want_output = not want_signs and not sinks
     out = None
@@ -179,7 +187,18 @@ def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tens
             arr[i].consumer_window_major = int(s.consumer.window_major)
         io.sinks = arr
         io.n_sinks = len(sinks)
-    capi.check(capi.lib().xnor_b200_conv_forward_io(C.byref(l.desc), C.byref(io), l.align_bit_weights_gpu.data_ptr(),
+    capi.check(capi.lib().xnor_b200_conv_forward_io(C.byref(l.desc), C.byref(io), weights.data_ptr(),
                                                    l.mean_arr_gpu.data_ptr(), l.biases_gpu.data_ptr(), l.scratch.data_ptr(),
                                                    l.scratch.numel(), _stream()), "xnor_b200_conv_forward_io")
     return out
+
+
+def tap_major_weights(l: ConvolutionalLayer) -> None:
+    """Fills l.tap_major_weights_gpu (xnor_b200_tap_major_weights): the packed weights in tap-major K order."""
+    l.tap_major_weights_gpu = torch.empty_like(l.align_bit_weights_gpu)
+    capi.check(capi.lib().xnor_b200_tap_major_weights(C.byref(l.desc), l.align_bit_weights_gpu.data_ptr(),
+                                                     l.tap_major_weights_gpu.data_ptr(), _stream()), "xnor_b200_tap_major_weights")
+
+
+def conv_takes_masks(l: ConvolutionalLayer) -> bool:
+    return bool(capi.lib().xnor_b200_conv_takes_masks(C.byref(l.desc)))

@@ -92,6 +92,8 @@ class Layer:
     yolo_done: bool = False          # [yolo] layer whose activation the previous layer already applied
     conv3_pool: int = 0              # first float conv (3 channels, 3x3): 2 = the 2x2/2 maxpool behind it is applied in the kernel
     emit_planes: bool = False        # ... and only the sign planes of the pooled output are written
+    emit_masks: bool = False         # ... as channel masks per pixel instead (the next layer's short-row GEMM reads them directly)
+    mask_source: Optional[int] = None
     emit_signs: bool = False
     # direct sign sinks (xnor_b200_sign_sink): this xnor conv's epilogue fills the packed operand of later xnor convs
     sinks: List = field(default_factory=list)      # of L.Sink
@@ -439,8 +441,13 @@ def link_first_conv(net: Network) -> None:
         if net.sign_chains and j + 1 not in referenced and j + 2 < len(net.layers):
             nxt = net.layers[j + 2]
             if nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None and nxt.c % 32 != 0 and nxt.pool_desc is None:
-                l.emit_planes = True
-                nxt.sign_source = j
+                if L.conv_takes_masks(nxt.xnor_layer):
+                    l.emit_masks = True
+                    nxt.mask_source = j
+                    L.tap_major_weights(nxt.xnor_layer)
+                else:
+                    l.emit_planes = True
+                    nxt.sign_source = j
                 net.sign_links += 1
 
 
@@ -481,12 +488,16 @@ def _float_conv3(net: Network, l: Layer, x: torch.Tensor) -> torch.Tensor:
     import ctypes as C
     desc = capi.ConvDesc(net.batch, l.c, l.h, l.w, l.n, l.size, l.stride, l.pad, capi.LEAKY if l.activation == "leaky" else capi.LINEAR)
     oh, ow = (l.out_h // 2, l.out_w // 2) if l.conv3_pool else (l.out_h, l.out_w)
-    if l.emit_planes:
+    if l.emit_masks:
+        out = torch.empty(net.batch, oh, ow, (l.n + 7) // 8, dtype=torch.uint8, device=x.device)
+    elif l.emit_planes:
         out = torch.empty(net.batch, l.n, oh, (ow + 31) // 32, dtype=torch.int32, device=x.device)
     else:
         out = torch.empty(net.batch, l.n, oh, ow, dtype=torch.float32, device=x.device)
+    fp32 = not (l.emit_planes or l.emit_masks)
     capi.check(capi.lib().xnor_b200_float_conv3_io(C.byref(desc), l.conv3_pool, x.data_ptr(), l.weights_gpu.data_ptr(), l.biases_gpu.data_ptr(),
-                                                  None if l.emit_planes else out.data_ptr(), out.data_ptr() if l.emit_planes else None,
+                                                  out.data_ptr() if fp32 else None, out.data_ptr() if l.emit_planes else None,
+                                                  out.data_ptr() if l.emit_masks else None,
                                                   torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv3_io")
     return out
 
@@ -608,19 +619,20 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
                 nxt = net.layers[l.index + 1] if l.index + 1 < len(net.layers) else None
                 if nxt is not None and nxt.blank:
                     xl.bin_conv_shortcut_in_gpu = net.layers[nxt.input_layers[0]].output_gpu
-                if l.emit_signs or l.sign_source is not None or l.sinks or l.packed_input or xl.window_major:
+                if l.emit_signs or l.sign_source is not None or l.mask_source is not None or l.sinks or l.packed_input or xl.window_major:
                     src = net.layers[l.sign_source].sign_out if l.sign_source is not None else None
+                    masks = net.layers[l.mask_source].sign_out if l.mask_source is not None else None
                     want_fp32 = not l.emit_signs and (l.need_fp32 or not l.sinks)
-                    out = L.forward_convolutional_layer_io(xl, x=None if (src is not None or l.packed_input) else cur, x_signs=src,
-                                                           pool=l.pool_desc, want_signs=l.emit_signs, packed=l.packed_input,
-                                                           sinks=l.sinks, want_output=want_fp32)
+                    out = L.forward_convolutional_layer_io(xl, x=None if (src is not None or masks is not None or l.packed_input) else cur,
+                                                           x_signs=src, pool=l.pool_desc, want_signs=l.emit_signs, packed=l.packed_input,
+                                                           sinks=l.sinks, want_output=want_fp32, x_masks=masks)
                     l.sign_out = out if l.emit_signs else None
                     cur = out if want_fp32 else None
                 else:
                     cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
             elif l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1 and l.activation in ("leaky", "linear"):
                 cur = _float_conv3(net, l, cur.contiguous())
-                if l.emit_planes:
+                if l.emit_planes or l.emit_masks:
                     l.sign_out, cur = cur, None
             elif l.c * l.size * l.size <= 128 and l.n <= 256 and l.activation in ("leaky", "linear"):
                 cur = _float_conv_small(net, l, cur)
@@ -699,8 +711,9 @@ def own_launches_per_forward(net: Network) -> int:
         if l.type == "convolutional":
             if l.xnor:
                 # GEMM (+ pack kernel); the short-K GEMM builds its rows from the first conv's sign planes itself
-                from_planes = (l.sign_source is not None and l.c % 32 != 0 and (l.size, l.stride, l.pad) == (3, 1, 1) and l.c * 9 <= 256
-                               and l.n * net.batch * l.out_h * l.out_w <= (4 << 20))
+                from_planes = l.mask_source is not None or (
+                    l.sign_source is not None and l.c % 32 != 0 and (l.size, l.stride, l.pad) == (3, 1, 1) and l.c * 9 <= 256
+                    and l.n * net.batch * l.out_h * l.out_w <= (4 << 20))
                 n += 1 if (l.packed_input or from_planes) else 2
             elif (l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1) or l.c * l.size * l.size <= 128 or l.weights_blocked_gpu is not None:
                 n += 1

@@ -218,7 +218,22 @@ typedef struct xnor_b200_conv_io
 	                                         pooled sink finds each window in four consecutive columns; outputs are unaffected */
 	const xnor_b200_sign_sink * sinks;    /* up to 2 direct consumers; may be combined with `output` (fp32 for a [route]) */
 	int n_sinks;
+	const uint8_t * input_masks;          /* fourth kind of input, for the first xnor layer behind xnor_b200_float_conv3_io when
+	                                         xnor_b200_conv_takes_masks() says so: channel masks [batch][h][w][c/8] (bit c%8 of byte
+	                                         c/8 = "channel c > 0").  The GEMM then builds its rows itself, in TAP-major K order, so
+	                                         the weights argument must be the xnor_b200_tap_major_weights() copy: */
+	int tap_major_weights;                /* 1 = it is; input_masks is refused otherwise */
 } xnor_b200_conv_io;
+
+/* 1 when a layer can take input_masks: c is 8 or 16, size 3, stride 1, pad 1, and the problem is small enough for the
+ * short-row GEMM kernel (batch * n * out_h * out_w <= 4 Mi and no kernel override in the environment). */
+XNOR_B200_API int xnor_b200_conv_takes_masks(const xnor_b200_conv_desc * desc);
+
+/* Re-orders packed weights of a c % 32 != 0 layer from the reference's K order (bit c*size*size + tap,
+ * src-lib/convolutional_layer.cpp:1403-1411) to tap-major (bit tap*c + c'), same row pitch.  XNOR-popcount does not care
+ * about the order as long as both operands agree; tap-major makes an activation row nine neighbouring channel masks. */
+XNOR_B200_API int xnor_b200_tap_major_weights(const xnor_b200_conv_desc * desc, const uint8_t * align_bit_weights, uint8_t * tap_major,
+		void * stream);
 
 /* xnor_b200_conv_forward for chains of xnor layers.  A layer marked bin_output=1 feeds nothing but the next
  * binarised convolution (src-lib/darknet_network.cpp:1794-1797 drops its activation for that reason), which only
@@ -245,11 +260,13 @@ XNOR_B200_API int xnor_b200_float_conv_small(const xnor_b200_conv_desc * desc, c
  *   output              fp32 [batch][n][h][w] (pool 0) or [batch][n][h/2][w/2] (pool 2), bias and activation applied
  *   output_sign_planes  pool 2 only: sign of the pooled output as x-packed planes [batch][n][h/2][ceil(w/2/32)],
  *                       the input_signs format of xnor_b200_conv_forward_io for c % 32 != 0
- * Exactly one of the two is non-NULL.  Every value is formed as in xnor_b200_float_conv_small, so the planes equal
+ *   output_sign_masks   pool 2 only: the same signs channel-packed per pixel, [batch][h/2][w/2][ceil(n/8)] bytes, the
+ *                       input_masks format of xnor_b200_conv_forward_io
+ * Exactly one of the three is non-NULL.  Every value is formed as in xnor_b200_float_conv_small, so the planes equal
  * the sign of maxpool(that call's output) bit for bit.  Replaces forward_convolutional_layer_gpu (float branch) +
  * forward_maxpool_layer_gpu (src-lib/maxpool_layer_kernels.cu:48-86) + the sign step of the next layer. */
 XNOR_B200_API int xnor_b200_float_conv3_io(const xnor_b200_conv_desc * desc, int pool, const float * input, const float * weights,
-		const float * biases, float * output, uint32_t * output_sign_planes, void * stream);
+		const float * biases, float * output, uint32_t * output_sign_planes, uint8_t * output_sign_masks, void * stream);
 
 /* The float convolutions behind the path (many channels on a small map: the 3x3 256->512 layer on 13x13 and the
  * 1x1 layers in front of the yolo heads): the same float branch of forward_convolutional_layer_gpu

@@ -103,15 +103,19 @@ def test_float_conv_map_rejects_other_shapes():
         assert lib.xnor_b200_float_conv_map(C.byref(bad), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None) == 1
 
 
-def _conv3(desc, pool, x, wt, b, planes=False):
+def _conv3(desc, pool, x, wt, b, planes=False, masks=False):
     n, h, w = desc.n, desc.h, desc.w
     oh, ow = (h // 2, w // 2) if pool else (h, w)
-    if planes:
+    if masks:
+        out = torch.full((desc.batch, oh, ow, (n + 7) // 8), 0xAA, dtype=torch.uint8, device="cuda")
+    elif planes:
         out = torch.full((desc.batch, n, oh, (ow + 31) // 32), -1, dtype=torch.int32, device="cuda")
     else:
         out = torch.full((desc.batch, n, oh, ow), float("nan"), dtype=torch.float32, device="cuda")
+    fp32 = not (planes or masks)
     capi.check(capi.lib().xnor_b200_float_conv3_io(C.byref(desc), pool, x.data_ptr(), wt.data_ptr(), b.data_ptr(),
-                                                  None if planes else out.data_ptr(), out.data_ptr() if planes else None, None), "conv3_io")
+                                                  out.data_ptr() if fp32 else None, out.data_ptr() if planes else None,
+                                                  out.data_ptr() if masks else None, None), "conv3_io")
     torch.cuda.synchronize()
     return out
 
@@ -142,6 +146,12 @@ def test_float_conv3_io_equals_small_kernel_and_its_pooled_sign(case):
     bits = padded.reshape(pos.shape[:3] + (-1, 32))
     words = (bits.astype(np.uint64) << np.arange(32, dtype=np.uint64)).sum(-1).astype(np.uint32)
     assert np.array_equal(planes, words)
+    masks = _conv3(desc, 2, x, wt, b, masks=True).cpu().numpy()                  # [batch][h/2][w/2][ceil(n/8)]
+    nb = (n + 7) // 8
+    chan = np.zeros((batch, h // 2, ow, nb * 8), dtype=np.uint8)
+    chan[..., :n] = np.moveaxis(pos, 1, -1)
+    want_masks = (chan.reshape(batch, h // 2, ow, nb, 8) << np.arange(8, dtype=np.uint8)).sum(-1).astype(np.uint8)
+    assert np.array_equal(masks, want_masks)
 
 
 def test_float_conv3_planes_feed_the_bit_path_xnor_layer():
@@ -154,14 +164,20 @@ def test_float_conv3_planes_feed_the_bit_path_xnor_layer():
     desc = capi.ConvDesc(batch, 3, h, w, 16, 3, 1, 1, capi.LEAKY)
     pooled = _conv3(desc, 2, x, wt, b)
     planes = _conv3(desc, 2, x, wt, b, planes=True)
+    masks = _conv3(desc, 2, x, wt, b, masks=True)
     for stride in (1, 2):
         l = L.make_convolutional_layer(batch, h // 2, w // 2, 16, 32, 3, stride, 1, capi.LEAKY)
         l.load_weights(torch.from_numpy(synth.bell(8, (32, 16 * 9), 0.05)).cuda(), torch.from_numpy(synth.bell(9, (32,), 0.01)).cuda())
         L.binary_align_weights(l)
         want = L.forward_convolutional_layer_gpu(l, pooled).clone()
-        got = L.forward_convolutional_layer_io(l, x_signs=planes)
+        got = L.forward_convolutional_layer_io(l, x_signs=planes).clone()
         torch.cuda.synchronize()
         assert torch.equal(got, want)
+        if stride == 1:
+            assert L.conv_takes_masks(l)
+            assert torch.equal(L.forward_convolutional_layer_io(l, x_masks=masks), want)
+        else:
+            assert not L.conv_takes_masks(l)
 
 
 def test_float_conv3_io_argument_checks():
@@ -170,11 +186,13 @@ def test_float_conv3_io_argument_checks():
     ok = capi.ConvDesc(1, 3, 8, 8, 8, 3, 1, 1, capi.LINEAR)
     odd = capi.ConvDesc(1, 3, 9, 8, 8, 3, 1, 1, capi.LINEAR)
     four = capi.ConvDesc(1, 4, 8, 8, 8, 3, 1, 1, capi.LINEAR)
-    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, None) == 2        # no output
-    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, z.data_ptr(), None) == 1  # planes need the pool
-    assert lib.xnor_b200_float_conv3_io(C.byref(odd), 2, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 1  # odd height
-    assert lib.xnor_b200_float_conv3_io(C.byref(four), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 1
-    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 3, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 1
+    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, None, None) == 2        # no output
+    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, z.data_ptr(), None, None) == 1  # planes need the pool
+    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, z.data_ptr(), None) == 1  # masks too
+    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 2, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 2  # two outputs
+    assert lib.xnor_b200_float_conv3_io(C.byref(odd), 2, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, None) == 1  # odd height
+    assert lib.xnor_b200_float_conv3_io(C.byref(four), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, None) == 1
+    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 3, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, None) == 1
 
 
 def test_float_conv_map_yolo_equals_conv_then_yolo_activate():

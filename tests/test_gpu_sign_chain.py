@@ -98,7 +98,7 @@ def test_network_with_sign_chains_equals_fp32_network(tmp_path, batch):
         assert not linked.layers[8].need_fp32 and linked.layers[13].need_fp32
     else:
         assert linked.sink_links == 0 and linked.sign_links >= 4
-    assert linked.layers[0].emit_planes and linked.layers[0].conv3_pool == 2
+    assert (linked.layers[0].emit_planes or linked.layers[0].emit_masks) and linked.layers[0].conv3_pool == 2
     got = network.forward_network_gpu(linked, x)
     want = network.forward_network_gpu(plain, x)
     assert len(got) == len(want) == 2
