@@ -146,7 +146,7 @@ struct TcShape
 };
 
 template <int NF>
-__global__ void __launch_bounds__(TcShape<NF>::THREADS, (NF == 128) ? 3 : 2)      // co-resident CTAs: one epilogue overlaps another main loop
+__global__ void __launch_bounds__(TcShape<NF>::THREADS, (NF == 256) ? 2 : (NF == 128) ? 3 : 4)      // co-resident CTAs: one epilogue overlaps another main loop
 xnor_gemm_tc_kernel(const TcParams p)
 {
 	using S = TcShape<NF>;
@@ -297,8 +297,9 @@ xnor_gemm_tc_kernel(const TcParams p)
 		// A warp may read TMEM lanes 32*(warp%4) .. +31.  The producer warps 1..PRODUCER_WARPS cover every lane
 		// quarter PRODUCER_WARPS/4 times; warps sharing a quarter interleave over the 32-column chunks.
 		const int quarter = warp & 3;
-		const int share = (warp - 1) >> 2;                    // 0 .. PRODUCER_WARPS/4 - 1
 		constexpr int SHARES = S::PRODUCER_WARPS / 4;
+		// 0 .. SHARES - 1; the odd producer warps of the narrow tiles (5 or 6 producer warps) have nothing left to read
+		const int share = ((warp - 1) >> 2) < SHARES ? ((warp - 1) >> 2) : NF;
 		const int pix_local = quarter * 32 + lane;
 		const int col = n0 + pix_local;                       // global pixel (column of C)
 		const bool col_ok = col < p.n_total;
@@ -424,22 +425,23 @@ xnor_gemm_tc_kernel(const TcParams p)
 
 bool tc_gemm_eligible(int M, int n_total, int K)
 {
-	// Needs enough filters to fill the N side of the MMA and enough K to amortise the TMEM round trip; beyond that the
-	// faster of two estimates fitted to measurements on B200 (batch 8..64 layer shapes) decides:
+	// The faster of two estimates fitted to measurements on B200 (batch 8..64 layer shapes) decides:
 	//   tensor-core kernel: ~14 us of fixed cost (launch with 100+ KB of shared memory, TMEM allocation, pipeline fill,
-	//                       drain) + per tile 0.6 us per 128-bit K block and 4 us of epilogue (half of both for 128-filter
-	//                       tiles), times the tiles the busiest SM gets (co-resident CTAs share the SM's shared-memory bandwidth);
-	//   integer kernel:     ~4 us + binary ops at 250 T/s.
-	if (M < 96 || K < 256) { return false; }
-	const int nf = (M > 128) ? 256 : 128;
+	//                       drain) + per tile 0.6 us per 128-bit K block and 4 us of epilogue for 256-filter tiles (0.33 + 2.5,
+	//                       0.25 + 2.0, 0.2 + 1.4 for 128, 64 and 32 filters), times the tiles the busiest SM gets (co-resident
+	//                       CTAs share the SM's shared-memory bandwidth);
+	//   integer kernel:     ~4 us + binary ops (over the K words it actually walks) at 250 T/s.
+	if (M < 16 || K < 128) { return false; }
+	const int nf = (M > 128) ? 256 : (M > 64) ? 128 : (M > 32) ? 64 : 32;
 	const long long tiles = (long long)((M + nf - 1) / nf) * ((n_total + TC_PIX - 1) / TC_PIX);
 	const double kb = (double)((K + 127) / 128);
-	const double per_tile = (nf == 256) ? 0.6 * kb + 4.0 : 0.33 * kb + 2.5;
+	const double per_tile = (nf == 256) ? 0.6 * kb + 4.0 : (nf == 128) ? 0.33 * kb + 2.5 : (nf == 64) ? 0.25 * kb + 2.0 : 0.2 * kb + 1.4;
 	double load = (double)tiles / (double)sm_count();
 	if (nf == 256) { load = (double)((tiles + sm_count() - 1) / sm_count()); }
 	if (load < 1.0) { load = 1.0; }
 	const double t_tc = 14.0 + per_tile * load;
-	const double t_int = 4.0 + 2.0 * (double)M * (double)n_total * (double)K / 250.0e6;
+	const double k_int = (double)(((K + 31) / 32 + 3) / 4 * 4 * 32);       // the integer kernel walks whole 16-byte groups of K words
+	const double t_int = 4.0 + 2.0 * (double)M * (double)n_total * k_int / 250.0e6;
 	return t_tc < t_int;
 }
 
@@ -474,7 +476,9 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	p.kblocks = (K + 127) / 128;
 	p.C = C; p.ldc = ldc; p.mean_arr = mean_arr; p.bias = bias; p.leaky = leaky;
 	p.shortcut_in = shortcut_in; p.shortcut_out = shortcut_out; p.counts = counts;
-	return (M > 128) ? launch_tc<256>(p, stream) : launch_tc<128>(p, stream);
+	if (M > 128) { return launch_tc<256>(p, stream); }
+	if (M > 64) { return launch_tc<128>(p, stream); }
+	return (M > 32) ? launch_tc<64>(p, stream) : launch_tc<32>(p, stream);
 }
 
 int read_tc_error(int * out, bool clear)
