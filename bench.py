@@ -285,7 +285,7 @@ def run_gpu_arm(args) -> None:
     ms_e2e = timed_steps(args.steps, True)
     barrier()
     ms_e2e = max_over_ranks(ms_e2e)
-    for hh, hd in zip(head_host, heads_e2e):           # the pinned host copies are the device heads of the last step
+    for hh, hd in zip(head_host, heads):               # what the end-to-end steps left in pinned host memory = the device-resident forward
         if not torch.equal(hh, hd.cpu()):
             raise SystemExit("bench: host copy of a head differs from the device tensor")
     clocks = sampler.stop() if sampler else None

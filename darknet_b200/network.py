@@ -124,6 +124,7 @@ class Network:
     fuse_first_conv: bool = True
     float_map_max_pixels: int = 4096       # batch*out_h*out_w up to which float convs use the cluster split-K kernel
     sign_links: int = 0
+    heads_direct_to_host: bool = True      # with heads_host: a fused head convolution stores into the pinned host tensor itself
     side_branches: bool = True             # a head branch that nothing later reads runs on a second stream
     side_stream: Optional[torch.cuda.Stream] = None
     sink_max_batch: int = 1 << 30          # batch up to which direct sign sinks are linked (measured: a gain at every batch for yolov3-tiny, within 2% either way for the other two networks at batch 32-256)
@@ -539,11 +540,13 @@ def prepare_float_map_convs(net: Network) -> None:
                                                               torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_map_prepare")
 
 
-def _float_conv_map(net: Network, l: Layer, x: torch.Tensor) -> torch.Tensor:
-    """A many-channel float convolution on a small map: cluster split-K kernel with bias and activation fused."""
+def _float_conv_map(net: Network, l: Layer, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A many-channel float convolution on a small map: cluster split-K kernel with bias and activation fused.  `out` may be
+    a pinned host tensor (the device writes a finished head straight into host memory)."""
     import ctypes as C
     desc = _map_conv_desc(net, l)
-    out = torch.empty(net.batch, l.n, l.out_h, l.out_w, dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty(net.batch, l.n, l.out_h, l.out_w, dtype=torch.float32, device=x.device)
     capi.check(capi.lib().xnor_b200_float_conv_map_yolo(C.byref(desc), x.data_ptr(), l.weights_blocked_gpu.data_ptr(), l.biases_gpu.data_ptr(),
                                                        out.data_ptr(), l.yolo_entries, torch.cuda.current_stream().cuda_stream),
                "xnor_b200_float_conv_map_yolo")
@@ -637,7 +640,9 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
             elif l.c * l.size * l.size <= 128 and l.n <= 256 and l.activation in ("leaky", "linear"):
                 cur = _float_conv_small(net, l, cur)
             elif l.weights_blocked_gpu is not None:
-                cur = _float_conv_map(net, l, cur.contiguous())
+                # a head whose yolo activation runs in this kernel can be written straight into the caller's pinned host tensor
+                direct = heads_host is not None and l.yolo_entries > 0 and net.heads_direct_to_host
+                cur = _float_conv_map(net, l, cur.contiguous(), heads_host[len(heads)] if direct else None)
             elif l.size == 1 and l.stride == 1 and l.pad == 0:
                 # a 1x1 convolution is a plain matrix product per image (cuBLAS sgemm, fp32)
                 b = cur.shape[0]
@@ -668,7 +673,7 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
         elif l.type == "yolo":
             cur = cur if l.yolo_done else _yolo(cur, l)
             heads.append(cur)
-            if heads_host is not None:
+            if heads_host is not None and cur is not heads_host[len(heads) - 1]:
                 heads_host[len(heads) - 1].copy_(cur, non_blocking=True)
         elif l.type == "region":
             cur = _region(cur, l)
