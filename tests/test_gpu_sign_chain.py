@@ -104,3 +104,29 @@ def test_network_with_sign_chains_equals_fp32_network(tmp_path, batch):
     assert len(got) == len(want) == 2
     for a, b in zip(got, want):
         assert torch.equal(a, b)
+
+
+def test_heads_written_to_pinned_host_memory(tmp_path):
+    """forward_network_gpu(heads_host=...): the fused head convolutions store into the pinned host tensors themselves;
+    what arrives there equals the device heads of a plain forward."""
+    from darknet_b200 import cfgs, network
+    cfg = tmp_path / "net.cfg"
+    cfg.write_text(cfgs.yolov3_tiny_xnor_cfg(96, 96))
+    net_cpu = network.parse_network_cfg(str(cfg), 1, "cpu")
+    w = tmp_path / "net.weights"
+    network.write_synthetic_weights(net_cpu, str(w), seed=5)
+    x = torch.from_numpy(synth.uniform01(9, (1, 3, 96, 96))).cuda()
+    net = network.load_network_custom(str(cfg), str(w), 1)
+    want = [h.clone() for h in network.forward_network_gpu(net, x)]
+    host = [torch.full(h.shape, float("nan")).pin_memory() for h in want]
+    got = network.forward_network_gpu(net, x, host)
+    torch.cuda.synchronize()
+    assert all(g is h for g, h in zip(got, host))          # the returned heads are the host tensors
+    for h, d in zip(host, want):
+        assert torch.equal(h, d.cpu())
+    net.heads_direct_to_host = False                        # the copy route gives the same
+    host2 = [torch.full(h.shape, float("nan")).pin_memory() for h in want]
+    network.forward_network_gpu(net, x, host2)
+    torch.cuda.synchronize()
+    for h, d in zip(host2, want):
+        assert torch.equal(h, d.cpu())
