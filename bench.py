@@ -349,7 +349,10 @@ def run_gpu_arm(args) -> None:
         roofline = {
             "kernel": "xnor_gemm_kernel (9 launches = the xnor layers of one forward, stand-alone calls with fp32 epilogue)",
             "bound": "int_popc", "achieved": achieved, "peak": popc_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)",
-            "frac": achieved / popc_peak_tops, "traffic": None,
+            # dram__bytes_read + dram__bytes_write summed over the 9 launches of one forward (batch 1), one ncu capture:
+            # profiles/xnor_gemm_kernels_b1_dram_traffic.md.  Algorithmic bytes = packed operands read once + fp32 outputs.
+            "frac": achieved / popc_peak_tops, "traffic": 4.36e6 if batch == 1 else None,
+            "algorithmic_bytes": sum((xl.n + batch * xl.geom.n_out) * xl.geom.new_lda // 8 + 4 * xl.n * batch * xl.geom.n_out for xl in xl_layers),
             "peak_source": "measured in this run: register-resident XOR+POPC+ADD loop on all SMs",
             "b1_mma_sync_peak": bmma_peak_tops, "ms_per_forward": ms_gemm,
         }
