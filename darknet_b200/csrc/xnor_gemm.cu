@@ -592,9 +592,11 @@ static float estimate_cycles(const TileConfig & c, int M, int n_total, int kw, i
 	return per_sm * (cta_cycles + store_cycles) + 700.0f * ((per_sm + c.max_resident - 1) / c.max_resident) + fixed;
 }
 
-static bool short_k_problem(int M, int n_total, int kw)
+// rows_in_kernel: the kernel would build its rows from planes / masks, i.e. the alternative is a pack kernel plus a GEMM
+// over a 32-byte-per-pixel operand; that pays at every size, the plain short-K kernel only while launches dominate.
+static bool short_k_problem(int M, int n_total, int kw, bool rows_in_kernel = false)
 {
-	return kw <= 8 && (long long)M * n_total <= (4ll << 20) && std::getenv("XNOR_B200_GEMM_FORCE") == nullptr
+	return kw <= 8 && (rows_in_kernel || (long long)M * n_total <= (4ll << 20)) && std::getenv("XNOR_B200_GEMM_FORCE") == nullptr
 			&& std::getenv("XNOR_B200_GEMM_TC") == nullptr;
 }
 
@@ -602,7 +604,7 @@ bool gemm_takes_planes(int M, int n_total, int c, int size, int stride, int pad)
 {
 	const int K = c * size * size;
 	return size == 3 && stride == 1 && pad == 1 && c % 32 != 0 && K <= 256
-			&& short_k_problem(M, n_total, (int)round_up((size_t)(K + 31) / 32, 4));
+			&& short_k_problem(M, n_total, (int)round_up((size_t)(K + 31) / 32, 4), true);
 }
 
 int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
@@ -649,7 +651,7 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 
 	// Short rows on a small problem: one pixel per thread, no tiling (latency, not throughput, is the issue there).
 	const bool from_planes = (p.x.planes != nullptr || p.x.masks != nullptr);
-	if (counts == nullptr && shortcut_out == nullptr && short_k_problem(M, n_total, p.kw)
+	if (counts == nullptr && shortcut_out == nullptr && short_k_problem(M, n_total, p.kw, from_planes)
 			&& (((uintptr_t)A | (uintptr_t)B) & 15u) == 0 && lda_words % 4 == 0 && ldb_words % 4 == 0)
 	{
 		switch (p.kw / 4)

@@ -717,8 +717,7 @@ def own_launches_per_forward(net: Network) -> int:
             if l.xnor:
                 # GEMM (+ pack kernel); the short-K GEMM builds its rows from the first conv's sign planes itself
                 from_planes = l.mask_source is not None or (
-                    l.sign_source is not None and l.c % 32 != 0 and (l.size, l.stride, l.pad) == (3, 1, 1) and l.c * 9 <= 256
-                    and l.n * net.batch * l.out_h * l.out_w <= (4 << 20))
+                    l.sign_source is not None and l.c % 32 != 0 and (l.size, l.stride, l.pad) == (3, 1, 1) and l.c * 9 <= 256)
                 n += 1 if (l.packed_input or from_planes) else 2
             elif (l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1) or l.c * l.size * l.size <= 128 or l.weights_blocked_gpu is not None:
                 n += 1

@@ -225,8 +225,7 @@ typedef struct xnor_b200_conv_io
 	int tap_major_weights;                /* 1 = it is; input_masks is refused otherwise */
 } xnor_b200_conv_io;
 
-/* 1 when a layer can take input_masks: c is 8 or 16, size 3, stride 1, pad 1, and the problem is small enough for the
- * short-row GEMM kernel (batch * n * out_h * out_w <= 4 Mi and no kernel override in the environment). */
+/* 1 when a layer can take input_masks: c is 8 or 16, size 3, stride 1, pad 1 (and no kernel override in the environment). */
 XNOR_B200_API int xnor_b200_conv_takes_masks(const xnor_b200_conv_desc * desc);
 
 /* Re-orders packed weights of a c % 32 != 0 layer from the reference's K order (bit c*size*size + tap,
