@@ -340,7 +340,9 @@ constexpr int SK_THREADS = 128;
 
 // FPT = filters per thread (32: a thread owns the whole sign word of its pixel; 8: four neighbouring lanes share a
 // pixel and combine their byte of the word with two shuffles -- used when there are too few pixels to fill the GPU).
-template <int KW4, int FPT>
+// TAIL = K words that carry data in the last 16-byte group (1..4): the words behind them are zero in both operands
+// and are not visited (a 16-channel 3x3 layer has 4.5 data words in its 8-word row).
+template <int KW4, int FPT, int TAIL>
 __global__ void __launch_bounds__(SK_THREADS)
 xnor_gemm_smallk_kernel(const GemmParams p)
 {
@@ -457,7 +459,10 @@ xnor_gemm_smallk_kernel(const GemmParams p)
 		for (int q = 0; q < KW4; ++q)
 		{
 			const uint4 a = reinterpret_cast<const uint4 *>(s_a)[f * KW4 + q];
-			cnt += __popc(a.x ^ b[q].x) + __popc(a.y ^ b[q].y) + __popc(a.z ^ b[q].z) + __popc(a.w ^ b[q].w);
+			cnt += __popc(a.x ^ b[q].x);
+			if (q < KW4 - 1 || TAIL > 1) { cnt += __popc(a.y ^ b[q].y); }
+			if (q < KW4 - 1 || TAIL > 2) { cnt += __popc(a.z ^ b[q].z); }
+			if (q < KW4 - 1 || TAIL > 3) { cnt += __popc(a.w ^ b[q].w); }
 		}
 		float v = __fmul_rn((float)(p.K - 2 * cnt), __ldg(p.mean_arr + m));
 		if (p.bias != nullptr) { v = __fadd_rn(v, __ldg(p.bias + m)); }
@@ -508,7 +513,7 @@ xnor_gemm_smallk_kernel(const GemmParams p)
 	}
 }
 
-template <int KW4>
+template <int KW4, int TAIL>
 static int launch_smallk(const GemmParams & p, cudaStream_t stream)
 {
 	const int gy = (p.M + 31) / 32;
@@ -517,8 +522,8 @@ static int launch_smallk(const GemmParams & p, cudaStream_t stream)
 	const int cols_per_cta = wide ? SK_THREADS : SK_THREADS / 4;
 	const long long gx = ((long long)p.n_total + cols_per_cta - 1) / cols_per_cta;
 	if (gx > 0x7fffffffLL || gy > 65535) { return XNOR_B200_ERR_TOO_LARGE; }
-	if (wide) { xnor_gemm_smallk_kernel<KW4, 32><<<dim3((unsigned)gx, (unsigned)gy, 1), SK_THREADS, 0, stream>>>(p); }
-	else { xnor_gemm_smallk_kernel<KW4, 8><<<dim3((unsigned)gx, (unsigned)gy, 1), SK_THREADS, 0, stream>>>(p); }
+	if (wide) { xnor_gemm_smallk_kernel<KW4, 32, TAIL><<<dim3((unsigned)gx, (unsigned)gy, 1), SK_THREADS, 0, stream>>>(p); }
+	else { xnor_gemm_smallk_kernel<KW4, 8, TAIL><<<dim3((unsigned)gx, (unsigned)gy, 1), SK_THREADS, 0, stream>>>(p); }
 	return check_launch();
 }
 
@@ -654,13 +659,16 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	if (counts == nullptr && shortcut_out == nullptr && short_k_problem(M, n_total, p.kw, from_planes)
 			&& (((uintptr_t)A | (uintptr_t)B) & 15u) == 0 && lda_words % 4 == 0 && ldb_words % 4 == 0)
 	{
-		switch (p.kw / 4)
+		switch ((K + 31) / 32)                              // K words that carry data: 1..8
 		{
-			case 1: return launch_smallk<1>(p, stream);
-			case 2: return launch_smallk<2>(p, stream);
-			case 3: return launch_smallk<3>(p, stream);
-			case 4: return launch_smallk<4>(p, stream);
-			default: return launch_smallk<5>(p, stream);
+			case 1: return launch_smallk<1, 1>(p, stream);
+			case 2: return launch_smallk<1, 2>(p, stream);
+			case 3: return launch_smallk<1, 3>(p, stream);
+			case 4: return launch_smallk<1, 4>(p, stream);
+			case 5: return launch_smallk<2, 1>(p, stream);
+			case 6: return launch_smallk<2, 2>(p, stream);
+			case 7: return launch_smallk<2, 3>(p, stream);
+			default: return launch_smallk<2, 4>(p, stream);
 		}
 	}
 
