@@ -348,7 +348,13 @@ xnor_gemm_smallk_kernel(const GemmParams p)
 {
 	constexpr int SUBS = 32 / FPT;
 	__shared__ __align__(16) uint32_t s_a[32 * KW4 * 4];
+	__shared__ float2 s_mb[32];                               // (mean, bias) of the group's filters
 	const int m0 = blockIdx.y * 32;
+	if (threadIdx.x < 32)
+	{
+		const int m = m0 + threadIdx.x;
+		s_mb[threadIdx.x] = make_float2((m < p.M) ? __ldg(p.mean_arr + m) : 0.0f, (m < p.M && p.bias != nullptr) ? __ldg(p.bias + m) : 0.0f);
+	}
 	for (int i = threadIdx.x; i < 32 * KW4; i += SK_THREADS)
 	{
 		const int f = i / KW4;
@@ -364,7 +370,7 @@ xnor_gemm_smallk_kernel(const GemmParams p)
 	const int pixcol = live ? col - img * p.n_per_image : 0;
 	const int pix = col_to_pixel(p.x, pixcol);
 	uint4 b[KW4];
-	if (FPT == 8 && KW4 <= 2 && p.x.masks != nullptr)
+	if (KW4 <= 2 && p.x.masks != nullptr)
 	{
 		// Tap-major rows: bits [t*C, t*C + C) are the channel mask of the pixel under tap t (zero outside the image).
 		// C is 8 or 16, so a mask never straddles a word.
@@ -464,8 +470,9 @@ xnor_gemm_smallk_kernel(const GemmParams p)
 			if (q < KW4 - 1 || TAIL > 2) { cnt += __popc(a.z ^ b[q].z); }
 			if (q < KW4 - 1 || TAIL > 3) { cnt += __popc(a.w ^ b[q].w); }
 		}
-		float v = __fmul_rn((float)(p.K - 2 * cnt), __ldg(p.mean_arr + m));
-		if (p.bias != nullptr) { v = __fadd_rn(v, __ldg(p.bias + m)); }
+		const float2 mb = s_mb[f];
+		float v = __fmul_rn((float)(p.K - 2 * cnt), mb.x);
+		if (p.bias != nullptr) { v = __fadd_rn(v, mb.y); }
 		word |= (v > 0.0f ? 1u : 0u) << f;
 		if (p.C != nullptr && live)
 		{
@@ -518,7 +525,7 @@ static int launch_smallk(const GemmParams & p, cudaStream_t stream)
 {
 	const int gy = (p.M + 31) / 32;
 	// enough pixels to give every SM a few hundred threads: one pixel per thread, else four lanes per pixel
-	const bool wide = ((long long)p.n_total * gy >= (long long)sm_count() * 256) && p.x.planes == nullptr && p.x.masks == nullptr;   // rows from planes / masks: built in the four-lane variant
+	const bool wide = ((long long)p.n_total * gy >= (long long)sm_count() * 256) && p.x.planes == nullptr;   // rows from planes: built in the four-lane variant
 	const int cols_per_cta = wide ? SK_THREADS : SK_THREADS / 4;
 	const long long gx = ((long long)p.n_total + cols_per_cta - 1) / cols_per_cta;
 	if (gx > 0x7fffffffLL || gy > 65535) { return XNOR_B200_ERR_TOO_LARGE; }
