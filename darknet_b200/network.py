@@ -122,7 +122,7 @@ class Network:
     fold_maxpool_min_batch: int = 4
     sign_chains: bool = True
     fuse_first_conv: bool = True
-    float_map_max_pixels: int = 4096       # batch*out_h*out_w up to which float convs use the cluster split-K kernel
+    float_map_max_pixels: int = 1024       # batch*out_h*out_w up to which float convs use the cluster split-K kernel (measured: it wins at 676 pixels, loses to cuDNN/cuBLAS at 1352)
     sign_links: int = 0
     heads_direct_to_host: bool = True      # with heads_host: a fused head convolution stores into the pinned host tensor itself
     side_branches: bool = True             # a head branch that nothing later reads runs on a second stream
@@ -701,6 +701,8 @@ def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "c
     net.sign_chains = sign_chains
     net.fuse_first_conv = fuse_first_conv
     net.side_branches = side_branches
+    if os.environ.get("XNOR_B200_FLOAT_MAP_MAX_PIXELS"):      # tuning aid
+        net.float_map_max_pixels = int(os.environ["XNOR_B200_FLOAT_MAP_MAX_PIXELS"])
     if os.environ.get("XNOR_B200_SINK_MAX_BATCH"):            # tuning aid: batch up to which sign sinks are linked
         net.sink_max_batch = int(os.environ["XNOR_B200_SINK_MAX_BATCH"])
     load_weights(net, weights)
