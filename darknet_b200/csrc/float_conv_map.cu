@@ -279,6 +279,111 @@ float_conv_map_kernel(const FloatMapParams p)
 	if (S > 1) { cg::this_cluster().sync(); }       // nobody leaves while a peer still reads its partial sums
 }
 
+// ---- 1x1 layers: one load, one pass -------------------------------------------------------------------------
+// A 1x1 convolution on a small map is a tiny matrix product (255 x 169 x 512 for a yolo head): the pipeline, the
+// cluster and its two barriers above cost more than the arithmetic.  Here a CTA owns 16 filters x 32 pixels, issues
+// ALL of its operand loads at once (K x 16 weights as 16-byte copies out of the blocked layout, K x 32 inputs as 4-byte
+// copies: 48 KB for K = 256), waits once, lets each of its 8 warps run over an eighth of the channels (lane = pixel, 16
+// accumulators, weights read as broadcasts), and adds the eight partial tiles through shared memory.  One barrier pair,
+// no cluster, and enough CTAs (96 for the 13x13 head, 352 for the 26x26 one) to cover the chip in one wave.
+constexpr int F1_THREADS = 256;
+constexpr int F1_FT = 16;                  // filters per CTA (half of a 32-filter block of the blocked weights)
+constexpr int F1_PT = 32;                  // pixels per CTA
+constexpr int F1_MAX_K = 512;              // 192 bytes of shared memory per channel: two CTAs per SM at the limit
+
+__global__ void __launch_bounds__(F1_THREADS)
+float_conv_1x1_kernel(const FloatMapParams p)
+{
+	extern __shared__ __align__(16) float s_mem[];
+	const int K = p.C;
+	float * s_w = s_mem;                    // [K][16]
+	float * s_x = s_mem + (size_t)K * F1_FT;  // [K][32]
+	const int tid = threadIdx.x;
+	const int lane = tid & 31;
+	const int warp = tid >> 5;
+	const int HW = p.H * p.W;
+	const int img = blockIdx.x / p.ptiles;
+	const int pt = blockIdx.x - img * p.ptiles;
+	const int ft = blockIdx.y;                                    // 16-filter tile
+	const int px = pt * F1_PT + lane;
+	const float * in_img = p.in + (size_t)img * p.C * HW;
+	const float * wsrc = p.wblk + ((size_t)(ft >> 1) * K) * FM_FT + (ft & 1) * F1_FT;   // row k at wsrc + k*32
+
+	for (int v = tid; v < K * (F1_FT / 4); v += F1_THREADS)
+	{
+		const int k = v >> 2;
+		const int q = v & 3;
+		cp_async_16f(s_w + k * F1_FT + q * 4, wsrc + (size_t)k * FM_FT + q * 4);
+	}
+	for (int k = warp; k < K; k += F1_THREADS / 32)
+	{
+		cp_async_4z(s_x + k * F1_PT + lane, (px < HW) ? in_img + (size_t)k * HW + px : in_img, px < HW);
+	}
+	cp_commit();
+	cp_wait<0>();
+	__syncthreads();
+
+	// warp w takes channels w, w + 8, ...
+	float acc[F1_FT];
+	#pragma unroll
+	for (int f = 0; f < F1_FT; ++f) { acc[f] = 0.0f; }
+	#pragma unroll 4
+	for (int k = warp; k < K; k += F1_THREADS / 32)
+	{
+		const float xv = s_x[k * F1_PT + lane];
+		const float4 * wr = reinterpret_cast<const float4 *>(s_w + k * F1_FT);
+		#pragma unroll
+		for (int q = 0; q < 4; ++q)
+		{
+			const float4 w = wr[q];
+			acc[4 * q + 0] = fmaf(w.x, xv, acc[4 * q + 0]);
+			acc[4 * q + 1] = fmaf(w.y, xv, acc[4 * q + 1]);
+			acc[4 * q + 2] = fmaf(w.z, xv, acc[4 * q + 2]);
+			acc[4 * q + 3] = fmaf(w.w, xv, acc[4 * q + 3]);
+		}
+	}
+	__syncthreads();                                              // operands are dead: reuse the front of shared memory
+	float * s_part = s_mem;                                       // [8 warps][16 filters][32 pixels]
+	#pragma unroll
+	for (int f = 0; f < F1_FT; ++f) { s_part[(warp * F1_FT + f) * F1_PT + lane] = acc[f]; }
+	__syncthreads();
+	for (int o = tid; o < F1_FT * F1_PT; o += F1_THREADS)
+	{
+		const int fl = o / F1_PT;
+		const int sl = o - fl * F1_PT;
+		float sum = 0.0f;
+		#pragma unroll
+		for (int w = 0; w < F1_THREADS / 32; ++w) { sum += s_part[(w * F1_FT + fl) * F1_PT + sl]; }      // fixed order
+		const int f = ft * F1_FT + fl;
+		const int q = pt * F1_PT + sl;
+		if (f < p.N && q < HW)
+		{
+			if (p.bias != nullptr) { sum += p.bias[f]; }
+			if (p.leaky) { sum = (sum > 0.0f) ? sum : sum * 0.1f; }
+			if (p.yolo_entries > 0)
+			{
+				const int e = f % p.yolo_entries;
+				if (e != 2 && e != 3) { sum = 1.0f / (1.0f + expf(-sum)); }
+			}
+			p.out[((size_t)img * p.N + f) * HW + q] = sum;
+		}
+	}
+}
+
+static int launch_float_1x1(const xnor_b200_conv_desc * desc, FloatMapParams p, cudaStream_t stream)
+{
+	const int HW = desc->h * desc->w;
+	p.ptiles = (HW + F1_PT - 1) / F1_PT;
+	const int ftiles = (desc->n + F1_FT - 1) / F1_FT;
+	const long long gx = (long long)p.ptiles * desc->batch;
+	if (gx > 0x7fffffffLL || ftiles > 65535) { return XNOR_B200_ERR_TOO_LARGE; }
+	const size_t smem = max((size_t)desc->c * (F1_FT + F1_PT), (size_t)(F1_THREADS / 32) * F1_FT * F1_PT) * sizeof(float);
+	int rc = ensure_dynamic_smem((const void *)float_conv_1x1_kernel, smem);
+	if (rc != XNOR_B200_OK) { return rc; }
+	float_conv_1x1_kernel<<<dim3((unsigned)gx, (unsigned)ftiles, 1), F1_THREADS, smem, stream>>>(p);
+	return check_launch();
+}
+
 // [n][K] -> [ceil(n/32)][K][32], zero filters behind n
 __global__ void float_conv_map_block_weights_kernel(const float * __restrict__ w, float * __restrict__ blk, int N, int K, size_t total)
 {
@@ -440,7 +545,11 @@ extern "C" int xnor_b200_float_conv_map_yolo(const xnor_b200_conv_desc * desc, c
 	p.leaky = (desc->activation == XNOR_B200_LEAKY) ? 1 : 0;
 	p.yolo_entries = yolo_entries;
 	// channels per pipeline stage: 16 for 3x3 on the small pitch when the channel count allows (half the barriers)
-	if (desc->size == 1) { return launch_float_map_best<1, 16, 32>(desc, p, (cudaStream_t)stream); }
+	if (desc->size == 1)
+	{
+		if (desc->c <= F1_MAX_K) { return launch_float_1x1(desc, p, (cudaStream_t)stream); }
+		return launch_float_map_best<1, 16, 32>(desc, p, (cudaStream_t)stream);
+	}
 	if (desc->h <= 14 && desc->w <= 14)
 	{
 		return (desc->c % 64 == 0) ? launch_float_map_best<3, 16, 16>(desc, p, (cudaStream_t)stream)
