@@ -534,6 +534,154 @@ static int launch_smallk(const GemmParams & p, cudaStream_t stream)
 	return check_launch();
 }
 
+// ---- one-shot kernel ---------------------------------------------------------------------------
+// Mid-sized layers on a small batch (13x13 and 26x26 maps with hundreds of filters and K up to a few thousand bits):
+// the ring, the cluster and its barriers in the tiled kernel cost more than the arithmetic.  Here a CTA owns 32 filters x
+// 32 pixels and loads everything it needs once: the 32 filter rows into shared memory, and every thread its own slice of
+// its pixel's row straight into registers.  The 8 warps split K (warp w takes the w-th slice of KS4 16-byte groups);
+// lane = pixel; a thread walks the 32 filters with broadcast reads, exactly like the short-K kernel.  The eight partial
+// counts per output are added through shared memory (integers: exact in any order), then warp w finishes filters
+// 4w .. 4w+3 of its lane's pixel and warp 0 assembles the sign word for the sign outputs and sinks.
+constexpr int OS_THREADS = 256;
+constexpr int OS_WARPS = OS_THREADS / 32;
+
+template <int KS4>
+__global__ void __launch_bounds__(OS_THREADS)
+xnor_gemm_oneshot_kernel(const GemmParams p)
+{
+	constexpr int SLICE = KS4 * 4;                 // K words per warp
+	constexpr int KWP = OS_WARPS * SLICE;          // K words per (zero-padded) row in shared memory
+	extern __shared__ __align__(16) uint32_t smem[];
+	uint32_t * s_a = smem;                                             // [32][KWP]
+	int * s_red = reinterpret_cast<int *>(smem + 32 * KWP);            // [8 warps][32 filters][32 pixels]
+	uint8_t * s_bits = reinterpret_cast<uint8_t *>(smem + 32 * KWP + OS_WARPS * 32 * 32);   // [8 warps][32 pixels]
+	const int lane = threadIdx.x & 31;
+	const int warp = threadIdx.x >> 5;
+	const int m0 = blockIdx.y * 32;
+	const int col = blockIdx.x * 32 + lane;
+	const bool live = (col < p.n_total);
+
+	for (int i = threadIdx.x; i < 32 * (KWP / 4); i += OS_THREADS)
+	{
+		const int f = i / (KWP / 4);
+		const int q = i - f * (KWP / 4);
+		uint4 v = make_uint4(0u, 0u, 0u, 0u);
+		if (m0 + f < p.M && q * 4 < p.kw) { v = __ldg(reinterpret_cast<const uint4 *>(p.A + (size_t)(m0 + f) * p.lda_words) + q); }
+		reinterpret_cast<uint4 *>(s_a)[i] = v;
+	}
+	uint4 b[KS4];
+	#pragma unroll
+	for (int q = 0; q < KS4; ++q)
+	{
+		const int w4 = warp * KS4 + q;                 // 16-byte group of the row
+		b[q] = (live && w4 * 4 < p.kw) ? __ldg(reinterpret_cast<const uint4 *>(p.B + (size_t)col * p.ldb_words) + w4) : make_uint4(0u, 0u, 0u, 0u);
+	}
+	__syncthreads();
+
+	#pragma unroll 4
+	for (int f = 0; f < 32; ++f)
+	{
+		const uint4 * ar = reinterpret_cast<const uint4 *>(s_a + f * KWP + warp * SLICE);
+		int cnt = 0;
+		#pragma unroll
+		for (int q = 0; q < KS4; ++q)
+		{
+			const uint4 a = ar[q];
+			cnt += __popc(a.x ^ b[q].x) + __popc(a.y ^ b[q].y) + __popc(a.z ^ b[q].z) + __popc(a.w ^ b[q].w);
+		}
+		s_red[(warp * 32 + f) * 32 + lane] = cnt;
+	}
+	__syncthreads();
+
+	const int img = live ? col / p.n_per_image : 0;
+	const int pixcol = live ? col - img * p.n_per_image : 0;
+	const int pix = col_to_pixel(p.x, pixcol);
+	uint32_t bits = 0;
+	#pragma unroll
+	for (int ff = 0; ff < 4; ++ff)
+	{
+		const int f = warp * 4 + ff;
+		const int m = m0 + f;
+		int cnt = 0;
+		#pragma unroll
+		for (int w = 0; w < OS_WARPS; ++w) { cnt += s_red[(w * 32 + f) * 32 + lane]; }
+		if (m < p.M)
+		{
+			float v = __fmul_rn((float)(p.K - 2 * cnt), __ldg(p.mean_arr + m));
+			if (p.bias != nullptr) { v = __fadd_rn(v, __ldg(p.bias + m)); }
+			bits |= (v > 0.0f ? 1u : 0u) << ff;
+			if (p.C != nullptr && live)
+			{
+				if (p.leaky) { v = (v < 0.0f) ? __fmul_rn(v, 0.1f) : v; }
+				p.C[((size_t)img * p.M + m) * p.ldc + pix] = v;
+			}
+		}
+	}
+	if (p.signs == nullptr && p.x.n_sinks == 0) { return; }
+	s_bits[warp * 32 + lane] = (uint8_t)bits;
+	__syncthreads();
+	if (warp != 0) { return; }
+	uint32_t word = 0;
+	#pragma unroll
+	for (int w = 0; w < OS_WARPS; ++w) { word |= (uint32_t)s_bits[w * 32 + lane] << (4 * w); }
+	const int mwords = p.M >> 5;
+	const int mw = blockIdx.y;
+	if (p.signs != nullptr && live) { p.signs[((size_t)img * mwords + mw) * p.n_per_image + pix] = word; }
+	#pragma unroll
+	for (int si = 0; si < 2; ++si)
+	{
+		if (si >= p.x.n_sinks) { break; }
+		const SinkParams & s = p.x.sinks[si];
+		if (s.pool != 0)
+		{
+			// window-major columns: lanes 4w .. 4w+3 hold one 2x2 window and share the taps of its pooled word
+			uint32_t w = live ? word : 0u;
+			w |= __shfl_xor_sync(0xffffffffu, w, 1);
+			w |= __shfl_xor_sync(0xffffffffu, w, 2);
+			if (!live) { continue; }
+			const int q = pixcol >> 2;
+			const int wy = q / p.x.win_w;
+			const int wx = q - wy * p.x.win_w;
+			for (int tap = col & 3; tap < s.taps; tap += 4) { sink_store_tap(s, img, wy, wx, mw, tap, w); }
+		}
+		else if (live)
+		{
+			const int oy = pix / p.x.out_w;
+			const int ox = pix - oy * p.x.out_w;
+			const int copies = (s.up == 2) ? 4 : 1;
+			for (int t = 0; t < copies * s.taps; ++t)
+			{
+				const int cp = t / s.taps;
+				const int tap = t - cp * s.taps;
+				sink_store_tap(s, img, (s.up == 2) ? 2 * oy + (cp >> 1) : oy, (s.up == 2) ? 2 * ox + (cp & 1) : ox, mw, tap, word);
+			}
+		}
+	}
+}
+
+template <int KS4>
+static int launch_oneshot(const GemmParams & p, cudaStream_t stream)
+{
+	const long long gx = ((long long)p.n_total + 31) / 32;
+	const int gy = (p.M + 31) / 32;
+	if (gx > 0x7fffffffLL || gy > 65535) { return XNOR_B200_ERR_TOO_LARGE; }
+	const size_t smem = (size_t)(32 * OS_WARPS * KS4 * 4 + OS_WARPS * 32 * 32) * 4 + OS_WARPS * 32;
+	int rc = ensure_dynamic_smem((const void *)xnor_gemm_oneshot_kernel<KS4>, smem);
+	if (rc != XNOR_B200_OK) { return rc; }
+	xnor_gemm_oneshot_kernel<KS4><<<dim3((unsigned)gx, (unsigned)gy, 1), OS_THREADS, smem, stream>>>(p);
+	return check_launch();
+}
+
+// Problems whose 32x32 output tiles fit the GPU in a single wave, with rows of at most 8 x 32 words.  Measured on B200:
+// 512x169x2304 7.0 vs 8.6 us, 256x169x1024 4.0 vs 5.0 us against the tiled kernel; with more tiles than SMs (1024x169x4608:
+// 192 tiles) the busiest SM gets two CTAs of POPC work and the tiled kernel with cluster split-K wins (13.8 vs 16.1 us).
+static bool oneshot_problem(int M, int n_total, int kw)
+{
+	const long long ctas = (long long)((M + 31) / 32) * ((n_total + 31) / 32);
+	return kw > 8 && kw <= OS_WARPS * 32 && ctas <= (long long)sm_count() && std::getenv("XNOR_B200_GEMM_FORCE") == nullptr
+			&& std::getenv("XNOR_B200_GEMM_TC") == nullptr;
+}
+
 // ---- configurations ----------------------------------------------------------------------------
 
 struct TileConfig
@@ -680,6 +828,22 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	}
 
 	if (from_planes) { return XNOR_B200_ERR_INVALID; }      // only the short-K kernel builds rows from planes
+
+	if (counts == nullptr && shortcut_out == nullptr && oneshot_problem(M, n_total, p.kw)
+			&& (((uintptr_t)A | (uintptr_t)B) & 15u) == 0 && lda_words % 4 == 0 && ldb_words % 4 == 0)
+	{
+		switch ((p.kw / 4 + OS_WARPS - 1) / OS_WARPS)               // 16-byte groups per warp
+		{
+			case 1: return launch_oneshot<1>(p, stream);
+			case 2: return launch_oneshot<2>(p, stream);
+			case 3: return launch_oneshot<3>(p, stream);
+			case 4: return launch_oneshot<4>(p, stream);
+			case 5: return launch_oneshot<5>(p, stream);
+			case 6: return launch_oneshot<6>(p, stream);
+			case 7: return launch_oneshot<7>(p, stream);
+			default: return launch_oneshot<8>(p, stream);
+		}
+	}
 
 	const int sms = sm_count();
 	int best_cfg = 0, best_split = 1;
