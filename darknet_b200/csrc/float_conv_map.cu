@@ -162,12 +162,13 @@ float_conv_map_kernel(const FloatMapParams p)
 		}
 	};
 
-	float acc[8][FM_PJ];
+	// accumulators as filter pairs: one packed FMA (fma.rn.f32x2, two independent IEEE FMAs) per pair and pixel
+	float2 acc2[4][FM_PJ];
 	#pragma unroll
-	for (int f = 0; f < 8; ++f)
+	for (int f = 0; f < 4; ++f)
 	{
 		#pragma unroll
-		for (int j = 0; j < FM_PJ; ++j) { acc[f][j] = 0.0f; }
+		for (int j = 0; j < FM_PJ; ++j) { acc2[f][j] = make_float2(0.0f, 0.0f); }
 	}
 
 	#pragma unroll
@@ -199,14 +200,11 @@ float_conv_map_kernel(const FloatMapParams p)
 				for (int j = 0; j < FM_PJ; ++j)
 				{
 					const float xv = sxj[j][cc * KG * AREA + ((KS == 3) ? (t / KS) * PITCH + (t % KS) : 0)];
-					acc[0][j] = fmaf(w0.x, xv, acc[0][j]);
-					acc[1][j] = fmaf(w0.y, xv, acc[1][j]);
-					acc[2][j] = fmaf(w0.z, xv, acc[2][j]);
-					acc[3][j] = fmaf(w0.w, xv, acc[3][j]);
-					acc[4][j] = fmaf(w1.x, xv, acc[4][j]);
-					acc[5][j] = fmaf(w1.y, xv, acc[5][j]);
-					acc[6][j] = fmaf(w1.z, xv, acc[6][j]);
-					acc[7][j] = fmaf(w1.w, xv, acc[7][j]);
+					const float2 xx = make_float2(xv, xv);
+					acc2[0][j] = __ffma2_rn(make_float2(w0.x, w0.y), xx, acc2[0][j]);
+					acc2[1][j] = __ffma2_rn(make_float2(w0.z, w0.w), xx, acc2[1][j]);
+					acc2[2][j] = __ffma2_rn(make_float2(w1.x, w1.y), xx, acc2[2][j]);
+					acc2[3][j] = __ffma2_rn(make_float2(w1.z, w1.w), xx, acc2[3][j]);
 				}
 			}
 		}
@@ -229,7 +227,8 @@ float_conv_map_kernel(const FloatMapParams p)
 				for (int j = 0; j < FM_PJ; ++j)
 				{
 					float * dst = s_part + (f_first + f) * PT + slot0 + 16 * j;
-					*dst = (g == 0) ? acc[f][j] : *dst + acc[f][j];
+					const float a = (f & 1) ? acc2[f >> 1][j].y : acc2[f >> 1][j].x;
+					*dst = (g == 0) ? a : *dst + a;
 				}
 			}
 		}
