@@ -323,24 +323,26 @@ float_conv_1x1_kernel(const FloatMapParams p)
 	__syncthreads();
 
 	// warp w takes channels w, w + 8, ...
-	float acc[F1_FT];
+	float2 acc2[F1_FT / 2];                                       // filter pairs: one packed FMA (fma.rn.f32x2) each
 	#pragma unroll
-	for (int f = 0; f < F1_FT; ++f) { acc[f] = 0.0f; }
+	for (int f = 0; f < F1_FT / 2; ++f) { acc2[f] = make_float2(0.0f, 0.0f); }
 	#pragma unroll 4
 	for (int k = warp; k < K; k += F1_THREADS / 32)
 	{
 		const float xv = s_x[k * F1_PT + lane];
+		const float2 xx = make_float2(xv, xv);
 		const float4 * wr = reinterpret_cast<const float4 *>(s_w + k * F1_FT);
 		#pragma unroll
 		for (int q = 0; q < 4; ++q)
 		{
 			const float4 w = wr[q];
-			acc[4 * q + 0] = fmaf(w.x, xv, acc[4 * q + 0]);
-			acc[4 * q + 1] = fmaf(w.y, xv, acc[4 * q + 1]);
-			acc[4 * q + 2] = fmaf(w.z, xv, acc[4 * q + 2]);
-			acc[4 * q + 3] = fmaf(w.w, xv, acc[4 * q + 3]);
+			acc2[2 * q] = __ffma2_rn(make_float2(w.x, w.y), xx, acc2[2 * q]);
+			acc2[2 * q + 1] = __ffma2_rn(make_float2(w.z, w.w), xx, acc2[2 * q + 1]);
 		}
 	}
+	float acc[F1_FT];
+	#pragma unroll
+	for (int f = 0; f < F1_FT / 2; ++f) { acc[2 * f] = acc2[f].x; acc[2 * f + 1] = acc2[f].y; }
 	__syncthreads();                                              // operands are dead: reuse the front of shared memory
 	float * s_part = s_mem;                                       // [8 warps][16 filters][32 pixels]
 	#pragma unroll
