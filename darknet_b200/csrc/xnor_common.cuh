@@ -91,7 +91,7 @@ __device__ __forceinline__ int col_to_pixel(const GemmExtra & x, int pixcol)
 
 // Stores sign word `word` of consumer-input pixel (iy, ix), channel block cb, at the place of the consumer's packed
 // operand where its im2col puts tap (ky, kx): K-word cb*taps + ky*ks + kx of output pixel (iy + pad - ky, ix + pad - kx).
-__device__ __forceinline__ void sink_store_tap(const SinkParams & s, int img, int iy, int ix, int cb, int tap, uint32_t word)
+__device__ __forceinline__ void sink_store_tap(const SinkParams & s, int img, int iy, int ix, int cb, int tap, uint32_t word, int half = -1)
 {
 	const int ky = tap / s.ks;
 	const int kx = tap - ky * s.ks;
@@ -100,7 +100,9 @@ __device__ __forceinline__ void sink_store_tap(const SinkParams & s, int img, in
 	if (oy < 0 || oy >= s.out_h || ox < 0 || ox >= s.out_w) { return; }
 	const size_t row = (s.win_w > 0) ? ((size_t)(oy >> 1) * s.win_w + (ox >> 1)) * 4 + (oy & 1) * 2 + (ox & 1)
 	                                 : (size_t)oy * s.out_w + ox;
-	s.operand[((size_t)img * s.n_out + row) * s.ldw + (size_t)(s.cb_offset + cb) * s.taps + tap] = word;
+	uint32_t * dst = s.operand + ((size_t)img * s.n_out + row) * s.ldw + (size_t)(s.cb_offset + cb) * s.taps + tap;
+	if (half < 0) { *dst = word; }
+	else { reinterpret_cast<uint16_t *>(dst)[half] = (uint16_t)word; }      // a 16-filter tile owns one half of the word
 }
 #endif
 

@@ -545,23 +545,26 @@ static int launch_smallk(const GemmParams & p, cudaStream_t stream)
 constexpr int OS_THREADS = 256;
 constexpr int OS_WARPS = OS_THREADS / 32;
 
-template <int KS4>
+// FT = filters per CTA: 32, or 16 for layers that only write fp32 (no sign word to assemble) and whose 32-filter tiles would
+// leave the GPU with one and a bit waves.
+template <int KS4, int FT>
 __global__ void __launch_bounds__(OS_THREADS)
 xnor_gemm_oneshot_kernel(const GemmParams p)
 {
 	constexpr int SLICE = KS4 * 4;                 // K words per warp
 	constexpr int KWP = OS_WARPS * SLICE;          // K words per (zero-padded) row in shared memory
 	extern __shared__ __align__(16) uint32_t smem[];
-	uint32_t * s_a = smem;                                             // [32][KWP]
-	int * s_red = reinterpret_cast<int *>(smem + 32 * KWP);            // [8 warps][32 filters][32 pixels]
-	uint8_t * s_bits = reinterpret_cast<uint8_t *>(smem + 32 * KWP + OS_WARPS * 32 * 32);   // [8 warps][32 pixels]
+	constexpr int FPW = FT / OS_WARPS;             // filters a warp finishes
+	uint32_t * s_a = smem;                                             // [FT][KWP]
+	int * s_red = reinterpret_cast<int *>(smem + FT * KWP);            // [8 warps][FT filters][32 pixels]
+	uint8_t * s_bits = reinterpret_cast<uint8_t *>(smem + FT * KWP + OS_WARPS * FT * 32);   // [8 warps][32 pixels]
 	const int lane = threadIdx.x & 31;
 	const int warp = threadIdx.x >> 5;
-	const int m0 = blockIdx.y * 32;
+	const int m0 = blockIdx.y * FT;
 	const int col = blockIdx.x * 32 + lane;
 	const bool live = (col < p.n_total);
 
-	for (int i = threadIdx.x; i < 32 * (KWP / 4); i += OS_THREADS)
+	for (int i = threadIdx.x; i < FT * (KWP / 4); i += OS_THREADS)
 	{
 		const int f = i / (KWP / 4);
 		const int q = i - f * (KWP / 4);
@@ -579,7 +582,7 @@ xnor_gemm_oneshot_kernel(const GemmParams p)
 	__syncthreads();
 
 	#pragma unroll 4
-	for (int f = 0; f < 32; ++f)
+	for (int f = 0; f < FT; ++f)
 	{
 		const uint4 * ar = reinterpret_cast<const uint4 *>(s_a + f * KWP + warp * SLICE);
 		int cnt = 0;
@@ -589,7 +592,7 @@ xnor_gemm_oneshot_kernel(const GemmParams p)
 			const uint4 a = ar[q];
 			cnt += __popc(a.x ^ b[q].x) + __popc(a.y ^ b[q].y) + __popc(a.z ^ b[q].z) + __popc(a.w ^ b[q].w);
 		}
-		s_red[(warp * 32 + f) * 32 + lane] = cnt;
+		s_red[(warp * FT + f) * 32 + lane] = cnt;
 	}
 	__syncthreads();
 
@@ -598,13 +601,13 @@ xnor_gemm_oneshot_kernel(const GemmParams p)
 	const int pix = col_to_pixel(p.x, pixcol);
 	uint32_t bits = 0;
 	#pragma unroll
-	for (int ff = 0; ff < 4; ++ff)
+	for (int ff = 0; ff < FPW; ++ff)
 	{
-		const int f = warp * 4 + ff;
+		const int f = warp * FPW + ff;
 		const int m = m0 + f;
 		int cnt = 0;
 		#pragma unroll
-		for (int w = 0; w < OS_WARPS; ++w) { cnt += s_red[(w * 32 + f) * 32 + lane]; }
+		for (int w = 0; w < OS_WARPS; ++w) { cnt += s_red[(w * FT + f) * 32 + lane]; }
 		if (m < p.M)
 		{
 			float v = __fmul_rn((float)(p.K - 2 * cnt), __ldg(p.mean_arr + m));
@@ -620,13 +623,20 @@ xnor_gemm_oneshot_kernel(const GemmParams p)
 	if (p.signs == nullptr && p.x.n_sinks == 0) { return; }
 	s_bits[warp * 32 + lane] = (uint8_t)bits;
 	__syncthreads();
-	if (warp != 0) { return; }
+	// the CTA's FT sign bits of this lane's pixel: the whole 32-filter word, or one 16-bit half of it.  Every warp assembles
+	// it; warp 0 stores the sign words, the sink taps are dealt out over the 8 warps.
 	uint32_t word = 0;
 	#pragma unroll
-	for (int w = 0; w < OS_WARPS; ++w) { word |= (uint32_t)s_bits[w * 32 + lane] << (4 * w); }
+	for (int w = 0; w < OS_WARPS; ++w) { word |= (uint32_t)s_bits[w * 32 + lane] << (FPW * w); }
 	const int mwords = p.M >> 5;
-	const int mw = blockIdx.y;
-	if (p.signs != nullptr && live) { p.signs[((size_t)img * mwords + mw) * p.n_per_image + pix] = word; }
+	const int mw = (FT == 32) ? blockIdx.y : blockIdx.y >> 1;
+	const int half = (FT == 32) ? -1 : (blockIdx.y & 1);
+	if (p.signs != nullptr && live && warp == 0)
+	{
+		uint32_t * dst = p.signs + ((size_t)img * mwords + mw) * p.n_per_image + pix;
+		if (half < 0) { *dst = word; }
+		else { reinterpret_cast<uint16_t *>(dst)[half] = (uint16_t)word; }
+	}
 	#pragma unroll
 	for (int si = 0; si < 2; ++si)
 	{
@@ -634,7 +644,7 @@ xnor_gemm_oneshot_kernel(const GemmParams p)
 		const SinkParams & s = p.x.sinks[si];
 		if (s.pool != 0)
 		{
-			// window-major columns: lanes 4w .. 4w+3 hold one 2x2 window and share the taps of its pooled word
+			// window-major columns: lanes 4w .. 4w+3 hold one 2x2 window; its taps go to (warp, lane of the window) pairs
 			uint32_t w = live ? word : 0u;
 			w |= __shfl_xor_sync(0xffffffffu, w, 1);
 			w |= __shfl_xor_sync(0xffffffffu, w, 2);
@@ -642,44 +652,50 @@ xnor_gemm_oneshot_kernel(const GemmParams p)
 			const int q = pixcol >> 2;
 			const int wy = q / p.x.win_w;
 			const int wx = q - wy * p.x.win_w;
-			for (int tap = col & 3; tap < s.taps; tap += 4) { sink_store_tap(s, img, wy, wx, mw, tap, w); }
+			for (int tap = warp * 4 + (col & 3); tap < s.taps; tap += 4 * OS_WARPS) { sink_store_tap(s, img, wy, wx, mw, tap, w, half); }
 		}
 		else if (live)
 		{
 			const int oy = pix / p.x.out_w;
 			const int ox = pix - oy * p.x.out_w;
 			const int copies = (s.up == 2) ? 4 : 1;
-			for (int t = 0; t < copies * s.taps; ++t)
+			for (int t = warp; t < copies * s.taps; t += OS_WARPS)
 			{
 				const int cp = t / s.taps;
 				const int tap = t - cp * s.taps;
-				sink_store_tap(s, img, (s.up == 2) ? 2 * oy + (cp >> 1) : oy, (s.up == 2) ? 2 * ox + (cp & 1) : ox, mw, tap, word);
+				sink_store_tap(s, img, (s.up == 2) ? 2 * oy + (cp >> 1) : oy, (s.up == 2) ? 2 * ox + (cp & 1) : ox, mw, tap, word, half);
 			}
 		}
 	}
 }
 
-template <int KS4>
+template <int KS4, int FT>
 static int launch_oneshot(const GemmParams & p, cudaStream_t stream)
 {
 	const long long gx = ((long long)p.n_total + 31) / 32;
-	const int gy = (p.M + 31) / 32;
+	const int gy = (p.M + FT - 1) / FT;
 	if (gx > 0x7fffffffLL || gy > 65535) { return XNOR_B200_ERR_TOO_LARGE; }
-	const size_t smem = (size_t)(32 * OS_WARPS * KS4 * 4 + OS_WARPS * 32 * 32) * 4 + OS_WARPS * 32;
-	int rc = ensure_dynamic_smem((const void *)xnor_gemm_oneshot_kernel<KS4>, smem);
+	const size_t smem = (size_t)(FT * OS_WARPS * KS4 * 4 + OS_WARPS * FT * 32) * 4 + OS_WARPS * 32;
+	int rc = ensure_dynamic_smem((const void *)xnor_gemm_oneshot_kernel<KS4, FT>, smem);
 	if (rc != XNOR_B200_OK) { return rc; }
-	xnor_gemm_oneshot_kernel<KS4><<<dim3((unsigned)gx, (unsigned)gy, 1), OS_THREADS, smem, stream>>>(p);
+	xnor_gemm_oneshot_kernel<KS4, FT><<<dim3((unsigned)gx, (unsigned)gy, 1), OS_THREADS, smem, stream>>>(p);
 	return check_launch();
 }
 
 // Problems whose 32x32 output tiles fit the GPU in a single wave, with rows of at most 8 x 32 words.  Measured on B200:
 // 512x169x2304 7.0 vs 8.6 us, 256x169x1024 4.0 vs 5.0 us against the tiled kernel; with more tiles than SMs (1024x169x4608:
 // 192 tiles) the busiest SM gets two CTAs of POPC work and the tiled kernel with cluster split-K wins (13.8 vs 16.1 us).
-static bool oneshot_problem(int M, int n_total, int kw)
+// Returns the filter tile to use (32 or 16), 0 when the tiled kernel should keep the layer.  16-filter tiles (a CTA then owns
+// one 16-bit half of every sign word): layers with a bit more than one wave of 32-filter tiles (256x676x3456: 176 tiles ->
+// 352 half tiles, 10.1 vs 12.9 us; 1024x169x4608: 12.2 vs 14.1 us).
+static int oneshot_problem(int M, int n_total, int kw, bool fp32_only)
 {
-	const long long ctas = (long long)((M + 31) / 32) * ((n_total + 31) / 32);
-	return kw > 8 && kw <= OS_WARPS * 32 && ctas <= (long long)sm_count() && std::getenv("XNOR_B200_GEMM_FORCE") == nullptr
-			&& std::getenv("XNOR_B200_GEMM_TC") == nullptr;
+	(void)fp32_only;
+	if (kw <= 8 || kw > OS_WARPS * 32 || std::getenv("XNOR_B200_GEMM_FORCE") != nullptr || std::getenv("XNOR_B200_GEMM_TC") != nullptr) { return 0; }
+	const long long ntiles = ((long long)n_total + 31) / 32;
+	if ((long long)((M + 31) / 32) * ntiles <= (long long)sm_count()) { return 32; }
+	if (M % 32 == 0 && (long long)((M + 15) / 16) * ntiles <= 3ll * sm_count() && (long long)((M + 31) / 32) * ntiles <= 2ll * sm_count()) { return 16; }
+	return 0;
 }
 
 // ---- configurations ----------------------------------------------------------------------------
@@ -829,20 +845,18 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 
 	if (from_planes) { return XNOR_B200_ERR_INVALID; }      // only the short-K kernel builds rows from planes
 
-	if (counts == nullptr && shortcut_out == nullptr && oneshot_problem(M, n_total, p.kw)
-			&& (((uintptr_t)A | (uintptr_t)B) & 15u) == 0 && lda_words % 4 == 0 && ldb_words % 4 == 0)
+	const int os_ft = (counts == nullptr && shortcut_out == nullptr && (((uintptr_t)A | (uintptr_t)B) & 15u) == 0 && lda_words % 4 == 0 && ldb_words % 4 == 0)
+			? oneshot_problem(M, n_total, p.kw, signs == nullptr && p.x.n_sinks == 0) : 0;
+	if (os_ft != 0)
 	{
-		switch ((p.kw / 4 + OS_WARPS - 1) / OS_WARPS)               // 16-byte groups per warp
+		const int ks4 = (p.kw / 4 + OS_WARPS - 1) / OS_WARPS;      // 16-byte groups per warp
+		#define XNOR_OS_CASE(N) case N: return (os_ft == 32) ? launch_oneshot<N, 32>(p, stream) : launch_oneshot<N, 16>(p, stream);
+		switch (ks4)
 		{
-			case 1: return launch_oneshot<1>(p, stream);
-			case 2: return launch_oneshot<2>(p, stream);
-			case 3: return launch_oneshot<3>(p, stream);
-			case 4: return launch_oneshot<4>(p, stream);
-			case 5: return launch_oneshot<5>(p, stream);
-			case 6: return launch_oneshot<6>(p, stream);
-			case 7: return launch_oneshot<7>(p, stream);
-			default: return launch_oneshot<8>(p, stream);
+			XNOR_OS_CASE(1) XNOR_OS_CASE(2) XNOR_OS_CASE(3) XNOR_OS_CASE(4) XNOR_OS_CASE(5) XNOR_OS_CASE(6) XNOR_OS_CASE(7)
+			default: return (os_ft == 32) ? launch_oneshot<8, 32>(p, stream) : launch_oneshot<8, 16>(p, stream);
 		}
+		#undef XNOR_OS_CASE
 	}
 
 	const int sms = sm_count();

@@ -42,6 +42,7 @@ def operand(l, x):
 @pytest.mark.parametrize("case", [
     # batch, c1, h, w, n1 (= c2), n2, consumer kernel
     (1, 64, 26, 26, 128, 64, 3), (2, 32, 13, 13, 64, 40, 3), (1, 96, 13, 13, 256, 48, 1), (3, 32, 10, 14, 32, 33, 3),
+    (1, 64, 26, 26, 256, 64, 3),            # 176 tiles of 32 filters: the one-shot kernel runs 16-filter tiles (half-word stores)
 ], ids=lambda c: "b%d_c%d_%dx%d_n%d_n%d_k%d" % c)
 def test_plain_sink_fills_the_consumer_operand(case):
     batch, c1, h, w, n1, n2, ks2 = case
@@ -60,7 +61,7 @@ def test_plain_sink_fills_the_consumer_operand(case):
     assert torch.equal(got, want)
 
 
-@pytest.mark.parametrize("case", [(1, 32, 16, 16, 64, 48), (2, 16, 24, 40, 32, 24), (1, 64, 52, 52, 128, 32)],
+@pytest.mark.parametrize("case", [(1, 32, 16, 16, 64, 48), (2, 16, 24, 40, 32, 24), (1, 64, 52, 52, 128, 32), (1, 64, 26, 26, 256, 32)],
                          ids=lambda c: "b%d_c%d_%dx%d_n%d_n%d" % c)
 def test_pooled_sink_and_window_major_order(case):
     """Layer A runs window-major (its own operand rows permuted), pools in the epilogue and still returns the right
