@@ -130,3 +130,36 @@ def test_heads_written_to_pinned_host_memory(tmp_path):
     torch.cuda.synchronize()
     for h, d in zip(host2, want):
         assert torch.equal(h, d.cpu())
+
+
+@pytest.mark.parametrize("name,size,batch", [
+    ("yolov3-tiny_xnor", 416, 1),          # the bench workload at its full size
+    ("yolov3-tiny_xnor", 416, 8),          # tensor-core kernels with sinks
+    ("tiny-yolo_xnor", 416, 2),
+    ("darknet53_448_xnor", 224, 1),        # shortcuts, stride-2 xnor layers, softmax head
+    ("darknet53_448_xnor", 128, 4),
+])
+def test_linked_networks_equal_plain_networks_at_full_size(tmp_path, name, size, batch):
+    """Every fusion the runner sets up (sinks, sign words, masks, folded pools, fused first conv, side branch, fused head
+    activation) against the same network with all of them switched off: identical heads, bit for bit."""
+    from darknet_b200 import cfgs, network
+    cfg = tmp_path / "net.cfg"
+    cfg.write_text(cfgs.CFGS[name](size, size))
+    net_cpu = network.parse_network_cfg(str(cfg), batch, "cpu")
+    w = tmp_path / "net.weights"
+    network.write_synthetic_weights(net_cpu, str(w), seed=3)
+    x = torch.from_numpy(synth.uniform01(13, (batch, 3, size, size))).cuda()
+    linked = network.load_network_custom(str(cfg), str(w), batch)
+    plain = network.load_network_custom(str(cfg), str(w), batch, sign_chains=False, fuse_first_conv=False, side_branches=False)
+    assert linked.sink_links > 0 and plain.sink_links == 0
+    got = [h.clone() for h in network.forward_network_gpu(linked, x)]
+    want = network.forward_network_gpu(plain, x)
+    torch.cuda.synchronize()
+    assert len(got) == len(want) > 0
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    # a second forward through the same buffers gives the same again (no state left behind by sinks or masks)
+    again = network.forward_network_gpu(linked, x)
+    torch.cuda.synchronize()
+    for a, b in zip(again, want):
+        assert torch.equal(a, b)
