@@ -301,6 +301,25 @@ xnor_gemm_kernel(const GemmParams p)
 	}
 
 	// epilogue
+	// The shortcut operand of all TM x TN outputs is requested first: one load per output in program order (each
+	// behind the previous output's stores) would cost a thread a full memory latency per output.
+	float sc[TM][TN];
+	if (p.shortcut_out != nullptr)
+	{
+		#pragma unroll
+		for (int j = 0; j < TN; ++j)
+		{
+			const int col = n0 + j * TX + tx;
+			const int img = col / p.n_per_image;
+			const int pix = col_to_pixel(p.x, col - img * p.n_per_image);
+			#pragma unroll
+			for (int i = 0; i < TM; ++i)
+			{
+				const int m = m0 + i * TY + ty;
+				sc[i][j] = (col < p.n_total && m < p.M) ? __ldcs(p.shortcut_in + ((size_t)img * p.M + m) * p.ldc + pix) : 0.0f;
+			}
+		}
+	}
 	#pragma unroll
 	for (int j = 0; j < TN; ++j)
 	{
@@ -324,7 +343,7 @@ xnor_gemm_kernel(const GemmParams p)
 			if (p.bias != nullptr) { v = __fadd_rn(v, __ldg(p.bias + m)); }
 			if (p.leaky) { v = (v < 0.0f) ? __fmul_rn(v, 0.1f) : v; }
 			p.C[idx] = v;
-			if (p.shortcut_out != nullptr) { p.shortcut_out[idx] = __fadd_rn(__ldg(p.shortcut_in + idx), v); }
+			if (p.shortcut_out != nullptr) { p.shortcut_out[idx] = __fadd_rn(sc[i][j], v); }
 		}
 	}
 }

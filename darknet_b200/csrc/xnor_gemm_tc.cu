@@ -57,6 +57,9 @@ struct TcParams
 	GemmExtra x;            // window-major column order and direct sign sinks (all zero: none)
 };
 
+// read-once data (the shortcut operand): streaming load, evicted first
+__device__ __forceinline__ float ld_stream(const float * p) { return __ldcs(p); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t * bar, uint32_t count)
@@ -132,6 +135,104 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr)
 	d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
 	d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
 	return d;
+}
+
+// TMEM -> registers, G consecutive columns of this warp's 32 lanes
+template <int G>
+__device__ __forceinline__ void tmem_load(uint32_t taddr, uint32_t (&d)[G])
+{
+	static_assert(G == 16 || G == 32, "16 or 32 columns");
+	if constexpr (G == 16)
+	{
+		asm volatile(
+			"tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+			"{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+			: "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]),
+			  "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
+			: "r"(taddr) : "memory");
+	}
+	else
+	{
+		asm volatile(
+			"tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+			"{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+			"%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+			: "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]),
+			  "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]),
+			  "=r"(d[16]), "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]), "=r"(d[23]),
+			  "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
+			: "r"(taddr) : "memory");
+	}
+}
+
+// Epilogue of a tile that only writes fp32 values (no sign words, sinks or counts): this warp's 32-filter chunks
+// (share, share + shares, ...) in groups of G filters.  With a fused shortcut (SC) the loop is software-pipelined:
+// the shortcut operand of group i+1 is requested before group i is computed and stored, so a thread always has
+// G..2G loads in flight.  With one request per output in program order, or one batch per group and nothing in flight in
+// between, the 24 warps of an SM wait a full memory latency each time and the epilogue runs at a fraction of the memory rate.
+template <int G, bool SC>
+__device__ __forceinline__ void epilogue_values(const TcParams & p, const int4 * s_fil, uint32_t tlane, int share, int shares,
+		int my_chunks, int f0, int k_b, bool col_ok, float * c_pix, const float * sc_in, float * sc_out)
+{
+	constexpr int PER = 32 / G;
+	const int groups = my_chunks * PER;
+	auto group_base = [&](int i) { return (share + (i / PER) * shares) * 32 + (i % PER) * G; };
+	const bool has_bias = (p.bias != nullptr);
+	float sc[SC ? G : 1];
+	if (SC)
+	{
+		#pragma unroll
+		for (int u = 0; u < G; ++u) { sc[u] = 0.0f; }
+		if (groups > 0 && col_ok)
+		{
+			const int fb = group_base(0);
+			#pragma unroll
+			for (int u = 0; u < G; ++u) { if (f0 + fb + u < p.M) { sc[u] = ld_stream(sc_in + (size_t)(fb + u) * p.ldc); } }
+		}
+	}
+	#pragma unroll 1
+	for (int i = 0; i < groups; ++i)
+	{
+		const int fb = group_base(i);
+		uint32_t d[G];
+		tmem_load<G>(tlane + (uint32_t)fb, d);
+		float scn[SC ? G : 1];
+		if (SC)
+		{
+			#pragma unroll
+			for (int u = 0; u < G; ++u) { scn[u] = 0.0f; }
+			if (i + 1 < groups && col_ok)
+			{
+				const int fbn = group_base(i + 1);
+				#pragma unroll
+				for (int u = 0; u < G; ++u) { if (f0 + fbn + u < p.M) { scn[u] = ld_stream(sc_in + (size_t)(fbn + u) * p.ldc); } }
+			}
+		}
+		asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+		if (col_ok)
+		{
+			#pragma unroll
+			for (int u = 0; u < G; ++u)
+			{
+				if (f0 + fb + u < p.M)
+				{
+					const int4 fi = s_fil[fb + u];                 // one broadcast 16-byte read per filter
+					// 2*agree - K = (K - 2 popc(b)) - 2 popc(a) + 4 popc(a & b)
+					const int dot = k_b + fi.x + 4 * (int)d[u];
+					float v = __fmul_rn((float)dot, __int_as_float(fi.y));
+					if (has_bias) { v = __fadd_rn(v, __int_as_float(fi.z)); }
+					if (p.leaky) { v = (v < 0.0f) ? __fmul_rn(v, 0.1f) : v; }
+					if (c_pix != nullptr) { c_pix[(size_t)(fb + u) * p.ldc] = v; }
+					if (SC) { sc_out[(size_t)(fb + u) * p.ldc] = __fadd_rn(sc[u], v); }
+				}
+			}
+		}
+		if (SC)
+		{
+			#pragma unroll
+			for (int u = 0; u < G; ++u) { sc[u] = scn[u]; }
+		}
+	}
 }
 
 template <int NF>
@@ -312,8 +413,16 @@ xnor_gemm_tc_kernel(const TcParams p)
 		float * c_pix = (p.C != nullptr) ? p.C + pix_off : nullptr;
 		float * sc_out = (p.shortcut_out != nullptr) ? p.shortcut_out + pix_off : nullptr;
 		const float * sc_in = (p.shortcut_in != nullptr) ? p.shortcut_in + pix_off : nullptr;
+		const bool values_only = (p.signs == nullptr && p.x.n_sinks == 0 && p.counts == nullptr);
+		if (values_only)
+		{
+			const int my_chunks = (share < NF / 32) ? (NF / 32 - share + SHARES - 1) / SHARES : 0;
+			const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+			if (sc_in != nullptr) { epilogue_values<16, true>(p, s_fil, tlane, share, SHARES, my_chunks, f0, k_b, col_ok, c_pix, sc_in, sc_out); }
+			else { epilogue_values<32, false>(p, s_fil, tlane, share, SHARES, my_chunks, f0, k_b, col_ok, c_pix, nullptr, nullptr); }
+		}
 		#pragma unroll 1
-		for (int chunk = share; chunk < NF / 32; chunk += SHARES)
+		for (int chunk = values_only ? NF : share; chunk < NF / 32; chunk += SHARES)
 		{
 			uint32_t d[32];
 			const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(chunk * 32);
@@ -398,8 +507,7 @@ xnor_gemm_tc_kernel(const TcParams p)
 			{
 				if (f0 + fbase + j < p.M)
 				{
-					const int4 fi = s_fil[fbase + j];                  // one broadcast 16-byte read per filter
-					// 2*agree - K = (K - 2 popc(b)) - 2 popc(a) + 4 popc(a & b)
+					const int4 fi = s_fil[fbase + j];
 					const int dot = k_b + fi.x + 4 * (int)d[j];
 					float v = __fmul_rn((float)dot, __int_as_float(fi.y));
 					if (has_bias) { v = __fadd_rn(v, __int_as_float(fi.z)); }

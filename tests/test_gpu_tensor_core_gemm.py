@@ -100,3 +100,39 @@ def test_automatic_dispatch_uses_tensor_cores_for_large_layers_and_stays_exact(p
     assert torch.equal(y_auto, y_int)
     want = port.conv_forward(x1, wt, b, 1, 1, 1)
     assert np.array_equal(y_auto[:2].cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("shape", [(256, 640, 1152), (200, 300, 576), (96, 1000, 288), (48, 257, 300), (20, 129, 128), (512, 130, 2304)],
+                         ids=lambda s: "M%d_N%d_K%d" % s)
+def test_tensor_core_fused_shortcut_equals_integer_kernel(force_tc, shape):
+    """fp32 output + fused shortcut add (the pipelined epilogue of the tensor-core kernel; every filter-tile width, ragged
+    filter and pixel edges, ldc > N) against the integer-pipe kernel on the same operands, and without a shortcut."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + 3 * N + 5 * K)
+    A, ld = random_bits(rng, M, K)
+    B, _ = random_bits(rng, N, K)
+    Ag, Bg = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    ldc = N + 5
+    mean = torch.from_numpy(rng.random(M, dtype=np.float32)).cuda()
+    bias = torch.from_numpy(rng.standard_normal(M).astype(np.float32)).cuda()
+    sc_in = torch.from_numpy(rng.standard_normal((M, ldc)).astype(np.float32)).cuda()
+    outs = {}
+    for mode in ("1", "0"):
+        force_tc(mode)
+        for with_sc in (True, False):
+            C_ = torch.full((M, ldc), float("nan"), device="cuda")
+            sc_out = torch.full((M, ldc), float("nan"), device="cuda")
+            capi.check(capi.lib().xnor_b200_gemm_bin_mean_transposed(
+                M, N, K, Ag.data_ptr(), ld, Bg.data_ptr(), ld, C_.data_ptr(), ldc, mean.data_ptr(), bias.data_ptr(), 1,
+                sc_in.data_ptr() if with_sc else None, sc_out.data_ptr() if with_sc else None,
+                torch.cuda.current_stream().cuda_stream), "gemm")
+            torch.cuda.synchronize()
+            outs[(mode, with_sc)] = (C_[:, :N].clone(), sc_out[:, :N].clone())
+            assert torch.isnan(C_[:, N:]).all() and torch.isnan(sc_out[:, N:]).all()        # nothing written past N
+    assert device_status() == 0
+    ref_c, ref_sc = outs[("0", True)]
+    assert torch.equal(ref_sc, sc_in[:, :N] + ref_c)
+    for key, (c_, s_) in outs.items():
+        assert torch.equal(c_, ref_c), key
+        if key[1]:
+            assert torch.equal(s_, ref_sc), key
