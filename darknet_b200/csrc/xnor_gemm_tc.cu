@@ -534,12 +534,14 @@ xnor_gemm_tc_kernel(const TcParams p)
 bool tc_gemm_eligible(int M, int n_total, int K)
 {
 	// The faster of two estimates fitted to measurements on B200 (batch 8..64 layer shapes) decides:
-	//   tensor-core kernel: ~14 us of fixed cost (launch with 100+ KB of shared memory, TMEM allocation, pipeline fill,
+	//   tensor-core kernel: ~7 us of fixed cost (launch with 100+ KB of shared memory, TMEM allocation, pipeline fill,
 	//                       drain) + per tile 0.6 us per 128-bit K block and 4 us of epilogue for 256-filter tiles (0.33 + 2.5,
 	//                       0.25 + 2.0, 0.2 + 1.4 for 128, 64 and 32 filters), times the tiles the busiest SM gets (co-resident
 	//                       CTAs share the SM's shared-memory bandwidth);
-	//   integer kernel:     ~4 us + binary ops (over the K words it actually walks) at 250 T/s.
-	if (M < 16 || K < 128) { return false; }
+	//   integer kernel:     ~4 us + binary ops (over the K words it actually walks) at 250 T/s + 2 us per million outputs
+	//                       (index arithmetic and stores of its epilogue, which dominate when K is short: 1x1 layers
+	//                       over 64..256 channels at large batch run 1.3-2x faster on the tensor-core kernel).
+	if (M < 16 || K < 64) { return false; }
 	const int nf = (M > 128) ? 256 : (M > 64) ? 128 : (M > 32) ? 64 : 32;
 	const long long tiles = (long long)((M + nf - 1) / nf) * ((n_total + TC_PIX - 1) / TC_PIX);
 	const double kb = (double)((K + 127) / 128);
@@ -547,9 +549,9 @@ bool tc_gemm_eligible(int M, int n_total, int K)
 	double load = (double)tiles / (double)sm_count();
 	if (nf == 256) { load = (double)((tiles + sm_count() - 1) / sm_count()); }
 	if (load < 1.0) { load = 1.0; }
-	const double t_tc = 14.0 + per_tile * load;
+	const double t_tc = 7.0 + per_tile * load;
 	const double k_int = (double)(((K + 31) / 32 + 3) / 4 * 4 * 32);       // the integer kernel walks whole 16-byte groups of K words
-	const double t_int = 4.0 + 2.0 * (double)M * (double)n_total * k_int / 250.0e6;
+	const double t_int = 4.0 + 2.0 * (double)M * (double)n_total * k_int / 250.0e6 + (double)M * (double)n_total / 500.0e3;
 	return t_tc < t_int;
 }
 
