@@ -163,7 +163,7 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_c
 	if (n_in != 1) { return XNOR_B200_ERR_NULL; }
 	if (io.n_sinks < 0 || io.n_sinks > 2 || (io.n_sinks > 0 && io.sinks == nullptr)) { return XNOR_B200_ERR_INVALID; }
 	if (io.output != nullptr && io.output_signs != nullptr) { return XNOR_B200_ERR_INVALID; }
-	if (io.output == nullptr && io.output_signs == nullptr && io.n_sinks == 0) { return XNOR_B200_ERR_NULL; }
+	if (io.output == nullptr && io.output_signs == nullptr && io.n_sinks == 0 && io.shortcut_out == nullptr) { return XNOR_B200_ERR_NULL; }
 	if ((io.output_signs != nullptr || io.n_sinks > 0) && desc->n % 32 != 0) { return XNOR_B200_ERR_INVALID; }
 	if (io.output_signs != nullptr && io.shortcut_out != nullptr) { return XNOR_B200_ERR_INVALID; }
 	if (io.input_signs != nullptr && desc->c % 32 != 0 && io.pool != nullptr) { return XNOR_B200_ERR_INVALID; }
@@ -173,7 +173,9 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_c
 	if (rc != XNOR_B200_OK) { return rc; }
 	if (scratch_bytes < round_up(g.packed_input_bytes, 256)) { return XNOR_B200_ERR_SCRATCH; }
 	if ((((uintptr_t)scratch) & 255u) != 0 || (((uintptr_t)align_bit_weights) & 15u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
-	if (io.shortcut_out != nullptr && (io.shortcut_in == nullptr || io.output == nullptr)) { return XNOR_B200_ERR_NULL; }
+	if (io.shortcut_out != nullptr && io.shortcut_in == nullptr) { return XNOR_B200_ERR_NULL; }
+	// the layer's own tensor may be left out when only the fused shortcut sum is wanted -- not together with sign outputs
+	if (io.shortcut_out != nullptr && io.output == nullptr && (io.n_sinks > 0 || io.output_signs != nullptr)) { return XNOR_B200_ERR_INVALID; }
 	if (io.window_major && (g.out_h % 2 != 0 || g.out_w % 2 != 0)) { return XNOR_B200_ERR_INVALID; }
 
 	GemmExtra extra = GemmExtra();

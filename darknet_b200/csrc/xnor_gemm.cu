@@ -342,7 +342,7 @@ xnor_gemm_kernel(const GemmParams p)
 			float v = __fmul_rn(dot, __ldg(p.mean_arr + m));
 			if (p.bias != nullptr) { v = __fadd_rn(v, __ldg(p.bias + m)); }
 			if (p.leaky) { v = (v < 0.0f) ? __fmul_rn(v, 0.1f) : v; }
-			p.C[idx] = v;
+			if (p.C != nullptr) { p.C[idx] = v; }
 			if (p.shortcut_out != nullptr) { p.shortcut_out[idx] = __fadd_rn(sc[i][j], v); }
 		}
 	}

@@ -146,10 +146,12 @@ class Sink:
 
 def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tensor] = None, x_signs: Optional[torch.Tensor] = None,
                                    pool: Optional[capi.PoolDesc] = None, want_signs: bool = False, packed: bool = False,
-                                   sinks=(), want_output: Optional[bool] = None, x_masks: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                                   sinks=(), want_output: Optional[bool] = None, x_masks: Optional[torch.Tensor] = None,
+                                   shortcut_only: bool = False) -> Optional[torch.Tensor]:
     """xnor_b200_conv_forward_io.  Input: fp32 `x`, sign words / planes `x_signs`, or `packed` (the producers' sinks have
     filled l.scratch).  Output: the fp32 tensor (default when there are no sinks, or with want_output), the sign words
-    int32 [batch][n/32][out_h*out_w] (want_signs), and/or the consumers' operands (sinks)."""
+    int32 [batch][n/32][out_h*out_w] (want_signs), and/or the consumers' operands (sinks).  shortcut_only: only the fused
+    shortcut sum (l.bin_conv_shortcut_out_gpu) is written and returned; the layer's own tensor is left untouched."""
     if l.align_bit_weights_gpu is None:
         raise RuntimeError("binary_align_weights() has not been called for this layer")
     io = capi.ConvIO()
@@ -171,6 +173,10 @@ def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tens
     if want_signs:
         out = torch.empty(l.batch, l.n // 32, l.geom.n_out, dtype=torch.int32, device=l.device)
         io.output_signs = out.data_ptr()
+    elif shortcut_only:
+        out = l.bin_conv_shortcut_out_gpu
+        io.shortcut_in = _ptr(l.bin_conv_shortcut_in_gpu)
+        io.shortcut_out = out.data_ptr()
     elif want_output:
         out = l.output_gpu
         io.output = out.data_ptr()

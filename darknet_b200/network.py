@@ -99,6 +99,7 @@ class Layer:
     sinks: List = field(default_factory=list)      # of L.Sink
     packed_input: bool = False       # xnor conv: every input channel arrives through producers' sinks
     need_fp32: bool = True           # somebody still reads this layer's fp32 output
+    shortcut_only: bool = False      # xnor conv whose output only the fused [shortcut] behind it reads: just the sum is written
     skip: bool = False               # maxpool / upsample / route that only sat between a sink producer and its consumer
     sign_source: Optional[int] = None
     sign_out: Optional[torch.Tensor] = None
@@ -121,6 +122,7 @@ class Network:
     folded_maxpools: int = 0
     fold_maxpool_min_batch: int = 4
     sign_chains: bool = True
+    skip_fused_conv_outputs: bool = True   # an xnor conv read only by its fused [shortcut] does not write its own tensor
     fuse_first_conv: bool = True
     float_map_max_pixels: int = 1024       # batch*out_h*out_w up to which float convs use the cluster split-K kernel (measured: it wins at 676 pixels, loses to cuDNN/cuBLAS at 1352)
     sign_links: int = 0
@@ -271,6 +273,12 @@ def calculate_binary_weights(net: Network) -> None:
                 sc.blank = True
                 sc.output_gpu = torch.empty(net.batch, sc.out_c, sc.out_h, sc.out_w, device=dev)
                 xl.bin_conv_shortcut_out_gpu = sc.output_gpu
+    readers = _readers(net)
+    for j, l in enumerate(net.layers[:-1]):
+        # Darknet's fused kernel writes the convolution's own tensor and the sum (src-lib/im2col_kernels.cu:940-953); with the
+        # [shortcut] layer blanked nothing reads the former, and at large batch it is a third of the layer's memory traffic
+        l.shortcut_only = (net.skip_fused_conv_outputs and l.type == "convolutional" and l.xnor and net.layers[j + 1].blank
+                           and readers[j] == [j + 1])
     prepare_float_map_convs(net)
     link_branches(net)
     if net.sign_chains:
@@ -626,11 +634,15 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
                     src = net.layers[l.sign_source].sign_out if l.sign_source is not None else None
                     masks = net.layers[l.mask_source].sign_out if l.mask_source is not None else None
                     want_fp32 = not l.emit_signs and (l.need_fp32 or not l.sinks)
+                    so = l.shortcut_only and want_fp32 and not l.sinks
                     out = L.forward_convolutional_layer_io(xl, x=None if (src is not None or masks is not None or l.packed_input) else cur,
                                                            x_signs=src, pool=l.pool_desc, want_signs=l.emit_signs, packed=l.packed_input,
-                                                           sinks=l.sinks, want_output=want_fp32, x_masks=masks)
+                                                           sinks=l.sinks, want_output=want_fp32, x_masks=masks, shortcut_only=so)
                     l.sign_out = out if l.emit_signs else None
-                    cur = out if want_fp32 else None
+                    cur = out if (want_fp32 and not so) else None
+                elif l.shortcut_only:
+                    L.forward_convolutional_layer_io(xl, x=cur, pool=l.pool_desc, shortcut_only=True)
+                    cur = None
                 else:
                     cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
             elif l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1 and l.activation in ("leaky", "linear"):
@@ -699,6 +711,7 @@ def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "c
     torch.backends.cuda.matmul.allow_tf32 = False
     net = parse_network_cfg(cfg, batch, device)
     net.sign_chains = sign_chains
+    net.skip_fused_conv_outputs = sign_chains      # the plain network keeps every layer's own tensor
     net.fuse_first_conv = fuse_first_conv
     net.side_branches = side_branches
     if os.environ.get("XNOR_B200_FLOAT_MAP_MAX_PIXELS"):      # tuning aid

@@ -208,7 +208,7 @@ typedef struct xnor_b200_conv_io
 	const float * input;
 	const uint32_t * input_signs;
 	const xnor_b200_pool_desc * pool;     /* optional maxpool between the previous layer and this one */
-	float * output;
+	float * output;                       /* may be NULL together with shortcut_out: only the fused sum is written then */
 	uint32_t * output_signs;
 	const float * shortcut_in;
 	float * shortcut_out;

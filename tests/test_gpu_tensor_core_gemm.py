@@ -136,3 +136,38 @@ def test_tensor_core_fused_shortcut_equals_integer_kernel(force_tc, shape):
         assert torch.equal(c_, ref_c), key
         if key[1]:
             assert torch.equal(s_, ref_sc), key
+
+
+@pytest.mark.parametrize("mode", ["0", "1"], ids=["integer", "tensor-core"])
+def test_shortcut_sum_without_the_layers_own_tensor(force_tc, mode):
+    """xnor_b200_conv_forward_io with output = NULL and a fused shortcut: the sum equals the one of the full call, the
+    layer's own tensor is not touched; NULL output together with sign outputs is refused."""
+    batch, c, h, w, n = 2, 64, 20, 20, 96
+    x, wt, b = synth.conv_case(999, batch, c, h, w, n, 3)
+    l = L.make_convolutional_layer(batch, h, w, c, n, 3, 1, 1, capi.LEAKY)
+    l.load_weights(torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda())
+    L.binary_align_weights(l)
+    xg = torch.from_numpy(x).cuda()
+    l.bin_conv_shortcut_in_gpu = torch.randn(batch, n, h, w, device="cuda")
+    l.bin_conv_shortcut_out_gpu = torch.empty(batch, n, h, w, device="cuda")
+    force_tc(mode)
+    y = L.forward_convolutional_layer_gpu(l, xg).clone()
+    want = l.bin_conv_shortcut_out_gpu.clone()
+    assert torch.equal(want, l.bin_conv_shortcut_in_gpu + y)
+    l.output_gpu.fill_(float("nan"))
+    l.bin_conv_shortcut_out_gpu.fill_(float("nan"))
+    got = L.forward_convolutional_layer_io(l, x=xg, shortcut_only=True)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert torch.isnan(l.output_gpu).all()
+    assert device_status() == 0
+    import ctypes as C
+    io = capi.ConvIO()
+    io.input = xg.data_ptr()
+    io.shortcut_in = l.bin_conv_shortcut_in_gpu.data_ptr()
+    io.shortcut_out = l.bin_conv_shortcut_out_gpu.data_ptr()
+    signs = torch.empty(batch, n // 32, h * w, dtype=torch.int32, device="cuda")
+    io.output_signs = signs.data_ptr()
+    rc = capi.lib().xnor_b200_conv_forward_io(C.byref(l.desc), C.byref(io), l.align_bit_weights_gpu.data_ptr(), l.mean_arr_gpu.data_ptr(),
+                                              l.biases_gpu.data_ptr(), l.scratch.data_ptr(), l.scratch.numel(), None)
+    assert rc != capi.OK
