@@ -597,6 +597,11 @@ def _region(x: torch.Tensor, l: Layer) -> torch.Tensor:
     classes = int(l.opts.get("classes", 20))
     coords = int(l.opts.get("coords", 4))
     b = x.shape[0]
+    if x.is_cuda and x.is_contiguous() and coords >= 2:
+        out = torch.empty_like(x)
+        capi.check(capi.lib().xnor_b200_region_activate(x.data_ptr(), out.data_ptr(), b, num, coords, classes, int(l.opts.get("softmax", 0)),
+                                                       l.h * l.w, torch.cuda.current_stream().cuda_stream), "xnor_b200_region_activate")
+        return out
     v = x.reshape(b, num, coords + 1 + classes, l.h * l.w).clone()
     v[:, :, 0:2] = torch.sigmoid(v[:, :, 0:2])
     v[:, :, coords] = torch.sigmoid(v[:, :, coords])
@@ -736,7 +741,7 @@ def own_launches_per_forward(net: Network) -> int:
                 n += 1 if (l.packed_input or from_planes) else 2
             elif (l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1) or l.c * l.size * l.size <= 128 or l.weights_blocked_gpu is not None:
                 n += 1
-        elif l.type == "yolo" and not l.yolo_done:
+        elif (l.type == "yolo" and not l.yolo_done) or l.type == "region":
             n += 1
     return n
 

@@ -288,6 +288,11 @@ XNOR_B200_API int xnor_b200_float_conv_map_yolo(const xnor_b200_conv_desc * desc
  * x, y, objectness and class entries of every anchor, w and h raw, in one pass.  input/output
  * [batch][anchors][4 + 1 + classes][hw] (may be the same pointer).  Box decoding and NMS stay on the host side. */
 XNOR_B200_API int xnor_b200_yolo_activate(const float * input, float * output, int batch, int anchors, int classes, int hw, void * stream);
+/* The activation step of the [region] head (forward_region_layer, src-lib/region_layer.cpp:494-537): logistic on x, y and
+ * objectness, w and h raw, and with softmax != 0 a softmax over the class entries of every anchor and cell.
+ * input/output [batch][anchors][coords + 1 + classes][hw], different pointers.  Agrees with Darknet's softmax to rounding. */
+XNOR_B200_API int xnor_b200_region_activate(const float * input, float * output, int batch, int anchors, int coords, int classes,
+		int softmax, int hw, void * stream);
 
 /* Bytes of the library-resident scratch array behind xnor_b200_conv_forward_static. */
 #define XNOR_B200_STATIC_SCRATCH_BYTES (8u << 20)

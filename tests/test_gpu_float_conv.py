@@ -214,3 +214,24 @@ def test_float_conv_map_yolo_equals_conv_then_yolo_activate():
     torch.cuda.synchronize()
     assert torch.equal(got, want)
     assert lib.xnor_b200_float_conv_map_yolo(C.byref(desc), x.data_ptr(), blocked.data_ptr(), b.data_ptr(), got.data_ptr(), 7, None) == 1
+
+
+@pytest.mark.parametrize("case", [(2, 5, 4, 80, 1, 169), (3, 5, 4, 20, 1, 49), (1, 3, 4, 7, 0, 33), (2, 2, 6, 0, 1, 10)],
+                         ids=lambda c: "b%d_a%d_coords%d_cls%d_sm%d_hw%d" % c)
+def test_region_activate_matches_its_definition(case):
+    """[region] head in one kernel against the same steps written with torch (logistic x, y, objectness; softmax over classes)."""
+    batch, anchors, coords, classes, softmax, hw = case
+    entries = coords + 1 + classes
+    x = torch.from_numpy(synth.bell(91, (batch, anchors * entries, hw), 2.0)).cuda()
+    out = torch.full_like(x, float("nan"))
+    capi.check(capi.lib().xnor_b200_region_activate(x.data_ptr(), out.data_ptr(), batch, anchors, coords, classes, softmax, hw, None), "region")
+    torch.cuda.synchronize()
+    v = x.reshape(batch, anchors, entries, hw).double().clone()
+    v[:, :, 0:2] = torch.sigmoid(v[:, :, 0:2])
+    v[:, :, coords] = torch.sigmoid(v[:, :, coords])
+    if softmax and classes > 0:
+        v[:, :, coords + 1:] = torch.softmax(v[:, :, coords + 1:], dim=2)
+    got = out.reshape(batch, anchors, entries, hw).double()
+    assert torch.equal(got[:, :, 2:coords], v[:, :, 2:coords])                 # w, h (and further coords) untouched
+    assert (got - v).abs().max().item() < 2e-6
+    assert capi.lib().xnor_b200_region_activate(x.data_ptr(), x.data_ptr(), batch, anchors, coords, classes, softmax, hw, None) == 1   # in place: refused
