@@ -212,6 +212,33 @@ float_conv3_block_kernel(const FloatBlockParams p)
 
 	const bool col1 = (2 * bx + 1 < p.W);
 	const bool row1 = (2 * by + 1 < p.H);
+	if (p.masks != nullptr && !p.pooled)
+	{
+		// sign of this thread's 8 filters at each of its four pixels, one byte of each pixel's channel mask; with 32
+		// filters the four bytes of a pixel are the channel-packed sign word an xnor layer over 32 channels reads
+		uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;
+		#pragma unroll
+		for (int f = 0; f < FB_FILTERS; ++f)
+		{
+			const uint32_t on = (f0 + f < p.N) ? 1u : 0u;
+			m0 |= (on & (acc[f][0] + s_b[f] > 0.0f ? 1u : 0u)) << f;
+			m1 |= (on & (acc[f][1] + s_b[f] > 0.0f ? 1u : 0u)) << f;
+			m2 |= (on & (acc[f][2] + s_b[f] > 0.0f ? 1u : 0u)) << f;
+			m3 |= (on & (acc[f][3] + s_b[f] > 0.0f ? 1u : 0u)) << f;
+		}
+		if (live)
+		{
+			uint8_t * dst = p.masks + (((size_t)blockIdx.z * p.H + 2 * by) * p.W + 2 * bx) * gridDim.y + blockIdx.y;
+			dst[0] = (uint8_t)m0;
+			if (col1) { dst[gridDim.y] = (uint8_t)m1; }
+			if (row1)
+			{
+				dst[(size_t)p.W * gridDim.y] = (uint8_t)m2;
+				if (col1) { dst[(size_t)(p.W + 1) * gridDim.y] = (uint8_t)m3; }
+			}
+		}
+		return;
+	}
 	if (p.masks != nullptr)
 	{
 		// pooled sign of this thread's 8 filters as one byte of the pixel's channel mask
@@ -313,7 +340,7 @@ extern "C" int xnor_b200_float_conv3_io(const xnor_b200_conv_desc * desc, int po
 	if (desc->c != 3 || desc->size != 3 || desc->stride != 1 || desc->pad != 1) { return XNOR_B200_ERR_INVALID; }
 	if (pool != 0 && pool != 2) { return XNOR_B200_ERR_INVALID; }
 	if (pool == 2 && (desc->h % 2 != 0 || desc->w % 2 != 0)) { return XNOR_B200_ERR_INVALID; }
-	if ((output_sign_planes != nullptr || output_sign_masks != nullptr) && pool != 2) { return XNOR_B200_ERR_INVALID; }
+	if (output_sign_planes != nullptr && pool != 2) { return XNOR_B200_ERR_INVALID; }
 	FloatBlockParams p;
 	p.in = input; p.weights = weights; p.biases = biases; p.out = output; p.planes = output_sign_planes; p.masks = output_sign_masks;
 	p.H = desc->h; p.W = desc->w; p.N = desc->n;

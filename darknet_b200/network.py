@@ -441,6 +441,14 @@ def link_first_conv(net: Network) -> None:
             continue
         if j in referenced or j + 1 >= len(net.layers):
             continue
+        nxt = net.layers[j + 1]
+        if (net.sign_chains and l.n == 32 and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None and nxt.c == 32
+                and nxt.pool_desc is None):
+            # 32 filters straight into an xnor layer: the kernel writes one sign word per pixel, no fp32 tensor
+            l.emit_masks = True
+            nxt.sign_source = j
+            net.sign_links += 1
+            continue
         mp = net.layers[j + 1]
         if not (mp.type == "maxpool" and not mp.folded and mp.size == 2 and mp.stride == 2 and mp.pad // 2 == 0
                 and mp.h % 2 == 0 and mp.w % 2 == 0):

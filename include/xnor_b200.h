@@ -259,8 +259,10 @@ XNOR_B200_API int xnor_b200_float_conv_small(const xnor_b200_conv_desc * desc, c
  *   output              fp32 [batch][n][h][w] (pool 0) or [batch][n][h/2][w/2] (pool 2), bias and activation applied
  *   output_sign_planes  pool 2 only: sign of the pooled output as x-packed planes [batch][n][h/2][ceil(w/2/32)],
  *                       the input_signs format of xnor_b200_conv_forward_io for c % 32 != 0
- *   output_sign_masks   pool 2 only: the same signs channel-packed per pixel, [batch][h/2][w/2][ceil(n/8)] bytes, the
- *                       input_masks format of xnor_b200_conv_forward_io
+ *   output_sign_masks   the signs channel-packed per pixel, [batch][h/2][w/2][ceil(n/8)] bytes (pool 2: the input_masks
+ *                       format of xnor_b200_conv_forward_io) or [batch][h][w][ceil(n/8)] bytes (pool 0; with n = 32 the four
+ *                       bytes of a pixel are one word of the input_signs format, [batch][1][h*w], for an xnor layer over
+ *                       those 32 channels, e.g. the stride-2 layer behind darknet53's first convolution)
  * Exactly one of the three is non-NULL.  Every value is formed as in xnor_b200_float_conv_small, so the planes equal
  * the sign of maxpool(that call's output) bit for bit.  Replaces forward_convolutional_layer_gpu (float branch) +
  * forward_maxpool_layer_gpu (src-lib/maxpool_layer_kernels.cu:48-86) + the sign step of the next layer. */

@@ -9,7 +9,7 @@ import synth
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
-from darknet_b200 import capi  # noqa: E402
+from darknet_b200 import capi, layer as L  # noqa: E402
 
 
 @pytest.mark.parametrize("case", [
@@ -188,7 +188,6 @@ def test_float_conv3_io_argument_checks():
     four = capi.ConvDesc(1, 4, 8, 8, 8, 3, 1, 1, capi.LINEAR)
     assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, None, None) == 2        # no output
     assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, z.data_ptr(), None, None) == 1  # planes need the pool
-    assert lib.xnor_b200_float_conv3_io(C.byref(ok), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, z.data_ptr(), None) == 1  # masks too
     assert lib.xnor_b200_float_conv3_io(C.byref(ok), 2, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None) == 2  # two outputs
     assert lib.xnor_b200_float_conv3_io(C.byref(odd), 2, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, None) == 1  # odd height
     assert lib.xnor_b200_float_conv3_io(C.byref(four), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None, None, None) == 1
@@ -235,3 +234,30 @@ def test_region_activate_matches_its_definition(case):
     assert torch.equal(got[:, :, 2:coords], v[:, :, 2:coords])                 # w, h (and further coords) untouched
     assert (got - v).abs().max().item() < 2e-6
     assert capi.lib().xnor_b200_region_activate(x.data_ptr(), x.data_ptr(), batch, anchors, coords, classes, softmax, hw, None) == 1   # in place: refused
+
+
+@pytest.mark.parametrize("case", [(2, 33, 47, 32, 1), (1, 64, 64, 32, 0), (1, 20, 30, 20, 1)], ids=lambda c: "b%d_%dx%d_n%d_%d" % c)
+def test_float_conv3_unpooled_masks_are_the_sign_words_of_the_output(case):
+    """pool = 0 with output_sign_masks: byte f/8, bit f%8 of pixel (y, x) = (output of filter f > 0), odd sizes included;
+    with 32 filters the tensor is the sign-word input of an xnor layer over those channels (here the stride-2 3x3 layer
+    that follows darknet53's first convolution), which then gives the same output as from the fp32 tensor."""
+    batch, h, w, n, leaky = case
+    x = torch.from_numpy(synth.bell(sum(case) + 5, (batch, 3, h, w), 1.0)).cuda()
+    wt = torch.from_numpy(synth.bell(sum(case) + 6, (n, 3, 3, 3), 0.3)).cuda()
+    b = torch.from_numpy(synth.bell(sum(case) + 7, (n,), 0.1)).cuda()
+    desc = capi.ConvDesc(batch, 3, h, w, n, 3, 1, 1, capi.LEAKY if leaky else capi.LINEAR)
+    full = _conv3(desc, 0, x, wt, b)
+    masks = _conv3(desc, 0, x, wt, b, masks=True)
+    nb = (n + 7) // 8
+    bits = torch.zeros(batch, nb * 8, h, w, dtype=torch.bool, device="cuda")
+    bits[:, :n] = full > 0
+    weights8 = (2 ** torch.arange(8, device="cuda")).view(1, 1, 8, 1, 1)
+    want = (bits.view(batch, nb, 8, h, w) * weights8).sum(2).permute(0, 2, 3, 1).to(torch.uint8)
+    assert torch.equal(masks, want)
+    if n == 32:
+        l = L.make_convolutional_layer(batch, h, w, 32, 64, 3, 2, 1, capi.LEAKY)
+        l.load_weights(torch.from_numpy(synth.bell(3, (64, 32 * 9), 0.05)).cuda(), torch.from_numpy(synth.bell(4, (64,), 0.3)).cuda())
+        L.binary_align_weights(l)
+        ref = L.forward_convolutional_layer_gpu(l, full).clone()
+        words = masks.view(torch.int32).reshape(batch, 1, h * w)
+        assert torch.equal(L.forward_convolutional_layer_io(l, x_signs=words), ref)
