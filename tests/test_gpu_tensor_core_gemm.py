@@ -47,7 +47,7 @@ def device_status():
 
 @pytest.mark.parametrize("shape", [
     (128, 128, 128), (128, 128, 1024), (256, 384, 2304), (130, 200, 675), (100, 131, 300), (384, 1000, 4608),
-    (128, 4097, 1152), (1, 1, 1), (257, 129, 9216),
+    (128, 4097, 1152), (1, 1, 1), (257, 129, 9216), (64, 70000, 288), (32, 1000, 64), (100, 5000, 384), (128, 257, 129),
 ], ids=lambda s: "M%d_N%d_K%d" % s)
 def test_tensor_core_counts_match_oracle(port, force_tc, shape):
     M, N, K = shape
