@@ -212,7 +212,12 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_c
 				: launch_pack_input(*desc, io.pool, io.input, (uint32_t *)scratch, s, 0, io.window_major);
 		if (rc != XNOR_B200_OK) { return rc; }
 	}
-	const bool extras = (extra.win_w > 0 || extra.n_sinks > 0 || extra.planes != nullptr || extra.masks != nullptr);
+	if (io.shortcut_signs != nullptr)
+	{
+		if (io.shortcut_out == nullptr || desc->n % 32 != 0 || io.n_sinks > 0 || io.output_signs != nullptr) { return XNOR_B200_ERR_INVALID; }
+		extra.sum_signs = io.shortcut_signs;
+	}
+	const bool extras = (extra.win_w > 0 || extra.n_sinks > 0 || extra.planes != nullptr || extra.masks != nullptr || extra.sum_signs != nullptr);
 	return launch_xnor_gemm(desc->n, desc->batch * g.n_out, g.n_out, g.k,
 			(const uint32_t *)align_bit_weights, g.new_lda / 32, (const uint32_t *)scratch, g.new_lda / 32,
 			io.output, g.n_out, mean_arr, biases, desc->activation == XNOR_B200_LEAKY,

@@ -73,6 +73,9 @@ struct GemmExtra
 	// Same, from channel masks [image][pl_h][pl_w][pl_c/8] bytes (bit c%8 of byte c/8), pl_c 8 or 16, with the rows and the
 	// weights in TAP-major K order (bit t*pl_c + c): a row is then nine neighbouring masks side by side.
 	const uint8_t * masks;
+	// Tensor-core kernel only, with a fused shortcut: also write the sign of shortcut_out as channel-packed words
+	// [image][M/32][pixels per image] (the input_signs format of the layer that reads the sum).
+	uint32_t * sum_signs;
 };
 
 // True when launch_xnor_gemm would run such a layer on the short-K kernel, i.e. when `planes` may be used.

@@ -808,7 +808,10 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs,
 		const GemmExtra * extra)
 {
-	const bool extras = (extra != nullptr && (extra->win_w > 0 || extra->n_sinks > 0 || extra->planes != nullptr || extra->masks != nullptr));
+	const bool sum_signs = (extra != nullptr && extra->sum_signs != nullptr);
+	// signs of the fused shortcut sum: written by the tensor-core kernel's fp32 epilogue only
+	if (sum_signs && (shortcut_out == nullptr || M % 32 != 0 || counts != nullptr || signs != nullptr || extra->n_sinks > 0)) { return XNOR_B200_ERR_INVALID; }
+	const bool extras = (extra != nullptr && (extra->win_w > 0 || extra->n_sinks > 0 || extra->planes != nullptr || extra->masks != nullptr || sum_signs));
 	if ((signs != nullptr || (extra != nullptr && extra->n_sinks > 0)) && M % 32 != 0) { return XNOR_B200_ERR_INVALID; }
 	if (extras && counts != nullptr) { return XNOR_B200_ERR_INVALID; }
 	if (extras && n_per_image % 4 != 0 && (extra->win_w > 0)) { return XNOR_B200_ERR_INVALID; }
@@ -836,7 +839,7 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	// =1 sends every shape to the tensor-core kernel (tuning and test aid).
 	{
 		const char * tc = std::getenv("XNOR_B200_GEMM_TC");
-		const bool use_tc = (tc != nullptr) ? (tc[0] == '1') : tc_gemm_eligible(M, n_total, K);
+		const bool use_tc = sum_signs || ((tc != nullptr) ? (tc[0] == '1') : tc_gemm_eligible(M, n_total, K));
 		if (use_tc && !(extra != nullptr && (extra->planes != nullptr || extra->masks != nullptr)))
 		{
 			return launch_xnor_gemm_tc(M, n_total, n_per_image, K, A, lda_words, B, ldb_words, C, ldc, mean_arr, bias, leaky,

@@ -172,8 +172,12 @@ __device__ __forceinline__ void tmem_load(uint32_t taddr, uint32_t (&d)[G])
 // between, the 24 warps of an SM wait a full memory latency each time and the epilogue runs at a fraction of the memory rate.
 template <int G, bool SC>
 __device__ __forceinline__ void epilogue_values(const TcParams & p, const int4 * s_fil, uint32_t tlane, int share, int shares,
-		int my_chunks, int f0, int k_b, bool col_ok, float * c_pix, const float * sc_in, float * sc_out)
+		int my_chunks, int f0, int k_b, bool col_ok, float * c_pix, const float * sc_in, float * sc_out,
+		uint32_t * sum_words = nullptr, int sum_stride = 0)
 {
+	// sum_words (SC only, G == 16): word of this pixel for the tile's first 32 filters in the sign tensor of the sum, sum_stride
+	// words between consecutive 32-filter blocks; the two groups of a block give the low and the high half of its word
+	uint32_t word = 0;
 	constexpr int PER = 32 / G;
 	const int groups = my_chunks * PER;
 	auto group_base = [&](int i) { return (share + (i / PER) * shares) * 32 + (i % PER) * G; };
@@ -211,6 +215,7 @@ __device__ __forceinline__ void epilogue_values(const TcParams & p, const int4 *
 		asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 		if (col_ok)
 		{
+			uint32_t bits = 0;
 			#pragma unroll
 			for (int u = 0; u < G; ++u)
 			{
@@ -223,7 +228,21 @@ __device__ __forceinline__ void epilogue_values(const TcParams & p, const int4 *
 					if (has_bias) { v = __fadd_rn(v, __int_as_float(fi.z)); }
 					if (p.leaky) { v = (v < 0.0f) ? __fmul_rn(v, 0.1f) : v; }
 					if (c_pix != nullptr) { c_pix[(size_t)(fb + u) * p.ldc] = v; }
-					if (SC) { sc_out[(size_t)(fb + u) * p.ldc] = __fadd_rn(sc[u], v); }
+					if (SC)
+					{
+						const float sum = __fadd_rn(sc[u], v);
+						sc_out[(size_t)(fb + u) * p.ldc] = sum;
+						bits |= (sum > 0.0f ? 1u : 0u) << u;
+					}
+				}
+			}
+			if (SC && G == 16 && sum_words != nullptr)
+			{
+				if ((fb & 16) == 0) { word = bits; }
+				else
+				{
+					word |= bits << 16;
+					if (f0 + fb < p.M) { sum_words[(size_t)(fb >> 5) * sum_stride] = word; }
 				}
 			}
 		}
@@ -418,7 +437,12 @@ xnor_gemm_tc_kernel(const TcParams p)
 		{
 			const int my_chunks = (share < NF / 32) ? (NF / 32 - share + SHARES - 1) / SHARES : 0;
 			const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-			if (sc_in != nullptr) { epilogue_values<16, true>(p, s_fil, tlane, share, SHARES, my_chunks, f0, k_b, col_ok, c_pix, sc_in, sc_out); }
+			if (sc_in != nullptr)
+			{
+				uint32_t * sum_words = (p.x.sum_signs != nullptr)
+						? p.x.sum_signs + ((size_t)img * (p.M >> 5) + (f0 >> 5)) * p.n_per_image + pix : nullptr;
+				epilogue_values<16, true>(p, s_fil, tlane, share, SHARES, my_chunks, f0, k_b, col_ok, c_pix, sc_in, sc_out, sum_words, p.n_per_image);
+			}
 			else { epilogue_values<32, false>(p, s_fil, tlane, share, SHARES, my_chunks, f0, k_b, col_ok, c_pix, nullptr, nullptr); }
 		}
 		#pragma unroll 1

@@ -100,6 +100,7 @@ class Layer:
     packed_input: bool = False       # xnor conv: every input channel arrives through producers' sinks
     need_fp32: bool = True           # somebody still reads this layer's fp32 output
     shortcut_only: bool = False      # xnor conv whose output only the fused [shortcut] behind it reads: just the sum is written
+    emit_sum_signs: bool = False     # xnor conv with a fused [shortcut] whose sum the next xnor layer reads: also writes its sign words
     skip: bool = False               # maxpool / upsample / route that only sat between a sink producer and its consumer
     sign_source: Optional[int] = None
     sign_out: Optional[torch.Tensor] = None
@@ -123,6 +124,8 @@ class Network:
     fold_maxpool_min_batch: int = 4
     sign_chains: bool = True
     skip_fused_conv_outputs: bool = True   # an xnor conv read only by its fused [shortcut] does not write its own tensor
+    sum_signs_min_batch: int = 8           # from this batch on the sign of a fused shortcut sum is handed to the next xnor layer as words (the call runs on the tensor-core kernel, which is the choice for these layers from about this batch anyway)
+    sum_sign_links: int = 0
     fuse_first_conv: bool = True
     float_map_max_pixels: int = 1024       # batch*out_h*out_w up to which float convs use the cluster split-K kernel (measured: it wins at 676 pixels, loses to cuDNN/cuBLAS at 1352)
     sign_links: int = 0
@@ -279,6 +282,16 @@ def calculate_binary_weights(net: Network) -> None:
         # [shortcut] layer blanked nothing reads the former, and at large batch it is a third of the layer's memory traffic
         l.shortcut_only = (net.skip_fused_conv_outputs and l.type == "convolutional" and l.xnor and net.layers[j + 1].blank
                            and readers[j] == [j + 1])
+    if net.sign_chains and net.batch >= net.sum_signs_min_batch:
+        for j, l in enumerate(net.layers[:-2]):
+            nxt = net.layers[j + 2]
+            # conv j + fused [shortcut] j+1 -> xnor conv j+2: the consumer packs from the sum's sign words, not from the fp32 sum
+            if (l.type == "convolutional" and l.xnor and net.layers[j + 1].blank and l.n % 32 == 0
+                    and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None and nxt.c % 32 == 0):
+                l.emit_sum_signs = True
+                l.xnor_layer.shortcut_signs_gpu = torch.empty(net.batch, l.n // 32, l.out_h * l.out_w, dtype=torch.int32, device=dev)
+                nxt.sign_source = j + 1
+                net.sum_sign_links += 1
     prepare_float_map_convs(net)
     link_branches(net)
     if net.sign_chains:
@@ -650,12 +663,14 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
                     so = l.shortcut_only and want_fp32 and not l.sinks
                     out = L.forward_convolutional_layer_io(xl, x=None if (src is not None or masks is not None or l.packed_input) else cur,
                                                            x_signs=src, pool=l.pool_desc, want_signs=l.emit_signs, packed=l.packed_input,
-                                                           sinks=l.sinks, want_output=want_fp32, x_masks=masks, shortcut_only=so)
+                                                           sinks=l.sinks, want_output=want_fp32, x_masks=masks, shortcut_only=so,
+                                                           shortcut_signs=l.emit_sum_signs)
                     l.sign_out = out if l.emit_signs else None
                     cur = out if (want_fp32 and not so) else None
-                elif l.shortcut_only:
-                    L.forward_convolutional_layer_io(xl, x=cur, pool=l.pool_desc, shortcut_only=True)
-                    cur = None
+                elif l.shortcut_only or l.emit_sum_signs:
+                    out = L.forward_convolutional_layer_io(xl, x=cur, pool=l.pool_desc, shortcut_only=l.shortcut_only, want_output=True,
+                                                           shortcut_signs=l.emit_sum_signs)
+                    cur = None if l.shortcut_only else out
                 else:
                     cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)
             elif l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1 and l.activation in ("leaky", "linear"):
@@ -686,6 +701,9 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
                 torch.cat([net.layers[i].output_gpu for i in l.input_layers], 1)
         elif l.type == "shortcut":
             cur = l.output_gpu if l.blank else _activate(cur + net.layers[l.input_layers[0]].output_gpu, l.activation)
+            prev = net.layers[l.index - 1]
+            if l.blank and prev.emit_sum_signs:
+                l.sign_out = prev.xnor_layer.shortcut_signs_gpu
         elif l.type == "upsample":
             cur = F.interpolate(cur, scale_factor=l.stride, mode="nearest")
         elif l.type == "avgpool":

@@ -223,6 +223,10 @@ typedef struct xnor_b200_conv_io
 	                                         c/8 = "channel c > 0").  The GEMM then builds its rows itself, in TAP-major K order, so
 	                                         the weights argument must be the xnor_b200_tap_major_weights() copy: */
 	int tap_major_weights;                /* 1 = it is; input_masks is refused otherwise */
+	uint32_t * shortcut_signs;            /* optional, with shortcut_out (n % 32 == 0): the sign of the fused sum as channel-packed
+	                                         words [batch][n/32][out_h*out_w], i.e. the input_signs of the xnor layer that reads the
+	                                         [shortcut]; that layer then packs from 1 bit per value instead of the fp32 sum.  The call
+	                                         runs on the tensor-core kernel whatever its size, so use it for batched layers */
 } xnor_b200_conv_io;
 
 /* 1 when a layer can take input_masks: c is 8 or 16, size 3, stride 1, pad 1 (and no kernel override in the environment). */

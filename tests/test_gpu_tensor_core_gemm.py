@@ -171,3 +171,35 @@ def test_shortcut_sum_without_the_layers_own_tensor(force_tc, mode):
     rc = capi.lib().xnor_b200_conv_forward_io(C.byref(l.desc), C.byref(io), l.align_bit_weights_gpu.data_ptr(), l.mean_arr_gpu.data_ptr(),
                                               l.biases_gpu.data_ptr(), l.scratch.data_ptr(), l.scratch.numel(), None)
     assert rc != capi.OK
+
+
+@pytest.mark.parametrize("case", [(2, 64, 20, 20, 96, 3), (1, 32, 16, 12, 256, 3), (3, 128, 9, 9, 64, 1)], ids=lambda c: "b%d_c%d_%dx%d_n%d_k%d" % c)
+def test_sign_words_of_the_fused_shortcut_sum(case):
+    """shortcut_signs: bit f%32 of word [image][f/32][pixel] = (shortcut_out of filter f > 0); the call runs on the tensor-core
+    kernel by itself, the sum and the layer's own tensor stay what the plain call writes, and an xnor layer fed with the words
+    gives the same output as from the fp32 sum."""
+    batch, c, h, w, n, ks = case
+    x, wt, b = synth.conv_case(4242 + n, batch, c, h, w, n, ks)
+    l = L.make_convolutional_layer(batch, h, w, c, n, ks, 1, ks // 2, capi.LEAKY)
+    l.load_weights(torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda())
+    L.binary_align_weights(l)
+    xg = torch.from_numpy(x).cuda()
+    l.bin_conv_shortcut_in_gpu = torch.from_numpy(synth.bell(7, (batch, n, h, w), 1.0)).cuda()
+    l.bin_conv_shortcut_out_gpu = torch.empty(batch, n, h, w, device="cuda")
+    y = L.forward_convolutional_layer_gpu(l, xg).clone()
+    want_sum = l.bin_conv_shortcut_out_gpu.clone()
+    l.output_gpu.fill_(float("nan"))
+    l.bin_conv_shortcut_out_gpu.fill_(float("nan"))
+    got = L.forward_convolutional_layer_io(l, x=xg, want_output=True, shortcut_signs=True)
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    assert torch.equal(got, y) and torch.equal(l.bin_conv_shortcut_out_gpu, want_sum)
+    bits = (want_sum > 0).view(batch, n // 32, 32, h * w).to(torch.int64)
+    words = (bits << torch.arange(32, device="cuda").view(1, 1, 32, 1)).sum(2)
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
+    assert torch.equal(l.shortcut_signs_gpu, words)
+    nxt = L.make_convolutional_layer(batch, h, w, n, 64, 1, 1, 0, capi.LINEAR)
+    nxt.load_weights(torch.from_numpy(synth.bell(9, (64, n), 0.05)).cuda(), torch.from_numpy(synth.bell(10, (64,), 0.3)).cuda())
+    L.binary_align_weights(nxt)
+    ref = L.forward_convolutional_layer_gpu(nxt, want_sum).clone()
+    assert torch.equal(L.forward_convolutional_layer_io(nxt, x_signs=l.shortcut_signs_gpu), ref)
