@@ -51,7 +51,8 @@ class ConvIO(C.Structure):
     _fields_ = [("input", C.c_void_p), ("input_signs", C.c_void_p), ("pool", C.POINTER(PoolDesc)), ("output", C.c_void_p),
                 ("output_signs", C.c_void_p), ("shortcut_in", C.c_void_p), ("shortcut_out", C.c_void_p),
                 ("input_packed", C.c_int), ("window_major", C.c_int), ("sinks", C.POINTER(SignSink)), ("n_sinks", C.c_int),
-                ("input_masks", C.c_void_p), ("tap_major_weights", C.c_int), ("shortcut_signs", C.c_void_p)]
+                ("input_masks", C.c_void_p), ("tap_major_weights", C.c_int), ("shortcut_signs", C.c_void_p),
+                ("shortcut_sink", C.POINTER(SignSink))]
 
 
 class ConvGeom(C.Structure):

@@ -217,7 +217,24 @@ static int conv_forward_impl(const xnor_b200_conv_desc * desc, const xnor_b200_c
 		if (io.shortcut_out == nullptr || desc->n % 32 != 0 || io.n_sinks > 0 || io.output_signs != nullptr) { return XNOR_B200_ERR_INVALID; }
 		extra.sum_signs = io.shortcut_signs;
 	}
-	const bool extras = (extra.win_w > 0 || extra.n_sinks > 0 || extra.planes != nullptr || extra.masks != nullptr || extra.sum_signs != nullptr);
+	if (io.shortcut_sink != nullptr)
+	{
+		// the reader of the fused sum: a 1x1 / stride-1 xnor layer over exactly this layer's filters on the same map
+		const xnor_b200_sign_sink & sk = *io.shortcut_sink;
+		if (sk.consumer == nullptr || sk.consumer_scratch == nullptr) { return XNOR_B200_ERR_NULL; }
+		const xnor_b200_conv_desc & cd = *sk.consumer;
+		if (io.shortcut_out == nullptr || desc->n % 32 != 0 || io.n_sinks > 0 || io.output_signs != nullptr || io.window_major) { return XNOR_B200_ERR_INVALID; }
+		if (cd.size != 1 || cd.stride != 1 || cd.pad != 0 || cd.c != desc->n || cd.h != g.out_h || cd.w != g.out_w || cd.batch != desc->batch
+				|| sk.channel_offset != 0 || sk.pool != 0 || sk.upsample > 1 || sk.consumer_window_major != 0) { return XNOR_B200_ERR_INVALID; }
+		if ((((uintptr_t)sk.consumer_scratch) & 255u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
+		xnor_b200_conv_geom cg;
+		rc = xnor_b200_conv_geometry(&cd, &cg);
+		if (rc != XNOR_B200_OK) { return rc; }
+		extra.sum_rows = (uint32_t *)sk.consumer_scratch;
+		extra.sum_ldw = cg.new_lda / 32;
+	}
+	const bool extras = (extra.win_w > 0 || extra.n_sinks > 0 || extra.planes != nullptr || extra.masks != nullptr || extra.sum_signs != nullptr
+			|| extra.sum_rows != nullptr);
 	return launch_xnor_gemm(desc->n, desc->batch * g.n_out, g.n_out, g.k,
 			(const uint32_t *)align_bit_weights, g.new_lda / 32, (const uint32_t *)scratch, g.new_lda / 32,
 			io.output, g.n_out, mean_arr, biases, desc->activation == XNOR_B200_LEAKY,

@@ -76,6 +76,10 @@ struct GemmExtra
 	// Tensor-core kernel only, with a fused shortcut: also write the sign of shortcut_out as channel-packed words
 	// [image][M/32][pixels per image] (the input_signs format of the layer that reads the sum).
 	uint32_t * sum_signs;
+	// ... or straight into the packed operand of a 1x1 / stride-1 xnor layer over exactly these filters: rows of sum_ldw words,
+	// one row per pixel, word f/32 of a row = the signs of filters f .. f+31 at that pixel.
+	uint32_t * sum_rows;
+	int sum_ldw;
 };
 
 // True when launch_xnor_gemm would run such a layer on the short-K kernel, i.e. when `planes` may be used.

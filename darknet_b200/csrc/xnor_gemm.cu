@@ -808,7 +808,7 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 		const float * shortcut_in, float * shortcut_out, int32_t * counts, cudaStream_t stream, uint32_t * signs,
 		const GemmExtra * extra)
 {
-	const bool sum_signs = (extra != nullptr && extra->sum_signs != nullptr);
+	const bool sum_signs = (extra != nullptr && (extra->sum_signs != nullptr || extra->sum_rows != nullptr));
 	// signs of the fused shortcut sum: written by the tensor-core kernel's fp32 epilogue only
 	if (sum_signs && (shortcut_out == nullptr || M % 32 != 0 || counts != nullptr || signs != nullptr || extra->n_sinks > 0)) { return XNOR_B200_ERR_INVALID; }
 	const bool extras = (extra != nullptr && (extra->win_w > 0 || extra->n_sinks > 0 || extra->planes != nullptr || extra->masks != nullptr || sum_signs));

@@ -173,8 +173,9 @@ __device__ __forceinline__ void tmem_load(uint32_t taddr, uint32_t (&d)[G])
 template <int G, bool SC>
 __device__ __forceinline__ void epilogue_values(const TcParams & p, const int4 * s_fil, uint32_t tlane, int share, int shares,
 		int my_chunks, int f0, int k_b, bool col_ok, float * c_pix, const float * sc_in, float * sc_out,
-		uint32_t * sum_words = nullptr, int sum_stride = 0)
+		uint32_t * sum_words = nullptr, int sum_stride = 0, uint32_t * row_words = nullptr)
 {
+	// row_words: this pixel's row in the packed operand of the 1x1 layer that reads the sum, at the tile's first 32-filter block
 	// sum_words (SC only, G == 16): word of this pixel for the tile's first 32 filters in the sign tensor of the sum, sum_stride
 	// words between consecutive 32-filter blocks; the two groups of a block give the low and the high half of its word
 	uint32_t word = 0;
@@ -236,13 +237,17 @@ __device__ __forceinline__ void epilogue_values(const TcParams & p, const int4 *
 					}
 				}
 			}
-			if (SC && G == 16 && sum_words != nullptr)
+			if (SC && G == 16 && (sum_words != nullptr || row_words != nullptr))
 			{
 				if ((fb & 16) == 0) { word = bits; }
 				else
 				{
 					word |= bits << 16;
-					if (f0 + fb < p.M) { sum_words[(size_t)(fb >> 5) * sum_stride] = word; }
+					if (f0 + fb < p.M)
+					{
+						if (sum_words != nullptr) { sum_words[(size_t)(fb >> 5) * sum_stride] = word; }
+						if (row_words != nullptr) { row_words[fb >> 5] = word; }
+					}
 				}
 			}
 		}
@@ -441,7 +446,10 @@ xnor_gemm_tc_kernel(const TcParams p)
 			{
 				uint32_t * sum_words = (p.x.sum_signs != nullptr)
 						? p.x.sum_signs + ((size_t)img * (p.M >> 5) + (f0 >> 5)) * p.n_per_image + pix : nullptr;
-				epilogue_values<16, true>(p, s_fil, tlane, share, SHARES, my_chunks, f0, k_b, col_ok, c_pix, sc_in, sc_out, sum_words, p.n_per_image);
+				uint32_t * row_words = (p.x.sum_rows != nullptr)
+						? p.x.sum_rows + ((size_t)img * p.n_per_image + pix) * p.x.sum_ldw + (f0 >> 5) : nullptr;
+				epilogue_values<16, true>(p, s_fil, tlane, share, SHARES, my_chunks, f0, k_b, col_ok, c_pix, sc_in, sc_out, sum_words, p.n_per_image,
+						row_words);
 			}
 			else { epilogue_values<32, false>(p, s_fil, tlane, share, SHARES, my_chunks, f0, k_b, col_ok, c_pix, nullptr, nullptr); }
 		}

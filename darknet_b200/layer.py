@@ -148,12 +148,14 @@ class Sink:
 def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tensor] = None, x_signs: Optional[torch.Tensor] = None,
                                    pool: Optional[capi.PoolDesc] = None, want_signs: bool = False, packed: bool = False,
                                    sinks=(), want_output: Optional[bool] = None, x_masks: Optional[torch.Tensor] = None,
-                                   shortcut_only: bool = False, shortcut_signs: bool = False) -> Optional[torch.Tensor]:
+                                   shortcut_only: bool = False, shortcut_signs: bool = False,
+                                   shortcut_sink: Optional["ConvolutionalLayer"] = None) -> Optional[torch.Tensor]:
     """xnor_b200_conv_forward_io.  Input: fp32 `x`, sign words / planes `x_signs`, or `packed` (the producers' sinks have
     filled l.scratch).  Output: the fp32 tensor (default when there are no sinks, or with want_output), the sign words
     int32 [batch][n/32][out_h*out_w] (want_signs), and/or the consumers' operands (sinks).  shortcut_only: only the fused
     shortcut sum (l.bin_conv_shortcut_out_gpu) is written and returned; the layer's own tensor is left untouched.
-    shortcut_signs: the sign words of the sum are written to l.shortcut_signs_gpu as well."""
+    shortcut_signs: the sign words of the sum are written to l.shortcut_signs_gpu as well.  shortcut_sink: the 1x1 layer
+    that reads the sum; the signs go straight into its packed operand (its scratch)."""
     if l.align_bit_weights_gpu is None:
         raise RuntimeError("binary_align_weights() has not been called for this layer")
     io = capi.ConvIO()
@@ -188,6 +190,11 @@ def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tens
         if l.shortcut_signs_gpu is None:
             l.shortcut_signs_gpu = torch.empty(l.batch, l.n // 32, l.geom.n_out, dtype=torch.int32, device=l.device)
         io.shortcut_signs = l.shortcut_signs_gpu.data_ptr()
+    if shortcut_sink is not None:
+        sk = capi.SignSink()
+        sk.consumer = C.pointer(shortcut_sink.desc)
+        sk.consumer_scratch = shortcut_sink.scratch.data_ptr()
+        io.shortcut_sink = C.pointer(sk)
     if sinks:
         arr = (capi.SignSink * len(sinks))()
         for i, s in enumerate(sinks):

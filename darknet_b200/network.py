@@ -101,6 +101,7 @@ class Layer:
     need_fp32: bool = True           # somebody still reads this layer's fp32 output
     shortcut_only: bool = False      # xnor conv whose output only the fused [shortcut] behind it reads: just the sum is written
     emit_sum_signs: bool = False     # xnor conv with a fused [shortcut] whose sum the next xnor layer reads: also writes its sign words
+    sum_sink_to: Optional[int] = None  # ... or, when that reader is a 1x1 layer, writes them into its packed operand (layer index)
     skip: bool = False               # maxpool / upsample / route that only sat between a sink producer and its consumer
     sign_source: Optional[int] = None
     sign_out: Optional[torch.Tensor] = None
@@ -288,9 +289,14 @@ def calculate_binary_weights(net: Network) -> None:
             # conv j + fused [shortcut] j+1 -> xnor conv j+2: the consumer packs from the sum's sign words, not from the fp32 sum
             if (l.type == "convolutional" and l.xnor and net.layers[j + 1].blank and l.n % 32 == 0
                     and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None and nxt.c % 32 == 0):
-                l.emit_sum_signs = True
-                l.xnor_layer.shortcut_signs_gpu = torch.empty(net.batch, l.n // 32, l.out_h * l.out_w, dtype=torch.int32, device=dev)
-                nxt.sign_source = j + 1
+                if nxt.size == 1 and nxt.stride == 1 and nxt.pad == 0 and nxt.c == l.n and not nxt.xnor_layer.window_major:
+                    # a 1x1 reader: the signs go straight into its packed operand, it runs without a pack kernel
+                    l.sum_sink_to = j + 2
+                    nxt.packed_input = True
+                else:
+                    l.emit_sum_signs = True
+                    l.xnor_layer.shortcut_signs_gpu = torch.empty(net.batch, l.n // 32, l.out_h * l.out_w, dtype=torch.int32, device=dev)
+                    nxt.sign_source = j + 1
                 net.sum_sign_links += 1
     prepare_float_map_convs(net)
     link_branches(net)
@@ -664,12 +670,14 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
                     out = L.forward_convolutional_layer_io(xl, x=None if (src is not None or masks is not None or l.packed_input) else cur,
                                                            x_signs=src, pool=l.pool_desc, want_signs=l.emit_signs, packed=l.packed_input,
                                                            sinks=l.sinks, want_output=want_fp32, x_masks=masks, shortcut_only=so,
-                                                           shortcut_signs=l.emit_sum_signs)
+                                                           shortcut_signs=l.emit_sum_signs,
+                                                           shortcut_sink=net.layers[l.sum_sink_to].xnor_layer if l.sum_sink_to is not None else None)
                     l.sign_out = out if l.emit_signs else None
                     cur = out if (want_fp32 and not so) else None
-                elif l.shortcut_only or l.emit_sum_signs:
+                elif l.shortcut_only or l.emit_sum_signs or l.sum_sink_to is not None:
                     out = L.forward_convolutional_layer_io(xl, x=cur, pool=l.pool_desc, shortcut_only=l.shortcut_only, want_output=True,
-                                                           shortcut_signs=l.emit_sum_signs)
+                                                           shortcut_signs=l.emit_sum_signs,
+                                                           shortcut_sink=net.layers[l.sum_sink_to].xnor_layer if l.sum_sink_to is not None else None)
                     cur = None if l.shortcut_only else out
                 else:
                     cur = L.forward_convolutional_layer_gpu(xl, cur, l.pool_desc)

@@ -227,6 +227,11 @@ typedef struct xnor_b200_conv_io
 	                                         words [batch][n/32][out_h*out_w], i.e. the input_signs of the xnor layer that reads the
 	                                         [shortcut]; that layer then packs from 1 bit per value instead of the fp32 sum.  The call
 	                                         runs on the tensor-core kernel whatever its size, so use it for batched layers */
+	const xnor_b200_sign_sink * shortcut_sink;  /* optional, same conditions: when the reader of the [shortcut] is a 1x1 / stride-1 /
+	                                         pad-0 xnor layer over exactly these n channels on the same map, the signs of the sum go
+	                                         straight into its packed operand (consumer_scratch, zero-filled once at load time); it
+	                                         then runs with input_packed = 1 and no pack kernel.  channel_offset, pool, upsample and
+	                                         consumer_window_major of the sink must be 0 */
 } xnor_b200_conv_io;
 
 /* 1 when a layer can take input_masks: c is 8 or 16, size 3, stride 1, pad 1 (and no kernel override in the environment). */

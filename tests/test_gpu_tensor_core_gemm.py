@@ -203,3 +203,36 @@ def test_sign_words_of_the_fused_shortcut_sum(case):
     L.binary_align_weights(nxt)
     ref = L.forward_convolutional_layer_gpu(nxt, want_sum).clone()
     assert torch.equal(L.forward_convolutional_layer_io(nxt, x_signs=l.shortcut_signs_gpu), ref)
+
+
+@pytest.mark.parametrize("case", [(2, 64, 20, 20, 96), (1, 32, 16, 12, 256), (3, 128, 9, 9, 64)], ids=lambda c: "b%d_c%d_%dx%d_n%d" % c)
+def test_shortcut_sum_signs_straight_into_a_1x1_readers_operand(case):
+    """shortcut_sink: the 1x1 layer that reads the fused sum finds its packed operand filled by the producer's epilogue
+    (equal to what its own pack kernel makes of the fp32 sum, padding words untouched) and gives the same output."""
+    batch, c, h, w, n = case
+    x, wt, b = synth.conv_case(777 + n, batch, c, h, w, n, 3)
+    l = L.make_convolutional_layer(batch, h, w, c, n, 3, 1, 1, capi.LEAKY)
+    l.load_weights(torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda())
+    L.binary_align_weights(l)
+    xg = torch.from_numpy(x).cuda()
+    l.bin_conv_shortcut_in_gpu = torch.from_numpy(synth.bell(17, (batch, n, h, w), 1.0)).cuda()
+    l.bin_conv_shortcut_out_gpu = torch.empty(batch, n, h, w, device="cuda")
+    L.forward_convolutional_layer_gpu(l, xg)
+    want_sum = l.bin_conv_shortcut_out_gpu.clone()
+    nxt = L.make_convolutional_layer(batch, h, w, n, 40, 1, 1, 0, capi.LEAKY)
+    nxt.load_weights(torch.from_numpy(synth.bell(19, (40, n), 0.05)).cuda(), torch.from_numpy(synth.bell(20, (40,), 0.3)).cuda())
+    L.binary_align_weights(nxt)
+    want_op = L.pack_input(nxt, want_sum).clone()
+    ref = L.forward_convolutional_layer_gpu(nxt, want_sum).clone()
+    nxt.scratch.zero_()
+    l.bin_conv_shortcut_out_gpu.fill_(float("nan"))
+    got_sum = L.forward_convolutional_layer_io(l, x=xg, shortcut_only=True, shortcut_sink=nxt)
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    assert torch.equal(got_sum, want_sum)
+    assert torch.equal(nxt.scratch[:want_op.numel()].view(want_op.shape), want_op)
+    assert torch.equal(L.forward_convolutional_layer_io(nxt, packed=True), ref)
+    # a reader that is not 1x1 over these channels is refused
+    bad = L.make_convolutional_layer(batch, h, w, n, 40, 3, 1, 1, capi.LEAKY)
+    with pytest.raises(capi.XnorError, match="invalid"):
+        L.forward_convolutional_layer_io(l, x=xg, shortcut_only=True, shortcut_sink=bad)
