@@ -125,7 +125,7 @@ class Network:
     fold_maxpool_min_batch: int = 4
     sign_chains: bool = True
     skip_fused_conv_outputs: bool = True   # an xnor conv read only by its fused [shortcut] does not write its own tensor
-    sum_signs_min_batch: int = 8           # from this batch on the sign of a fused shortcut sum is handed to the next xnor layer as words (the call runs on the tensor-core kernel, which is the choice for these layers from about this batch anyway)
+    sum_signs_min_batch: int = 4           # from this batch on the sign of a fused shortcut sum is handed to the next xnor layer (the call runs on the tensor-core kernel; measured on darknet53: +5 % at batch 4, -7 % at batch 2, -26 % at batch 1)
     sum_sign_links: int = 0
     fuse_first_conv: bool = True
     float_map_max_pixels: int = 1024       # batch*out_h*out_w up to which float convs use the cluster split-K kernel (measured: it wins at 676 pixels, loses to cuDNN/cuBLAS at 1352)
@@ -755,6 +755,8 @@ def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "c
     net.side_branches = side_branches
     if os.environ.get("XNOR_B200_FLOAT_MAP_MAX_PIXELS"):      # tuning aid
         net.float_map_max_pixels = int(os.environ["XNOR_B200_FLOAT_MAP_MAX_PIXELS"])
+    if os.environ.get("XNOR_B200_SUM_SIGNS_MIN_BATCH"):       # tuning aid: batch from which the signs of fused shortcut sums are handed on
+        net.sum_signs_min_batch = int(os.environ["XNOR_B200_SUM_SIGNS_MIN_BATCH"])
     if os.environ.get("XNOR_B200_SINK_MAX_BATCH"):            # tuning aid: batch up to which sign sinks are linked
         net.sink_max_batch = int(os.environ["XNOR_B200_SINK_MAX_BATCH"])
     load_weights(net, weights)
