@@ -1,25 +1,32 @@
 #!/usr/bin/env python
-"""Benchmark of the xnor conv path on B200: yolov3-tiny_xnor forward at 416x416, batch 1 per GPU.
+"""Benchmark of the xnor conv path on B200.  Default workload: yolov3-tiny_xnor forward at 416x416, batch 1 per GPU.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload NET] [--batch B | --global-batch B] [--forwards-per-step F]
+    python bench.py --kernel gemm --shape M N K [--route auto|integer|tensor|tiled] [--shortcut] [--reps R]
+    python bench.py --kernel pack --shape BATCH C H W N KS [--reps R]
+    python bench.py --kernel gemms | --kernel fconv --shape CASE
 
-One "step" is one forward pass of the network over one batch of seeded synthetic input with seeded
-random weights (no dataset or checkpoint is involved).  Every xnor=1 convolution runs through
-libxnor_b200.so; the float layers around the path run through cuDNN/ATen as they run through cuDNN in
-Darknet.  The forward is captured once into a CUDA graph and replayed.
+One forward is one pass of the network over one batch of seeded synthetic input with seeded random weights (no
+dataset or checkpoint is involved), captured once into a CUDA graph and replayed.  One STEP is `forwards_per_step`
+forwards (stated in `config`), so that a 20-step run times well over 100 ms; every forward is timed with its own
+pair of CUDA events on the launch stream and the L2 is flushed between forwards, outside the intervals.
 
 Printed JSON (one line, rank 0):
-  value      images/s, inputs resident in HBM, per-step CUDA-event time (max over ranks), L2 flushed
-             between steps
-  e2e        images/s through the same call with the input copied from pinned host memory and the head
-             outputs copied back inside the timed region
-  roofline   the XNOR GEMM launches of one forward, timed alone with CUDA events on their stream, against
-             the integer XOR+POPC+ADD issue rate measured on the same GPU in the same run
-  cpu_baseline  the reference's own CPU xnor code (oracle/_ref) on the same layer shapes, host cores
+  value         images/s, inputs resident in HBM (sum of the per-forward event intervals, max over ranks)
+  e2e           images/s with the input copied from pinned host memory and the head outputs copied back inside the
+                timed region; e2e.blocking_call = the same through a blocking predict call (copy in, forward, copy
+                out, stream synchronise per call) timed with the host clock, and e2e.double_buffered = that loop
+                with the next input's copy overlapping the current forward
+  roofline*     single kernels timed alone with CUDA events on their stream against a peak measured in the same
+                run (integer XOR+POPC+ADD issue rate, tcgen05 kind::i8 rate) or MEASURED_PEAKS.json (HBM)
+  cpu_baseline  the reference's own CPU xnor code (oracle/_ref) on the same layer shapes, all host cores and one
 
 --impl reference times only that CPU code (xnor layers of the same network) and prints its own line.
-With N > 1 (torchrun) every rank runs an independent replica on its GPU: replicas only, no collective on
-the data path; NCCL is used for the barrier and the max over ranks.
+With N > 1 (torchrun) every rank runs an independent replica on its GPU: replicas only, no collective on the data
+path; NCCL is used for the barrier and the max over ranks.  --global-batch cuts one batch over the ranks instead.
+--kernel runs one kernel of the library on random operands and prints its median time (the command the profiler
+captures are made with).
 """
 from __future__ import annotations
 
@@ -38,67 +45,95 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-WORKLOAD = "yolov3-tiny_xnor forward, 416x416x3 fp32 input U[0,1), batch 1 per GPU, seeded random weights"
 METRIC = "images/s yolov3-tiny_xnor@416"
 L2_FLUSH_BYTES = 256 << 20
+TARGET_STEP_MS = 8.0
+ROUTES = {"auto": 0, "integer": 1, "tensor": 2, "tiled": 3}
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=500)
-    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--batch", type=int, default=1, help="images per GPU per step (the metric is quoted at 1)")
+    ap.add_argument("--batch", type=int, default=1, help="images per GPU per forward (the metric is quoted at 1)")
+    ap.add_argument("--global-batch", type=int, default=0,
+                    help="images per forward over ALL GPUs, cut into per-rank slices (strong scaling; BASELINE configurations 4 "
+                         "and 5); 0 = --batch images on every GPU (weak scaling, the default)")
+    ap.add_argument("--forwards-per-step", type=int, default=0,
+                    help="forward passes that make up one step (0 = as many as bring a step to about 8 ms, at least 1)")
     ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
     ap.add_argument("--workload", default="yolov3-tiny_xnor", choices=["yolov3-tiny_xnor", "tiny-yolo_xnor", "darknet53_448_xnor"],
                     help="network to run; the default is the configuration the metric is quoted on, the others are the "
-                         "batched BASELINE configurations (use with --batch)")
+                         "batched BASELINE configurations (use with --batch or --global-batch)")
+    ap.add_argument("--kernel", default=None, choices=["gemm", "gemms", "pack", "fconv"], help="time one kernel instead of the network")
+    ap.add_argument("--shape", type=int, nargs="*", default=[])
+    ap.add_argument("--route", default="auto", choices=sorted(ROUTES))
+    ap.add_argument("--shortcut", action="store_true")
+    ap.add_argument("--reps", type=int, default=5)
     return ap.parse_args()
+
+
+def workload_text(name: str, size: int, batch_text: str) -> str:
+    return f"{name} forward, {size}x{size}x3 fp32 input U[0,1), {batch_text}, seeded random weights"
 
 
 # ---- CPU reference arm ---------------------------------------------------------------------------
 
-def xnor_layer_table():
+def xnor_layer_table(workload: str):
     import torch  # noqa: F401  (network.py imports torch; CPU only here)
     from darknet_b200 import cfgs, network
     with tempfile.TemporaryDirectory() as td:
         p = os.path.join(td, "net.cfg")
         with open(p, "w") as fh:
-            fh.write(cfgs.yolov3_tiny_xnor_cfg())
+            fh.write(cfgs.CFGS[workload]())
         net = network.parse_network_cfg(p, 1, "cpu")
     # bin_output layers lose their activation at load (calculate_binary_weights)
     rows = network.xnor_layer_shapes(net)
     for r, l in zip(rows, [l for l in net.layers if l.type == "convolutional" and l.xnor]):
         r["leaky"] = int(l.activation == "leaky" and not l.use_bin_output)
-    return rows
+    return rows, net.h
 
 
 class CpuReference:
-    """The reference's CPU xnor forward (oracle/_ref: its own sources compiled unmodified) over the xnor layers
-    of the workload; where that build is absent, the plain-C restatement.  Built once, then timed."""
+    """The reference's CPU xnor forward (oracle/_ref: its own sources compiled unmodified, preferably the build with the
+    reference's own optimisation flags) over the xnor layers of the workload; where neither build is present, the plain-C
+    restatement.  Built once, then timed."""
 
-    def __init__(self, threads: int | None = None) -> None:
+    def __init__(self, workload: str, threads: int | None = None) -> None:
         import synth
-        from oracle.binding import Port, Ref
-        self.rows = xnor_layer_table()
+        from oracle import binding
+        self.workload = workload
+        self.rows, self.size = xnor_layer_table(workload)
         self.cores = threads or os.cpu_count() or 1
-        if Ref.available():
-            ref = Ref()
-            ref.set_gpu_index(-1)
-            ref.set_num_threads(self.cores)
-            self.kind = "reference"
+        fast = getattr(binding, "REF_FAST_SO", None)
+        if fast and os.path.exists(fast):
+            self.ref, self.kind = binding.Ref(fast), "reference"
+            self.build = "reference flags (-O3 -ffp-contract=fast -funsafe-math-optimizations, AVX2)"
+        elif binding.Ref.available():
+            self.ref, self.kind, self.build = binding.Ref(), "reference", "checker flags (-O3, AVX2, no fast-math)"
+        else:
+            self.ref, self.kind, self.build = None, "port", "plain-C restatement"
+        if self.ref is not None:
+            self.ref.set_gpu_index(-1)
+            self.ref.set_num_threads(self.cores)
             self.layers = []
             for i, r in enumerate(self.rows):
                 x, wt, b = synth.conv_case(900 + i, 1, r["c"], r["h"], r["w"], r["n"], r["size"])
-                self.layers.append((ref.layer((r["c"], r["h"], r["w"]), wt, b, r["stride"], r["pad"], bool(r["leaky"])), x[0]))
+                self.layers.append((self.ref.layer((r["c"], r["h"], r["w"]), wt, b, r["stride"], r["pad"], bool(r["leaky"])), x[0]))
             self._one = lambda: [lay.forward(x) for lay, x in self.layers]
         else:
-            port = Port()
-            self.kind = "port"
+            port = binding.Port()
             cases = [(synth.conv_case(900 + i, 1, r["c"], r["h"], r["w"], r["n"], r["size"]), r) for i, r in enumerate(self.rows)]
             self._one = lambda: [port.conv_forward(x, wt, b, r["stride"], r["pad"], r["leaky"]) for (x, wt, b), r in cases]
         self._one()  # warm-up (page-in, OpenMP pool)
+
+    def set_threads(self, n: int) -> None:
+        self.cores = n
+        if self.ref is not None:
+            self.ref.set_num_threads(n)
+        self._one()
 
     def run(self, images: int) -> float:
         """Seconds for `images` single-image forwards of all xnor layers."""
@@ -112,22 +147,28 @@ class CpuReference:
         return max(1, int(seconds / t))
 
     def describe(self, images: int, seconds: float) -> str:
-        return (f"{images} images x {len(self.rows)} xnor layers of yolov3-tiny_xnor@416 (float layers excluded), "
-                f"{seconds:.1f} s, {self.cores} threads")
+        return (f"{images} images x {len(self.rows)} xnor layers of {self.workload}@{self.size} (float layers excluded), "
+                f"{seconds:.1f} s, {self.cores} threads, {self.build}")
 
 
-def time_cpu_reference(budget_s: float):
-    cpu = CpuReference()
-    n = cpu.images_for(budget_s)
+def time_cpu_reference(workload: str, budget_s: float):
+    cpu = CpuReference(workload)
+    n = cpu.images_for(budget_s * 0.7)
     el = cpu.run(n)
-    return n / el, cpu.kind, cpu.cores, cpu.describe(n, el)
+    all_cores = {"value": n / el, "unit": "images/s", "cores": cpu.cores, "kind": cpu.kind, "sample": cpu.describe(n, el)}
+    if cpu.ref is not None:
+        cpu.set_threads(1)
+        n1 = cpu.images_for(budget_s * 0.3)
+        el1 = cpu.run(n1)
+        all_cores["one_thread"] = {"value": n1 / el1, "unit": "images/s", "cores": 1, "sample": cpu.describe(n1, el1)}
+    return all_cores
 
 
 def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cpu = CpuReference()
+    cpu = CpuReference(args.workload)
     per_step = max(0.2, min(2.0, 150.0 / max(args.steps + args.warmup, 1)))
     n = cpu.images_for(per_step)        # images per step: a bounded sample of the workload
     for _ in range(args.warmup):
@@ -137,12 +178,19 @@ def run_reference_arm(args) -> None:
         cpu.run(n)
     el = time.perf_counter() - t0
     value = n * args.steps / el
+    default = (args.workload == "yolov3-tiny_xnor")
+    if args.global_batch:
+        batch_text = f"global batch {args.global_batch} cut over {args.gpus} GPU(s)"
+    else:
+        batch_text = f"batch {args.batch} per GPU"
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * el / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "scope": "xnor conv layers only (the path), reference CPU code on host cores",
-                   "images_per_step": n},
+        "impl": "reference", "metric": METRIC if default else f"images/s {args.workload}@{cpu.size}", "value": value, "unit": "images/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * el / args.steps,
+        "higher_is_better": True, "scaling": "strong" if args.global_batch else "weak", "vs_baseline": None, "dtype": "u32",
+        "data": "synthetic",
+        "config": {"workload": workload_text(args.workload, cpu.size, batch_text)},
+        "reference_scope": {"layers": "xnor conv layers only (the path), reference CPU code on host cores, one image at a time as the reference runs it",
+                            "images_per_step": n},
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": cpu.cores, "kind": cpu.kind,
                          "sample": cpu.describe(n * args.steps, el)},
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -193,12 +241,28 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def captured_traffic(key: str):
+    """DRAM bytes (read + write) of one launch as an ncu capture recorded them.  profiles/dram_traffic.json, written when
+    a capture is summarised, holds per entry the kernel, its shape, the bytes and the date.  (None, None) when absent."""
+    try:
+        table = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))
+        e = table[key]
+        return float(e["bytes_per_launch"]), f"ncu capture of {e['kernel']} ({e['shape']}), {e['captured']}"
+    except (OSError, ValueError, KeyError):
+        return None, None
+
+
+def device_status(capi) -> int:
+    st = C.c_int(-1)
+    capi.check(capi.lib().xnor_b200_take_device_status(C.byref(st)), "xnor_b200_take_device_status")
+    return st.value
+
+
 def run_gpu_arm(args) -> None:
     import torch
     import torch.distributed as dist
     import synth
     from darknet_b200 import capi, cfgs, network, replicas
-    from darknet_b200 import layer as L
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -211,9 +275,16 @@ def run_gpu_arm(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     capi.lib()  # fail loudly if the CUDA library is missing
 
-    batch = args.batch
+    if args.global_batch:
+        first_image, batch = replicas.shard_batch(args.global_batch, world)[rank]
+        if batch == 0:
+            raise SystemExit("bench: --global-batch must give every rank at least one image")
+        images_per_forward = args.global_batch
+    else:
+        first_image, batch = rank * args.batch, args.batch
+        images_per_forward = world * batch
     with tempfile.TemporaryDirectory() as td:
-        cfg_path, w_path = os.path.join(td, "yolov3-tiny_xnor.cfg"), os.path.join(td, "synthetic.weights")
+        cfg_path, w_path = os.path.join(td, "net.cfg"), os.path.join(td, "synthetic.weights")
         with open(cfg_path, "w") as fh:
             fh.write(cfgs.CFGS[args.workload]())
         net0 = network.parse_network_cfg(cfg_path, batch, "cpu")
@@ -223,10 +294,10 @@ def run_gpu_arm(args) -> None:
     binops_per_image = sum(r["binops"] for r in rows)
 
     default_workload = (args.workload == "yolov3-tiny_xnor")
-    workload_text = WORKLOAD if default_workload and batch == 1 else \
-        f"{args.workload} forward, {net.h}x{net.w}x3 fp32 input U[0,1), batch {batch} per GPU, seeded random weights"
+    batch_text = f"global batch {args.global_batch} cut over {world} GPU(s)" if args.global_batch else f"batch {batch} per GPU"
     metric_text = METRIC if default_workload else f"images/s {args.workload}@{net.h}"
-    x_host = torch.from_numpy(synth.uniform01(1 + rank, (batch, 3, net.h, net.w))).pin_memory()
+    # image i of the global batch is the same tensor whatever the number of ranks
+    x_host = torch.from_numpy(np.concatenate([synth.uniform01(1 + first_image + i, (1, 3, net.h, net.w)) for i in range(batch)], 0)).pin_memory()
     x_dev = x_host.to(dev, non_blocking=True)
     stream = torch.cuda.Stream(dev)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
@@ -240,12 +311,12 @@ def run_gpu_arm(args) -> None:
     with torch.cuda.graph(graph, stream=stream):
         heads = network.forward_network_gpu(net, x_dev)
     head_host = [torch.empty(h.shape, dtype=h.dtype).pin_memory() for h in heads]
-    # the end-to-end step as one graph: input copy from pinned memory, forward, every head copied to pinned memory on
+    # the end-to-end forward as one graph: input copy from pinned memory, forward, every head copied to pinned memory on
     # the stream that produced it
     graph_e2e = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph_e2e, stream=stream):
         x_dev.copy_(x_host, non_blocking=True)
-        heads_e2e = network.forward_network_gpu(net, x_dev, head_host)
+        network.forward_network_gpu(net, x_dev, head_host)
     h2d_bytes = x_host.numel() * 4
     d2h_bytes = sum(h.numel() * 4 for h in heads)
 
@@ -255,185 +326,128 @@ def run_gpu_arm(args) -> None:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    def timed_steps(n_steps: int, end_to_end: bool) -> float:
-        """Returns total milliseconds of n_steps forwards (sum of per-step CUDA-event intervals; the L2 flush
-        between steps sits outside the intervals)."""
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_steps)]
-        with torch.cuda.stream(stream):
-            for a, b in evs:
-                flush.fill_(1)
-                a.record(stream)
-                if end_to_end:
-                    graph_e2e.replay()
-                else:
-                    graph.replay()
-                b.record(stream)
-        stream.synchronize()
-        return float(sum(a.elapsed_time(b) for a, b in evs))
+    def timed_forwards(n: int, end_to_end: bool) -> float:
+        """Total milliseconds of n forwards (sum of per-forward CUDA-event intervals; the L2 flush between forwards sits
+        outside the intervals)."""
+        total = 0.0
+        while n > 0:
+            chunk = min(n, 512)
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(chunk)]
+            with torch.cuda.stream(stream):
+                for a, b in evs:
+                    flush.fill_(1)
+                    a.record(stream)
+                    (graph_e2e if end_to_end else graph).replay()
+                    b.record(stream)
+            stream.synchronize()
+            total += float(sum(a.elapsed_time(b) for a, b in evs))
+            n -= chunk
+        return total
 
-    def max_over_ranks(ms: float) -> float:
-        return replicas.max_over_ranks(ms, dev)
-
+    fps = args.forwards_per_step
+    if fps <= 0:
+        probe_ms = replicas.max_over_ranks(timed_forwards(5, False) / 5.0, dev)
+        fps = max(1, int(round(TARGET_STEP_MS / max(probe_ms, 1e-3))))
     sampler = ClockSampler(local) if rank == 0 else None
-    timed_steps(args.warmup, False)
+    timed_forwards(args.warmup * fps, False)
     barrier()
-    ms_total = timed_steps(args.steps, False)
+    ms_total = timed_forwards(args.steps * fps, False)
     barrier()
-    ms_total = max_over_ranks(ms_total)
-    timed_steps(max(3, args.warmup // 4), True)
+    ms_total = replicas.max_over_ranks(ms_total, dev)
+    timed_forwards(max(3, args.warmup) * fps, True)
     barrier()
-    ms_e2e = timed_steps(args.steps, True)
+    ms_e2e = timed_forwards(args.steps * fps, True)
     barrier()
-    ms_e2e = max_over_ranks(ms_e2e)
-    for hh, hd in zip(head_host, heads):               # what the end-to-end steps left in pinned host memory = the device-resident forward
+    ms_e2e = replicas.max_over_ranks(ms_e2e, dev)
+    for hh, hd in zip(head_host, heads):               # what the end-to-end forwards left in pinned host memory = the device-resident forward
         if not torch.equal(hh, hd.cpu()):
             raise SystemExit("bench: host copy of a head differs from the device tensor")
     clocks = sampler.stop() if sampler else None
 
-    value = world * batch * args.steps / (ms_total * 1e-3)
-    e2e_value = world * batch * args.steps / (ms_e2e * 1e-3)
+    # The same end-to-end forward as a blocking predict call (Darknet's network_predict_gpu pushes the input, runs the
+    # layers and synchronises the stream once per call, src-lib/network_kernels.cu:748-761), timed with the host clock.
+    n_block = max(20, min(args.steps * fps, 400))
 
-    # ---- roofline of the dominant kernel (XNOR GEMM), rank 0 only ----
-    roofline = pack_roofline = large_roofline = large_pack_roofline = cpu_baseline = None
-    if rank == 0 and default_workload:
-        lib = capi.lib()
-        xl_layers = [l.xnor_layer for l in net.layers if l.type == "convolutional" and l.xnor]
-        inputs = [torch.from_numpy(synth.bell(50 + i, (batch, xl.c, xl.h, xl.w))).to(dev) for i, xl in enumerate(xl_layers)]
-        packed = [L.pack_input(xl, xi) for xl, xi in zip(xl_layers, inputs)]
-        torch.cuda.synchronize(dev)
-        reps = 50
+    def blocking_calls(n: int) -> float:
+        with torch.cuda.stream(stream):
+            t0 = time.perf_counter()
+            for _ in range(n):
+                graph_e2e.replay()
+                stream.synchronize()
+            return time.perf_counter() - t0
 
-        def time_launches(fn) -> float:
-            """Average ms of one pass over all xnor layers: the launches are captured into a CUDA graph (so host
-            launch overhead is not what gets timed) and replayed with the L2 flushed before each pass."""
+    blocking_calls(5)
+    barrier()
+    wall_block = replicas.max_over_ranks(blocking_calls(n_block), dev)
+    # Double-buffered variant: a second input buffer and copy stream; the copy of input i+1 runs under forward i.  The
+    # forward graph reads x_dev, so the staged input is moved into it device-to-device at the start of each forward.
+    copy_stream = torch.cuda.Stream(dev)
+    x_stage = torch.empty_like(x_dev)
+
+    def double_buffered(n: int) -> float:
+        staged, consumed = torch.cuda.Event(), torch.cuda.Event()
+        with torch.cuda.stream(copy_stream):
+            x_stage.copy_(x_host, non_blocking=True)
+            staged.record(copy_stream)
+        t0 = time.perf_counter()
+        for i in range(n):
             with torch.cuda.stream(stream):
-                fn()
+                stream.wait_event(staged)
+                x_dev.copy_(x_stage, non_blocking=True)
+                consumed.record(stream)
+                graph.replay()
+                for hh, hd in zip(head_host, heads):
+                    hh.copy_(hd, non_blocking=True)
+            if i + 1 < n:
+                with torch.cuda.stream(copy_stream):
+                    copy_stream.wait_event(consumed)
+                    x_stage.copy_(x_host, non_blocking=True)
+                    staged.record(copy_stream)
             stream.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                fn()
-            evs = []
-            with torch.cuda.stream(stream):
-                for _ in range(5):
-                    g.replay()
-                for _ in range(reps):
-                    flush.fill_(1)
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record(stream)
-                    g.replay()
-                    b.record(stream)
-                    evs.append((a, b))
-            stream.synchronize()
-            return sum(a.elapsed_time(b) for a, b in evs) / reps
+        return time.perf_counter() - t0
 
-        def all_gemms():
-            for xl, pk in zip(xl_layers, packed):
-                g = xl.geom
-                capi.check(lib.xnor_b200_gemm_bin_mean_transposed(
-                    xl.n, batch * g.n_out, g.k, xl.align_bit_weights_gpu.data_ptr(), g.new_lda, pk.data_ptr(), g.new_lda,
-                    xl.output_gpu.data_ptr(), batch * g.n_out, xl.mean_arr_gpu.data_ptr(), xl.biases_gpu.data_ptr(),
-                    int(xl.activation == capi.LEAKY), None, None, torch.cuda.current_stream().cuda_stream), "gemm")
+    double_buffered(5)
+    barrier()
+    wall_db = replicas.max_over_ranks(double_buffered(n_block), dev)
+    status = device_status(capi)
+    if status != 0:
+        raise SystemExit(f"bench: the tensor-core GEMM reported device status {status} (a bounded wait ran out); the timings are void")
 
-        def all_packs():
-            for xl, xi, pk in zip(xl_layers, inputs, packed):
-                capi.check(lib.xnor_b200_pack_input(C.byref(xl.desc), xi.data_ptr(), pk.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+    value = images_per_forward * args.steps * fps / (ms_total * 1e-3)
+    e2e_value = images_per_forward * args.steps * fps / (ms_e2e * 1e-3)
 
-        ms_gemm = time_launches(all_gemms)
-        ms_pack = time_launches(all_packs)
-        g_, m_ = C.c_double(), C.c_double()
-        capi.check(lib.xnor_b200_measure_popc_peak(20000, C.byref(g_), C.byref(m_)), "popc peak")
-        popc_peak_tops = g_.value / 1e3
-        capi.check(lib.xnor_b200_measure_bmma_peak(2000, C.byref(g_), C.byref(m_)), "bmma peak")
-        bmma_peak_tops = g_.value / 1e3
-        achieved = binops_per_image * batch / (ms_gemm * 1e-3) / 1e12
-        roofline = {
-            "kernel": "xnor_gemm_kernel (9 launches = the xnor layers of one forward, stand-alone calls with fp32 epilogue)",
-            "bound": "int_popc", "achieved": achieved, "peak": popc_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)",
-            # dram__bytes_read + dram__bytes_write summed over the 9 launches of one forward (batch 1), one ncu capture:
-            # profiles/xnor_gemm_kernels_b1_dram_traffic.md.  Algorithmic bytes = packed operands read once + fp32 outputs.
-            "frac": achieved / popc_peak_tops, "traffic": 4.36e6 if batch == 1 else None,
-            "algorithmic_bytes": sum((xl.n + batch * xl.geom.n_out) * xl.geom.new_lda // 8 + 4 * xl.n * batch * xl.geom.n_out for xl in xl_layers),
-            "peak_source": "measured in this run: register-resident XOR+POPC+ADD loop on all SMs",
-            "b1_mma_sync_peak": bmma_peak_tops, "ms_per_forward": ms_gemm,
-        }
-        pack_bytes = sum(batch * (4 * xl.c * xl.h * xl.w + xl.geom.n_out * xl.geom.new_lda // 8) for xl in xl_layers)
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except (OSError, ValueError):
-            pass
-        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-        pack_gbs = pack_bytes / (ms_pack * 1e-3) / 1e9
-        pack_roofline = {
-            "kernel": "pack_input_*_kernel (9 launches: every xnor layer's stand-alone xnor_b200_pack_input; the linked forward replaces most of them by sign sinks)", "bound": "hbm", "achieved": pack_gbs, "peak": hbm_peak, "unit": "GB/s",
-            "frac": pack_gbs / hbm_peak, "traffic": None, "ms_per_forward": ms_pack,
-            "peak_source": "MEASURED_PEAKS.json (of measured)" if peaks else "fallback 6650 GB/s (of fallback)",
-        }
-        # The same GEMM entry point on a batch-64 layer (BASELINE config 1 shape: 256 -> 512 filters, 26x26, 3x3), where the
-        # library switches to the tcgen05 kernel: reported beside the headline because batch-1 launches are latency-bound.
-        capi.check(lib.xnor_b200_measure_umma_i8_peak(4000, C.byref(g_), C.byref(m_)), "umma peak")
-        umma_peak_tops = g_.value / 1e3
-        M_, N_, K_ = 512, 64 * 676, 2304
-        lda_ = K_ + (256 - K_ % 256)
-        A_ = torch.randint(0, 256, (M_, lda_ // 8), dtype=torch.uint8, device=dev)
-        B_ = torch.randint(0, 256, (N_, lda_ // 8), dtype=torch.uint8, device=dev)
-        A_[:, K_ // 8:] = 0
-        B_[:, K_ // 8:] = 0
-        C_ = torch.empty(M_, N_, device=dev)
-        mean_ = torch.rand(M_, device=dev)
-        bias_ = torch.rand(M_, device=dev)
-
-        def big_gemm():
-            capi.check(lib.xnor_b200_gemm_bin_mean_transposed(M_, N_, K_, A_.data_ptr(), lda_, B_.data_ptr(), lda_, C_.data_ptr(), N_,
-                                                              mean_.data_ptr(), bias_.data_ptr(), 1, None, None,
-                                                              torch.cuda.current_stream().cuda_stream), "gemm")
-        ms_big = time_launches(big_gemm)
-        big_tops = 2.0 * M_ * N_ * K_ / (ms_big * 1e-3) / 1e12
-        large_roofline = {
-            "kernel": "xnor_gemm_tc_kernel<256> (tcgen05 kind::i8), M=512 N=64x676 K=2304", "bound": "tensor", "achieved": big_tops,
-            "peak": umma_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": big_tops / umma_peak_tops,
-            # dram read + write of one launch of this shape, ncu capture summarised in profiles/xnor_gemm_tc_kernel_m512_n43264_k2304.md
-            "traffic": 44.41e6,
-            "peak_source": "measured in this run: back-to-back tcgen05.mma kind::i8 128x256x32 from resident shared memory",
-            "vs_int_popc_peak": big_tops / popc_peak_tops, "ms": ms_big,
-        }
-        # The pack kernel of the same batch-64 layer (256 channels, 26x26, 3x3): HBM-bound, reported beside the batch-1 figure.
-        from darknet_b200 import layer as L2
-        lp = L2.make_convolutional_layer(64, 26, 26, 256, 512, 3, 1, 1, capi.LEAKY, device=str(dev))
-        xp = torch.from_numpy(synth.bell(77, (64, 256, 26, 26))).to(dev)
-        outp = torch.empty(64 * lp.geom.n_out, lp.new_lda // 8, dtype=torch.uint8, device=dev)
-
-        def big_pack():
-            capi.check(lib.xnor_b200_pack_input(C.byref(lp.desc), xp.data_ptr(), outp.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
-        ms_bp = time_launches(big_pack)
-        bp_bytes = 64 * (4 * 256 * 26 * 26 + lp.geom.n_out * lp.new_lda // 8)
-        large_pack_roofline = {
-            "kernel": "pack_input_words_kernel<2,1,0>, batch 64, C=256, 26x26, 3x3", "bound": "hbm", "achieved": bp_bytes / (ms_bp * 1e-3) / 1e9,
-            "peak": hbm_peak, "unit": "GB/s", "frac": bp_bytes / (ms_bp * 1e-3) / 1e9 / hbm_peak,
-            # dram read + write of one launch, ncu capture summarised in profiles/pack_input_words_kernel_b64_c256_26x26.md
-            "traffic": 44.41e6, "ms": ms_bp,
-            "peak_source": pack_roofline["peak_source"],
-        }
+    # ---- rooflines of single kernels, rank 0 only ----
+    extra = {}
+    cpu_baseline = None
+    roofline = None
+    if rank == 0 and default_workload and not args.global_batch:
+        extra, roofline = kernel_rooflines(net, batch, binops_per_image, stream, flush, dev)
         if world == 1:
-            ips, kind, cores, sample = time_cpu_reference(args.cpu_baseline_seconds)
-            cpu_baseline = {"value": ips, "unit": "images/s", "cores": cores, "kind": kind, "sample": sample}
+            cpu_baseline = time_cpu_reference(args.workload, args.cpu_baseline_seconds)
 
     if rank == 0:
         line = {
             "metric": metric_text, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "u32", "data": "synthetic",
-            "config": {"workload": workload_text, "global_batch": world * batch, "folded_maxpools": net.folded_maxpools, "sign_sinks": net.sink_links, "sign_links": net.sign_links,
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong" if args.global_batch else "weak",
+            "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+            "config": {"workload": workload_text(args.workload, net.h, batch_text), "global_batch": images_per_forward,
+                       "forwards_per_step": fps, "images_per_step": images_per_forward * fps,
+                       "folded_maxpools": net.folded_maxpools, "sign_sinks": net.sink_links, "sign_links": net.sign_links,
                        "side_branch": any(l.branch_start for l in net.layers), "parallelism": f"replicas x{world} (no collective)",
-                       "l2": "256 MiB buffer written between timed steps", "timing": "per-step CUDA events on the launch stream, CUDA graph replay",
+                       "l2": "256 MiB buffer written between timed forwards", "timing": "per-forward CUDA events on the launch stream, CUDA graph replay",
                        "float_layers": "this library's fp32 kernels at small batch (first conv + pool + sign, small-map convs with the yolo activation), cuDNN/ATen otherwise",
                        "xnor_binops_per_image": binops_per_image},
             "xnor_gemm_tops": roofline["achieved"] if roofline else None,
-            "roofline": roofline, "roofline_pack": pack_roofline, "roofline_large_batch": large_roofline, "roofline_pack_large_batch": large_pack_roofline,
+            "roofline": roofline, **extra,
             "cpu_baseline": cpu_baseline,
-            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
-                    "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": args.steps * network.own_launches_per_forward(net),
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d_bytes * fps, "d2h_bytes_per_step": d2h_bytes * fps,
+                    "ms_per_step": ms_e2e / args.steps,
+                    "blocking_call": {"value": images_per_forward * n_block / wall_block, "unit": "images/s", "ms_per_call": 1000.0 * wall_block / n_block,
+                                      "timing": "host clock around copy-in + forward + copy-out + stream synchronise per call", "calls": n_block},
+                    "double_buffered": {"value": images_per_forward * n_block / wall_db, "unit": "images/s", "ms_per_call": 1000.0 * wall_db / n_block,
+                                        "timing": "host clock; the next input's host-to-device copy overlaps the current forward", "calls": n_block}},
+            "gpu_launches": args.steps * fps * network.own_launches_per_forward(net),
+            "device_status": status,
             "clocks": clocks,
         }
         print(json.dumps(line))
@@ -441,9 +455,246 @@ def run_gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
+def kernel_rooflines(net, batch, binops_per_image, stream, flush, dev):
+    """Single kernels timed alone (CUDA graph of the launches, L2 flushed before each pass) against measured peaks."""
+    import torch
+    import synth
+    from darknet_b200 import capi
+    from darknet_b200 import layer as L
+    lib = capi.lib()
+    xl_layers = [l.xnor_layer for l in net.layers if l.type == "convolutional" and l.xnor]
+    inputs = [torch.from_numpy(synth.bell(50 + i, (batch, xl.c, xl.h, xl.w))).to(dev) for i, xl in enumerate(xl_layers)]
+    packed = [L.pack_input(xl, xi) for xl, xi in zip(xl_layers, inputs)]
+    torch.cuda.synchronize(dev)
+    reps = 50
+
+    def time_launches(fn) -> float:
+        """Average ms of one pass: the launches are captured into a CUDA graph (so host launch overhead is not what gets
+        timed) and replayed with the L2 flushed before each pass."""
+        with torch.cuda.stream(stream):
+            fn()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        evs = []
+        with torch.cuda.stream(stream):
+            for _ in range(5):
+                g.replay()
+            for _ in range(reps):
+                flush.fill_(1)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                g.replay()
+                b.record(stream)
+                evs.append((a, b))
+        stream.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / reps
+
+    def all_gemms():
+        for xl, pk in zip(xl_layers, packed):
+            g = xl.geom
+            capi.check(lib.xnor_b200_gemm_bin_mean_transposed(
+                xl.n, batch * g.n_out, g.k, xl.align_bit_weights_gpu.data_ptr(), g.new_lda, pk.data_ptr(), g.new_lda,
+                xl.output_gpu.data_ptr(), batch * g.n_out, xl.mean_arr_gpu.data_ptr(), xl.biases_gpu.data_ptr(),
+                int(xl.activation == capi.LEAKY), None, None, torch.cuda.current_stream().cuda_stream), "gemm")
+
+    def all_packs():
+        for xl, xi, pk in zip(xl_layers, inputs, packed):
+            capi.check(lib.xnor_b200_pack_input(C.byref(xl.desc), xi.data_ptr(), pk.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+
+    ms_gemm = time_launches(all_gemms)
+    ms_pack = time_launches(all_packs)
+    g_, m_ = C.c_double(), C.c_double()
+    capi.check(lib.xnor_b200_measure_popc_peak(20000, C.byref(g_), C.byref(m_)), "popc peak")
+    popc_peak_tops = g_.value / 1e3
+    capi.check(lib.xnor_b200_measure_bmma_peak(2000, C.byref(g_), C.byref(m_)), "bmma peak")
+    bmma_peak_tops = g_.value / 1e3
+    capi.check(lib.xnor_b200_measure_umma_i8_peak(4000, C.byref(g_), C.byref(m_)), "umma peak")
+    umma_peak_tops = g_.value / 1e3
+    achieved = binops_per_image * batch / (ms_gemm * 1e-3) / 1e12
+    traffic, traffic_source = captured_traffic("xnor_gemm_b1_yolov3_tiny_set") if batch == 1 else (None, None)
+    roofline = {
+        "kernel": "xnor GEMM kernels of one forward (9 launches = the xnor layers of yolov3-tiny_xnor, stand-alone calls with fp32 epilogue)",
+        "bound": "int_popc", "achieved": achieved, "peak": popc_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)",
+        "frac": achieved / popc_peak_tops, "traffic": traffic, "traffic_source": traffic_source,
+        "algorithmic_bytes": sum((xl.n + batch * xl.geom.n_out) * xl.geom.new_lda // 8 + 4 * xl.n * batch * xl.geom.n_out for xl in xl_layers),
+        "peak_source": "measured in this run: register-resident XOR+POPC+ADD loop on all SMs",
+        "b1_mma_sync_peak": bmma_peak_tops, "ms_per_forward": ms_gemm,
+    }
+    pack_bytes = sum(batch * (4 * xl.c * xl.h * xl.w + xl.geom.n_out * xl.geom.new_lda // 8) for xl in xl_layers)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    hbm_source = "MEASURED_PEAKS.json (of measured)" if peaks else "fallback 6650 GB/s (of fallback)"
+    pack_gbs = pack_bytes / (ms_pack * 1e-3) / 1e9
+    out = {"roofline_pack": {
+        "kernel": "pack_input_*_kernel (9 launches: every xnor layer's stand-alone xnor_b200_pack_input; the linked forward replaces most of them by sign sinks)",
+        "bound": "hbm", "achieved": pack_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": pack_gbs / hbm_peak, "traffic": None,
+        "ms_per_forward": ms_pack, "peak_source": hbm_source}}
+
+    # BASELINE configuration 1 (256 -> 512 filters, 26x26, 3x3) at batch 64, one GEMM call, each route pinned in turn
+    # through xnor_b200_set_tuning: the tcgen05 kernel against the kind::i8 rate, the integer kernels against the popc rate.
+    M_, N_, K_ = 512, 64 * 676, 2304
+    lda_ = K_ + (256 - K_ % 256)
+    A_ = torch.randint(0, 256, (M_, lda_ // 8), dtype=torch.uint8, device=dev)
+    B_ = torch.randint(0, 256, (N_, lda_ // 8), dtype=torch.uint8, device=dev)
+    A_[:, K_ // 8:] = 0
+    B_[:, K_ // 8:] = 0
+    C_ = torch.empty(M_, N_, device=dev)
+    mean_ = torch.rand(M_, device=dev)
+    bias_ = torch.rand(M_, device=dev)
+
+    def big_gemm():
+        capi.check(lib.xnor_b200_gemm_bin_mean_transposed(M_, N_, K_, A_.data_ptr(), lda_, B_.data_ptr(), lda_, C_.data_ptr(), N_,
+                                                          mean_.data_ptr(), bias_.data_ptr(), 1, None, None,
+                                                          torch.cuda.current_stream().cuda_stream), "gemm")
+    ops_big = 2.0 * M_ * N_ * K_
+    alg_big = (M_ + N_) * lda_ // 8 + 4 * M_ * N_
+    capi.set_tuning(gemm_route=capi.ROUTE_TENSOR)
+    ms_big = time_launches(big_gemm)
+    tc_out = C_.clone()
+    capi.set_tuning(gemm_route=capi.ROUTE_INTEGER)
+    ms_int = time_launches(big_gemm)
+    same = bool(torch.equal(tc_out, C_))
+    capi.set_tuning()
+    big_tops, int_tops = ops_big / (ms_big * 1e-3) / 1e12, ops_big / (ms_int * 1e-3) / 1e12
+    traffic, traffic_source = captured_traffic("xnor_gemm_tc_m512_n43264_k2304")
+    out["roofline_large_batch"] = {
+        "kernel": "tcgen05 kind::i8 XNOR GEMM, M=512 N=64x676 K=2304", "bound": "tensor", "achieved": big_tops,
+        "peak": umma_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": big_tops / umma_peak_tops,
+        "traffic": traffic, "traffic_source": traffic_source, "algorithmic_bytes": alg_big,
+        "peak_source": "measured in this run: back-to-back tcgen05.mma kind::i8 128x256x32 from resident shared memory",
+        "vs_int_popc_peak": big_tops / popc_peak_tops, "ms": ms_big, "equals_integer_kernel": same,
+    }
+    out["roofline_int_large_batch"] = {
+        "kernel": "integer-pipe XNOR GEMM (tiled kernel, route pinned), M=512 N=64x676 K=2304", "bound": "int_popc", "achieved": int_tops,
+        "peak": popc_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": int_tops / popc_peak_tops, "traffic": None,
+        "algorithmic_bytes": alg_big, "peak_source": roofline["peak_source"], "ms": ms_int,
+    }
+    # The pack kernel of the same batch-64 layer (256 channels, 26x26, 3x3): HBM-bound, reported beside the batch-1 figure.
+    lp = L.make_convolutional_layer(64, 26, 26, 256, 512, 3, 1, 1, capi.LEAKY, device=str(dev))
+    xp = torch.from_numpy(synth.bell(77, (64, 256, 26, 26))).to(dev)
+    outp = torch.empty(64 * lp.geom.n_out, lp.new_lda // 8, dtype=torch.uint8, device=dev)
+
+    def big_pack():
+        capi.check(lib.xnor_b200_pack_input(C.byref(lp.desc), xp.data_ptr(), outp.data_ptr(), torch.cuda.current_stream().cuda_stream), "pack")
+    ms_bp = time_launches(big_pack)
+    bp_bytes = 64 * (4 * 256 * 26 * 26 + lp.geom.n_out * lp.new_lda // 8)
+    traffic, traffic_source = captured_traffic("pack_input_words_b64_c256_26x26")
+    out["roofline_pack_large_batch"] = {
+        "kernel": "pack_input_words_kernel, batch 64, C=256, 26x26, 3x3", "bound": "hbm", "achieved": bp_bytes / (ms_bp * 1e-3) / 1e9,
+        "peak": hbm_peak, "unit": "GB/s", "frac": bp_bytes / (ms_bp * 1e-3) / 1e9 / hbm_peak,
+        "traffic": traffic, "traffic_source": traffic_source, "algorithmic_bytes": bp_bytes, "ms": ms_bp, "peak_source": hbm_source,
+    }
+    if device_status(capi) != 0:
+        raise SystemExit("bench: a bounded wait ran out in a roofline launch")
+    return out, roofline
+
+
+# ---- single kernels (profiler captures, quick timings) ---------------------------------------------
+
+YOLOV3_TINY_GEMMS = [(32, 43264, 144), (64, 10816, 288), (128, 2704, 576), (256, 676, 1152), (512, 169, 2304), (1024, 169, 4608),
+                     (256, 169, 1024), (128, 169, 256), (256, 676, 3456)]
+FCONV_CASES = [(1, 256, 13, 13, 512, 3, 1), (1, 512, 13, 13, 255, 1, 0), (1, 256, 26, 26, 255, 1, 0)]
+
+
+def run_kernel(args) -> None:
+    """One kernel of libxnor_b200.so on random operands, `reps` calls each between two CUDA events; prints the median
+    (not meaningful under a profiler).  Ends with a synchronize and a device-status check."""
+    import torch
+    from darknet_b200 import capi
+    from darknet_b200 import layer as L
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --kernel needs a CUDA device")
+    lib = capi.lib()
+    capi.set_tuning(gemm_route=ROUTES[args.route])
+
+    def stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    def timed(fn, reps: int) -> float:
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1000.0)
+        return sorted(ts)[len(ts) // 2]
+
+    def gemm_call(M, N, K, shortcut):
+        lda = K + (256 - K % 256)
+        A = torch.randint(0, 256, (M, lda // 8), dtype=torch.uint8, device="cuda")
+        B = torch.randint(0, 256, (N, lda // 8), dtype=torch.uint8, device="cuda")
+        A[:, K // 8:] = 0
+        B[:, K // 8:] = 0
+        out = torch.empty(M, N, device="cuda")
+        mean, bias = torch.rand(M, device="cuda"), torch.rand(M, device="cuda")
+        sc_in = torch.randn(M, N, device="cuda") if shortcut else None
+        sc_out = torch.empty(M, N, device="cuda") if shortcut else None
+        keep = (A, B, out, mean, bias, sc_in, sc_out)
+
+        def call():
+            capi.check(lib.xnor_b200_gemm_bin_mean_transposed(
+                M, N, K, A.data_ptr(), lda, B.data_ptr(), lda, out.data_ptr(), N, mean.data_ptr(), bias.data_ptr(), 1,
+                sc_in.data_ptr() if shortcut else None, sc_out.data_ptr() if shortcut else None, stream()), "xnor_b200_gemm_bin_mean_transposed")
+        return call, keep
+
+    if args.kernel == "gemm":
+        M, N, K = args.shape
+        call, _keep = gemm_call(M, N, K, args.shortcut)
+        us = timed(call, args.reps)
+        print(f"gemm M={M} N={N} K={K} route={args.route} shortcut={int(args.shortcut)}: {us:.1f} us/call, {2.0 * M * N * K / us / 1e6:.1f} T binary ops/s")
+    elif args.kernel == "gemms":
+        keep = []
+        for _ in range(2):
+            for (M, N, K) in YOLOV3_TINY_GEMMS:
+                call, k = gemm_call(M, N, K, False)
+                keep.append(k)
+                call()
+        torch.cuda.synchronize()
+        print("ok")
+    elif args.kernel == "pack":
+        batch, c, h, w, n, ks = args.shape
+        l = L.make_convolutional_layer(batch, h, w, c, n, ks, 1, ks // 2, capi.LINEAR)
+        x = torch.randn(batch, c, h, w, device="cuda")
+        out = torch.empty(batch * l.geom.n_out, l.new_lda // 8, dtype=torch.uint8, device="cuda")
+
+        def call():
+            capi.check(lib.xnor_b200_pack_input(C.byref(l.desc), x.data_ptr(), out.data_ptr(), stream()), "xnor_b200_pack_input")
+        us = timed(call, args.reps)
+        moved = x.numel() * 4 + out.numel()
+        print(f"pack b={batch} c={c} {h}x{w} ks={ks}: {us:.1f} us/call, {moved / us / 1e3:.0f} GB/s")
+    else:
+        b, c, h, w, n, ks, leaky = FCONV_CASES[args.shape[0]]
+        x = torch.randn(b, c, h, w, device="cuda")
+        wt = torch.randn(n, c, ks, ks, device="cuda") * 0.05
+        bias = torch.randn(n, device="cuda")
+        d = capi.ConvDesc(b, c, h, w, n, ks, 1, ks // 2, capi.LEAKY if leaky else capi.LINEAR)
+        blocked = torch.empty(lib.xnor_b200_float_conv_map_weights_bytes(C.byref(d)) // 4, device="cuda")
+        out = torch.empty(b, n, h, w, device="cuda")
+        capi.check(lib.xnor_b200_float_conv_map_prepare(C.byref(d), wt.data_ptr(), blocked.data_ptr(), stream()), "xnor_b200_float_conv_map_prepare")
+
+        def call():
+            capi.check(lib.xnor_b200_float_conv_map(C.byref(d), x.data_ptr(), blocked.data_ptr(), bias.data_ptr(), out.data_ptr(), stream()),
+                       "xnor_b200_float_conv_map")
+        us = timed(call, args.reps)
+        print(f"fconv {FCONV_CASES[args.shape[0]]}: {us:.1f} us/call")
+    st = device_status(capi)
+    if st != 0:
+        raise SystemExit(f"device status {st}: a bounded wait ran out")
+
+
 def main() -> None:
     args = parse_args()
-    if args.impl == "reference":
+    if args.kernel is not None:
+        run_kernel(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

@@ -19,7 +19,7 @@ STATIC_SCRATCH_BYTES = 8 << 20  # XNOR_B200_STATIC_SCRATCH_BYTES
 
 # Every symbol include/xnor_b200.h declares; tests check that the library exports each one.
 EXPORTS = (
-    "xnor_b200_strerror", "xnor_b200_last_cuda_error", "xnor_b200_conv_geometry",
+    "xnor_b200_strerror", "xnor_b200_last_cuda_error", "xnor_b200_set_tuning", "xnor_b200_conv_geometry",
     "xnor_b200_binarize_weights", "xnor_b200_binary_align_weights", "xnor_b200_float_to_bit",
     "xnor_b200_repack_input_bin", "xnor_b200_pack_input", "xnor_b200_gemm_bin_mean_transposed",
     "xnor_b200_gemm_counts", "xnor_b200_scratch_bytes", "xnor_b200_conv_forward",
@@ -55,6 +55,14 @@ class ConvIO(C.Structure):
                 ("shortcut_sink", C.POINTER(SignSink))]
 
 
+ROUTE_AUTO, ROUTE_INTEGER, ROUTE_TENSOR, ROUTE_TILED = 0, 1, 2, 3
+
+
+class Tuning(C.Structure):
+    """struct xnor_b200_tuning"""
+    _fields_ = [(n, C.c_int) for n in ("gemm_route", "gemm_tile", "gemm_split", "pack_ctas_per_sm", "tc_wait_polls", "tc_withhold_arrival")]
+
+
 class ConvGeom(C.Structure):
     """struct xnor_b200_conv_geom"""
     _fields_ = [(n, C.c_int) for n in ("out_h", "out_w", "n_out", "k", "new_lda", "bit_align", "word_path")] + \
@@ -88,6 +96,7 @@ def lib() -> C.CDLL:
     L.xnor_b200_strerror.restype = C.c_char_p
     L.xnor_b200_strerror.argtypes = [ci]
     L.xnor_b200_last_cuda_error.restype = ci
+    L.xnor_b200_set_tuning.argtypes = [C.POINTER(Tuning)]
     L.xnor_b200_conv_geometry.argtypes = [dp, gp]
     L.xnor_b200_binarize_weights.argtypes = [vp, ci, ci, vp, vp, vp]
     L.xnor_b200_binary_align_weights.argtypes = [dp, vp, vp, vp, ci, vp]
@@ -126,6 +135,17 @@ def lib() -> C.CDLL:
 def check(code: int, where: str) -> None:
     if code != OK:
         raise XnorError(code, where)
+
+
+def set_tuning(**fields) -> None:
+    """xnor_b200_set_tuning: pins kernel choices process-wide (tests and benchmarks); no arguments = library defaults."""
+    if not fields:
+        check(lib().xnor_b200_set_tuning(None), "xnor_b200_set_tuning")
+        return
+    t = Tuning()
+    for k, v in fields.items():
+        setattr(t, k, v)
+    check(lib().xnor_b200_set_tuning(C.byref(t)), "xnor_b200_set_tuning")
 
 
 def geometry(desc: ConvDesc) -> ConvGeom:

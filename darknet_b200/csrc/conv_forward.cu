@@ -13,6 +13,10 @@ namespace xnor
 
 thread_local int g_last_cuda_error = 0;
 
+static xnor_b200_tuning g_tuning = {};
+
+const xnor_b200_tuning & tuning() { return g_tuning; }
+
 int sm_count()
 {
 	static int cached[64] = {0};
@@ -87,6 +91,20 @@ extern "C" const char * xnor_b200_strerror(int code)
 }
 
 extern "C" int xnor_b200_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int xnor_b200_set_tuning(const xnor_b200_tuning * t)
+{
+	if (t == nullptr)
+	{
+		g_tuning = xnor_b200_tuning();
+		return XNOR_B200_OK;
+	}
+	if (t->gemm_route < XNOR_B200_ROUTE_AUTO || t->gemm_route > XNOR_B200_ROUTE_TILED) { return XNOR_B200_ERR_INVALID; }
+	if (t->gemm_tile < 0 || t->gemm_split < 0 || t->gemm_split > 8 || t->pack_ctas_per_sm < 0 || t->pack_ctas_per_sm > 32) { return XNOR_B200_ERR_INVALID; }
+	if (t->tc_wait_polls < 0 || t->tc_withhold_arrival < 0 || t->tc_withhold_arrival > 1) { return XNOR_B200_ERR_INVALID; }
+	g_tuning = *t;
+	return XNOR_B200_OK;
+}
 
 extern "C" int xnor_b200_take_device_status(int * status)
 {

@@ -21,8 +21,6 @@
 // N*new_ldb/8 bytes written.
 #include "xnor_common.cuh"
 
-#include <cstdlib>
-
 namespace xnor
 {
 
@@ -619,9 +617,8 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc *
 	const bool word_path = (d.c % 32 == 0);
 	if (d.size > 63) { return XNOR_B200_ERR_TOO_LARGE; }             // kernel offsets are kept in 6-bit fields
 	// CTAs to aim for.  Each CTA loads, synchronises, then stores, so overlap of loads and stores comes from
-	// several CTAs sharing an SM.  XNOR_B200_PACK_CTAS_PER_SM overrides the factor (tuning aid).
-	int ctas_per_sm = 4;
-	if (const char * e = std::getenv("XNOR_B200_PACK_CTAS_PER_SM")) { ctas_per_sm = max(1, atoi(e)); }
+	// several CTAs sharing an SM.  xnor_b200_set_tuning may override the factor.
+	const int ctas_per_sm = (tuning().pack_ctas_per_sm > 0) ? tuning().pack_ctas_per_sm : 4;
 	const int want_ctas = ctas_per_sm * sm_count();
 	auto in_rows = [&](int out_rows) { return (out_rows - 1) * d.stride + d.size; };
 

@@ -36,6 +36,9 @@ inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 int validate_desc(const xnor_b200_conv_desc * d);
 
+// Process-wide overrides set through xnor_b200_set_tuning (all zero: every choice is the library's own).
+const xnor_b200_tuning & tuning();
+
 // Raises a kernel's dynamic shared-memory limit once per (device, kernel); later calls are a table lookup,
 // so launchers stay free of runtime attribute calls once warmed up (e.g. while a stream is being captured).
 int ensure_dynamic_smem(const void * kernel, size_t bytes);

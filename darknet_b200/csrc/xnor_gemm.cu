@@ -27,8 +27,6 @@
 #include "xnor_common.cuh"
 
 #include <cooperative_groups.h>
-#include <cstdio>
-#include <cstdlib>
 
 namespace cg = cooperative_groups;
 
@@ -710,7 +708,7 @@ static int launch_oneshot(const GemmParams & p, cudaStream_t stream)
 static int oneshot_problem(int M, int n_total, int kw, bool fp32_only)
 {
 	(void)fp32_only;
-	if (kw <= 8 || kw > OS_WARPS * 32 || std::getenv("XNOR_B200_GEMM_FORCE") != nullptr || std::getenv("XNOR_B200_GEMM_TC") != nullptr) { return 0; }
+	if (kw <= 8 || kw > OS_WARPS * 32 || tuning().gemm_route >= XNOR_B200_ROUTE_TENSOR) { return 0; }
 	const long long ntiles = ((long long)n_total + 31) / 32;
 	if ((long long)((M + 31) / 32) * ntiles <= (long long)sm_count()) { return 32; }
 	if (M % 32 == 0 && (long long)((M + 15) / 16) * ntiles <= 3ll * sm_count() && (long long)((M + 31) / 32) * ntiles <= 2ll * sm_count()) { return 16; }
@@ -791,8 +789,7 @@ static float estimate_cycles(const TileConfig & c, int M, int n_total, int kw, i
 // over a 32-byte-per-pixel operand; that pays at every size, the plain short-K kernel only while launches dominate.
 static bool short_k_problem(int M, int n_total, int kw, bool rows_in_kernel = false)
 {
-	return kw <= 8 && (rows_in_kernel || (long long)M * n_total <= (4ll << 20)) && std::getenv("XNOR_B200_GEMM_FORCE") == nullptr
-			&& std::getenv("XNOR_B200_GEMM_TC") == nullptr;
+	return kw <= 8 && (rows_in_kernel || (long long)M * n_total <= (4ll << 20)) && tuning().gemm_route < XNOR_B200_ROUTE_TENSOR;
 }
 
 bool gemm_takes_planes(int M, int n_total, int c, int size, int stride, int pad)
@@ -835,11 +832,10 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 	p.C = C; p.ldc = ldc; p.mean_arr = mean_arr; p.bias = bias; p.leaky = leaky;
 	p.shortcut_in = shortcut_in; p.shortcut_out = shortcut_out; p.counts = counts;
 
-	// Large layers go to the tensor-core kernel.  XNOR_B200_GEMM_TC=0 keeps everything on the integer pipe,
-	// =1 sends every shape to the tensor-core kernel (tuning and test aid).
+	// Large layers go to the tensor-core kernel unless xnor_b200_set_tuning pinned the route.
 	{
-		const char * tc = std::getenv("XNOR_B200_GEMM_TC");
-		const bool use_tc = sum_signs || ((tc != nullptr) ? (tc[0] == '1') : tc_gemm_eligible(M, n_total, K));
+		const int route = tuning().gemm_route;
+		const bool use_tc = sum_signs || ((route == XNOR_B200_ROUTE_AUTO) ? tc_gemm_eligible(M, n_total, K) : (route == XNOR_B200_ROUTE_TENSOR));
 		if (use_tc && !(extra != nullptr && (extra->planes != nullptr || extra->masks != nullptr)))
 		{
 			return launch_xnor_gemm_tc(M, n_total, n_per_image, K, A, lda_words, B, ldb_words, C, ldc, mean_arr, bias, leaky,
@@ -894,15 +890,11 @@ int launch_xnor_gemm(int M, int n_total, int n_per_image, int K,
 			if (t < best) { best = t; best_cfg = c; best_split = split; }
 		}
 	}
-	// Tuning aid: XNOR_B200_GEMM_FORCE="<config index>,<split>" overrides the choice (used by the sweep scripts).
-	if (const char * force = std::getenv("XNOR_B200_GEMM_FORCE"))
+	// xnor_b200_set_tuning may pin the tile configuration and the cluster split of the tiled kernel
+	if (tuning().gemm_route == XNOR_B200_ROUTE_TILED && tuning().gemm_tile >= 1 && tuning().gemm_tile <= NUM_CONFIGS)
 	{
-		int c = -1, s = 1;
-		if (std::sscanf(force, "%d,%d", &c, &s) >= 1 && c >= 0 && c < NUM_CONFIGS && s >= 1 && s <= 8)
-		{
-			best_cfg = c;
-			best_split = s;
-		}
+		best_cfg = tuning().gemm_tile - 1;
+		best_split = (tuning().gemm_split >= 1 && tuning().gemm_split <= 8) ? tuning().gemm_split : 1;
 	}
 	p.split = best_split;
 	p.kw_slice = (int)round_up((size_t)(p.kw + best_split - 1) / best_split, 4);

@@ -194,6 +194,7 @@ def forward_convolutional_layer_io(l: ConvolutionalLayer, x: Optional[torch.Tens
         sk = capi.SignSink()
         sk.consumer = C.pointer(shortcut_sink.desc)
         sk.consumer_scratch = shortcut_sink.scratch.data_ptr()
+        sk.consumer_window_major = int(shortcut_sink.window_major)      # refused by the library: the epilogue writes row-major rows
         io.shortcut_sink = C.pointer(sk)
     if sinks:
         arr = (capi.SignSink * len(sinks))()

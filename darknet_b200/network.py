@@ -17,8 +17,6 @@ Only the section types and keys that occur in the three shipped xnor cfgs are un
 """
 from __future__ import annotations
 
-import os
-
 import math
 import struct
 from dataclasses import dataclass, field
@@ -160,8 +158,8 @@ def parse_network_cfg(path: str, batch: int = 1, device: str = "cuda:0") -> Netw
             l.out_h = (h + 2 * l.pad - l.size) // l.stride + 1
             l.out_w = (w + 2 * l.pad - l.size) // l.stride + 1
         elif name == "maxpool":
-            l.size = int(o.get("size", 2))
-            l.stride = int(o.get("stride", 1))
+            l.stride = int(o.get("stride", 1))                    # defaults as in src-lib/darknet_cfg.cpp:1597-1601
+            l.size = int(o.get("size", l.stride))
             l.pad = int(o.get("padding", l.size - 1))
             l.out_c = c
             l.out_h = (h + l.pad - l.size) // l.stride + 1       # src-lib/maxpool_layer.cpp:129-130
@@ -273,6 +271,8 @@ def calculate_binary_weights(net: Network) -> None:
         net.xnor_launches_per_forward += 2
         if j + 1 < len(net.layers):
             sc = net.layers[j + 1]
+            # Darknet's GPU build fuses whatever the [shortcut]'s activation is and thereby drops it (the blanked layer does
+            # nothing); its CPU build applies it.  Only a linear shortcut is fused here, so both semantics coincide.
             if sc.type == "shortcut" and (sc.w, sc.h, sc.c) == (sc.out_w, sc.out_h, sc.out_c) and sc.activation == "linear":
                 sc.blank = True
                 sc.output_gpu = torch.empty(net.batch, sc.out_c, sc.out_h, sc.out_w, device=dev)
@@ -283,26 +283,15 @@ def calculate_binary_weights(net: Network) -> None:
         # [shortcut] layer blanked nothing reads the former, and at large batch it is a third of the layer's memory traffic
         l.shortcut_only = (net.skip_fused_conv_outputs and l.type == "convolutional" and l.xnor and net.layers[j + 1].blank
                            and readers[j] == [j + 1])
-    if net.sign_chains and net.batch >= net.sum_signs_min_batch:
-        for j, l in enumerate(net.layers[:-2]):
-            nxt = net.layers[j + 2]
-            # conv j + fused [shortcut] j+1 -> xnor conv j+2: the consumer packs from the sum's sign words, not from the fp32 sum
-            if (l.type == "convolutional" and l.xnor and net.layers[j + 1].blank and l.n % 32 == 0
-                    and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None and nxt.c % 32 == 0):
-                if nxt.size == 1 and nxt.stride == 1 and nxt.pad == 0 and nxt.c == l.n and not nxt.xnor_layer.window_major:
-                    # a 1x1 reader: the signs go straight into its packed operand, it runs without a pack kernel
-                    l.sum_sink_to = j + 2
-                    nxt.packed_input = True
-                else:
-                    l.emit_sum_signs = True
-                    l.xnor_layer.shortcut_signs_gpu = torch.empty(net.batch, l.n // 32, l.out_h * l.out_w, dtype=torch.int32, device=dev)
-                    nxt.sign_source = j + 1
-                net.sum_sign_links += 1
     prepare_float_map_convs(net)
     link_branches(net)
     if net.sign_chains:
         link_sinks(net)
         link_sign_chains(net)
+        link_shortcut_sums(net)
+        for l in net.layers:
+            if l.emit_sum_signs:
+                l.xnor_layer.shortcut_signs_gpu = torch.empty(net.batch, l.n // 32, l.out_h * l.out_w, dtype=torch.int32, device=dev)
     if net.fuse_first_conv:
         link_first_conv(net)
     fold_maxpools(net)
@@ -411,6 +400,30 @@ def link_sinks(net: Network) -> None:
         l.need_fp32 = need
         if l.type in ("maxpool", "upsample", "route") and not need:
             l.skip = True
+
+
+def link_shortcut_sums(net: Network) -> None:
+    """conv j + fused [shortcut] j+1 -> xnor conv j+2: the consumer takes the sign of the sum instead of the fp32 sum, as
+    channel-packed words that its pack kernel reads (emit_sum_signs), or -- a 1x1 reader over exactly these filters --
+    straight into its packed operand (sum_sink_to; it then runs without a pack kernel).  Runs after link_sinks: the
+    epilogue writes that operand in row-major pixel order, so a reader that link_sinks made window-major (it feeds a
+    pooled sink of its own) takes the words instead."""
+    if net.batch < net.sum_signs_min_batch:
+        return
+    for j, l in enumerate(net.layers[:-2]):
+        nxt = net.layers[j + 2]
+        if not (l.type == "convolutional" and l.xnor and net.layers[j + 1].blank and l.n % 32 == 0
+                and nxt.type == "convolutional" and nxt.xnor and nxt.xnor_layer is not None and nxt.c % 32 == 0):
+            continue
+        if nxt.packed_input or nxt.sign_source is not None or nxt.pool_desc is not None:
+            continue
+        if nxt.size == 1 and nxt.stride == 1 and nxt.pad == 0 and nxt.c == l.n and not nxt.xnor_layer.window_major:
+            l.sum_sink_to = j + 2
+            nxt.packed_input = True
+        else:
+            l.emit_sum_signs = True
+            nxt.sign_source = j + 1
+        net.sum_sign_links += 1
 
 
 def link_sign_chains(net: Network) -> None:
@@ -744,8 +757,10 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
 
 
 def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "cuda:0", sign_chains: bool = True,
-                        fuse_first_conv: bool = True, side_branches: bool = True) -> Network:
-    """load_network_custom (src-lib/weights.cpp:665-691): parse, load, fold batch-norm, pack binary weights."""
+                        fuse_first_conv: bool = True, side_branches: bool = True, float_map_max_pixels: Optional[int] = None,
+                        sum_signs_min_batch: Optional[int] = None, sink_max_batch: Optional[int] = None) -> Network:
+    """load_network_custom (src-lib/weights.cpp:665-691): parse, load, fold batch-norm, pack binary weights.
+    The last three arguments override the measured hand-over thresholds of the Network (tuning runs)."""
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
     net = parse_network_cfg(cfg, batch, device)
@@ -753,12 +768,12 @@ def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "c
     net.skip_fused_conv_outputs = sign_chains      # the plain network keeps every layer's own tensor
     net.fuse_first_conv = fuse_first_conv
     net.side_branches = side_branches
-    if os.environ.get("XNOR_B200_FLOAT_MAP_MAX_PIXELS"):      # tuning aid
-        net.float_map_max_pixels = int(os.environ["XNOR_B200_FLOAT_MAP_MAX_PIXELS"])
-    if os.environ.get("XNOR_B200_SUM_SIGNS_MIN_BATCH"):       # tuning aid: batch from which the signs of fused shortcut sums are handed on
-        net.sum_signs_min_batch = int(os.environ["XNOR_B200_SUM_SIGNS_MIN_BATCH"])
-    if os.environ.get("XNOR_B200_SINK_MAX_BATCH"):            # tuning aid: batch up to which sign sinks are linked
-        net.sink_max_batch = int(os.environ["XNOR_B200_SINK_MAX_BATCH"])
+    if float_map_max_pixels is not None:
+        net.float_map_max_pixels = float_map_max_pixels
+    if sum_signs_min_batch is not None:
+        net.sum_signs_min_batch = sum_signs_min_batch
+    if sink_max_batch is not None:
+        net.sink_max_batch = sink_max_batch
     load_weights(net, weights)
     fuse_conv_batchnorm(net)
     calculate_binary_weights(net)

@@ -75,6 +75,25 @@ XNOR_B200_API const char * xnor_b200_strerror(int code);
 /* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
 XNOR_B200_API int xnor_b200_last_cuda_error(void);
 
+/* Kernel-selection overrides for tests, benchmarks and tuning runs (no reference counterpart: Darknet has one kernel per
+ * step).  Process-wide and read at every launch; set them while no other thread is launching.  A zeroed struct, or
+ * xnor_b200_set_tuning(NULL), restores the library's own choices.  Every route computes identical results. */
+#define XNOR_B200_ROUTE_AUTO    0  /* the library picks the GEMM kernel per call from its time estimates            */
+#define XNOR_B200_ROUTE_INTEGER 1  /* integer-pipe kernels only (tiled, one-shot, short-row), tensor-core route off */
+#define XNOR_B200_ROUTE_TENSOR  2  /* the tcgen05 kernel for every call                                            */
+#define XNOR_B200_ROUTE_TILED   3  /* the tiled integer kernel for every call                                       */
+typedef struct xnor_b200_tuning
+{
+	int gemm_route;           /* XNOR_B200_ROUTE_*                                                                     */
+	int gemm_tile;            /* ROUTE_TILED only: 1-based tile configuration to pin (0 = estimated)                   */
+	int gemm_split;           /* ROUTE_TILED only, with gemm_tile: cluster split-K factor 1..8 (0 = 1)                 */
+	int pack_ctas_per_sm;     /* CTAs per SM the pack kernels size their grid for (0 = default)                        */
+	int tc_wait_polls;        /* polls after which a barrier wait of the tcgen05 kernel gives up (0 = default limit)   */
+	int tc_withhold_arrival;  /* failure-detection test aid: 1 = one producer arrival per tile is withheld, so that a  */
+	                          /* bounded wait runs out and the kernel leaves through its give-up path                  */
+} xnor_b200_tuning;
+XNOR_B200_API int xnor_b200_set_tuning(const xnor_b200_tuning * tuning);
+
 /* Fills *geom.  Replaces the size arithmetic of make_convolutional_layer
  * (src-lib/convolutional_layer.cpp:833-853) and binary_align_weights (:1343-1351). */
 XNOR_B200_API int xnor_b200_conv_geometry(const xnor_b200_conv_desc * desc, xnor_b200_conv_geom * geom);
@@ -234,7 +253,7 @@ typedef struct xnor_b200_conv_io
 	                                         consumer_window_major of the sink must be 0 */
 } xnor_b200_conv_io;
 
-/* 1 when a layer can take input_masks: c is 8 or 16, size 3, stride 1, pad 1 (and no kernel override in the environment). */
+/* 1 when a layer can take input_masks: c is 8 or 16, size 3, stride 1, pad 1 (and no route pinned through xnor_b200_set_tuning). */
 XNOR_B200_API int xnor_b200_conv_takes_masks(const xnor_b200_conv_desc * desc);
 
 /* Re-orders packed weights of a c % 32 != 0 layer from the reference's K order (bit c*size*size + tap,

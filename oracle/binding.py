@@ -18,6 +18,22 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_SO = os.path.join(_HERE, "_build", "liboracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "liboracle_ref.so")
+REF_FAST_SO = os.path.join(_HERE, "_ref", "liboracle_ref_fast.so")      # same sources, the reference's own optimisation flags (timing only)
+
+
+def reference_dir() -> str:
+    """Where the darknet tree is mounted when it is present at all: $DARKNET_REFERENCE_DIR, else the default mount.
+    The one place this location is written down; the Makefile beside this file receives it as REF=..."""
+    return os.environ.get("DARKNET_REFERENCE_DIR", "/root/reference")
+
+
+def build_ref(target: str = "ref") -> bool:
+    """Runs `make <target>` against the mounted reference tree; False when the tree is not there."""
+    ref = reference_dir()
+    if not os.path.isdir(os.path.join(ref, "src-lib")):
+        return False
+    subprocess.check_call(["make", "-C", _HERE, target, f"REF={ref}"], stdout=subprocess.DEVNULL)
+    return True
 
 _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
@@ -138,10 +154,10 @@ class Ref:
     def available() -> bool:
         return os.path.exists(REF_SO)
 
-    def __init__(self) -> None:
-        if not self.available():
-            raise FileNotFoundError(REF_SO)
-        self.lib = C.CDLL(REF_SO)
+    def __init__(self, path: str = REF_SO) -> None:
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        self.lib = C.CDLL(path)
         L = self.lib
         L.ref_set_gpu_index.argtypes = [C.c_int]
         L.ref_set_num_threads.argtypes = [C.c_int]

@@ -5,7 +5,8 @@ The CPU side runs every xnor layer through the C restatement of the reference (o
 convolution in front of the first xnor layer is summed in a different order on the two sides, so an activation
 within rounding distance of zero may binarise differently; the test therefore (a) feeds the oracle's xnor layers
 the GPU's own float-layer outputs for the strict per-layer bit-exact check, and (b) compares the final head
-outputs of the fully independent CPU run within the 1e-3 tolerance stated for detections."""
+outputs of the CPU run within the 1e-3 tolerance stated for detections, every value, once the CPU side binarises
+the same first-layer tensor (the sign differences of that one tensor are counted and bounded separately)."""
 import numpy as np
 import pytest
 
@@ -28,7 +29,7 @@ def cpu_forward(net_cpu, x, port, xnor_inputs_from=None):
         if l.type == "convolutional":
             if l.xnor:
                 leaky = (l.activation == "leaky")
-                src = cur if xnor_inputs_from is None else xnor_inputs_from[l.index]
+                src = cur if xnor_inputs_from is None else xnor_inputs_from.get(l.index, cur)
                 y = port.conv_forward(np.ascontiguousarray(src.numpy()), l.weights, l.biases, l.stride, l.pad, leaky)
                 cur = torch.from_numpy(y)
             else:
@@ -51,18 +52,54 @@ def cpu_forward(net_cpu, x, port, xnor_inputs_from=None):
     return heads, outs
 
 
-@pytest.mark.parametrize("name,size", [("yolov3-tiny_xnor", 160), ("tiny-yolo_xnor", 128)])
-def test_network_heads_match_cpu_oracle_network(port, tmp_path, name, size):
-    cfg = tmp_path / "net.cfg"
-    cfg.write_text(cfgs.CFGS[name](size, size))
-    net_cpu = network.parse_network_cfg(str(cfg), 1, "cpu")
-    w = tmp_path / "net.weights"
-    network.write_synthetic_weights(net_cpu, str(w), seed=11)
-    network.load_weights(net_cpu, str(w))
+def device_status() -> int:
+    import ctypes as C
+    from darknet_b200 import capi
+    st = C.c_int(-1)
+    capi.check(capi.lib().xnor_b200_take_device_status(C.byref(st)), "xnor_b200_take_device_status")
+    return st.value
+
+
+def prepared_cpu_network(cfg_path, w_path, batch, seed):
+    net_cpu = network.parse_network_cfg(str(cfg_path), batch, "cpu")
+    network.write_synthetic_weights(net_cpu, str(w_path), seed=seed)
+    network.load_weights(net_cpu, str(w_path))
     network.fuse_conv_batchnorm(net_cpu)
     for l in net_cpu.layers:                                   # calculate_binary_weights' activation rule
         if l.type == "convolutional" and l.xnor and l.use_bin_output:
             l.activation = "linear"
+    return net_cpu
+
+
+def check_xnor_layers_against_oracle(net, net_cpu, x, port):
+    """Every xnor layer of a network that keeps all fp32 tensors, fed the GPU's own input: bit-exact against the oracle,
+    the fused [shortcut] sum included.  Returns the number of layers checked."""
+    checked = 0
+    for i, l in enumerate(net.layers):
+        if not (l.type == "convolutional" and l.xnor):
+            continue
+        lc = net_cpu.layers[i]
+        src = (x if i == 0 else net.layers[i - 1].output_gpu).cpu()
+        want = port.conv_forward(np.ascontiguousarray(src.numpy()), lc.weights, lc.biases, lc.stride, lc.pad, lc.activation == "leaky")
+        got = l.xnor_layer.output_gpu.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"xnor layer {i} differs from the oracle"
+        nxt = net.layers[i + 1] if i + 1 < len(net.layers) else None
+        if nxt is not None and nxt.blank:
+            add = net.layers[nxt.input_layers[0]].output_gpu.cpu().numpy()
+            total = (add + want).astype(np.float32)                       # one fp32 addition per element, as in the fused epilogue
+            assert np.array_equal(nxt.output_gpu.cpu().numpy().view(np.uint32), total.view(np.uint32)), f"fused shortcut {i + 1} differs"
+        checked += 1
+    return checked
+
+
+@pytest.mark.parametrize("name,size", [("yolov3-tiny_xnor", 160), ("tiny-yolo_xnor", 128), ("yolov3-tiny_xnor", 416), ("tiny-yolo_xnor", 416)])
+def test_network_heads_match_cpu_oracle_network(port, tmp_path, name, size):
+    """BASELINE configurations 2 and 4 at their 416x416 input (and two small sizes): per-layer bit-exactness against the
+    oracle, then the detection-head outputs of an independent CPU network within 1e-3, with the one documented source of
+    divergence accounted for instead of tolerated."""
+    cfg, w = tmp_path / "net.cfg", tmp_path / "net.weights"
+    cfg.write_text(cfgs.CFGS[name](size, size))
+    net_cpu = prepared_cpu_network(cfg, w, 1, 11)
     x = torch.from_numpy(synth.uniform01(21, (1, 3, size, size)))
 
     # the per-layer check needs every fp32 tensor, so this network keeps them; the default network hands sign bits
@@ -72,30 +109,47 @@ def test_network_heads_match_cpu_oracle_network(port, tmp_path, name, size):
     linked = network.load_network_custom(str(cfg), str(w), 1)
     for a, b in zip(heads_gpu, network.forward_network_gpu(linked, x.cuda())):
         assert torch.equal(a, b.cpu())
-    gpu_inputs = {}
-    for i, l in enumerate(net.layers):
-        if l.type == "convolutional" and l.xnor:
-            gpu_inputs[i] = (x.cuda() if i == 0 else net.layers[i - 1].output_gpu).cpu()
+    assert device_status() == 0
 
     # (a) every xnor layer, fed the GPU's own input: bit-exact against the oracle
-    for i, l in enumerate(net.layers):
-        if l.type == "convolutional" and l.xnor:
-            lc = net_cpu.layers[i]
-            want = port.conv_forward(np.ascontiguousarray(gpu_inputs[i].numpy()), lc.weights, lc.biases, lc.stride, lc.pad,
-                                     lc.activation == "leaky")
-            got = l.output_gpu.cpu().numpy()
-            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"xnor layer {i} differs from the oracle"
+    assert check_xnor_layers_against_oracle(net, net_cpu, x.cuda(), port) == sum(1 for l in net.layers if l.type == "convolutional" and l.xnor)
 
-    # (b) fully independent CPU network: head outputs within the detection tolerance
-    heads_cpu, _ = cpu_forward(net_cpu, x, port)
+    # (b) independent CPU network.  The float convolution in front of the first xnor layer is summed in a different order on
+    # the two sides, so a value within rounding of zero can binarise differently there; everything behind it is either
+    # bit-exact (xnor layers, maxpool, route, upsample) or a float layer that feeds no binarisation.  So: count the elements of
+    # the first xnor layer's input whose sign differs between the two sides, then give the CPU network the GPU's tensor at
+    # that one place and require EVERY head value within 1e-3.
+    first = next(i for i, l in enumerate(net.layers) if l.type == "convolutional" and l.xnor)
+    _, outs_cpu = cpu_forward(net_cpu, x, port)
+    gpu_in = net.layers[first - 1].output_gpu.cpu()
+    cpu_in = outs_cpu[first - 1]
+    sign_flips = int(((gpu_in > 0) != (cpu_in > 0)).sum())
+    assert sign_flips <= max(4, gpu_in.numel() // 100000), f"{sign_flips} of {gpu_in.numel()} first-layer signs differ"
+    assert (gpu_in - cpu_in).abs().max().item() <= 1e-5
+    heads_cpu, _ = cpu_forward(net_cpu, x, port, xnor_inputs_from={first: gpu_in})
     assert len(heads_cpu) == len(heads_gpu) > 0
-    worst = 0.0
-    flipped = 0
     for a, b in zip(heads_gpu, heads_cpu):
-        d = (a - b).abs()
-        worst = max(worst, d.max().item())
-        flipped += int((d > 1e-3).sum())
-    total = sum(h.numel() for h in heads_gpu)
-    # Report both numbers in the failure message: a handful of sign flips near zero in the first binarised layer is
-    # the documented sensitivity, anything systematic would show up as a large fraction.
-    assert flipped <= total * 1e-3, f"{flipped} of {total} head values differ by more than 1e-3 (worst {worst:.3e})"
+        worst = (a - b).abs().max().item()
+        assert worst <= 1e-3, f"head differs by {worst:.3e} with identical first-layer signs ({sign_flips} sign flips without)"
+
+
+@pytest.mark.parametrize("size,batch", [(128, 1), (128, 4), (448, 1), (224, 4)])
+def test_darknet53_xnor_layers_match_oracle_at_network_level(port, tmp_path, size, batch):
+    """BASELINE configuration 5's network: all 51 xnor layers and the 23 fused [shortcut] sums of one forward, each fed the
+    GPU's own input, bit-exact against the oracle; then the fully linked network (from batch 4 with the sign words and the
+    direct sinks of the shortcut sums) reaches the same softmax output bit for bit."""
+    cfg, w = tmp_path / "net.cfg", tmp_path / "net.weights"
+    cfg.write_text(cfgs.CFGS["darknet53_448_xnor"](size, size))
+    net_cpu = prepared_cpu_network(cfg, w, batch, 17)
+    x = torch.from_numpy(synth.uniform01(23, (batch, 3, size, size))).cuda()
+    plain = network.load_network_custom(str(cfg), str(w), batch, sign_chains=False, fuse_first_conv=False, side_branches=False)
+    want = [h.clone() for h in network.forward_network_gpu(plain, x)]
+    assert check_xnor_layers_against_oracle(plain, net_cpu, x, port) == 51
+    assert sum(1 for l in plain.layers if l.blank) == 23
+    linked = network.load_network_custom(str(cfg), str(w), batch)
+    assert (linked.sum_sign_links > 0) == (batch >= 4)
+    got = network.forward_network_gpu(linked, x)
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)

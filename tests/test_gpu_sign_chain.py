@@ -37,8 +37,7 @@ def build(batch, c, h, w, n, ks, leaky, seed):
 ], ids=lambda c: "b%d_c%d_%dx%d_n%d_n%d_%s" % c)
 def test_sign_chain_equals_fp32_chain(case, tc):
     batch, c1, h, w, n1, n2, pool = case
-    old = os.environ.get("XNOR_B200_GEMM_TC")
-    os.environ["XNOR_B200_GEMM_TC"] = tc
+    capi.set_tuning(gemm_route=capi.ROUTE_TENSOR if tc == "1" else capi.ROUTE_TILED)
     try:
         l1, x = build(batch, c1, h, w, n1, 3, 0, 31 + c1)
         y1 = L.forward_convolutional_layer_gpu(l1, x).clone()
@@ -62,10 +61,7 @@ def test_sign_chain_equals_fp32_chain(case, tc):
         got = L.forward_convolutional_layer_io(l2, x_signs=signs, pool=pd).clone()
         assert torch.equal(got, want)
     finally:
-        if old is None:
-            os.environ.pop("XNOR_B200_GEMM_TC", None)
-        else:
-            os.environ["XNOR_B200_GEMM_TC"] = old
+        capi.set_tuning()
 
 
 def test_io_argument_checks():

@@ -17,14 +17,12 @@ from darknet_b200 import capi, layer as L  # noqa: E402
 
 
 @pytest.fixture(autouse=True, params=["auto", "tensor-core"])
-def gemm_kernel(request, monkeypatch):
+def gemm_kernel(request):
     """Every test runs once with the library's own kernel choice (integer / short-K kernels at these sizes) and once
     with every GEMM forced onto the tcgen05 kernel, which has its own sink epilogue."""
-    if request.param == "tensor-core":
-        monkeypatch.setenv("XNOR_B200_GEMM_TC", "1")
-    else:
-        monkeypatch.delenv("XNOR_B200_GEMM_TC", raising=False)
-    return request.param
+    capi.set_tuning(gemm_route=capi.ROUTE_TENSOR if request.param == "tensor-core" else capi.ROUTE_AUTO)
+    yield request.param
+    capi.set_tuning()
 
 
 def make(batch, c, h, w, n, ks, seed, act=capi.LINEAR):

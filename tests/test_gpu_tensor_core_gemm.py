@@ -1,9 +1,7 @@
 """The tcgen05 (tensor-core) variant of the XNOR GEMM against the oracle and against the integer-pipe kernel.
 
-XNOR_B200_GEMM_TC=1 routes every GEMM call to the tensor-core kernel, =0 to the integer-pipe kernel, so both are
-exercised on identical operands.  Integer accumulators and fp32 outputs must be bit-identical to the oracle."""
-import os
-
+xnor_b200_set_tuning pins the route of every GEMM call -- "1" = the tensor-core kernel, "0" = the tiled integer-pipe
+kernel, None = the library's own choice -- so both are exercised on identical operands.  Integer accumulators and fp32 outputs must be bit-identical to the oracle."""
 import numpy as np
 import pytest
 
@@ -18,15 +16,10 @@ from darknet_b200 import capi, layer as L  # noqa: E402
 
 @pytest.fixture
 def force_tc():
-    old = os.environ.get("XNOR_B200_GEMM_TC")
-
     def set_mode(v):
-        if v is None:
-            os.environ.pop("XNOR_B200_GEMM_TC", None)
-        else:
-            os.environ["XNOR_B200_GEMM_TC"] = v
+        capi.set_tuning(gemm_route={None: capi.ROUTE_AUTO, "0": capi.ROUTE_TILED, "1": capi.ROUTE_TENSOR}[v])
     yield set_mode
-    set_mode(old)
+    capi.set_tuning()
 
 
 def random_bits(rng, rows, K):
@@ -84,10 +77,10 @@ def test_tensor_core_layer_output_matches_oracle_and_integer_kernel(port, force_
 
 
 def test_automatic_dispatch_uses_tensor_cores_for_large_layers_and_stays_exact(port, force_tc):
-    """A batch-64 BASELINE-sized layer (eligible for the tensor-core kernel) equals the integer kernel bit for bit."""
+    """A batch-64 BASELINE-sized layer (eligible for the tensor-core kernel), 64 distinct images: every image equals the
+    oracle bit for bit, and the integer kernel gives the same tensor."""
     batch, c, h, w, n, ks = 64, 256, 26, 26, 512, 3
-    x1, wt, b = synth.conv_case(777, 2, c, h, w, n, ks)
-    x = np.concatenate([x1] * (batch // 2), 0)
+    x, wt, b = synth.conv_case(777, batch, c, h, w, n, ks)
     l = L.make_convolutional_layer(batch, h, w, c, n, ks, 1, 1, capi.LEAKY)
     l.load_weights(torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda())
     L.binary_align_weights(l)
@@ -98,8 +91,8 @@ def test_automatic_dispatch_uses_tensor_cores_for_large_layers_and_stays_exact(p
     force_tc("0")
     y_int = L.forward_convolutional_layer_gpu(l, xg).clone()
     assert torch.equal(y_auto, y_int)
-    want = port.conv_forward(x1, wt, b, 1, 1, 1)
-    assert np.array_equal(y_auto[:2].cpu().numpy().view(np.uint32), want.view(np.uint32))
+    want = port.conv_forward(x, wt, b, 1, 1, 1)
+    assert np.array_equal(y_auto.cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
 @pytest.mark.parametrize("shape", [(256, 640, 1152), (200, 300, 576), (96, 1000, 288), (48, 257, 300), (20, 129, 128), (512, 130, 2304)],

@@ -8,7 +8,9 @@ import pytest
 torch = pytest.importorskip("torch")
 from darknet_b200 import cfgs, network  # noqa: E402
 
-REF_CFG = "/root/reference/cfg"
+from oracle.binding import reference_dir  # noqa: E402
+
+REF_CFG = os.path.join(reference_dir(), "cfg")
 
 
 def parse_text(text, tmp_path, name="net.cfg"):

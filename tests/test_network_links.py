@@ -88,3 +88,40 @@ def test_other_networks_link_consistently(name, tmp_path):
         if c.packed_input:
             got = sum(p.n for p in L for s in p.sinks if s.consumer is c.xnor_layer)
             assert got == c.c
+
+
+def test_shortcut_sum_reader_that_pools_takes_words_not_rows(tmp_path):
+    """conv + fused [shortcut] -> 1x1 xnor conv -> 2x2/2 maxpool -> xnor conv: link_sinks makes the 1x1 layer window-major
+    (it feeds a pooled sink), so the sum's signs must reach it as words through its pack kernel; writing them straight
+    into its operand would put row-major rows under a window-major GEMM."""
+    text = "\n".join([
+        "[net]\nbatch=1\nwidth=32\nheight=32\nchannels=3\n",
+        cfgs._conv(32, 3),
+        cfgs._conv(64, 3, xnor=1),
+        cfgs._conv(64, 3, xnor=1),
+        "[shortcut]\nfrom=-2\nactivation=linear\n",
+        cfgs._conv(64, 1, xnor=1),
+        cfgs._maxpool(2, 2),
+        cfgs._conv(64, 3, xnor=1),
+        # same block without the pool: the reader stays row-major and takes the signs straight into its operand
+        cfgs._conv(64, 3, xnor=1),
+        "[shortcut]\nfrom=-2\nactivation=linear\n",
+        cfgs._conv(64, 1, xnor=1),
+        cfgs._conv(32, 1, bn=0, activation="linear"),
+    ])
+    cfg = tmp_path / "net.cfg"
+    cfg.write_text(text)
+    net = network.parse_network_cfg(str(cfg), 4, "cpu")
+    for l in net.layers:
+        if l.type == "convolutional" and l.xnor:
+            l.xnor_layer = types.SimpleNamespace(window_major=False)
+    net.layers[3].blank = True
+    net.layers[8].blank = True
+    network.link_sinks(net)
+    network.link_sign_chains(net)
+    network.link_shortcut_sums(net)
+    L = net.layers
+    assert L[4].xnor_layer.window_major and L[6].packed_input            # 4 -> (maxpool 5) -> 6 is a pooled sink
+    assert L[2].emit_sum_signs and L[2].sum_sink_to is None and L[4].sign_source == 3 and not L[4].packed_input
+    assert L[7].sum_sink_to == 9 and L[9].packed_input and not L[9].xnor_layer.window_major
+    assert net.sum_sign_links == 2
