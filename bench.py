@@ -70,6 +70,7 @@ def parse_args():
     ap.add_argument("--kernel", default=None, choices=["gemm", "gemms", "pack", "fconv"], help="time one kernel instead of the network")
     ap.add_argument("--shape", type=int, nargs="*", default=[])
     ap.add_argument("--route", default="auto", choices=sorted(ROUTES))
+    ap.add_argument("--tc-kernel", type=int, default=0, choices=[0, 1, 2], help="--kernel gemm with --route tensor: 1 = one tile per CTA, 2 = persistent")
     ap.add_argument("--shortcut", action="store_true")
     ap.add_argument("--reps", type=int, default=5)
     return ap.parse_args()
@@ -611,7 +612,7 @@ def run_kernel(args) -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py --kernel needs a CUDA device")
     lib = capi.lib()
-    capi.set_tuning(gemm_route=ROUTES[args.route])
+    capi.set_tuning(gemm_route=ROUTES[args.route], tc_kernel=args.tc_kernel)
 
     def stream() -> int:
         return torch.cuda.current_stream().cuda_stream

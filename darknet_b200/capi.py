@@ -60,7 +60,7 @@ ROUTE_AUTO, ROUTE_INTEGER, ROUTE_TENSOR, ROUTE_TILED = 0, 1, 2, 3
 
 class Tuning(C.Structure):
     """struct xnor_b200_tuning"""
-    _fields_ = [(n, C.c_int) for n in ("gemm_route", "gemm_tile", "gemm_split", "pack_ctas_per_sm", "tc_wait_polls", "tc_withhold_arrival")]
+    _fields_ = [(n, C.c_int) for n in ("gemm_route", "gemm_tile", "gemm_split", "pack_ctas_per_sm", "tc_kernel", "tc_wait_polls", "tc_withhold_arrival")]
 
 
 class ConvGeom(C.Structure):

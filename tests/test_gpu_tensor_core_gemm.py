@@ -16,8 +16,9 @@ from darknet_b200 import capi, layer as L  # noqa: E402
 
 @pytest.fixture
 def force_tc():
-    def set_mode(v):
-        capi.set_tuning(gemm_route={None: capi.ROUTE_AUTO, "0": capi.ROUTE_TILED, "1": capi.ROUTE_TENSOR}[v])
+    def set_mode(v, tc_kernel=0):
+        """tc_kernel: 0 = the library picks the tcgen05 kernel, 1 = one tile per CTA, 2 = persistent."""
+        capi.set_tuning(gemm_route={None: capi.ROUTE_AUTO, "0": capi.ROUTE_TILED, "1": capi.ROUTE_TENSOR}[v], tc_kernel=tc_kernel)
     yield set_mode
     capi.set_tuning()
 
@@ -49,13 +50,14 @@ def test_tensor_core_counts_match_oracle(port, force_tc, shape):
     B, _ = random_bits(rng, N, K)
     want = port.gemm_counts(M, N, K, A, ld, B, ld)
     Ag, Bg = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
-    force_tc("1")
-    got_tc = L.gemm_counts(M, N, K, Ag, ld, Bg, ld).cpu().numpy()
-    assert device_status() == 0
+    for variant in (1, 2):                      # both tcgen05 kernels, whatever the library would pick for this shape
+        force_tc("1", variant)
+        got_tc = L.gemm_counts(M, N, K, Ag, ld, Bg, ld).cpu().numpy()
+        assert device_status() == 0
+        assert np.array_equal(got_tc, want), f"tensor-core kernel {variant}: counts differ in {np.count_nonzero(got_tc != want)} of {want.size} entries"
     force_tc("0")
     got_int = L.gemm_counts(M, N, K, Ag, ld, Bg, ld).cpu().numpy()
     assert np.array_equal(got_int, want)
-    assert np.array_equal(got_tc, want), f"tensor-core counts differ in {np.count_nonzero(got_tc != want)} of {want.size} entries"
 
 
 def test_tensor_core_layer_output_matches_oracle_and_integer_kernel(port, force_tc):
@@ -110,8 +112,8 @@ def test_tensor_core_fused_shortcut_equals_integer_kernel(force_tc, shape):
     bias = torch.from_numpy(rng.standard_normal(M).astype(np.float32)).cuda()
     sc_in = torch.from_numpy(rng.standard_normal((M, ldc)).astype(np.float32)).cuda()
     outs = {}
-    for mode in ("1", "0"):
-        force_tc(mode)
+    for mode in ("1", "1p", "0"):
+        force_tc(mode[0], 2 if mode == "1p" else 1)
         for with_sc in (True, False):
             C_ = torch.full((M, ldc), float("nan"), device="cuda")
             sc_out = torch.full((M, ldc), float("nan"), device="cuda")
