@@ -38,8 +38,8 @@ struct TcParams
 // The status word of the current device (resolved once per device), the poll limit and the test switches for a launch.
 int tc_fill_launch_fields(TcParams & p);
 
-// The persistent kernel (xnor_gemm_tcp.cu): layers with more than 64 filters.
-bool tcp_takes(int M);
+// The persistent kernel (xnor_gemm_tcp.cu).
+bool tcp_takes(const TcParams & p);
 int launch_xnor_gemm_tcp(TcParams & p, cudaStream_t stream);
 
 // read-once data (the shortcut operand): streaming load, evicted first

@@ -300,9 +300,9 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	p.shortcut_in = shortcut_in; p.shortcut_out = shortcut_out; p.counts = counts;
 	int rc = tc_fill_launch_fields(p);
 	if (rc != XNOR_B200_OK) { return rc; }
-	// layers with more than 64 filters: the persistent kernel, unless xnor_b200_set_tuning pinned the other one
+	// the persistent kernel where it measured faster, unless xnor_b200_set_tuning pinned one of the two
 	const int variant = tuning().tc_kernel;
-	if (variant == 2 || (variant == 0 && tcp_takes(M))) { return launch_xnor_gemm_tcp(p, stream); }
+	if (variant == 2 || (variant == 0 && tcp_takes(p))) { return launch_xnor_gemm_tcp(p, stream); }
 	if (M > 128) { return launch_tc<256>(p, stream); }
 	if (M > 64) { return launch_tc<128>(p, stream); }
 	return (M > 32) ? launch_tc<64>(p, stream) : launch_tc<32>(p, stream);

@@ -231,3 +231,60 @@ def test_shortcut_sum_signs_straight_into_a_1x1_readers_operand(case):
     bad = L.make_convolutional_layer(batch, h, w, n, 40, 3, 1, 1, capi.LEAKY)
     with pytest.raises(capi.XnorError, match="invalid"):
         L.forward_convolutional_layer_io(l, x=xg, shortcut_only=True, shortcut_sink=bad)
+
+
+@pytest.mark.parametrize("variant", [1, 2], ids=["tile-per-cta", "persistent"])
+def test_many_tiles_per_cta_repeatedly_equal_the_integer_kernel(force_tc, variant):
+    """A GEMM with several tiles per SM (the persistent kernel walks five of them per CTA, re-using its operand rings, its two
+    accumulator buffers and the per-row tables), launched five times on the same operands: every launch equals the integer
+    kernel bit for bit.  A hand-over that is only right for some timings shows up here as a launch that differs."""
+    M, N, K = 512, 148 * 128 * 5 + 77, 2304
+    rng = np.random.default_rng(20241)
+    A, ld = random_bits(rng, M, K)
+    B, _ = random_bits(rng, N, K)
+    Ag, Bg = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    mean = torch.from_numpy(rng.random(M, dtype=np.float32)).cuda()
+    bias = torch.from_numpy(rng.standard_normal(M).astype(np.float32)).cuda()
+
+    def run():
+        out = torch.full((M, N), float("nan"), device="cuda")
+        capi.check(capi.lib().xnor_b200_gemm_bin_mean_transposed(M, N, K, Ag.data_ptr(), ld, Bg.data_ptr(), ld, out.data_ptr(), N,
+                                                                 mean.data_ptr(), bias.data_ptr(), 1, None, None,
+                                                                 torch.cuda.current_stream().cuda_stream), "gemm")
+        torch.cuda.synchronize()
+        return out
+
+    force_tc("0")
+    want = run()
+    force_tc("1", variant)
+    for i in range(5):
+        got = run()
+        assert device_status() == 0
+        assert torch.equal(got, want), f"launch {i}: {int((got != want).sum())} values differ"
+
+
+@pytest.mark.parametrize("variant", [1, 2], ids=["tile-per-cta", "persistent"])
+def test_bounded_wait_runs_out_and_the_kernel_recovers(port, variant):
+    """Failure detection without a fault: xnor_b200_set_tuning withholds one producer arrival of the first K block and gives
+    every barrier wait a few thousand polls, so the issuer's wait runs out.  The kernel must come back by itself (every role
+    leaves through the give-up path, tensor memory released), report it through xnor_b200_take_device_status once, and leave
+    the device fit for the next launch, whose counts equal the oracle's."""
+    M, N, K = 256, 1000, 1152
+    rng = np.random.default_rng(99)
+    A, ld = random_bits(rng, M, K)
+    B, _ = random_bits(rng, N, K)
+    Ag, Bg = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    want = port.gemm_counts(M, N, K, A, ld, B, ld)
+    try:
+        assert device_status() == 0
+        capi.set_tuning(gemm_route=capi.ROUTE_TENSOR, tc_kernel=variant, tc_wait_polls=4000, tc_withhold_arrival=1)
+        L.gemm_counts(M, N, K, Ag, ld, Bg, ld)
+        assert device_status() == 1            # a wait ran out; the word is sticky until taken
+        assert device_status() == 0            # ... and cleared by the call that took it
+        capi.set_tuning(gemm_route=capi.ROUTE_TENSOR, tc_kernel=variant)
+        for _ in range(2):
+            got = L.gemm_counts(M, N, K, Ag, ld, Bg, ld).cpu().numpy()
+            assert device_status() == 0
+            assert np.array_equal(got, want)
+    finally:
+        capi.set_tuning()
