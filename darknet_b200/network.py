@@ -18,7 +18,9 @@ Only the section types and keys that occur in the three shipped xnor cfgs are un
 from __future__ import annotations
 
 import math
+import os
 import struct
+import zlib
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
@@ -131,6 +133,7 @@ class Network:
     heads_direct_to_host: bool = True      # with heads_host: a fused head convolution stores into the pinned host tensor itself
     side_branches: bool = True             # a head branch that nothing later reads runs on a second stream
     side_stream: Optional[torch.cuda.Stream] = None
+    packed_from_cache: int = 0             # xnor layers whose packed weights came from the cache file beside the .weights file
     sink_max_batch: int = 1 << 30          # batch up to which direct sign sinks are linked (measured: a gain at every batch for yolov3-tiny, within 2% either way for the other two networks at batch 32-256)
     sink_links: int = 0
 
@@ -234,6 +237,88 @@ def load_weights(net: Network, path: str) -> None:
             l.weights = take(l.n * l.c * l.size * l.size).reshape(l.n, l.c, l.size, l.size)
 
 
+# ---- packed-weight cache -------------------------------------------------------------------------
+# Darknet carries a dormant writer for bit-packed weights (save_convolutional_weights_binary, src-lib/weights.cpp:70-116:
+# per filter the mean and size/8 bytes of sign bits) and re-packs every xnor layer in a host triple loop at each load
+# (src-lib/convolutional_layer.cpp:1371-1391).  The cache keeps what the path actually consumes -- align_bit_weights in its
+# final K order with the row padding, and mean_arr -- beside the .weights file, keyed by the layer geometry and a CRC of
+# the batch-norm-folded fp32 weights it was packed from, so a stale or foreign file is never used.
+#
+# file: "XNORPACK" | u32 version | u32 entries | entries | u32 crc32 of everything before it
+# entry: i32 layer index, c, n, size, stride, pad, new_lda | u32 crc32(fp32 weights) | u64 bits bytes | bits | f32 mean[n]
+
+PACK_MAGIC = b"XNORPACK"
+PACK_VERSION = 1
+
+
+def packed_cache_path(weights_path: str) -> str:
+    return weights_path + ".xnorpack"
+
+
+def weights_crc(l: Layer) -> int:
+    """CRC-32 of the layer's fp32 weights as the packer sees them (after fuse_conv_batchnorm)."""
+    return zlib.crc32(np.ascontiguousarray(l.weights, "<f4").tobytes()) & 0xFFFFFFFF
+
+
+def write_packed_cache(path: str, entries: List[dict]) -> None:
+    """entries: dicts with index, c, n, size, stride, pad, new_lda, crc, bits (uint8 [n*new_lda/8]), mean (float32 [n])."""
+    body = bytearray(PACK_MAGIC + struct.pack("<II", PACK_VERSION, len(entries)))
+    for e in entries:
+        bits = np.ascontiguousarray(e["bits"], np.uint8)
+        mean = np.ascontiguousarray(e["mean"], "<f4")
+        if bits.size != e["n"] * e["new_lda"] // 8 or mean.size != e["n"]:
+            raise ValueError("packed-weight entry has the wrong size")
+        body += struct.pack("<7iIQ", e["index"], e["c"], e["n"], e["size"], e["stride"], e["pad"], e["new_lda"], e["crc"], bits.size)
+        body += bits.tobytes() + mean.tobytes()
+    body += struct.pack("<I", zlib.crc32(bytes(body)) & 0xFFFFFFFF)
+    tmp = path + ".tmp"
+    with open(tmp, "wb") as fh:
+        fh.write(body)
+    os.replace(tmp, path)
+
+
+def read_packed_cache(path: str) -> Dict[int, dict]:
+    """Layer index -> entry.  Raises ValueError on a damaged, truncated or foreign file."""
+    with open(path, "rb") as fh:
+        data = fh.read()
+    if len(data) < 20 or data[:8] != PACK_MAGIC:
+        raise ValueError("not a packed-weight cache")
+    if zlib.crc32(data[:-4]) & 0xFFFFFFFF != struct.unpack("<I", data[-4:])[0]:
+        raise ValueError("packed-weight cache is damaged (checksum)")
+    version, count = struct.unpack_from("<II", data, 8)
+    if version != PACK_VERSION:
+        raise ValueError("packed-weight cache has another version")
+    out: Dict[int, dict] = {}
+    off = 16
+    for _ in range(count):
+        index, c, n, size, stride, pad, new_lda, crc, nbytes = struct.unpack_from("<7iIQ", data, off)
+        off += struct.calcsize("<7iIQ")
+        if n <= 0 or new_lda <= 0 or nbytes != n * new_lda // 8 or off + nbytes + 4 * n > len(data) - 4:
+            raise ValueError("packed-weight cache entry is inconsistent")
+        bits = np.frombuffer(data, np.uint8, nbytes, off).copy()
+        off += nbytes
+        mean = np.frombuffer(data, "<f4", n, off).astype(np.float32)
+        off += 4 * n
+        out[index] = dict(index=index, c=c, n=n, size=size, stride=stride, pad=pad, new_lda=new_lda, crc=crc, bits=bits, mean=mean)
+    return out
+
+
+def cache_entry_matches(e: Optional[dict], l: Layer, new_lda: int) -> bool:
+    return (e is not None and (e["c"], e["n"], e["size"], e["stride"], e["pad"], e["new_lda"]) == (l.c, l.n, l.size, l.stride, l.pad, new_lda)
+            and e["crc"] == weights_crc(l))
+
+
+def packed_entries(net: Network) -> List[dict]:
+    """What the loaded network holds, ready for write_packed_cache."""
+    out = []
+    for l in net.layers:
+        if l.type == "convolutional" and l.xnor and l.xnor_layer is not None:
+            xl = l.xnor_layer
+            out.append(dict(index=l.index, c=l.c, n=l.n, size=l.size, stride=l.stride, pad=l.pad, new_lda=xl.new_lda, crc=weights_crc(l),
+                            bits=xl.align_bit_weights_gpu.cpu().numpy(), mean=xl.mean_arr_gpu.cpu().numpy()))
+    return out
+
+
 # ---- load-time preparation -----------------------------------------------------------------------
 
 def fuse_conv_batchnorm(net: Network) -> None:
@@ -247,9 +332,10 @@ def fuse_conv_batchnorm(net: Network) -> None:
             l.batch_normalize = 0
 
 
-def calculate_binary_weights(net: Network) -> None:
-    """Packs every xnor conv through the C ABI, drops the activation of bin_output layers and fuses a
-    same-shape [shortcut] that directly follows an xnor conv (src-lib/darknet_network.cpp:1778-1817)."""
+def calculate_binary_weights(net: Network, packed: Optional[Dict[int, dict]] = None) -> None:
+    """Packs every xnor conv through the C ABI (or takes its packed weights from `packed`, the entries of a cache file,
+    where geometry and weight checksum match), drops the activation of bin_output layers and fuses a same-shape
+    [shortcut] that directly follows an xnor conv (src-lib/darknet_network.cpp:1778-1817)."""
     dev = net.device
     for j, l in enumerate(net.layers):
         if l.type != "convolutional":
@@ -265,7 +351,13 @@ def calculate_binary_weights(net: Network) -> None:
         act = capi.LEAKY if l.activation == "leaky" else capi.LINEAR
         xl = L.make_convolutional_layer(net.batch, l.h, l.w, l.c, l.n, l.size, l.stride, l.pad, act, device=str(dev))
         xl.load_weights(l.weights_gpu, l.biases_gpu)
-        L.binary_align_weights(xl)
+        cached = packed.get(j) if packed else None
+        if cache_entry_matches(cached, l, xl.new_lda):
+            xl.align_bit_weights_gpu = torch.from_numpy(cached["bits"]).to(dev)
+            xl.mean_arr_gpu.copy_(torch.from_numpy(cached["mean"]))
+            net.packed_from_cache += 1
+        else:
+            L.binary_align_weights(xl)
         l.xnor_layer = xl
         l.output_gpu = xl.output_gpu
         net.xnor_launches_per_forward += 2
@@ -758,9 +850,12 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
 
 def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "cuda:0", sign_chains: bool = True,
                         fuse_first_conv: bool = True, side_branches: bool = True, float_map_max_pixels: Optional[int] = None,
-                        sum_signs_min_batch: Optional[int] = None, sink_max_batch: Optional[int] = None) -> Network:
+                        sum_signs_min_batch: Optional[int] = None, sink_max_batch: Optional[int] = None,
+                        packed_cache: bool = False) -> Network:
     """load_network_custom (src-lib/weights.cpp:665-691): parse, load, fold batch-norm, pack binary weights.
-    The last three arguments override the measured hand-over thresholds of the Network (tuning runs)."""
+    float_map_max_pixels, sum_signs_min_batch and sink_max_batch override the measured hand-over thresholds of the Network
+    (tuning runs).  packed_cache: read the packed weights from <weights>.xnorpack where it matches, and (re)write that file
+    when any layer had to be packed afresh."""
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
     net = parse_network_cfg(cfg, batch, device)
@@ -776,7 +871,16 @@ def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "c
         net.sink_max_batch = sink_max_batch
     load_weights(net, weights)
     fuse_conv_batchnorm(net)
-    calculate_binary_weights(net)
+    packed = None
+    if packed_cache and os.path.exists(packed_cache_path(weights)):
+        try:
+            packed = read_packed_cache(packed_cache_path(weights))
+        except (OSError, ValueError):
+            packed = None                    # unusable file: pack afresh and replace it
+    calculate_binary_weights(net, packed)
+    n_xnor = sum(1 for l in net.layers if l.type == "convolutional" and l.xnor)
+    if packed_cache and net.packed_from_cache < n_xnor:
+        write_packed_cache(packed_cache_path(weights), packed_entries(net))
     return net
 
 
