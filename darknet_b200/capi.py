@@ -26,6 +26,7 @@ EXPORTS = (
     "xnor_b200_conv_forward_static", "xnor_b200_take_device_status",
     "xnor_b200_pack_input_pooled", "xnor_b200_conv_forward_pooled", "xnor_b200_float_conv_small", "xnor_b200_float_conv3_io", "xnor_b200_float_conv_map_weights_bytes",
     "xnor_b200_float_conv_map_prepare", "xnor_b200_float_conv_map", "xnor_b200_float_conv_map_yolo", "xnor_b200_yolo_activate", "xnor_b200_region_activate", "xnor_b200_conv_forward_io", "xnor_b200_conv_takes_masks", "xnor_b200_tap_major_weights",
+    "xnor_b200_yolo_detections", "xnor_b200_nms_sort", "xnor_b200_detection_rows",
     "xnor_b200_measure_popc_peak", "xnor_b200_measure_bmma_peak", "xnor_b200_measure_umma_i8_peak",
 )
 
@@ -61,6 +62,18 @@ ROUTE_AUTO, ROUTE_INTEGER, ROUTE_TENSOR, ROUTE_TILED = 0, 1, 2, 3
 class Tuning(C.Structure):
     """struct xnor_b200_tuning"""
     _fields_ = [(n, C.c_int) for n in ("gemm_route", "gemm_tile", "gemm_split", "pack_ctas_per_sm", "tc_kernel", "tc_wait_polls", "tc_withhold_arrival")]
+
+
+class YoloHead(C.Structure):
+    """struct xnor_b200_yolo_head"""
+    _fields_ = [("output", C.c_void_p), ("w", C.c_int), ("h", C.c_int), ("n", C.c_int), ("classes", C.c_int), ("anchors", C.c_float * 32),
+                ("new_coords", C.c_int)]
+
+
+class Detections(C.Structure):
+    """struct xnor_b200_detections"""
+    _fields_ = [("boxes", C.c_void_p), ("objectness", C.c_void_p), ("probs", C.c_void_p), ("count", C.c_void_p), ("max_dets", C.c_int),
+                ("classes", C.c_int)]
 
 
 class ConvGeom(C.Structure):
@@ -123,6 +136,9 @@ def lib() -> C.CDLL:
     L.xnor_b200_yolo_activate.argtypes = [vp, vp, ci, ci, ci, ci, vp]
     L.xnor_b200_region_activate.argtypes = [vp, vp, ci, ci, ci, ci, ci, ci, vp]
     L.xnor_b200_conv_forward_io.argtypes = [dp, C.POINTER(ConvIO), vp, vp, vp, vp, sz, vp]
+    L.xnor_b200_yolo_detections.argtypes = [C.POINTER(YoloHead), ci, ci, ci, ci, ci, C.c_float, ci, ci, ci, C.POINTER(Detections), vp]
+    L.xnor_b200_nms_sort.argtypes = [C.POINTER(Detections), ci, C.c_float, vp]
+    L.xnor_b200_detection_rows.argtypes = [C.POINTER(Detections), ci, vp, ci, vp, vp]
     L.xnor_b200_conv_forward_static.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
     L.xnor_b200_take_device_status.argtypes = [C.POINTER(ci)]
     L.xnor_b200_measure_popc_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]

@@ -201,20 +201,37 @@ def parse_network_cfg(path: str, batch: int = 1, device: str = "cuda:0") -> Netw
 # (src-lib/weights.cpp:460-478); per conv: biases[n], then scales/rolling_mean/rolling_variance[n] when
 # batch_normalize, then weights[n*c*size*size] fp32 (src-lib/weights.cpp:369-398).
 
-def write_synthetic_weights(net: Network, path: str, seed: int = 1) -> None:
-    """Seeded weights: w ~ N(0, 0.05), b ~ N(0, 0.01), BN scales 1, rolling mean 0, rolling variance 1."""
+def write_synthetic_weights(net: Network, path: str, seed: int = 1, random_batchnorm: bool = False, exact_first_conv: bool = False) -> None:
+    """Seeded weights: w ~ N(0, 0.05), b ~ N(0, 0.01), BN scales 1, rolling mean 0, rolling variance 1.
+    random_batchnorm: scales, means and variances drawn at random instead (exercises fuse_conv_batchnorm).
+    exact_first_conv: the first convolution's weights and biases are multiples of 2^-10 and its rolling variance makes the
+    batch-norm factor round to one, so that with inputs on a 2^-8 grid every partial sum of that layer is exact in fp32 and
+    two implementations that add in different orders still produce bit-identical activations."""
     rng = np.random.default_rng(seed)
+    first = True
     with open(path, "wb") as fh:
         fh.write(struct.pack("<iiiQ", 0, 2, 5, 0))
         for l in net.layers:
             if l.type != "convolutional":
                 continue
-            fh.write((rng.standard_normal(l.n) * 0.01).astype("<f4").tobytes())
+            exact = exact_first_conv and first
+            first = False
+            b = rng.standard_normal(l.n) * 0.01
+            w = rng.standard_normal(l.n * l.c * l.size * l.size) * 0.05
+            if exact:
+                b, w = np.round(b * 1024) / 1024, np.clip(np.round(w * 1024) / 1024, -0.25, 0.25)
+            fh.write(b.astype("<f4").tobytes())
             if l.batch_normalize:
-                fh.write(np.ones(l.n, "<f4").tobytes())
-                fh.write(np.zeros(l.n, "<f4").tobytes())
-                fh.write(np.ones(l.n, "<f4").tobytes())
-            fh.write((rng.standard_normal(l.n * l.c * l.size * l.size) * 0.05).astype("<f4").tobytes())
+                if random_batchnorm and not exact:
+                    fh.write((0.5 + rng.random(l.n)).astype("<f4").tobytes())
+                    fh.write((rng.standard_normal(l.n) * 0.1).astype("<f4").tobytes())
+                    fh.write((0.25 + rng.random(l.n)).astype("<f4").tobytes())
+                else:
+                    fh.write(np.ones(l.n, "<f4").tobytes())
+                    fh.write(np.zeros(l.n, "<f4").tobytes())
+                    # 1 - 1e-5: sqrt(variance + 1e-5) is then within 1e-8 of one and weights on a coarse grid stay as they are
+                    fh.write(np.full(l.n, 1.0 - 1e-5 if exact else 1.0, "<f4").tobytes())
+            fh.write(w.astype("<f4").tobytes())
 
 
 def load_weights(net: Network, path: str) -> None:
@@ -846,6 +863,89 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
     for done in joins:                                # join: the caller's stream sees both branches finished
         torch.cuda.current_stream().wait_event(done)
     return heads
+
+
+# ---- detections ----------------------------------------------------------------------------------
+
+class DetectionBuffers:
+    """Device buffers of xnor_b200_detections plus the row list: one detection list per image of the batch."""
+
+    def __init__(self, batch: int, classes: int, max_dets: int = 2048, max_rows: int = 4096, device="cuda:0") -> None:
+        self.batch, self.classes, self.max_dets, self.max_rows = batch, classes, max_dets, max_rows
+        self.boxes = torch.empty(batch, max_dets, 4, dtype=torch.float32, device=device)
+        self.objectness = torch.empty(batch, max_dets, dtype=torch.float32, device=device)
+        self.probs = torch.empty(batch, max_dets, classes, dtype=torch.float32, device=device)
+        self.count = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.rows = torch.empty(batch, max_rows, 7, dtype=torch.float32, device=device)
+        self.row_count = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.desc = capi.Detections(self.boxes.data_ptr(), self.objectness.data_ptr(), self.probs.data_ptr(), self.count.data_ptr(),
+                                    max_dets, classes)
+
+    def rows_host(self) -> List[np.ndarray]:
+        """Per image the rows {x, y, w, h, objectness, class, probability} (one device-to-host copy of the counts, one of the rows)."""
+        counts = self.row_count.cpu().numpy()
+        rows = self.rows.cpu().numpy()
+        return [rows[b, :min(int(counts[b]), self.max_rows)].copy() for b in range(self.batch)]
+
+
+def yolo_head_desc(l: Layer, output: torch.Tensor) -> capi.YoloHead:
+    """The [yolo] section's own anchors (biases[2 * mask[a]], src-lib/yolo_layer.cpp:22-42) and sizes for xnor_b200_yolo_detections."""
+    mask = [int(v) for v in l.opts["mask"].split(",")]
+    anchors = [float(v) for v in l.opts["anchors"].split(",")]
+    hd = capi.YoloHead()
+    hd.output = output.data_ptr()
+    hd.w, hd.h, hd.n, hd.classes = l.w, l.h, len(mask), int(l.opts.get("classes", 20))
+    for a, m in enumerate(mask):
+        hd.anchors[2 * a], hd.anchors[2 * a + 1] = anchors[2 * m], anchors[2 * m + 1]
+    hd.new_coords = int(l.opts.get("new_coords", 0))
+    return hd
+
+
+def get_network_boxes(net: Network, heads: List[torch.Tensor], img_w: int, img_h: int, thresh: float, dets: DetectionBuffers,
+                      relative: int = 1, letter: int = 0) -> DetectionBuffers:
+    """get_network_boxes (src-lib/darknet_network.cpp:1250) on the device: every [yolo] head of the network, in layer order, appended
+    to one detection list per image.  `heads` are the activated head outputs forward_network_gpu returned (device tensors)."""
+    import ctypes as C
+    yolo_layers = [l for l in net.layers if l.type == "yolo"]
+    if len(yolo_layers) != len(heads) or not yolo_layers:
+        raise ValueError("one activated output per [yolo] layer is needed")
+    stream = torch.cuda.current_stream().cuda_stream
+    for k, (l, h) in enumerate(zip(yolo_layers, heads)):
+        if not (h.is_cuda and h.is_contiguous() and h.dtype == torch.float32):
+            raise ValueError("head outputs must be contiguous fp32 device tensors")
+        hd = yolo_head_desc(l, h)
+        capi.check(capi.lib().xnor_b200_yolo_detections(C.byref(hd), net.batch, net.w, net.h, img_w, img_h, thresh, relative, letter,
+                                                       1 if k else 0, C.byref(dets.desc), stream), "xnor_b200_yolo_detections")
+    return dets
+
+
+def do_nms_sort(dets: DetectionBuffers, nms_thresh: float) -> None:
+    """do_nms_sort (src-lib/box.cpp:951) on the device, every image and class at once."""
+    import ctypes as C
+    capi.check(capi.lib().xnor_b200_nms_sort(C.byref(dets.desc), dets.batch, nms_thresh, torch.cuda.current_stream().cuda_stream),
+               "xnor_b200_nms_sort")
+
+
+def detection_rows(dets: DetectionBuffers) -> None:
+    """Fills dets.rows / dets.row_count with the surviving (detection, class) pairs."""
+    import ctypes as C
+    capi.check(capi.lib().xnor_b200_detection_rows(C.byref(dets.desc), dets.batch, dets.rows.data_ptr(), dets.max_rows,
+                                                  dets.row_count.data_ptr(), torch.cuda.current_stream().cuda_stream), "xnor_b200_detection_rows")
+
+
+def network_detections(net: Network, x: torch.Tensor, thresh: float = 0.25, nms_thresh: float = 0.45,
+                       dets: Optional[DetectionBuffers] = None, img_w: Optional[int] = None, img_h: Optional[int] = None) -> DetectionBuffers:
+    """Forward + decode + suppress + compact, all on the device: what a caller of Darknet's predict API does with
+    network_predict, get_network_boxes and do_nms_sort.  The result's rows are the only thing that has to cross to the host."""
+    heads = forward_network_gpu(net, x)
+    if dets is None:
+        classes = int(next(l for l in net.layers if l.type == "yolo").opts.get("classes", 20))
+        dets = DetectionBuffers(net.batch, classes, device=x.device)
+    get_network_boxes(net, heads, img_w or net.w, img_h or net.h, thresh, dets)
+    if nms_thresh > 0:
+        do_nms_sort(dets, nms_thresh)
+    detection_rows(dets)
+    return dets
 
 
 def load_network_custom(cfg: str, weights: str, batch: int = 1, device: str = "cuda:0", sign_chains: bool = True,

@@ -317,13 +317,60 @@ XNOR_B200_API int xnor_b200_float_conv_map_yolo(const xnor_b200_conv_desc * desc
 
 /* The activation step of forward_yolo_layer_gpu (src-lib/yolo_layer.cpp:1439-1489) behind the path: logistic on the
  * x, y, objectness and class entries of every anchor, w and h raw, in one pass.  input/output
- * [batch][anchors][4 + 1 + classes][hw] (may be the same pointer).  Box decoding and NMS stay on the host side. */
+ * [batch][anchors][4 + 1 + classes][hw] (may be the same pointer).  Box decoding and NMS: xnor_b200_yolo_detections below. */
 XNOR_B200_API int xnor_b200_yolo_activate(const float * input, float * output, int batch, int anchors, int classes, int hw, void * stream);
 /* The activation step of the [region] head (forward_region_layer, src-lib/region_layer.cpp:494-537): logistic on x, y and
  * objectness, w and h raw, and with softmax != 0 a softmax over the class entries of every anchor and cell.
  * input/output [batch][anchors][coords + 1 + classes][hw], different pointers.  Agrees with Darknet's softmax to rounding. */
 XNOR_B200_API int xnor_b200_region_activate(const float * input, float * output, int batch, int anchors, int coords, int classes,
 		int softmax, int hw, void * stream);
+
+/* ---- detection heads on the device ------------------------------------------------------------------------------
+ * Darknet pulls every [yolo] output to the host after each forward (src-lib/yolo_layer.cpp:1439-1489) and decodes, filters
+ * and suppresses there.  These three calls do it on the device and leave a compact list of rows to copy back. */
+#define XNOR_B200_MAX_DETECTIONS 4096          /* largest max_dets (the suppression kernel keeps its lists in shared memory) */
+
+/* One [yolo] layer after its activation step (xnor_b200_yolo_activate): output [batch][n][4 + 1 + classes][h * w];
+ * anchors = the layer's own n anchor boxes in network pixels, {w0, h0, w1, h1, ...} = biases[2*mask[a]], biases[2*mask[a]+1]
+ * (src-lib/yolo_layer.cpp:22-42); new_coords as in the cfg. */
+typedef struct xnor_b200_yolo_head
+{
+	const float * output;
+	int w, h, n, classes;
+	float anchors[32];
+	int new_coords;
+} xnor_b200_yolo_head;
+
+/* Device buffers of a detection list, one list per image: boxes [batch][max_dets][4] = {x, y, w, h} (16-byte aligned),
+ * objectness [batch][max_dets], probs [batch][max_dets][classes], count [batch].  count may exceed max_dets when more
+ * detections pass the threshold than fit; only the first max_dets are stored, in the reference's scan order. */
+typedef struct xnor_b200_detections
+{
+	float * boxes;
+	float * objectness;
+	float * probs;
+	int * count;
+	int max_dets;
+	int classes;
+} xnor_b200_detections;
+
+/* get_yolo_detections + get_yolo_box + correct_yolo_boxes (src-lib/yolo_layer.cpp:1306-1348, :22-42, :1161-1222) for every
+ * image of the batch: each (cell, anchor) with objectness > thresh becomes a detection with prob[j] = objectness *
+ * class probability where that exceeds thresh, else 0.  img_w, img_h, relative, letter as in get_network_boxes
+ * (src-lib/darknet_network.cpp:1250).  append = 0 starts the lists, append = 1 continues them behind what an earlier head
+ * left (a network's heads in layer order, as fill_network_boxes does). */
+XNOR_B200_API int xnor_b200_yolo_detections(const xnor_b200_yolo_head * head, int batch, int netw, int neth, int img_w, int img_h,
+		float thresh, int relative, int letter, int append, const xnor_b200_detections * dets, void * stream);
+
+/* do_nms_sort (src-lib/box.cpp:951-1003): per class, in decreasing order of that class's probability, a kept detection
+ * zeroes the class probability of every later detection whose box_iou (:310-344) with it exceeds nms_thresh.  Equal
+ * probabilities keep their storage order (the reference's std::sort leaves that order unspecified). */
+XNOR_B200_API int xnor_b200_nms_sort(const xnor_b200_detections * dets, int batch, float nms_thresh, void * stream);
+
+/* The (detection, class) pairs with a probability above zero, detection-major, as rows of 7 floats {x, y, w, h, objectness,
+ * class, probability}: rows [batch][max_rows][7], row_count [batch] (may exceed max_rows; the surplus is not stored). */
+XNOR_B200_API int xnor_b200_detection_rows(const xnor_b200_detections * dets, int batch, float * rows, int max_rows, int * row_count,
+		void * stream);
 
 /* Bytes of the library-resident scratch array behind xnor_b200_conv_forward_static. */
 #define XNOR_B200_STATIC_SCRATCH_BYTES (8u << 20)

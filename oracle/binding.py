@@ -244,3 +244,89 @@ class RefLayer:
             self.close()
         except Exception:
             pass
+
+
+REFNET_SO = os.path.join(_HERE, "_ref", "liboracle_refnet.so")
+
+
+class RefNet:
+    """The reference's own network code on the CPU (oracle/_ref/liboracle_refnet.so, see build_refnet.py): load_network_custom
+    on a .cfg and a .weights file, network_predict, per-layer outputs, get_network_boxes + do_nms_sort."""
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REFNET_SO)
+
+    _lib = None
+
+    @classmethod
+    def lib(cls):
+        if cls._lib is None:
+            L = C.CDLL(REFNET_SO)
+            L.refnet_load.restype = C.c_void_p
+            L.refnet_load.argtypes = [C.c_char_p, C.c_char_p, C.c_int]
+            L.refnet_free.argtypes = [C.c_void_p]
+            L.refnet_layers.argtypes = [C.c_void_p]
+            L.refnet_layer_info.argtypes = [C.c_void_p, C.c_int, _i32p]
+            L.refnet_predict.argtypes = [C.c_void_p, _f32p]
+            L.refnet_layer_output.argtypes = [C.c_void_p, C.c_int, _f32p, C.c_int]
+            L.refnet_layer_weights.argtypes = [C.c_void_p, C.c_int, _f32p, C.c_int, _f32p, C.c_int]
+            L.refnet_detections.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int, _f32p, C.c_int]
+            L.refnet_nms_sort.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_float]
+            cls._lib = L
+        return cls._lib
+
+    def __init__(self, cfg_path: str, weights_path: str, batch: int = 1) -> None:
+        if not self.available():
+            raise FileNotFoundError(REFNET_SO)
+        self.batch = batch
+        self.handle = self.lib().refnet_load(cfg_path.encode(), weights_path.encode(), batch)
+        if not self.handle:
+            raise RuntimeError("the reference could not load the network")
+        self.n = self.lib().refnet_layers(self.handle)
+
+    def layer_info(self, i: int) -> dict:
+        v = np.zeros(10, np.int32)
+        self.lib().refnet_layer_info(self.handle, i, v)
+        keys = ("type", "outputs", "out_c", "out_h", "out_w", "xnor", "batch", "n", "activation", "packed")
+        return dict(zip(keys, (int(x) for x in v)))
+
+    def predict(self, x: np.ndarray) -> None:
+        if self.lib().refnet_predict(self.handle, np.ascontiguousarray(x, np.float32).reshape(-1)) != 0:
+            raise RuntimeError("network_predict failed")
+
+    def layer_output(self, i: int) -> np.ndarray:
+        info = self.layer_info(i)
+        out = np.empty(info["batch"] * info["outputs"], np.float32)
+        if self.lib().refnet_layer_output(self.handle, i, out, out.size) != 0:
+            raise RuntimeError(f"layer {i} has no output")
+        if info["out_c"] * info["out_h"] * info["out_w"] == info["outputs"]:
+            return out.reshape(info["batch"], info["out_c"], info["out_h"], info["out_w"])
+        return out.reshape(info["batch"], -1)
+
+    def layer_weights(self, i: int, nweights: int, n: int):
+        w, b = np.empty(nweights, np.float32), np.empty(n, np.float32)
+        if self.lib().refnet_layer_weights(self.handle, i, w, nweights, b, n) != 0:
+            raise RuntimeError(f"layer {i} has no weights of that size")
+        return w, b
+
+    def detections(self, w: int, h: int, thresh: float, nms: float, letter: int = 0, max_rows: int = 100000) -> np.ndarray:
+        """Rows {x, y, w, h, objectness, class, probability} of image 0 after get_network_boxes + do_nms_sort."""
+        rows = np.empty((max_rows, 7), np.float32)
+        n = self.lib().refnet_detections(self.handle, w, h, thresh, nms, letter, rows.reshape(-1), max_rows)
+        return rows[:n].copy()
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib().refnet_free(self.handle)
+            self.handle = None
+
+    @classmethod
+    def nms_sort(cls, boxes: np.ndarray, objectness: np.ndarray, probs: np.ndarray, thresh: float) -> np.ndarray:
+        """The reference's do_nms_sort on boxes [n][4], objectness [n], probs [n][classes]; returns the probabilities after
+        suppression, in the caller's order."""
+        out = np.ascontiguousarray(probs, np.float32).copy()
+        n, classes = out.shape
+        cls.lib().refnet_nms_sort(np.ascontiguousarray(boxes, np.float32).reshape(-1), np.ascontiguousarray(objectness, np.float32),
+                                  out.reshape(-1), n, classes, thresh)
+        return out
