@@ -449,6 +449,7 @@ def run_gpu_arm(args) -> None:
                                         "timing": "host clock; the next input's host-to-device copy overlaps the current forward", "calls": n_block}},
             "gpu_launches": args.steps * fps * network.own_launches_per_forward(net),
             "device_status": status,
+            "max_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
             "clocks": clocks,
         }
         print(json.dumps(line))
@@ -591,9 +592,75 @@ def kernel_rooflines(net, batch, binops_per_image, stream, flush, dev):
         "peak": hbm_peak, "unit": "GB/s", "frac": bp_bytes / (ms_bp * 1e-3) / 1e9 / hbm_peak,
         "traffic": traffic, "traffic_source": traffic_source, "algorithmic_bytes": bp_bytes, "ms": ms_bp, "peak_source": hbm_source,
     }
+    out["gpu_reference"] = time_reference_gpu_kernels(time_launches, dev)
     if device_status(capi) != 0:
         raise SystemExit("bench: a bounded wait ran out in a roofline launch")
     return out, roofline
+
+
+def time_reference_gpu_kernels(time_launches, dev):
+    """The kernel to beat: the reference's OWN GPU xnor kernels (src-lib/im2col_kernels.cu, compiled unmodified for sm_100a
+    into oracle/_ref/liboracle_refgpu.so) on BASELINE configuration 1, one image, called as forward_convolutional_layer_gpu
+    calls them (repack_input_gpu_bin, im2col_ongpu, transpose_uint32_gpu, gemm_nn_custom_bin_mean_transposed_gpu = its wmma b1
+    kernel), timed the same way as the library's own pack + GEMM on the same tensors.  None where that build is absent."""
+    import torch
+    import synth
+    from darknet_b200 import capi
+    from darknet_b200 import layer as L
+    from oracle import binding
+    so = getattr(binding, "REFGPU_SO", None)
+    if not so or not os.path.exists(so):
+        return None
+    ref = C.CDLL(so)
+    vp, ci = C.c_void_p, C.c_int
+    ref.refgpu_xnor_chain.argtypes = [ci] * 7 + [vp] * 8 + [ci, ci, vp]
+    c, h, w, n, ks = 256, 26, 26, 512, 3
+    x, wt, b = synth.conv_case(4242, 1, c, h, w, n, ks)
+    xg = torch.from_numpy(x).to(dev)
+    l = L.make_convolutional_layer(1, h, w, c, n, ks, 1, 1, capi.LEAKY, device=str(dev))
+    l.load_weights(torch.from_numpy(wt).to(dev), torch.from_numpy(b).to(dev))
+    L.binary_align_weights(l)
+    ours = L.forward_convolutional_layer_gpu(l, xg).clone()
+    inv = L.make_convolutional_layer(1, h, w, c, n, ks, 1, 1, capi.LEAKY, device=str(dev))
+    inv.load_weights(torch.from_numpy(wt).to(dev), torch.from_numpy(b).to(dev))
+    L.binary_align_weights(inv, invert=True)              # the complemented layout Darknet's GPU build stores
+    g = l.geom
+    words = (g.bit_align * g.k)                            # the reference's own (generous) workspace size, in floats
+    align_ws = torch.zeros(words, dtype=torch.float32, device=dev)
+    workspace = torch.zeros(words, dtype=torch.float32, device=dev)
+    transposed = torch.zeros(g.n_out * g.new_lda // 8 + 64, dtype=torch.uint8, device=dev)
+    out = torch.empty(1, n, g.out_h, g.out_w, device=dev)
+
+    def chain(gemm_only):
+        rc = ref.refgpu_xnor_chain(c, h, w, n, ks, 1, 1, xg.data_ptr(), align_ws.data_ptr(), workspace.data_ptr(), transposed.data_ptr(),
+                                   inv.align_bit_weights_gpu.data_ptr(), inv.mean_arr_gpu.data_ptr(), inv.biases_gpu.data_ptr(), out.data_ptr(),
+                                   1, int(gemm_only), torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise SystemExit(f"bench: the reference GPU kernels reported {rc}")
+
+    ms_chain = time_launches(lambda: chain(False))
+    ms_gemm = time_launches(lambda: chain(True))
+    diff = float((out - ours).abs().max())
+    packed = L.pack_input(l, xg)
+
+    def own_layer():
+        L.forward_convolutional_layer_gpu(l, xg)
+
+    def own_gemm():
+        capi.check(capi.lib().xnor_b200_gemm_bin_mean_transposed(n, g.n_out, g.k, l.align_bit_weights_gpu.data_ptr(), g.new_lda, packed.data_ptr(),
+                                                                 g.new_lda, l.output_gpu.data_ptr(), g.n_out, l.mean_arr_gpu.data_ptr(), l.biases_gpu.data_ptr(),
+                                                                 1, None, None, torch.cuda.current_stream().cuda_stream), "gemm")
+    ms_own, ms_own_gemm = time_launches(own_layer), time_launches(own_gemm)
+    ops = 2.0 * n * g.n_out * g.k
+    return {
+        "what": "BASELINE configuration 1 (3x3, 256 -> 512 filters, 26x26, leaky), one image, cold L2, CUDA graph of the launches",
+        "reference_kernels": "darknet src-lib/im2col_kernels.cu compiled unmodified for sm_100a (wmma b1 tensor kernel + its three input kernels)",
+        "reference_layer_us": 1000.0 * ms_chain, "reference_gemm_us": 1000.0 * ms_gemm, "reference_gemm_tops": ops / (ms_gemm * 1e-3) / 1e12,
+        "own_layer_us": 1000.0 * ms_own, "own_gemm_us": 1000.0 * ms_own_gemm, "own_gemm_tops": ops / (ms_own_gemm * 1e-3) / 1e12,
+        "layer_speedup": ms_chain / ms_own, "gemm_speedup": ms_gemm / ms_own_gemm,
+        "max_abs_difference_of_outputs": diff,
+        "note": "the reference computes count*mean+bias with one fused multiply-add on the GPU, this library with the CPU path's two roundings, hence a last-bit difference",
+    }
 
 
 # ---- single kernels (profiler captures, quick timings) ---------------------------------------------

@@ -247,6 +247,7 @@ class RefLayer:
 
 
 REFNET_SO = os.path.join(_HERE, "_ref", "liboracle_refnet.so")
+REFGPU_SO = os.path.join(_HERE, "_ref", "liboracle_refgpu.so")       # the reference's own GPU xnor kernels (timing baseline only)
 
 
 class RefNet:
