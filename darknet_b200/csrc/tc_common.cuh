@@ -162,11 +162,12 @@ struct FilterConsts
 	__device__ __forceinline__ int x(int f) const { return base[f]; }
 	__device__ __forceinline__ int mean(int f) const { return base[nf + f]; }
 	__device__ __forceinline__ int bias(int f) const { return base[2 * nf + f]; }
-	// f a multiple of 4
-	__device__ __forceinline__ void load8(int f, int (&fx)[8], int (&fm)[8], int (&fb)[8]) const
+	// N consecutive filters from f on (f and N multiples of 4)
+	template <int N>
+	__device__ __forceinline__ void load(int f, int (&fx)[N], int (&fm)[N], int (&fb)[N]) const
 	{
 		#pragma unroll
-		for (int h = 0; h < 2; ++h)
+		for (int h = 0; h < N / 4; ++h)
 		{
 			const int4 a = *reinterpret_cast<const int4 *>(base + f + 4 * h);
 			const int4 m = *reinterpret_cast<const int4 *>(base + nf + f + 4 * h);
@@ -230,19 +231,20 @@ __device__ __forceinline__ void epilogue_values(const TcParams & p, const Filter
 		if (col_ok)
 		{
 			uint32_t bits = 0;
-			// Eight filters at a time: their constants are read from shared memory first, then the eight values are formed,
-			// then stored.  A shared-memory read behind a store through a generic pointer cannot be moved ahead of it by
+			// NB filters at a time (eight; four beside a fused shortcut, whose operands in flight need the registers): their
+			// constants are read from shared memory first, then the values are formed, then stored.  A shared-memory read behind a store through a generic pointer cannot be moved ahead of it by
 			// the compiler, so one read per output in program order leaves the few epilogue warps waiting on every one.
+			constexpr int NB = SC ? 4 : 8;
 			const bool all_in = (f0 + fb + G <= p.M);
 			const float slope = p.leaky ? 0.1f : 1.0f;             // leaky(v) = max(v, 0.1 v), linear(v) = max(v, v): same bits as the select
 			#pragma unroll
-			for (int u0 = 0; u0 < G; u0 += 8)
+			for (int u0 = 0; u0 < G; u0 += NB)
 			{
-				int fx[8], fm[8], fb_[8];
-				s_fil.load8(fb + u0, fx, fm, fb_);                                   // six broadcast 16-byte reads
-				float v[8];
+				int fx[NB], fm[NB], fb_[NB];
+				s_fil.load<NB>(fb + u0, fx, fm, fb_);                               // broadcast 16-byte reads
+				float v[NB];
 				#pragma unroll
-				for (int j = 0; j < 8; ++j)
+				for (int j = 0; j < NB; ++j)
 				{
 					// 2*agree - K = (K - 2 popc(b)) - 2 popc(a) + 4 popc(a & b)
 					const int dot = k_b + fx[j] + 4 * (int)d[u0 + j];
@@ -251,7 +253,7 @@ __device__ __forceinline__ void epilogue_values(const TcParams & p, const Filter
 					v[j] = fmaxf(v[j], __fmul_rn(v[j], slope));
 				}
 				#pragma unroll
-				for (int j = 0; j < 8; ++j)
+				for (int j = 0; j < NB; ++j)
 				{
 					const int u = u0 + j;
 					if (all_in || f0 + fb + u < p.M)
@@ -342,7 +344,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams & p, const int * s_
 				for (int j0 = 0; j0 < 32; j0 += 8)
 				{
 					int fx[8], fm[8], fb_[8];
-					s_fil.load8(fbase + j0, fx, fm, fb_);
+					s_fil.load<8>(fbase + j0, fx, fm, fb_);
 					#pragma unroll
 					for (int j = 0; j < 8; ++j)
 					{
@@ -407,7 +409,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams & p, const int * s_
 		for (int j0 = 0; j0 < 32; j0 += 8)
 		{
 			int fx[8], fm[8], fb_[8];
-			s_fil.load8(fbase + j0, fx, fm, fb_);
+			s_fil.load<8>(fbase + j0, fx, fm, fb_);
 			float v[8];
 			#pragma unroll
 			for (int j = 0; j < 8; ++j)
