@@ -21,7 +21,7 @@ STATIC_SCRATCH_BYTES = 8 << 20  # XNOR_B200_STATIC_SCRATCH_BYTES
 EXPORTS = (
     "xnor_b200_strerror", "xnor_b200_last_cuda_error", "xnor_b200_set_tuning", "xnor_b200_conv_geometry",
     "xnor_b200_binarize_weights", "xnor_b200_binary_align_weights", "xnor_b200_float_to_bit",
-    "xnor_b200_repack_input_bin", "xnor_b200_pack_input", "xnor_b200_gemm_bin_mean_transposed",
+    "xnor_b200_repack_input_bin", "xnor_b200_pack_input", "xnor_b200_pack_words_bytes", "xnor_b200_pack_input_staged", "xnor_b200_gemm_bin_mean_transposed",
     "xnor_b200_gemm_counts", "xnor_b200_scratch_bytes", "xnor_b200_conv_forward",
     "xnor_b200_conv_forward_static", "xnor_b200_take_device_status",
     "xnor_b200_pack_input_pooled", "xnor_b200_conv_forward_pooled", "xnor_b200_float_conv_small", "xnor_b200_float_conv3_io", "xnor_b200_float_conv_map_weights_bytes",
@@ -61,7 +61,7 @@ ROUTE_AUTO, ROUTE_INTEGER, ROUTE_TENSOR, ROUTE_TILED = 0, 1, 2, 3
 
 class Tuning(C.Structure):
     """struct xnor_b200_tuning"""
-    _fields_ = [(n, C.c_int) for n in ("gemm_route", "gemm_tile", "gemm_split", "pack_ctas_per_sm", "tc_kernel", "tc_wait_polls", "tc_withhold_arrival")]
+    _fields_ = [(n, C.c_int) for n in ("gemm_route", "gemm_tile", "gemm_split", "pack_ctas_per_sm", "tc_kernel", "tc_wait_polls", "tc_withhold_arrival", "pack_two_pass")]
 
 
 class YoloHead(C.Structure):
@@ -116,6 +116,9 @@ def lib() -> C.CDLL:
     L.xnor_b200_float_to_bit.argtypes = [vp, vp, sz, vp]
     L.xnor_b200_repack_input_bin.argtypes = [vp, vp, ci, ci, ci, vp]
     L.xnor_b200_pack_input.argtypes = [dp, vp, vp, vp]
+    L.xnor_b200_pack_words_bytes.restype = sz
+    L.xnor_b200_pack_words_bytes.argtypes = [dp]
+    L.xnor_b200_pack_input_staged.argtypes = [dp, vp, vp, vp, vp]
     L.xnor_b200_gemm_bin_mean_transposed.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, vp, vp, ci, vp, vp, vp]
     L.xnor_b200_gemm_counts.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp]
     L.xnor_b200_scratch_bytes.restype = sz

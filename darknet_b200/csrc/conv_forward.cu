@@ -101,6 +101,7 @@ extern "C" int xnor_b200_set_tuning(const xnor_b200_tuning * t)
 	}
 	if (t->gemm_route < XNOR_B200_ROUTE_AUTO || t->gemm_route > XNOR_B200_ROUTE_TILED) { return XNOR_B200_ERR_INVALID; }
 	if (t->gemm_tile < 0 || t->gemm_split < 0 || t->gemm_split > 8 || t->pack_ctas_per_sm < 0 || t->pack_ctas_per_sm > 32) { return XNOR_B200_ERR_INVALID; }
+	if (t->pack_two_pass < 0 || t->pack_two_pass > 2) { return XNOR_B200_ERR_INVALID; }
 	if (t->tc_kernel < 0 || t->tc_kernel > 2) { return XNOR_B200_ERR_INVALID; }
 	if (t->tc_wait_polls < 0 || t->tc_withhold_arrival < 0 || t->tc_withhold_arrival > 1) { return XNOR_B200_ERR_INVALID; }
 	g_tuning = *t;

@@ -39,8 +39,6 @@ struct PackParams
 	int groups;          // word path: channel-block groups per strip
 	int ldw;             // words per packed row (new_ldb/32)
 	int K;               // bits per row that carry data
-	int tab_offset;      // word path: offset (in words) of the K-word table behind the staged rows
-	int lpp_shift;       // word path: log2 of the lanes that share one output pixel in phase B
 	// Optional max-pool in front of the convolution (pool_size == 0: none).  H and W above are then the POOLED
 	// sizes the convolution sees, in_h and in_w the sizes of the tensor actually in memory.
 	int pool_size, pool_stride, pool_off;
@@ -48,7 +46,15 @@ struct PackParams
 	int pool_fast;       // 2x2 window, stride 2, origin 0, even in_h/in_w, 8-byte aligned planes: two float2 loads
 	int win_w;           // > 0: output rows of an image in 2x2-window-major pixel order (OW / 2), see out_row()
 	int from_planes;     // bit path: `in` holds sign planes uint32 [image][C][H][ceil(W/32)] (bit x%32 of word x/32) instead of floats
+	// word path: reciprocals for fast_div() of the divisors the kernels meet, made once on the host
+	uint32_t m_ow, m_wp, m_taps, m_ks, m_groups, m_tiles;
+	uint32_t m_nq[2];    // threads per pixel in phase B = min(uint4 per pixel of a group, PK_THREADS): [0] every group but the last, [1] the last
+	uint32_t m_rv[2];    // staged rows of a strip: [0] full strips, [1] the last (shorter) strip of an image
 };
+
+// n / d for 0 <= n < 2^32 / d with m = ceil(2^32 / d): one multiply instead of a division sequence.
+__device__ __forceinline__ int fast_div(int n, int d, uint32_t m) { return (d == 1) ? n : (int)__umulhi((uint32_t)n, m); }
+static uint32_t div_magic(int d) { return (d <= 1) ? 0u : (uint32_t)(0xffffffffu / (uint32_t)d + 1u); }
 
 // Row of the packed operand that belongs to output pixel (oy, ox) of image b.  Row-major by default; window-major
 // (the four pixels of a 2x2 pool window on consecutive rows) when the layer's GEMM epilogue pools its output.
@@ -87,68 +93,86 @@ __device__ __forceinline__ bool pooled_positive(const float * __restrict__ plane
 	return pos;
 }
 
-// Phase B of the word path, shared by the kernels that stage channel-packed words in shared memory: assembles the
-// packed rows of output rows y0..y1-1 for the channel blocks cb0..cb0+cbn-1 (group g) from s_words[cbl][R][W].
-__device__ __forceinline__ void words_phase_b(const PackParams & p, uint32_t * s_words, int b, int g, int y0, int y1,
-		int iy_lo, int R, int CB, int cb0, int cbn)
+// Staging layout of the word path, shared by the kernels below: s_words[cbl][RV][WP], the strip's input rows WITH the
+// convolution's zero padding written out -- RV = (rows - 1) * stride + ks virtual rows starting at input row
+// y0 * stride - pad, WP = W + 2 * pad columns starting at input column -pad.  A tap of an output pixel is then always
+// inside the staged block, so phase B needs no bounds checks.
+__device__ __forceinline__ int strip_virtual_rows(const PackParams & p, int y0, int y1) { return (y1 - y0 - 1) * p.stride + p.ks; }
+
+// Phase B of the word path: assembles the packed rows of output rows y0..y1-1 for the channel blocks cb0..cb0+cbn-1
+// (group g) from the staged block.  A thread owns one uint4 (4 K-words) position of the group's range and walks the
+// strip's pixels with it: the four offsets into the staged block are worked out once, and per pixel there remain four
+// shared loads, one 16-byte store and a few additions -- no table, no division, no bounds check.  `lanes` threads share a
+// pixel (all of the group's uint4 positions when there are at most PK_THREADS of them), so consecutive threads write
+// consecutive 16-byte pieces of one row and then of the next.
+template <bool WIN>
+__device__ __forceinline__ void words_phase_b_impl(const PackParams & p, const uint32_t * s_words, int b, int g, int y0, int y1,
+		int RV, int WP, int CB, int cb0, int cbn)
 {
-	// phase B: one uint4 (4 K-words) per thread-iteration over this CTA's word range.
-	// A small table maps every K-word of the range to (offset inside the staged rows, ky, kx) once per CTA, so
-	// the per-word work is a table read, two bounds checks and one shared load -- no integer division.
 	const int taps = p.ks * p.ks;
 	const int new_k = CB * taps;
 	const bool last_group = (g == p.groups - 1);
 	const int q_lo = (cb0 * taps) >> 2;                                   // cb0 % 4 == 0 whenever groups > 1
 	const int q_hi = last_group ? (p.ldw >> 2) : (((cb0 + cbn) * taps) >> 2);
 	const int nq = q_hi - q_lo;
-	uint32_t * s_tab = s_words + p.tab_offset;                            // nq*4 entries: off | ky << 20 | kx << 26
-	for (int i = threadIdx.x; i < nq * 4; i += PK_THREADS)
-	{
-		const int wi = q_lo * 4 + i;
-		uint32_t e = 0xffffffffu;                                         // padding word
-		if (wi < new_k)
-		{
-			const int cb = wi / taps;
-			const int t = wi - cb * taps;
-			const int ky = t / p.ks;
-			const int kx = t - ky * p.ks;
-			e = (uint32_t)(((cb - cb0) * R + ky) * p.W + kx) | ((uint32_t)ky << 20) | ((uint32_t)kx << 26);
-		}
-		s_tab[i] = e;
-	}
-	__syncthreads();
-
+	const int lanes = min(nq, PK_THREADS);
+	const uint32_t m_lanes = last_group ? p.m_nq[1] : p.m_nq[0];
+	const int slots = fast_div(PK_THREADS, lanes, m_lanes);               // pixels worked on at the same time
+	const int slot = fast_div(threadIdx.x, lanes, m_lanes);
+	const int lane = threadIdx.x - slot * lanes;
+	if (slot >= slots) { return; }                                        // PK_THREADS % lanes left-over threads
 	const int pixels = (y1 - y0) * p.OW;
-	const int lpp = 1 << p.lpp_shift;                                     // lanes per pixel: power of two >= min(nq, 32)
-	const int wq_first = threadIdx.x & (lpp - 1);
-	for (int pl = threadIdx.x >> p.lpp_shift; pl < pixels; pl += PK_THREADS >> p.lpp_shift)
+	const int yl0 = fast_div(slot, p.OW, p.m_ow), x0 = slot - yl0 * p.OW;
+	const int d_yl = fast_div(slots, p.OW, p.m_ow), d_x = slots - d_yl * p.OW;
+	const int d_base = (d_yl * WP + d_x) * p.stride;                      // staged offset of a pixel: (yl * WP + x) * stride
+	const int wrap_base = (WP - p.OW) * p.stride;                         // extra when x runs over the end of an output row
+	const int ldq = p.ldw >> 2;
+	uint4 * const out_img = reinterpret_cast<uint4 *>(p.out) + (size_t)b * p.OH * p.OW * ldq;
+	for (int wq = lane; wq < nq; wq += lanes)
 	{
-		const int yl = pl / p.OW;
-		const int x = pl - yl * p.OW;
-		const int iy_base = (y0 + yl) * p.stride - p.pad - iy_lo;   // relative to the staged rows
-		const int ix_base = x * p.stride - p.pad;
-		const int base_off = iy_base * p.W + ix_base;
-		uint4 * dst = reinterpret_cast<uint4 *>(p.out + out_row(p, b, y0 + yl, x) * p.ldw) + q_lo;
-		for (int wq = wq_first; wq < nq; wq += lpp)
+		int e[4];
+		#pragma unroll
+		for (int u = 0; u < 4; ++u)
 		{
-			const uint4 e4 = reinterpret_cast<const uint4 *>(s_tab)[wq];
-			const uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
-			uint32_t v[4];
-			#pragma unroll
-			for (int u = 0; u < 4; ++u)
+			const int wi = (q_lo + wq) * 4 + u;
+			const int cb = fast_div(wi, taps, p.m_taps);
+			const int t = wi - cb * taps;
+			const int ky = fast_div(t, p.ks, p.m_ks);
+			e[u] = (wi < new_k) ? ((cb - cb0) * RV + ky) * WP + (t - ky * p.ks) : -1;      // -1: padding word of the row
+		}
+		int yl = yl0, x = x0;
+		int base = (yl0 * WP + x0) * p.stride;
+		uint4 * dst = out_img + (size_t)(y0 * p.OW + slot) * ldq + q_lo + wq;               // row-major rows: a constant step per round
+		const size_t d_dst = (size_t)slots * ldq;
+		for (int pl = slot; pl < pixels; pl += slots)
+		{
+			uint4 v;
+			v.x = (e[0] >= 0) ? s_words[base + e[0]] : 0u;
+			v.y = (e[1] >= 0) ? s_words[base + e[1]] : 0u;
+			v.z = (e[2] >= 0) ? s_words[base + e[2]] : 0u;
+			v.w = (e[3] >= 0) ? s_words[base + e[3]] : 0u;
+			if (WIN)
 			{
-				uint32_t word = 0;
-				if (e[u] != 0xffffffffu)
-				{
-					const int r = iy_base + (int)((e[u] >> 20) & 63u);
-					const int ix = ix_base + (int)(e[u] >> 26);
-					if (r >= 0 && r < R && ix >= 0 && ix < p.W) { word = s_words[base_off + (int)(e[u] & 0xfffffu)]; }
-				}
-				v[u] = word;
+				const int oy = y0 + yl;
+				out_img[(size_t)(((oy >> 1) * p.win_w + (x >> 1)) * 4 + (oy & 1) * 2 + (x & 1)) * ldq + q_lo + wq] = v;
+				yl += d_yl;
 			}
-			dst[wq] = make_uint4(v[0], v[1], v[2], v[3]);
+			else
+			{
+				*dst = v;
+				dst += d_dst;
+			}
+			x += d_x; base += d_base;
+			if (x >= p.OW) { x -= p.OW; base += wrap_base; if (WIN) { ++yl; } }
 		}
 	}
+}
+
+__device__ __forceinline__ void words_phase_b(const PackParams & p, const uint32_t * s_words, int b, int g, int y0, int y1,
+		int RV, int WP, int CB, int cb0, int cbn)
+{
+	if (p.win_w > 0) { words_phase_b_impl<true>(p, s_words, b, g, y0, y1, RV, WP, CB, cb0, cbn); }
+	else { words_phase_b_impl<false>(p, s_words, b, g, y0, y1, RV, WP, CB, cb0, cbn); }
 }
 
 // ---- word path -----------------------------------------------------------------------------
@@ -158,25 +182,36 @@ __device__ __forceinline__ void words_phase_b(const PackParams & p, uint32_t * s
 //        to work; 1 on large ones, where a thread then keeps 32 independent loads in flight).
 // POOL = the tensor in memory is max-pooled on the fly (always with VEC == 1: pooled pixels are not contiguous).
 template <int VEC, int SUBS, bool POOL = false>
-__global__ void __launch_bounds__(PK_THREADS)
+__global__ void __launch_bounds__(PK_THREADS, 4)
 pack_input_words_kernel(const PackParams p)
 {
 	extern __shared__ uint32_t s_words[];
-	const int g = blockIdx.x % p.groups;
-	const int rest = blockIdx.x / p.groups;
-	const int tile = rest % p.tiles_per_image;
-	const int b = rest / p.tiles_per_image;
+	const int rest = fast_div((int)blockIdx.x, p.groups, p.m_groups);
+	const int g = (int)blockIdx.x - rest * p.groups;
+	const int b = fast_div(rest, p.tiles_per_image, p.m_tiles);
+	const int tile = rest - b * p.tiles_per_image;
 	const int y0 = tile * p.rows_per_cta;
 	const int y1 = min(y0 + p.rows_per_cta, p.OH);
-	const int iy_lo = max(y0 * p.stride - p.pad, 0);
+	const int iy_v0 = y0 * p.stride - p.pad;  // input row of staged row 0 (may be negative: padding)
+	const int iy_lo = max(iy_v0, 0);
 	const int iy_hi = min((y1 - 1) * p.stride - p.pad + p.ks - 1, p.H - 1);
-	const int R = iy_hi - iy_lo + 1;          // may be <= 0 when the strip only sees padding
+	const int R = iy_hi - iy_lo + 1;          // rows that exist in the image; may be <= 0 when the strip only sees padding
+	const int RV = strip_virtual_rows(p, y0, y1);
+	const int WP = p.W + 2 * p.pad;
 	const int CB = p.C >> 5;
 	const int cb0 = g * p.cb_per_cta;
 	const int cbn = min(p.cb_per_cta, CB - cb0);
 	const int span = max(R, 0) * p.W;         // contiguous floats per channel
 	const size_t chan_stride = POOL ? (size_t)p.in_h * p.in_w : (size_t)p.H * p.W;
 	const float * img = p.in + ((size_t)b * p.C + (size_t)cb0 * 32) * chan_stride + (POOL ? 0 : (size_t)iy_lo * p.W);
+
+	// the padding around the rows phase A fills
+	if (p.pad > 0 || R < RV)
+	{
+		for (int i = threadIdx.x; i < cbn * RV * WP; i += PK_THREADS) { s_words[i] = 0u; }
+		__syncthreads();
+	}
+	const int stage0 = (iy_lo - iy_v0) * WP + p.pad;   // staged offset of image element (iy_lo, 0)
 
 	// phase A: 32 channels -> one word per input pixel
 	{
@@ -240,15 +275,18 @@ pack_input_words_kernel(const PackParams p)
 					}
 				}
 			}
+			// VEC divides W, so the VEC positions share a row
+			const int r = (ev * VEC) / p.W;
+			const int at = (cbl * RV + r) * WP + stage0 + (ev * VEC - r * p.W);
 			if (SUBS == 1)
 			{
 				#pragma unroll
-				for (int j = 0; j < VEC; ++j) { s_words[(size_t)item * VEC + j] = w[j]; }
+				for (int j = 0; j < VEC; ++j) { s_words[at + j] = w[j]; }
 			}
 			else
 			{
 				// SUBS == 4: this thread owns byte `sub` of each word
-				uint8_t * dst = reinterpret_cast<uint8_t *>(s_words) + (size_t)item * VEC * 4 + sub;
+				uint8_t * dst = reinterpret_cast<uint8_t *>(s_words + at) + sub;
 				#pragma unroll
 				for (int j = 0; j < VEC; ++j) { dst[j * 4] = (uint8_t)w[j]; }
 			}
@@ -256,7 +294,7 @@ pack_input_words_kernel(const PackParams p)
 	}
 	__syncthreads();
 
-	words_phase_b(p, s_words, b, g, y0, y1, iy_lo, R, CB, cb0, cbn);
+	words_phase_b(p, s_words, b, g, y0, y1, RV, WP, CB, cb0, cbn);
 }
 
 // The same packing when the previous xnor layer already left its output as sign bits, 32 channels per word
@@ -267,52 +305,87 @@ __global__ void __launch_bounds__(PK_THREADS)
 pack_input_from_signs_kernel(const PackParams p)
 {
 	extern __shared__ uint32_t s_words[];
-	const int g = blockIdx.x % p.groups;
-	const int rest = blockIdx.x / p.groups;
-	const int tile = rest % p.tiles_per_image;
-	const int b = rest / p.tiles_per_image;
+	const int rest = fast_div((int)blockIdx.x, p.groups, p.m_groups);
+	const int g = (int)blockIdx.x - rest * p.groups;
+	const int b = fast_div(rest, p.tiles_per_image, p.m_tiles);
+	const int tile = rest - b * p.tiles_per_image;
 	const int y0 = tile * p.rows_per_cta;
 	const int y1 = min(y0 + p.rows_per_cta, p.OH);
-	const int iy_lo = max(y0 * p.stride - p.pad, 0);
-	const int iy_hi = min((y1 - 1) * p.stride - p.pad + p.ks - 1, p.H - 1);
-	const int R = iy_hi - iy_lo + 1;
+	const int iy_v0 = y0 * p.stride - p.pad;
+	const int RV = strip_virtual_rows(p, y0, y1);
+	const int WP = p.W + 2 * p.pad;
 	const int CB = p.C >> 5;
 	const int cb0 = g * p.cb_per_cta;
 	const int cbn = min(p.cb_per_cta, CB - cb0);
-	const int span = max(R, 0) * p.W;
 	const size_t plane = (size_t)p.in_h * p.in_w;
 	const uint32_t * bits = reinterpret_cast<const uint32_t *>(p.in) + ((size_t)b * CB + cb0) * plane;
-	for (int idx = threadIdx.x; idx < cbn * span; idx += PK_THREADS)
+	// phase A walks the staged block itself, padding included: a warp takes four staged rows at a time (four independent
+	// loads per lane), lanes run along the row
+	const int lane = threadIdx.x & 31;
+	const int warp = threadIdx.x >> 5;
+	constexpr int NW = PK_THREADS / 32;
+	const uint32_t m_rv = p.m_rv[(y1 - y0 == p.rows_per_cta) ? 0 : 1];
+	const int units = cbn * RV;
+	for (int u0 = warp; u0 < units; u0 += 4 * NW)
 	{
-		const int cbl = idx / span;
-		const int e = idx - cbl * span;
-		const uint32_t * src = bits + (size_t)cbl * plane;
-		uint32_t word = 0;
-		if (p.pool_size == 0)
+		const uint32_t * src[4];
+		bool ok[4];
+		#pragma unroll
+		for (int k = 0; k < 4; ++k)
 		{
-			word = __ldg(src + (size_t)iy_lo * p.W + e);
+			const int u = min(u0 + k * NW, units - 1);
+			const int cbl = fast_div(u, RV, m_rv);
+			const int iy = iy_v0 + (u - cbl * RV);
+			ok[k] = (u0 + k * NW < units) && iy >= 0 && iy < p.H;
+			src[k] = bits + (size_t)cbl * plane;
+			if (p.pool_size == 0) { src[k] += (ptrdiff_t)iy * p.W - p.pad; }
+			else { src[k] += (ptrdiff_t)(iy * p.pool_stride - p.pool_off) * p.in_w; }      // first window row
 		}
-		else
+		for (int cv = lane; cv < WP; cv += 32)
 		{
-			const int rl = e / p.W;
-			const int xl = e - rl * p.W;
-			const int py0 = (iy_lo + rl) * p.pool_stride - p.pool_off;
-			const int px0 = xl * p.pool_stride - p.pool_off;
-			for (int l = 0; l < p.pool_size; ++l)
+			const int ix = cv - p.pad;
+			const bool col_ok = (ix >= 0 && ix < p.W);
+			uint32_t v[4];
+			#pragma unroll
+			for (int k = 0; k < 4; ++k)
 			{
-				const int yy = py0 + l;
-				if (yy < 0 || yy >= p.in_h) { continue; }
-				for (int m = 0; m < p.pool_size; ++m)
+				uint32_t word = 0;
+				if (ok[k] && col_ok)
 				{
-					const int xx = px0 + m;
-					if (xx >= 0 && xx < p.in_w) { word |= __ldg(src + (size_t)yy * p.in_w + xx); }
+					if (p.pool_size == 0)
+					{
+						word = __ldg(src[k] + cv);
+					}
+					else
+					{
+						// src[k] is row py0 of the unpooled plane; rows and columns outside the image are skipped
+						const int u = u0 + k * NW;
+						const int iy = iy_v0 + (u - fast_div(u, RV, m_rv) * RV);
+						const int py0 = iy * p.pool_stride - p.pool_off;
+						const int px0 = ix * p.pool_stride - p.pool_off;
+						for (int l = 0; l < p.pool_size; ++l)
+						{
+							if (py0 + l < 0 || py0 + l >= p.in_h) { continue; }
+							for (int m = 0; m < p.pool_size; ++m)
+							{
+								const int xx = px0 + m;
+								if (xx >= 0 && xx < p.in_w) { word |= __ldg(src[k] + (ptrdiff_t)l * p.in_w + xx); }
+							}
+						}
+					}
 				}
+				v[k] = word;
+			}
+			#pragma unroll
+			for (int k = 0; k < 4; ++k)
+			{
+				const int u = u0 + k * NW;
+				if (u < units) { s_words[u * WP + cv] = v[k]; }
 			}
 		}
-		s_words[idx] = word;
 	}
 	__syncthreads();
-	words_phase_b(p, s_words, b, g, y0, y1, iy_lo, R, CB, cb0, cbn);
+	words_phase_b(p, s_words, b, g, y0, y1, RV, WP, CB, cb0, cbn);
 }
 
 // Phase A of the bit kernels: planes[c][rr][xw] = ballot of (input(c, iy0 + rr, 32*xw + lane - pad) > 0).
@@ -580,9 +653,105 @@ float_to_bit_kernel(const float * __restrict__ src, uint32_t * __restrict__ dst,
 	}
 }
 
-int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
-		uint32_t * t_bit_input, cudaStream_t stream, int from_signs, int window_major)
+
+// ---- first pass of the two-pass word path -------------------------------------------------------
+// input [blocks][32][hw] fp32 -> words [blocks][hw], bit ch of a word = input(block, ch, e) > 0; `blocks` = images x
+// 32-channel blocks.  A pure stream: a thread owns VEC consecutive positions of one block and keeps 16 independent
+// VEC-wide loads in flight, twice; no shared memory, no halo, nothing read twice.
+// Loads written as volatile inline PTX: the compiler otherwise folds load, compare and OR into a chain with a handful of
+// loads in flight, and this kernel lives on bytes in flight.
+template <int VEC> struct StreamLoad;
+template <> struct StreamLoad<4>
 {
+	static __device__ __forceinline__ void ld(const float * p, float (&v)[4])
+	{
+		asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "l"(p));
+	}
+};
+template <> struct StreamLoad<2>
+{
+	static __device__ __forceinline__ void ld(const float * p, float (&v)[2])
+	{
+		asm volatile("ld.global.nc.L1::no_allocate.v2.f32 {%0, %1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "l"(p));
+	}
+};
+template <> struct StreamLoad<1>
+{
+	static __device__ __forceinline__ void ld(const float * p, float (&v)[1])
+	{
+		asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v[0]) : "l"(p));
+	}
+};
+
+template <int VEC>
+__global__ void __launch_bounds__(PK_THREADS)
+sign_words_kernel(const float * __restrict__ in, uint32_t * __restrict__ words, int hwv, long long items)
+{
+	const long long idx = (long long)blockIdx.x * PK_THREADS + threadIdx.x;
+	if (idx >= items) { return; }
+	const long long blk = idx / hwv;
+	const int ev = (int)(idx - blk * hwv);
+	const size_t hw = (size_t)hwv * VEC;
+	const float * src = in + (size_t)blk * 32 * hw + (size_t)ev * VEC;
+	uint32_t w[VEC];
+	#pragma unroll
+	for (int j = 0; j < VEC; ++j) { w[j] = 0; }
+	#pragma unroll
+	for (int ch0 = 0; ch0 < 32; ch0 += 16)
+	{
+		float v[16][VEC];
+		#pragma unroll
+		for (int u = 0; u < 16; ++u) { StreamLoad<VEC>::ld(src + (size_t)(ch0 + u) * hw, v[u]); }
+		#pragma unroll
+		for (int u = 0; u < 16; ++u)
+		{
+			#pragma unroll
+			for (int j = 0; j < VEC; ++j) { w[j] |= (v[u][j] > 0 ? 1u : 0u) << (ch0 + u); }
+		}
+	}
+	uint32_t * dst = words + (size_t)blk * hw + (size_t)ev * VEC;
+	if (VEC == 4) { *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1 % VEC], w[2 % VEC], w[3 % VEC]); }
+	else if (VEC == 2) { *reinterpret_cast<uint2 *>(dst) = make_uint2(w[0], w[1 % VEC]); }
+	else { dst[0] = w[0]; }
+}
+
+size_t pack_words_bytes(const xnor_b200_conv_desc & d)
+{
+	if (d.c % 32 != 0) { return 0; }
+	return round_up((size_t)d.batch * (d.c / 32) * d.h * d.w * 4, 256);
+}
+
+static int launch_sign_words(const xnor_b200_conv_desc & d, const float * input, uint32_t * words, cudaStream_t stream)
+{
+	const size_t hw = (size_t)d.h * d.w;
+	const long long blocks = (long long)d.batch * (d.c / 32);
+	const bool a16 = (((uintptr_t)input | (uintptr_t)words) & 15u) == 0;
+	const bool a8 = (((uintptr_t)input | (uintptr_t)words) & 7u) == 0;
+	// the widest loads that still give every SM a CTA: bytes in flight per thread are what the kernel lives on
+	const long long min_items = (long long)sm_count() * PK_THREADS;
+	int vec = 1;
+	if (hw % 4 == 0 && a16 && blocks * (long long)(hw / 4) >= min_items) { vec = 4; }
+	else if (hw % 2 == 0 && a8 && blocks * (long long)(hw / 2) >= min_items) { vec = 2; }
+	const long long items = blocks * (long long)(hw / vec);
+	const long long grid = (items + PK_THREADS - 1) / PK_THREADS;
+	if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
+	if (vec == 4) { sign_words_kernel<4><<<(unsigned)grid, PK_THREADS, 0, stream>>>(input, words, (int)(hw / 4), items); }
+	else if (vec == 2) { sign_words_kernel<2><<<(unsigned)grid, PK_THREADS, 0, stream>>>(input, words, (int)(hw / 2), items); }
+	else { sign_words_kernel<1><<<(unsigned)grid, PK_THREADS, 0, stream>>>(input, words, (int)hw, items); }
+	return check_launch();
+}
+
+int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
+		uint32_t * t_bit_input, cudaStream_t stream, int from_signs, int window_major, uint32_t * words_scratch)
+{
+	// Two passes on request: a streaming pass leaves the sign words, the staging kernel then reads those (1/32 of the
+	// bytes, out of L2) instead of the floats.  Measured against the single kernel it only draws level on the largest maps.
+	if (words_scratch != nullptr && !from_signs && pool == nullptr && d.c % 32 == 0 && tuning().pack_two_pass == 2)
+	{
+		const int rc = launch_sign_words(d, input, words_scratch, stream);
+		if (rc != XNOR_B200_OK) { return rc; }
+		return launch_pack_input(d, nullptr, reinterpret_cast<const float *>(words_scratch), t_bit_input, stream, 1, window_major, nullptr);
+	}
 	if (from_signs && d.c % 32 != 0 && pool != nullptr) { return XNOR_B200_ERR_INVALID; }     // sign planes are made at the size the convolution sees
 	PackParams p;
 	p.from_planes = (from_signs && d.c % 32 != 0) ? 1 : 0;
@@ -612,8 +781,6 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc *
 	p.ks = d.size; p.stride = d.stride; p.pad = d.pad;
 	p.K = d.size * d.size * d.c;
 	p.ldw = aligned_lda(p.K) / 32;
-	p.tab_offset = 0;
-	p.lpp_shift = 0;
 	const bool word_path = (d.c % 32 == 0);
 	if (d.size > 63) { return XNOR_B200_ERR_TOO_LARGE; }             // kernel offsets are kept in 6-bit fields
 	// CTAs to aim for.  Each CTA loads, synchronises, then stores, so overlap of loads and stores comes from
@@ -638,24 +805,29 @@ int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc *
 		p.cb_per_cta = cb_per_cta;
 		p.groups = (CB + cb_per_cta - 1) / cb_per_cta;
 		ctas *= p.groups;
-		const size_t row_bytes = (size_t)cb_per_cta * d.w * 4;
-		if (row_bytes * (size_t)min(in_rows(1), d.h) > PK_MAX_SMEM) { return XNOR_B200_ERR_TOO_LARGE; }
-		const int strips = (int)min((long long)p.OH, max(1LL, (want_ctas + ctas - 1) / ctas));
+		const size_t row_bytes = (size_t)cb_per_cta * (d.w + 2 * d.pad) * 4;       // one staged row, padding columns included
+		if (row_bytes * (size_t)in_rows(1) > PK_MAX_SMEM) { return XNOR_B200_ERR_TOO_LARGE; }
+		// rounded down: a grid a little over what fits at once costs a second, nearly empty wave
+		const int strips = (int)min((long long)p.OH, max(1LL, want_ctas / ctas));
 		int rows = (p.OH + strips - 1) / strips;
-		const size_t room = PK_MAX_SMEM - (size_t)p.ldw * 4 - 16;            // staged rows share the limit with the K-word table
-		if (row_bytes * (size_t)min(in_rows(1), d.h) > room) { return XNOR_B200_ERR_TOO_LARGE; }
-		while (rows > 1 && row_bytes * (size_t)min(in_rows(rows), d.h) > room) { --rows; }
+		const size_t room = PK_MAX_SMEM;
+		while (rows > 1 && row_bytes * (size_t)in_rows(rows) > room) { --rows; }
 		p.rows_per_cta = rows;
 		p.tiles_per_image = (p.OH + rows - 1) / rows;
-		const size_t words_bytes = round_up(row_bytes * (size_t)min(in_rows(rows), d.h), 16);
-		p.tab_offset = (int)(words_bytes / 4);
-		const size_t smem = words_bytes + (size_t)p.ldw * 4;             // + the K-word table (at most ldw entries)
-		const int nq_max = (p.groups > 1) ? max((cb_per_cta * d.size * d.size) >> 2, (p.ldw >> 2) - (((p.groups - 1) * cb_per_cta * d.size * d.size) >> 2))
-		                                  : (p.ldw >> 2);
-		p.lpp_shift = 0;
-		while ((1 << p.lpp_shift) < min(nq_max, 32)) { ++p.lpp_shift; }
+		const size_t words_bytes = round_up(row_bytes * (size_t)in_rows(rows), 16);
+		{
+			const int taps = d.size * d.size, wp = d.w + 2 * d.pad;
+			const int nq_first = (cb_per_cta * taps) >> 2;
+			const int nq_last = (p.ldw >> 2) - (((p.groups - 1) * cb_per_cta * taps) >> 2);
+			const int last_rows = p.OH - (p.tiles_per_image - 1) * rows;
+			p.m_groups = div_magic(p.groups); p.m_tiles = div_magic(p.tiles_per_image);
+			p.m_ow = div_magic(p.OW); p.m_wp = div_magic(wp); p.m_taps = div_magic(taps); p.m_ks = div_magic(d.size);
+			p.m_nq[0] = div_magic(min(nq_first, PK_THREADS)); p.m_nq[1] = div_magic(min(nq_last, PK_THREADS));
+			p.m_rv[0] = div_magic(in_rows(rows)); p.m_rv[1] = div_magic(in_rows(last_rows));
+		}
+		const size_t smem = words_bytes;
 		const long long grid = (long long)d.batch * p.tiles_per_image * p.groups;
-		if (grid > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
+		if (grid > 0x7fffffffLL || grid * max(p.groups, p.tiles_per_image) > 0xffffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }   // fast_div range
 		const int vec = (pool != nullptr) ? 1
 				: ((d.w % 4 == 0) && (((uintptr_t)input & 15u) == 0)) ? 4
 				: ((d.w % 2 == 0) && (((uintptr_t)input & 7u) == 0)) ? 2 : 1;
@@ -713,6 +885,23 @@ extern "C" int xnor_b200_pack_input(const xnor_b200_conv_desc * desc, const floa
 	if (rc != XNOR_B200_OK) { return rc; }
 	if (((uintptr_t)t_bit_input & 15u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
 	return launch_pack_input(*desc, nullptr, input, (uint32_t *)t_bit_input, (cudaStream_t)stream);
+}
+
+extern "C" size_t xnor_b200_pack_words_bytes(const xnor_b200_conv_desc * desc)
+{
+	if (desc == nullptr || validate_desc(desc) != XNOR_B200_OK) { return 0; }
+	return pack_words_bytes(*desc);
+}
+
+extern "C" int xnor_b200_pack_input_staged(const xnor_b200_conv_desc * desc, const float * input, uint32_t * words,
+		uint8_t * t_bit_input, void * stream)
+{
+	if (desc == nullptr || input == nullptr || words == nullptr || t_bit_input == nullptr) { return XNOR_B200_ERR_NULL; }
+	int rc = validate_desc(desc);
+	if (rc != XNOR_B200_OK) { return rc; }
+	if (desc->c % 32 != 0) { return XNOR_B200_ERR_INVALID; }
+	if (((uintptr_t)t_bit_input & 15u) != 0 || ((uintptr_t)words & 15u) != 0) { return XNOR_B200_ERR_ALIGNMENT; }
+	return launch_pack_input(*desc, nullptr, input, (uint32_t *)t_bit_input, (cudaStream_t)stream, 0, 0, words);
 }
 
 extern "C" int xnor_b200_pack_input_pooled(const xnor_b200_conv_desc * desc, const xnor_b200_pool_desc * pool,

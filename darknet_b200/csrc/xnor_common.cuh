@@ -139,6 +139,8 @@ int read_tc_error(int * out, bool clear);
 // pool == nullptr: the tensor in memory is the convolution input; otherwise it is max-pooled on the fly.
 // from_signs != 0: `input` is not fp32 but the sign words [image][c/32][in_h*in_w] left by a sign-only GEMM epilogue.
 int launch_pack_input(const xnor_b200_conv_desc & d, const xnor_b200_pool_desc * pool, const float * input,
-		uint32_t * t_bit_input, cudaStream_t stream, int from_signs = 0, int window_major = 0);
+		uint32_t * t_bit_input, cudaStream_t stream, int from_signs = 0, int window_major = 0, uint32_t * words_scratch = nullptr);
+// words_scratch != nullptr (pack_words_bytes(d) bytes, 16-byte aligned) lets large c%32==0 problems run as two passes.
+size_t pack_words_bytes(const xnor_b200_conv_desc & d);
 
 }  // namespace xnor

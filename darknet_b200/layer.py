@@ -93,6 +93,15 @@ def pack_input(l: ConvolutionalLayer, x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def pack_input_staged(l: ConvolutionalLayer, x: torch.Tensor) -> torch.Tensor:
+    """pack_input through the two-pass route (sign words first, rows from the words); c % 32 == 0 only."""
+    out = torch.empty(l.batch * l.geom.n_out, l.new_lda // 8, dtype=torch.uint8, device=l.device)
+    words = torch.empty(capi.lib().xnor_b200_pack_words_bytes(C.byref(l.desc)), dtype=torch.uint8, device=l.device)
+    capi.check(capi.lib().xnor_b200_pack_input_staged(C.byref(l.desc), x.data_ptr(), words.data_ptr(), out.data_ptr(), _stream()),
+               "xnor_b200_pack_input_staged")
+    return out
+
+
 def gemm_nn_custom_bin_mean_transposed_gpu(M, N, K, A, lda, B, ldb, C_out, ldc, mean_arr, bias, leaky,
                                            shortcut_in=None, shortcut_out=None) -> None:
     """gemm_nn_custom_bin_mean_transposed_gpu (src-lib/im2col_kernels.cu:1156), non-inverted A."""

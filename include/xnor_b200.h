@@ -92,6 +92,7 @@ typedef struct xnor_b200_tuning
 	int tc_wait_polls;        /* polls after which a barrier wait of the tcgen05 kernel gives up (0 = default limit)   */
 	int tc_withhold_arrival;  /* failure-detection test aid: 1 = one producer arrival per tile is withheld, so that a  */
 	                          /* bounded wait runs out and the kernel leaves through its give-up path                  */
+	int pack_two_pass;        /* c%32==0 pack with room for sign words: 2 = sign words first, rows from the words; 0, 1 = one kernel */
 } xnor_b200_tuning;
 XNOR_B200_API int xnor_b200_set_tuning(const xnor_b200_tuning * tuning);
 
@@ -132,6 +133,17 @@ XNOR_B200_API int xnor_b200_repack_input_bin(const float * input, uint32_t * pac
  * the K sign bits of output pixel p of image b followed by zero padding (the reference leaves that
  * padding unwritten on the GPU).  t_bit_input must be 16-byte aligned. */
 XNOR_B200_API int xnor_b200_pack_input(const xnor_b200_conv_desc * desc, const float * input, uint8_t * t_bit_input, void * stream);
+
+/* The same packing in two passes for c%32==0, the reference's own split (repack_input_gpu_bin first,
+ * src-lib/im2col_kernels.cu:715-724, then im2col + transpose on the words): pass one streams the fp32 input once
+ * and leaves `words` = uint32 [batch][c/32][h*w] (xnor_b200_pack_words_bytes(desc) bytes, 16-byte aligned), pass two
+ * builds t_bit_input from those.  Taken only while xnor_b200_tuning.pack_two_pass is 2 (otherwise the call is
+ * xnor_b200_pack_input); the single kernel is as fast or faster on every shape measured, so this is kept for callers
+ * that want the channel-packed words as a by-product.  xnor_b200_conv_forward does the same when its scratch buffer
+ * has xnor_b200_pack_words_bytes() bytes more than xnor_b200_scratch_bytes() and the tuning asks for it. */
+XNOR_B200_API size_t xnor_b200_pack_words_bytes(const xnor_b200_conv_desc * desc);
+XNOR_B200_API int xnor_b200_pack_input_staged(const xnor_b200_conv_desc * desc, const float * input, uint32_t * words,
+		uint8_t * t_bit_input, void * stream);
 
 /* gemm_nn_custom_bin_mean_transposed_gpu (src-lib/im2col_kernels.cu:1156-1193), CPU
  * gemm_nn_custom_bin_mean_transposed (src-lib/gemm.cpp:907-1019) + add_bias
