@@ -363,6 +363,19 @@ pack_input_from_signs_kernel(const PackParams p)
 						const int iy = iy_v0 + (u - fast_div(u, RV, m_rv) * RV);
 						const int py0 = iy * p.pool_stride - p.pool_off;
 						const int px0 = ix * p.pool_stride - p.pool_off;
+						if (p.pool_size == 2)
+						{
+							// the usual window: four independent loads
+							const bool r0 = (py0 >= 0 && py0 < p.in_h), r1 = (py0 + 1 >= 0 && py0 + 1 < p.in_h);
+							const bool c0 = (px0 >= 0 && px0 < p.in_w), c1 = (px0 + 1 >= 0 && px0 + 1 < p.in_w);
+							const uint32_t * q = src[k] + px0;
+							const uint32_t a = (r0 && c0) ? __ldg(q) : 0u;
+							const uint32_t b2 = (r0 && c1) ? __ldg(q + 1) : 0u;
+							const uint32_t c2 = (r1 && c0) ? __ldg(q + p.in_w) : 0u;
+							const uint32_t d2 = (r1 && c1) ? __ldg(q + p.in_w + 1) : 0u;
+							word = (a | b2) | (c2 | d2);
+						}
+						else
 						for (int l = 0; l < p.pool_size; ++l)
 						{
 							if (py0 + l < 0 || py0 + l >= p.in_h) { continue; }
