@@ -398,7 +398,9 @@ XNOR_B200_API int xnor_b200_detection_rows(const xnor_b200_detections * dets, in
  *   - Limit: returns XNOR_B200_ERR_TOO_LARGE when geom.packed_input_bytes (batch*n_out*new_lda/8) exceeds
  *     XNOR_B200_STATIC_SCRATCH_BYTES; nothing is launched in that case.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
- *     device current) and remembers it; make that first call before starting any stream capture.
+ *     device current) and remembers it; make that first call before starting any stream capture.  Under the CUDA
+ *     runtime's lazy module loading that first call is also where the 8 MiB array is materialised on the device, so
+ *     it is the one call of this entry point that may allocate inside the driver: make it at start-up.
  *   - All calls on one device share the one array and it keeps the previous call's contents.  Nothing in it
  *     needs clearing (each call rewrites every word it later reads), but two calls whose kernels can overlap
  *     on the GPU -- different streams, or graph branches -- race on it: serialise them. */
