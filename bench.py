@@ -388,7 +388,7 @@ def run_gpu_arm(args) -> None:
     copy_stream = torch.cuda.Stream(dev)
     x_stage = torch.empty_like(x_dev)
 
-    def double_buffered(n: int) -> float:
+    def double_buffered(n: int, sync_every_call: bool = True) -> float:
         staged, consumed = torch.cuda.Event(), torch.cuda.Event()
         with torch.cuda.stream(copy_stream):
             x_stage.copy_(x_host, non_blocking=True)
@@ -407,12 +407,17 @@ def run_gpu_arm(args) -> None:
                     copy_stream.wait_event(consumed)
                     x_stage.copy_(x_host, non_blocking=True)
                     staged.record(copy_stream)
-            stream.synchronize()
+            if sync_every_call:
+                stream.synchronize()
+        stream.synchronize()
         return time.perf_counter() - t0
 
     double_buffered(5)
     barrier()
     wall_db = replicas.max_over_ranks(double_buffered(n_block), dev)
+    double_buffered(5, False)
+    barrier()
+    wall_stream = replicas.max_over_ranks(double_buffered(n_block, False), dev)
     status = device_status(capi)
     if status != 0:
         raise SystemExit(f"bench: the tensor-core GEMM reported device status {status} (a bounded wait ran out); the timings are void")
@@ -449,7 +454,10 @@ def run_gpu_arm(args) -> None:
                     "blocking_call": {"value": images_per_forward * n_block / wall_block, "unit": "images/s", "ms_per_call": 1000.0 * wall_block / n_block,
                                       "timing": "host clock around copy-in + forward + copy-out + stream synchronise per call", "calls": n_block},
                     "double_buffered": {"value": images_per_forward * n_block / wall_db, "unit": "images/s", "ms_per_call": 1000.0 * wall_db / n_block,
-                                        "timing": "host clock; the next input's host-to-device copy overlaps the current forward", "calls": n_block}},
+                                        "timing": "host clock; the next input's host-to-device copy overlaps the current forward", "calls": n_block},
+                    "streamed": {"value": images_per_forward * n_block / wall_stream, "unit": "images/s", "ms_per_call": 1000.0 * wall_stream / n_block,
+                                 "timing": "host clock over the whole run; as double_buffered, but the host only synchronises after the last call "
+                                           "(a stream of images whose results are read later)", "calls": n_block}},
             "gpu_launches": args.steps * fps * network.own_launches_per_forward(net),
             "device_status": status,
             "max_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
@@ -539,6 +547,8 @@ def kernel_rooflines(net, batch, binops_per_image, stream, flush, dev):
     capi.check(lib.xnor_b200_measure_bmma_peak(2000, C.byref(g_), C.byref(m_)), "bmma peak")
     bmma_peak_tops = g_.value / 1e3
     capi.check(lib.xnor_b200_measure_umma_i8_peak(4000, C.byref(g_), C.byref(m_)), "umma peak")
+    umma_i8_peak_tops = g_.value / 1e3
+    capi.check(lib.xnor_b200_measure_umma_mxf4_peak(4000, C.byref(g_), C.byref(m_)), "umma mxf4 peak")
     umma_peak_tops = g_.value / 1e3
     achieved = binops_per_image * batch / (ms_gemm * 1e-3) / 1e12
     traffic, traffic_source = captured_traffic("xnor_gemm_b1_yolov3_tiny_set") if batch == 1 else (None, None)
@@ -598,12 +608,41 @@ def kernel_rooflines(net, batch, binops_per_image, stream, flush, dev):
     big_tops, int_tops = ops_big / (ms_big * 1e-3) / 1e12, ops_big / (ms_int * 1e-3) / 1e12
     traffic, traffic_source = captured_traffic("xnor_gemm_tc_m512_n43264_k2304")
     out["roofline_large_batch"] = {
-        "kernel": "tcgen05 kind::i8 XNOR GEMM, M=512 N=64x676 K=2304", "bound": "tensor", "achieved": big_tops,
+        "kernel": "tcgen05 kind::mxf4 XNOR GEMM (bits widened to e2m1 +-1), M=512 N=64x676 K=2304", "bound": "tensor", "achieved": big_tops,
         "peak": umma_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": big_tops / umma_peak_tops,
         "traffic": traffic, "traffic_source": traffic_source, "algorithmic_bytes": alg_big,
-        "peak_source": "measured in this run: back-to-back tcgen05.mma kind::i8 128x256x32 from resident shared memory",
+        "peak_source": "measured in this run: back-to-back tcgen05.mma kind::mxf4 128x256x64 from resident shared memory",
+        "kind_i8_rate": umma_i8_peak_tops, "frac_of_kind_i8_rate": big_tops / umma_i8_peak_tops,
         "vs_int_popc_peak": big_tops / popc_peak_tops, "ms": ms_big, "equals_integer_kernel": same,
     }
+    # the longest rows of the three networks: tiny-yolo's last xnor layer at batch 256 (1024 filters, K = 9216)
+    del As_, Bs_, Cs_
+    Mk, Nk, Kk = 1024, 64 * 676, 9216
+    ldk = Kk + (256 - Kk % 256)
+    alg_k = (Mk + Nk) * ldk // 8 + 4 * Mk * Nk
+    Ak = torch.randint(0, 256, (Mk, ldk // 8), dtype=torch.uint8, device=dev)
+    Bk = torch.randint(0, 256, (Nk, ldk // 8), dtype=torch.uint8, device=dev)
+    Ak[:, Kk // 8:] = 0
+    Bk[:, Kk // 8:] = 0
+    Aks = [Ak] + [Ak.clone() for _ in range(copies_for(alg_k) - 1)]
+    Bks = [Bk] + [Bk.clone() for _ in range(len(Aks) - 1)]
+    Cks = [torch.empty(Mk, Nk, device=dev) for _ in Aks]
+    meank, biask = torch.rand(Mk, device=dev), torch.rand(Mk, device=dev)
+
+    def long_gemm(i):
+        def run():
+            capi.check(lib.xnor_b200_gemm_bin_mean_transposed(Mk, Nk, Kk, Aks[i].data_ptr(), ldk, Bks[i].data_ptr(), ldk, Cks[i].data_ptr(), Nk,
+                                                              meank.data_ptr(), biask.data_ptr(), 1, None, None, cur()), "gemm")
+        return run
+    ms_k = time_rotating([long_gemm(i) for i in range(len(Aks))])
+    k_tops = 2.0 * Mk * Nk * Kk / (ms_k * 1e-3) / 1e12
+    out["roofline_large_k"] = {
+        "kernel": "tcgen05 kind::mxf4 XNOR GEMM, M=1024 N=64x676 K=9216 (library's own choice of kernel)", "bound": "tensor", "achieved": k_tops,
+        "peak": umma_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": k_tops / umma_peak_tops, "traffic": None,
+        "algorithmic_bytes": alg_k, "peak_source": out["roofline_large_batch"]["peak_source"],
+        "frac_of_kind_i8_rate": k_tops / umma_i8_peak_tops, "vs_int_popc_peak": k_tops / popc_peak_tops, "ms": ms_k,
+    }
+    del Aks, Bks, Cks
     out["roofline_int_large_batch"] = {
         "kernel": "integer-pipe XNOR GEMM (tiled kernel, route pinned), M=512 N=64x676 K=2304", "bound": "int_popc", "achieved": int_tops,
         "peak": popc_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": int_tops / popc_peak_tops, "traffic": None,

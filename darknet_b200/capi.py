@@ -27,7 +27,7 @@ EXPORTS = (
     "xnor_b200_pack_input_pooled", "xnor_b200_conv_forward_pooled", "xnor_b200_float_conv_small", "xnor_b200_float_conv3_io", "xnor_b200_float_conv_map_weights_bytes",
     "xnor_b200_float_conv_map_prepare", "xnor_b200_float_conv_map", "xnor_b200_float_conv_map_yolo", "xnor_b200_yolo_activate", "xnor_b200_region_activate", "xnor_b200_conv_forward_io", "xnor_b200_conv_takes_masks", "xnor_b200_tap_major_weights",
     "xnor_b200_yolo_detections", "xnor_b200_nms_sort", "xnor_b200_detection_rows",
-    "xnor_b200_measure_popc_peak", "xnor_b200_measure_bmma_peak", "xnor_b200_measure_umma_i8_peak",
+    "xnor_b200_measure_popc_peak", "xnor_b200_measure_bmma_peak", "xnor_b200_measure_umma_i8_peak", "xnor_b200_measure_umma_mxf4_peak",
 )
 
 
@@ -147,6 +147,7 @@ def lib() -> C.CDLL:
     L.xnor_b200_measure_popc_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]
     L.xnor_b200_measure_bmma_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]
     L.xnor_b200_measure_umma_i8_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]
+    L.xnor_b200_measure_umma_mxf4_peak.argtypes = [ci, C.POINTER(C.c_double), C.POINTER(C.c_double)]
     _lib = L
     return L
 

@@ -17,7 +17,8 @@ struct TcParams
 	const uint32_t * B;     // pixels    [n_total][ldb_words]
 	int M, n_total, n_per_image, K;
 	int lda_words, ldb_words;
-	int kblocks;            // number of 128-bit K blocks
+	int kblocks;            // number of K blocks (128 bits for the kind::i8 kernel, 256 bits for the kind::mxf4 kernel)
+	int pad_bits;           // kind::mxf4 kernel: zero bits behind K that the K blocks cover (each counts as one agreeing position)
 	float * C;
 	int ldc;
 	const float * mean_arr;
@@ -38,8 +39,7 @@ struct TcParams
 // The status word of the current device (resolved once per device), the poll limit and the test switches for a launch.
 int tc_fill_launch_fields(TcParams & p);
 
-// The persistent kernel (xnor_gemm_tcp.cu).
-bool tcp_takes(const TcParams & p);
+// The persistent kind::i8 kernel (xnor_gemm_tcp.cu); run only when xnor_b200_set_tuning asks for it.
 int launch_xnor_gemm_tcp(TcParams & p, cudaStream_t stream);
 
 // read-once data (the shortcut operand): streaming load, evicted first
@@ -113,6 +113,34 @@ __device__ __forceinline__ void expand_row(uint32_t row_swz, const uint4 w)
 	}
 }
 
+// kind::mxf4 operands: 32 bits -> 32 four-bit floats (e2m1) in 16 bytes, +1.0 (0x2) where the bit is set, -1.0 (0xA) where it is
+// clear: the nibble is 0xA with its sign bit cleared by the data bit.  Word q of the result takes bits q, q+4, ..., q+28 (bit
+// q + 4 e lands in nibble e) -- again a permutation of K inside the chunk that both operands share.  One shift and one
+// three-input logic operation per word.
+__device__ __forceinline__ uint4 expand_fp4(uint32_t bits)
+{
+	constexpr uint32_t SIGN = 0x88888888u, MINUS_ONE = 0xAAAAAAAAu;
+	uint4 v;
+	v.x = ((bits << 3) & SIGN) ^ MINUS_ONE;
+	v.y = ((bits << 2) & SIGN) ^ MINUS_ONE;
+	v.z = ((bits << 1) & SIGN) ^ MINUS_ONE;
+	v.w = (bits & SIGN) ^ MINUS_ONE;
+	return v;
+}
+
+// One row of one 256-bit K block -> 128 bytes of a K-major SWIZZLE_128B tile (same placement rule as expand_row).
+__device__ __forceinline__ void expand_row_fp4(uint32_t row_swz, const uint4 lo, const uint4 hi)
+{
+	const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+	#pragma unroll
+	for (int c = 0; c < 8; ++c)
+	{
+		const uint4 v = expand_fp4(words[c]);
+		asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+				:: "r"(row_swz ^ (uint32_t)(c << 4)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+	}
+}
+
 // Shared-memory matrix descriptor: K-major, SWIZZLE_128B, rows 128 bytes apart, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr)
 {
@@ -153,6 +181,17 @@ __device__ __forceinline__ void tmem_load(uint32_t taddr, uint32_t (&d)[G])
 	}
 }
 
+// 2 * agreeing - K of one output, as a float, from its raw accumulator.
+//   ACCF == false (kind::i8, operands 0 / -1, s32 accumulator d = popc(a & b)):  (K - 2 popc(b)) - 2 popc(a) + 4 d = k_b + fx + 4 d
+//   ACCF == true  (kind::mxf4, operands +1 / -1 over the zero-padded rows, f32 accumulator): every position the K blocks cover
+//                 behind K is a zero bit in both rows, i.e. (-1)(-1) = +1, so the value is d - pad; exact, |d| <= 2^24.
+template <bool ACCF>
+__device__ __forceinline__ float acc_count(uint32_t d, int k_b, int fx, float pad)
+{
+	if (ACCF) { return __fsub_rn(__uint_as_float(d), pad); }
+	return (float)(k_b + fx + 4 * (int)d);
+}
+
 // Per-filter constants of a tile in shared memory, one array per constant so that eight consecutive filters are two 16-byte
 // reads each: x = -2 popc(filter row), mean and bias as float bits.  `base` is 16-byte aligned, the arrays `nf` ints apart.
 struct FilterConsts
@@ -184,7 +223,7 @@ struct FilterConsts
 // the shortcut operand of group i+1 is requested before group i is computed and stored, so a thread always has
 // G..2G loads in flight.  With one request per output in program order, or one batch per group and nothing in flight in
 // between, the 24 warps of an SM wait a full memory latency each time and the epilogue runs at a fraction of the memory rate.
-template <int G, bool SC>
+template <int G, bool SC, bool ACCF>
 __device__ __forceinline__ void epilogue_values(const TcParams & p, const FilterConsts s_fil, uint32_t tlane, int share, int shares,
 		int my_chunks, int f0, int k_b, bool col_ok, float * c_pix, const float * sc_in, float * sc_out,
 		uint32_t * sum_words = nullptr, int sum_stride = 0, uint32_t * row_words = nullptr)
@@ -236,6 +275,7 @@ __device__ __forceinline__ void epilogue_values(const TcParams & p, const Filter
 			// the compiler, so one read per output in program order leaves the few epilogue warps waiting on every one.
 			constexpr int NB = SC ? 4 : 8;
 			const bool all_in = (f0 + fb + G <= p.M);
+			const float pad = (float)p.pad_bits;
 			const float slope = p.leaky ? 0.1f : 1.0f;             // leaky(v) = max(v, 0.1 v), linear(v) = max(v, v): same bits as the select
 			#pragma unroll
 			for (int u0 = 0; u0 < G; u0 += NB)
@@ -246,9 +286,7 @@ __device__ __forceinline__ void epilogue_values(const TcParams & p, const Filter
 				#pragma unroll
 				for (int j = 0; j < NB; ++j)
 				{
-					// 2*agree - K = (K - 2 popc(b)) - 2 popc(a) + 4 popc(a & b)
-					const int dot = k_b + fx[j] + 4 * (int)d[u0 + j];
-					v[j] = __fmul_rn((float)dot, __int_as_float(fm[j]));
+					v[j] = __fmul_rn(acc_count<ACCF>(d[u0 + j], k_b, fx[j], pad), __int_as_float(fm[j]));
 					if (has_bias) { v[j] = __fadd_rn(v[j], __int_as_float(fb_[j])); }
 					v[j] = fmaxf(v[j], __fmul_rn(v[j], slope));
 				}
@@ -294,7 +332,7 @@ __device__ __forceinline__ void epilogue_values(const TcParams & p, const Filter
 // the `shares` warps that sit on the same quarter interleave over the tile's 32-column chunks (share, share + shares, ...).
 // tmem_acc = TMEM address of the accumulator's first column at lane 0; s_pop[pixel of the tile] = popc of its row;
 // s_fil = the per-filter constants of the tile (FilterConsts).
-template <int NF>
+template <int NF, bool ACCF = false>
 __device__ __forceinline__ void epilogue_tile(const TcParams & p, const int * s_pop, const FilterConsts s_fil, uint32_t tmem_acc,
 		int quarter, int lane, int share, int shares, int f0, int n0)
 {
@@ -304,7 +342,8 @@ __device__ __forceinline__ void epilogue_tile(const TcParams & p, const int * s_
 	const int img = col_ok ? col / p.n_per_image : 0;
 	const int pixcol = col_ok ? col - img * p.n_per_image : 0;
 	const int pix = col_to_pixel(p.x, pixcol);
-	const int k_b = p.K - 2 * s_pop[pix_local];
+	const int k_b = ACCF ? 0 : p.K - 2 * s_pop[pix_local];
+	const float pad = (float)p.pad_bits;
 	const bool has_bias = (p.bias != nullptr);
 	const size_t pix_off = ((size_t)img * p.M + f0) * p.ldc + pix;    // element (first filter of the tile, this pixel)
 	float * c_pix = (p.C != nullptr) ? p.C + pix_off : nullptr;
@@ -321,10 +360,10 @@ __device__ __forceinline__ void epilogue_tile(const TcParams & p, const int * s_
 					? p.x.sum_signs + ((size_t)img * (p.M >> 5) + (f0 >> 5)) * p.n_per_image + pix : nullptr;
 			uint32_t * row_words = (p.x.sum_rows != nullptr)
 					? p.x.sum_rows + ((size_t)img * p.n_per_image + pix) * p.x.sum_ldw + (f0 >> 5) : nullptr;
-			epilogue_values<16, true>(p, s_fil, tlane, share, shares, my_chunks, f0, k_b, col_ok, c_pix, sc_in, sc_out, sum_words, p.n_per_image,
+			epilogue_values<16, true, ACCF>(p, s_fil, tlane, share, shares, my_chunks, f0, k_b, col_ok, c_pix, sc_in, sc_out, sum_words, p.n_per_image,
 					row_words);
 		}
-		else { epilogue_values<32, false>(p, s_fil, tlane, share, shares, my_chunks, f0, k_b, col_ok, c_pix, nullptr, nullptr); }
+		else { epilogue_values<32, false, ACCF>(p, s_fil, tlane, share, shares, my_chunks, f0, k_b, col_ok, c_pix, nullptr, nullptr); }
 		return;
 	}
 	#pragma unroll 1
@@ -348,7 +387,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams & p, const int * s_
 					#pragma unroll
 					for (int j = 0; j < 8; ++j)
 					{
-						float v = __fmul_rn((float)(k_b + fx[j] + 4 * (int)d[j0 + j]), __int_as_float(fm[j]));
+						float v = __fmul_rn(acc_count<ACCF>(d[j0 + j], k_b, fx[j], pad), __int_as_float(fm[j]));
 						if (has_bias) { v = __fadd_rn(v, __int_as_float(fb_[j])); }
 						word |= (v > 0.0f ? 1u : 0u) << (j0 + j);
 					}
@@ -398,7 +437,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams & p, const int * s_
 				if (f0 + fbase + j < p.M)
 				{
 					// agreeing bits among the first K
-					p.counts[(size_t)(f0 + fbase + j) * p.n_total + col] = (k_b + s_fil.x(fbase + j) + 4 * (int)d[j] + p.K) >> 1;
+					p.counts[(size_t)(f0 + fbase + j) * p.n_total + col] = (__float2int_rn(acc_count<ACCF>(d[j], k_b, s_fil.x(fbase + j), pad)) + p.K) >> 1;
 				}
 			}
 			continue;
@@ -414,7 +453,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams & p, const int * s_
 			#pragma unroll
 			for (int j = 0; j < 8; ++j)
 			{
-				v[j] = __fmul_rn((float)(k_b + fx[j] + 4 * (int)d[j0 + j]), __int_as_float(fm[j]));
+				v[j] = __fmul_rn(acc_count<ACCF>(d[j0 + j], k_b, fx[j], pad), __int_as_float(fm[j]));
 				if (has_bias) { v[j] = __fadd_rn(v[j], __int_as_float(fb_[j])); }
 				v[j] = fmaxf(v[j], __fmul_rn(v[j], slope));
 			}

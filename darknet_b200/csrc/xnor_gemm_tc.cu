@@ -1,27 +1,30 @@
 // XNOR GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for large layers.
 //
-// tcgen05.mma has no 1-bit operand kind, and the legacy mma.sync b1 path measures slower than the integer
-// pipe on this GPU.  A binary dot product is nevertheless an integer GEMM: with both operands expanded to
-// signed bytes holding 0 or -1,
-//     D[j][i] = sum_k b_jk * a_ik = popc(B_j & A_i)            (kind::i8, s8 x s8 -> s32, exact)
-//     agreeing bits = K - popc(A_i) - popc(B_j) + 2 * D[j][i]
-// so the packed operands stay 1 bit per element in HBM and L2 (the same buffers the integer-pipe kernel reads)
-// and are widened to bytes only inside shared memory, next to the tensor core that consumes them.
+// tcgen05.mma has no 1-bit operand kind, and the legacy mma.sync b1 path measures slower than the integer pipe on this GPU.
+// A binary dot product is nevertheless an ordinary GEMM once a set bit is read as +1 and a clear bit as -1:
+//     D[j][i] = sum_k b_jk * a_ik = (agreeing positions) - (disagreeing positions) = 2 * agreeing - K
+// The narrowest operand type the tensor core takes is the 4-bit float e2m1 (kind::mxf4, block-scaled, K = 64 per instruction,
+// twice the rate of the 8-bit kinds): +1.0 is 0x2, -1.0 is 0xA, both scale-factor operands are held at 2^0, and the fp32
+// accumulator adds integers of magnitude <= K exactly.  The packed operands stay 1 bit per element in HBM and L2 (the same
+// buffers the integer-pipe kernel reads) and are widened to 4 bits only inside shared memory, next to the tensor core that
+// consumes them.  Positions behind K that a K block covers are zero bits in both rows, i.e. (-1)(-1) = +1 each: the epilogue
+// subtracts their number (TcParams::pad_bits).
 //
 // Orientation: the UMMA "M" dimension (128 TMEM lanes) carries OUTPUT PIXELS, the "N" dimension (TMEM columns)
 // carries FILTERS.  After tcgen05.ld each thread then owns one pixel and 32 consecutive filters per load, so
 // for every filter the 32 lanes of a warp store 32 consecutive pixels: NCHW output rows are written with fully
 // coalesced 128-byte stores.
 //
-// One CTA = 128 pixels x NF filters (NF = 128 or 256), warp-specialised:
-//   warp 0            allocates TMEM; one lane issues, per 128-bit K block, 4 x tcgen05.mma.cta_group::1.kind::i8
-//                     (M=128, N=NF, K=32) and a tcgen05.commit that frees the stage when the MMAs have read it;
-//   warps 1..(128+NF)/32   producers: each thread owns one operand row (pixel row or filter row), keeps three
-//                     K blocks of packed bits in flight from L2, expands 128 bits -> 128 bytes straight into the
-//                     canonical K-major SWIZZLE_128B tile of the current stage, counts its row's set bits, and
-//                     its warp arrives on the stage's "full" barrier; the same warps run the epilogue.
-// Two stages per CTA and two CTAs per SM: while one CTA drains its accumulators the other keeps the tensor
-// core busy.  The epilogue applies the popcount correction, mean scale, bias and leaky with the same
+// One CTA = 128 pixels x NF filters (NF = 32, 64 or 128), warp-specialised:
+//   warp 0            allocates TMEM (NF accumulator columns + 16 columns of scale factors, rounded to a power of two); one
+//                     lane issues, per 256-bit K block, 4 x tcgen05.mma.cta_group::1.kind::mxf4.block_scale (M=128, N=NF,
+//                     K=64) and a tcgen05.commit that frees the stage when the MMAs have read it;
+//   warps 1..(128+NF)/32   producers: each thread owns one operand row (pixel row or filter row), keeps two
+//                     K blocks of packed bits in flight from L2, expands 256 bits -> 128 bytes straight into the
+//                     canonical K-major SWIZZLE_128B tile of the current stage, and its warp arrives on the stage's
+//                     "full" barrier; warps 1..4 first write the scale factors; the same warps run the epilogue.
+// Two or three stages per CTA and two to four CTAs per SM (tensor memory allows 512 columns per SM): while one CTA drains
+// its accumulators the others keep the tensor core busy.  The epilogue applies mean scale, bias and leaky with the same
 // two-rounding fp32 sequence as the integer-pipe kernel, so both kernels give bit-identical outputs.
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel records a code in g_tc_error, all roles drop out
@@ -31,8 +34,6 @@
 #include <mutex>
 namespace xnor
 {
-
-constexpr int TC_STAGES = 2;
 
 // Sticky status word: set to 1 by a tensor-core GEMM kernel (either of the two) whose bounded wait ran out.
 __device__ int g_tc_error = 0;
@@ -68,23 +69,29 @@ struct TcShape
 	static constexpr int ROWS = TC_PIX + NF;                     // operand rows per stage
 	static constexpr int PRODUCER_WARPS = ROWS / 32;
 	static constexpr int THREADS = 32 + ROWS;                    // warp 0 + producers
+	static constexpr int STAGES = (NF == 128) ? 3 : 2;
 	static constexpr int PIX_TILE_BYTES = TC_PIX * 128;
-	static constexpr int STAGE_BYTES = ROWS * 128;
-	static constexpr int SMEM_BYTES = TC_STAGES * STAGE_BYTES + 1024;   // + slack to align the ring to 1024 bytes
+	static constexpr int STAGE_BYTES = ROWS * 128;               // one 256-bit K block of every row, four bits per element
+	static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + slack to align the ring to 1024 bytes
+	// tensor memory: NF accumulator columns, then 16 columns of scale factors (every byte 0x7F = 2^0); a power of two
+	static constexpr int TMEM_COLS = (NF <= 32) ? 64 : (NF <= 64) ? 128 : 256;
+	static constexpr int SF_COL = NF;                            // scale factors of the pixel operand: 4 columns
+	static constexpr int SFB_COL = NF + 8;                       // scale factors of the filter operand: NF / 32 columns
+	static constexpr int CTAS_PER_SM = (NF == 128) ? 2 : 4;      // tensor-memory columns and shared memory both allow this many
 };
 
 template <int NF>
-__global__ void __launch_bounds__(TcShape<NF>::THREADS, (NF == 256) ? 2 : (NF == 128) ? 3 : 4)      // co-resident CTAs: one epilogue overlaps another main loop
+__global__ void __launch_bounds__(TcShape<NF>::THREADS, TcShape<NF>::CTAS_PER_SM)      // co-resident CTAs: one epilogue overlaps another main loop
 xnor_gemm_tc_kernel(const TcParams p)
 {
 	using S = TcShape<NF>;
+	constexpr int STAGES = S::STAGES;
 	extern __shared__ uint8_t tc_smem_raw[];
-	__shared__ uint64_t bar_full[TC_STAGES];
-	__shared__ uint64_t bar_empty[TC_STAGES];
+	__shared__ uint64_t bar_full[STAGES];
+	__shared__ uint64_t bar_empty[STAGES];
 	__shared__ uint64_t bar_done;
 	__shared__ uint32_t tmem_base_slot;
-	__shared__ int s_pop[TC_PIX];                            // popc of every pixel row
-	__shared__ __align__(16) int s_fil[3][NF];               // per filter: -2 popc(row) | mean bits | bias bits
+	__shared__ __align__(16) int s_fil[3][NF];               // per filter: unused | mean bits | bias bits
 	__shared__ int s_failed_storage;
 	volatile int * s_failed = &s_failed_storage;
 
@@ -100,7 +107,7 @@ xnor_gemm_tc_kernel(const TcParams p)
 
 	if (tid == 0)
 	{
-		for (int s = 0; s < TC_STAGES; ++s)
+		for (int s = 0; s < STAGES; ++s)
 		{
 			mbar_init(&bar_full[s], S::PRODUCER_WARPS);
 			mbar_init(&bar_empty[s], 1);
@@ -112,7 +119,7 @@ xnor_gemm_tc_kernel(const TcParams p)
 	if (warp == 0)
 	{
 		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-				:: "r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)NF) : "memory");
+				:: "r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
 		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 	}
 	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -125,19 +132,21 @@ xnor_gemm_tc_kernel(const TcParams p)
 		// ---- MMA issuer -------------------------------------------------------------------------
 		if (lane == 0)
 		{
-			// instruction descriptor: D = s32, A = B = s8, both K-major, N = NF, M = 128
-			const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NF >> 3) << 17) | ((uint32_t)(TC_PIX >> 4) << 24);
+			// instruction descriptor (block-scaled): A = B = e2m1, both K-major, scales ue8m0, N = NF, M = 128, K = 64
+			const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NF >> 3) << 17) | (1u << 23) | ((uint32_t)(TC_PIX >> 4) << 24);
+			const uint32_t sfa = tmem_base + (uint32_t)S::SF_COL;
+			const uint32_t sfb = tmem_base + (uint32_t)S::SFB_COL;
 			bool ok = true;
 			for (int kb = 0; kb < p.kblocks && ok; ++kb)
 			{
-				const int s = kb % TC_STAGES;
-				ok = mbar_wait(&bar_full[s], (uint32_t)((kb / TC_STAGES) & 1), s_failed, p.spin_limit);
+				const int s = kb % STAGES;
+				ok = mbar_wait(&bar_full[s], (uint32_t)((kb / STAGES) & 1), s_failed, p.spin_limit);
 				if (!ok) { break; }
 				asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 				const uint32_t pix_addr = ring + (uint32_t)s * S::STAGE_BYTES;
 				const uint32_t fil_addr = pix_addr + S::PIX_TILE_BYTES;
 				#pragma unroll
-				for (int k = 0; k < 4; ++k)
+				for (int k = 0; k < 4; ++k)                       // 64 elements = 32 bytes of every row per instruction
 				{
 					const uint64_t adesc = make_smem_desc(pix_addr + k * 32);
 					const uint64_t bdesc = make_smem_desc(fil_addr + k * 32);
@@ -145,9 +154,8 @@ xnor_gemm_tc_kernel(const TcParams p)
 					asm volatile(
 						"{\n\t.reg .pred p;\n\t"
 						"setp.ne.b32 p, %4, 0;\n\t"
-						"tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-						:: "r"(tmem_base), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate),
-						   "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+						"tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+						:: "r"(tmem_base), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
 				}
 				// arrives on the stage's barrier once every MMA issued so far has finished reading shared memory
 				asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
@@ -164,10 +172,24 @@ xnor_gemm_tc_kernel(const TcParams p)
 	else
 	{
 		// ---- producers ----------------------------------------------------------------------------
+		if (warp <= 4)
+		{
+			// the scale factors of both operands: 16 columns of 2^0 on every lane (warps 1..4 sit on the four lane quarters);
+			// ordered before the first MMA by this warp's first arrival on bar_full
+			const uint32_t taddr = tmem_base + (uint32_t)S::SF_COL + ((uint32_t)((warp & 3) * 32) << 16);
+			const uint32_t one = 0x7F7F7F7Fu;
+			asm volatile(
+				"tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+				:: "r"(taddr), "r"(one) : "memory");
+			asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+			asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+		}
 		const int r = tid - 32;                               // operand row of this thread within the stage
 		const bool is_pix = r < TC_PIX;
 		const int row_in_tile = is_pix ? r : r - TC_PIX;
 		const bool row_ok = is_pix ? (n0 + row_in_tile < p.n_total) : (f0 + row_in_tile < p.M);
+		const int ld_words = is_pix ? p.ldb_words : p.lda_words;
+		const int ld4 = ld_words >> 2;                        // 16-byte pieces of the row that exist
 		const uint4 * src = reinterpret_cast<const uint4 *>(
 				is_pix ? p.B + (size_t)(row_ok ? n0 + row_in_tile : 0) * p.ldb_words
 				       : p.A + (size_t)(row_ok ? f0 + row_in_tile : 0) * p.lda_words);
@@ -175,48 +197,41 @@ xnor_gemm_tc_kernel(const TcParams p)
 		const uint32_t row_swz0 = (ring + (is_pix ? 0u : (uint32_t)S::PIX_TILE_BYTES) + (uint32_t)row_in_tile * 128u)
 				^ ((uint32_t)(row_in_tile & 7) << 4);
 		const uint4 zero4 = make_uint4(0, 0, 0, 0);
-		uint4 w0 = (row_ok && 0 < p.kblocks) ? __ldg(src + 0) : zero4;
-		uint4 w1 = (row_ok && 1 < p.kblocks) ? __ldg(src + 1) : zero4;
-		uint4 w2 = (row_ok && 2 < p.kblocks) ? __ldg(src + 2) : zero4;
-		int pop = 0;
+		// piece i of the row, zero behind the end of the row (rows are a multiple of 128 bits long, K blocks of 256)
+		auto piece = [&](int i) { return (row_ok && i < ld4 && i < 2 * p.kblocks) ? __ldg(src + i) : zero4; };
+		uint4 a0 = piece(0), a1 = piece(1), b0 = piece(2), b1 = piece(3);
 		bool ok = true;
 		for (int kb = 0; kb < p.kblocks; ++kb)
 		{
-			const int s = kb % TC_STAGES;
-			const uint4 cur = w0;
-			w0 = w1;
-			w1 = w2;
-			w2 = (row_ok && kb + 3 < p.kblocks) ? __ldg(src + kb + 3) : zero4;
-			if (kb >= TC_STAGES)
+			const int s = kb % STAGES;
+			const uint4 lo = a0, hi = a1;
+			a0 = b0; a1 = b1;
+			b0 = piece(2 * kb + 4); b1 = piece(2 * kb + 5);
+			if (kb >= STAGES)
 			{
 				// the MMAs that read this stage (issued STAGES blocks ago) must have completed
-				ok = mbar_wait(&bar_empty[s], (uint32_t)((kb / TC_STAGES - 1) & 1), s_failed, p.spin_limit);
+				ok = mbar_wait(&bar_empty[s], (uint32_t)((kb / STAGES - 1) & 1), s_failed, p.spin_limit);
 				if (!ok) { break; }
 			}
-			expand_row(row_swz0 + (uint32_t)s * S::STAGE_BYTES, cur);
-			pop += __popc(cur.x) + __popc(cur.y) + __popc(cur.z) + __popc(cur.w);
+			expand_row_fp4(row_swz0 + (uint32_t)s * S::STAGE_BYTES, lo, hi);
 			// generic-proxy writes -> visible to the tensor core's async proxy; then one arrival per warp
 			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 			__syncwarp();
 			if (lane == 0 && !(p.withhold != 0 && kb == 0 && warp == 1)) { mbar_arrive(&bar_full[s]); }
 		}
-		if (is_pix)
-		{
-			s_pop[row_in_tile] = pop;
-		}
-		else
+		if (!is_pix)
 		{
 			const int f = f0 + row_in_tile;
 			const float mean = (f < p.M && p.mean_arr != nullptr) ? __ldg(p.mean_arr + f) : 0.0f;
 			const float bias = (f < p.M && p.bias != nullptr) ? __ldg(p.bias + f) : 0.0f;
-			s_fil[0][row_in_tile] = -2 * pop;
+			s_fil[0][row_in_tile] = 0;
 			s_fil[1][row_in_tile] = __float_as_int(mean);
 			s_fil[2][row_in_tile] = __float_as_int(bias);
 		}
 	}
 
-	// ---- everyone: wait for the accumulators ----------------------------------------------------------
-	mbar_wait(&bar_done, 0, s_failed, p.spin_limit);
+	// ---- the accumulators are complete when the issuing thread has seen bar_done; everyone else meets it at the barrier ----
+	if (tid == 0) { mbar_wait<64>(&bar_done, 0, s_failed, p.spin_limit); }
 	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 	__syncthreads();
 	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -228,7 +243,7 @@ xnor_gemm_tc_kernel(const TcParams p)
 		// of the narrow tiles (5 or 6 producer warps) have nothing left to read
 		constexpr int SHARES = S::PRODUCER_WARPS / 4;
 		const int share = ((warp - 1) >> 2) < SHARES ? ((warp - 1) >> 2) : NF;
-		epilogue_tile<NF>(p, s_pop, FilterConsts{&s_fil[0][0], NF}, tmem_base, warp & 3, lane, share, SHARES, f0, n0);
+		epilogue_tile<NF, true>(p, nullptr, FilterConsts{&s_fil[0][0], NF}, tmem_base, warp & 3, lane, share, SHARES, f0, n0);
 	}
 	else if (failed && tid == 0)
 	{
@@ -239,27 +254,26 @@ xnor_gemm_tc_kernel(const TcParams p)
 	__syncthreads();
 	if (warp == 0)
 	{
-		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)NF) : "memory");
+		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
 	}
 }
 
 bool tc_gemm_eligible(int M, int n_total, int K)
 {
 	// The faster of two estimates fitted to measurements on B200 (batch 8..64 layer shapes) decides:
-	//   tensor-core kernel: ~7 us of fixed cost (launch with 100+ KB of shared memory, TMEM allocation, pipeline fill,
-	//                       drain) + per tile 0.6 us per 128-bit K block and 4 us of epilogue for 256-filter tiles (0.33 + 2.5,
-	//                       0.25 + 2.0, 0.2 + 1.4 for 128, 64 and 32 filters), times the tiles the busiest SM gets (co-resident
-	//                       CTAs share the SM's shared-memory bandwidth);
+	//   tensor-core kernel: ~7 us of fixed cost (launch with ~100 KB of shared memory, TMEM allocation, pipeline fill, drain)
+	//                       + per tile 0.6 us per 256-bit K block and 2.8 us of start-up and epilogue for 128-filter tiles
+	//                       (0.35 + 1.6 and 0.3 + 1.1 for 64 and 32 filters), times the tiles per SM (co-resident CTAs share
+	//                       the SM's issue slots and shared-memory bandwidth);
 	//   integer kernel:     ~4 us + binary ops (over the K words it actually walks) at 250 T/s + 2 us per million outputs
 	//                       (index arithmetic and stores of its epilogue, which dominate when K is short: 1x1 layers
 	//                       over 64..256 channels at large batch run 1.3-2x faster on the tensor-core kernel).
 	if (M < 16 || K < 64) { return false; }
-	const int nf = (M > 128) ? 256 : (M > 64) ? 128 : (M > 32) ? 64 : 32;
+	const int nf = (M > 64) ? 128 : (M > 32) ? 64 : 32;
 	const long long tiles = (long long)((M + nf - 1) / nf) * ((n_total + TC_PIX - 1) / TC_PIX);
-	const double kb = (double)((K + 127) / 128);
-	const double per_tile = (nf == 256) ? 0.6 * kb + 4.0 : (nf == 128) ? 0.33 * kb + 2.5 : (nf == 64) ? 0.25 * kb + 2.0 : 0.2 * kb + 1.4;
+	const double kb = (double)((K + 255) / 256);
+	const double per_tile = (nf == 128) ? 0.6 * kb + 2.8 : (nf == 64) ? 0.35 * kb + 1.6 : 0.3 * kb + 1.1;
 	double load = (double)tiles / (double)sm_count();
-	if (nf == 256) { load = (double)((tiles + sm_count() - 1) / sm_count()); }
 	if (load < 1.0) { load = 1.0; }
 	const double t_tc = 7.0 + per_tile * load;
 	const double k_int = (double)(((K + 31) / 32 + 3) / 4 * 4 * 32);       // the integer kernel walks whole 16-byte groups of K words
@@ -296,14 +310,17 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	p.M = M; p.n_total = n_total; p.n_per_image = n_per_image; p.K = K;
 	p.lda_words = lda_words; p.ldb_words = ldb_words;
 	p.kblocks = (K + 127) / 128;
+	p.pad_bits = 0;
 	p.C = C; p.ldc = ldc; p.mean_arr = mean_arr; p.bias = bias; p.leaky = leaky;
 	p.shortcut_in = shortcut_in; p.shortcut_out = shortcut_out; p.counts = counts;
 	int rc = tc_fill_launch_fields(p);
 	if (rc != XNOR_B200_OK) { return rc; }
-	// the persistent kernel where it measured faster, unless xnor_b200_set_tuning pinned one of the two
-	const int variant = tuning().tc_kernel;
-	if (variant == 2 || (variant == 0 && tcp_takes(p))) { return launch_xnor_gemm_tcp(p, stream); }
-	if (M > 128) { return launch_tc<256>(p, stream); }
+	// the persistent kind::i8 kernel only on request (xnor_b200_set_tuning): since this kernel moved to kind::mxf4 it is the
+	// faster one on every shape measured
+	if (tuning().tc_kernel == 2) { return launch_xnor_gemm_tcp(p, stream); }
+	// the kind::mxf4 kernel walks 256-bit K blocks; what they cover behind K is zero in both operands
+	p.kblocks = (K + 255) / 256;
+	p.pad_bits = p.kblocks * 256 - K;
 	if (M > 64) { return launch_tc<128>(p, stream); }
 	return (M > 32) ? launch_tc<64>(p, stream) : launch_tc<32>(p, stream);
 }

@@ -520,11 +520,6 @@ static int launch_tcp(TcParams & p, cudaStream_t stream)
 // (measured on B200 against the one-tile-per-CTA kernel: M=1024 N=43264 K=9216 471 vs 496 us, M=512 K=2304 level; with a
 // fused shortcut or short rows the other kernel's 24 epilogue warps per SM win, e.g. 137 vs 209 us for M=256 N=100352
 // K=1152 with shortcut).
-bool tcp_takes(const TcParams & p)
-{
-	return p.M >= 512 && p.K >= 4608 && p.shortcut_in == nullptr && p.signs == nullptr && p.counts == nullptr && p.x.n_sinks == 0;
-}
-
 
 int launch_xnor_gemm_tcp(TcParams & p, cudaStream_t stream)
 {

@@ -88,7 +88,7 @@ typedef struct xnor_b200_tuning
 	int gemm_tile;            /* ROUTE_TILED only: 1-based tile configuration to pin (0 = estimated)                   */
 	int gemm_split;           /* ROUTE_TILED only, with gemm_tile: cluster split-K factor 1..8 (0 = 1)                 */
 	int pack_ctas_per_sm;     /* CTAs per SM the pack kernels size their grid for (0 = default)                        */
-	int tc_kernel;            /* tcgen05 route: 0 = the library's choice, 1 = one tile per CTA, 2 = persistent kernel       */
+	int tc_kernel;            /* tcgen05 route: 0, 1 = one tile per CTA (kind::mxf4), 2 = the persistent kind::i8 kernel          */
 	int tc_wait_polls;        /* polls after which a barrier wait of the tcgen05 kernel gives up (0 = default limit)   */
 	int tc_withhold_arrival;  /* failure-detection test aid: 1 = one producer arrival per tile is withheld, so that a  */
 	                          /* bounded wait runs out and the kernel leaves through its give-up path                  */
@@ -417,6 +417,9 @@ XNOR_B200_API int xnor_b200_measure_bmma_peak(int iters, double * gops, double *
 /* Same, for the tensor-core route: back-to-back tcgen05.mma kind::i8 (M=128, N=256, K=32) from resident
  * shared-memory tiles on every SM, counted as 2*M*N*K operations per MMA (the GEMM's own convention). */
 XNOR_B200_API int xnor_b200_measure_umma_i8_peak(int iters, double * gops, double * ms);
+/* Same for tcgen05.mma kind::mxf4 (M=128, N=256, K=64, 4-bit operands, scale factors 2^0), the instruction of the one-tile
+ * tensor-core kernel. */
+XNOR_B200_API int xnor_b200_measure_umma_mxf4_peak(int iters, double * gops, double * ms);
 
 #ifdef __cplusplus
 }
