@@ -25,7 +25,7 @@ EXPORTS = (
     "xnor_b200_gemm_counts", "xnor_b200_scratch_bytes", "xnor_b200_conv_forward",
     "xnor_b200_conv_forward_static", "xnor_b200_take_device_status",
     "xnor_b200_pack_input_pooled", "xnor_b200_conv_forward_pooled", "xnor_b200_float_conv_small", "xnor_b200_float_conv3_io", "xnor_b200_float_conv_map_weights_bytes",
-    "xnor_b200_float_conv_map_prepare", "xnor_b200_float_conv_map", "xnor_b200_float_conv_map_yolo", "xnor_b200_yolo_activate", "xnor_b200_region_activate", "xnor_b200_conv_forward_io", "xnor_b200_conv_takes_masks", "xnor_b200_tap_major_weights",
+    "xnor_b200_float_conv_map_prepare", "xnor_b200_float_conv_map", "xnor_b200_float_conv_map_yolo", "xnor_b200_float_conv_1x1_tc", "xnor_b200_yolo_activate", "xnor_b200_region_activate", "xnor_b200_conv_forward_io", "xnor_b200_conv_takes_masks", "xnor_b200_tap_major_weights",
     "xnor_b200_yolo_detections", "xnor_b200_nms_sort", "xnor_b200_detection_rows",
     "xnor_b200_measure_popc_peak", "xnor_b200_measure_bmma_peak", "xnor_b200_measure_umma_i8_peak", "xnor_b200_measure_umma_mxf4_peak",
 )
@@ -135,6 +135,7 @@ def lib() -> C.CDLL:
     L.xnor_b200_float_conv_map_weights_bytes.restype = C.c_size_t
     L.xnor_b200_float_conv_map_prepare.argtypes = [dp, vp, vp, vp]
     L.xnor_b200_float_conv_map.argtypes = [dp, vp, vp, vp, vp, vp]
+    L.xnor_b200_float_conv_1x1_tc.argtypes = [dp, vp, vp, vp, vp, vp]
     L.xnor_b200_float_conv_map_yolo.argtypes = [dp, vp, vp, vp, vp, ci, vp]
     L.xnor_b200_yolo_activate.argtypes = [vp, vp, ci, ci, ci, ci, vp]
     L.xnor_b200_region_activate.argtypes = [vp, vp, ci, ci, ci, ci, ci, ci, vp]

@@ -697,6 +697,16 @@ def prepare_float_map_convs(net: Network) -> None:
                                                               torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_map_prepare")
 
 
+def _float_conv_1x1_tc(l: Layer, x: torch.Tensor) -> torch.Tensor:
+    """1x1 / stride-1 float convolution + bias + leaky/linear through xnor_b200_float_conv_1x1_tc."""
+    import ctypes as C
+    desc = capi.ConvDesc(x.shape[0], l.c, l.h, l.w, l.n, 1, 1, 0, capi.LEAKY if l.activation == "leaky" else capi.LINEAR)
+    out = torch.empty(x.shape[0], l.n, l.out_h, l.out_w, dtype=torch.float32, device=x.device)
+    capi.check(capi.lib().xnor_b200_float_conv_1x1_tc(C.byref(desc), x.data_ptr(), l.weights_gpu.data_ptr(), l.biases_gpu.data_ptr(),
+                                                     out.data_ptr(), torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_1x1_tc")
+    return out
+
+
 def _float_conv_map(net: Network, l: Layer, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """A many-channel float convolution on a small map: cluster split-K kernel with bias and activation fused.  `out` may be
     a pinned host tensor (the device writes a finished head straight into host memory)."""
@@ -813,8 +823,12 @@ def forward_network_gpu(net: Network, x: torch.Tensor, heads_host: Optional[List
                 # a head whose yolo activation runs in this kernel can be written straight into the caller's pinned host tensor
                 direct = heads_host is not None and l.yolo_entries > 0 and net.heads_direct_to_host
                 cur = _float_conv_map(net, l, cur.contiguous(), heads_host[len(heads)] if direct else None)
+            elif l.size == 1 and l.stride == 1 and l.pad == 0 and l.activation in ("leaky", "linear"):
+                # a 1x1 convolution over many pixels: one GEMM over the whole batch on the tensor cores (three tf32 products
+                # per operand pair), bias and activation in its epilogue
+                cur = _float_conv_1x1_tc(l, cur.contiguous())
             elif l.size == 1 and l.stride == 1 and l.pad == 0:
-                # a 1x1 convolution is a plain matrix product per image (cuBLAS sgemm, fp32)
+                # other activations: a plain matrix product per image (cuBLAS sgemm, fp32)
                 b = cur.shape[0]
                 y = torch.baddbmm(l.biases_gpu.view(1, l.n, 1), l.weights_gpu.view(1, l.n, l.c).expand(b, -1, -1),
                                   cur.reshape(b, l.c, l.h * l.w))
@@ -996,6 +1010,8 @@ def own_launches_per_forward(net: Network) -> int:
                 n += 1 if (l.packed_input or from_planes) else 2
             elif (l.c == 3 and l.size == 3 and l.stride == 1 and l.pad == 1) or l.c * l.size * l.size <= 128 or l.weights_blocked_gpu is not None:
                 n += 1
+            elif l.size == 1 and l.stride == 1 and l.pad == 0 and l.activation in ("leaky", "linear"):
+                n += 1                                    # tensor-core 1x1 float convolution
         elif (l.type == "yolo" and not l.yolo_done) or l.type == "region":
             n += 1
     return n

@@ -322,6 +322,14 @@ XNOR_B200_API size_t xnor_b200_float_conv_map_weights_bytes(const xnor_b200_conv
 XNOR_B200_API int xnor_b200_float_conv_map_prepare(const xnor_b200_conv_desc * desc, const float * weights, float * blocked, void * stream);
 XNOR_B200_API int xnor_b200_float_conv_map(const xnor_b200_conv_desc * desc, const float * input, const float * blocked_weights,
 		const float * biases, float * output, void * stream);
+/* 1x1 / stride-1 / pad-0 float convolutions with many pixels (the same layers at batch: tens of thousands of pixels, where
+ * the cluster split above no longer pays): one GEMM over all images on the tensor cores at fp32 accuracy -- every operand is
+ * split into a tf32 head and a tf32 remainder and three tcgen05.mma kind::tf32 products are accumulated per pair -- with
+ * add_bias_gpu and the linear / leaky activation in the epilogue.  weights: Darknet's [n][c] (batch-norm folded), any c and n.
+ * Replaces the per-image cuBLAS call of the float branch (src-lib/convolutional_kernels.cu:373-434).  Agrees with an fp64
+ * convolution to fp32 rounding (a few 1e-7 relative), not with cuBLAS bit for bit. */
+XNOR_B200_API int xnor_b200_float_conv_1x1_tc(const xnor_b200_conv_desc * desc, const float * input, const float * weights,
+		const float * biases, float * output, void * stream);
 /* Same, for the convolution right in front of a [yolo] layer: yolo_entries = 4 + 1 + classes (n must be a multiple of
  * it) also applies that layer's activation step (xnor_b200_yolo_activate below) to the result; 0 = plain call. */
 XNOR_B200_API int xnor_b200_float_conv_map_yolo(const xnor_b200_conv_desc * desc, const float * input, const float * blocked_weights,

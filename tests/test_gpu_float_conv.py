@@ -261,3 +261,43 @@ def test_float_conv3_unpooled_masks_are_the_sign_words_of_the_output(case):
         ref = L.forward_convolutional_layer_gpu(l, full).clone()
         words = masks.view(torch.int32).reshape(batch, 1, h * w)
         assert torch.equal(L.forward_convolutional_layer_io(l, x_signs=words), ref)
+
+
+@pytest.mark.parametrize("case", [
+    (4, 256, 13, 13, 255, 0),      # yolo head shape, filters not a multiple of the tile, pixels not a multiple of 128
+    (2, 1024, 13, 13, 425, 0),     # region head of tiny-yolo
+    (3, 64, 10, 7, 130, 1),        # two K blocks, a tile that straddles three images, leaky
+    (1, 50, 9, 9, 20, 1),          # channels neither a multiple of 32 nor of 4: scalar weight loads, zero-filled K tail
+    (16, 512, 26, 26, 255, 0),     # 10816 pixels: many tiles per SM
+], ids=lambda c: "b%d_c%d_%dx%d_n%d_%d" % c)
+def test_float_conv_1x1_tc_matches_fp64_convolution(case):
+    """The tensor-core 1x1 convolution (three tf32 products per operand pair) against an fp64 convolution."""
+    batch, c, h, w, n, leaky = case
+    x = torch.from_numpy(synth.bell(sum(case), (batch, c, h, w))).cuda()
+    wt = torch.from_numpy(synth.bell(sum(case) + 1, (n, c, 1, 1), 0.05)).cuda()
+    b = torch.from_numpy(synth.bell(sum(case) + 2, (n,), 0.01)).cuda()
+    want = torch.nn.functional.conv2d(x.double(), wt.double(), b.double())
+    if leaky:
+        want = torch.where(want > 0, want, want * 0.1)
+    desc = capi.ConvDesc(batch, c, h, w, n, 1, 1, 0, capi.LEAKY if leaky else capi.LINEAR)
+    out = torch.full(want.shape, float("nan"), dtype=torch.float32, device="cuda")
+    capi.check(capi.lib().xnor_b200_float_conv_1x1_tc(C.byref(desc), x.data_ptr(), wt.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                                     torch.cuda.current_stream().cuda_stream), "xnor_b200_float_conv_1x1_tc")
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all()
+    # sums of c products of magnitude ~0.05: |result| ~ 0.05 sqrt(c).  The tensor core's fp32 accumulation does not round to
+    # nearest, so the error grows with the number of accumulating instructions (12 per 32 channels, spread over four
+    # accumulators): 1e-5 + 4e-8 per channel covers it; a single tf32 product per pair would be off by ~1e-3.
+    err = (out.double() - want).abs().max().item()
+    assert err <= 1e-5 + 4e-8 * c, err
+    st = C.c_int(-1)
+    capi.check(capi.lib().xnor_b200_take_device_status(C.byref(st)), "xnor_b200_take_device_status")
+    assert st.value == 0
+
+
+def test_float_conv_1x1_tc_rejects_other_shapes():
+    z = torch.zeros(64, device="cuda")
+    desc = capi.ConvDesc(1, 32, 8, 8, 8, 3, 1, 1, capi.LINEAR)
+    assert capi.lib().xnor_b200_float_conv_1x1_tc(C.byref(desc), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), None) == 1
+    desc = capi.ConvDesc(1, 32, 8, 8, 8, 1, 1, 0, capi.LINEAR)
+    assert capi.lib().xnor_b200_float_conv_1x1_tc(C.byref(desc), None, z.data_ptr(), z.data_ptr(), z.data_ptr(), None) == 2
