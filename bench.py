@@ -3,8 +3,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
                     [--workload NET] [--batch B | --global-batch B] [--forwards-per-step F]
-    python bench.py --kernel gemm --shape M N K [--route auto|integer|tensor|tiled] [--shortcut] [--reps R]
-    python bench.py --kernel pack --shape BATCH C H W N KS [--reps R]
+    python bench.py --kernel gemm --shape M N K [--route auto|integer|tensor|tiled] [--tc-kernel 1|2] [--shortcut] [--reps R] [--no-graph]
+    python bench.py --kernel pack --shape BATCH C H W N KS [--pack-ctas-per-sm C] [--reps R] [--no-graph]
     python bench.py --kernel gemms | --kernel fconv --shape CASE
 
 One forward is one pass of the network over one batch of seeded synthetic input with seeded random weights (no
@@ -16,17 +16,22 @@ Printed JSON (one line, rank 0):
   value         images/s, inputs resident in HBM (sum of the per-forward event intervals, max over ranks)
   e2e           images/s with the input copied from pinned host memory and the head outputs copied back inside the
                 timed region; e2e.blocking_call = the same through a blocking predict call (copy in, forward, copy
-                out, stream synchronise per call) timed with the host clock, and e2e.double_buffered = that loop
-                with the next input's copy overlapping the current forward
-  roofline*     single kernels timed alone with CUDA events on their stream against a peak measured in the same
-                run (integer XOR+POPC+ADD issue rate, tcgen05 kind::i8 rate) or MEASURED_PEAKS.json (HBM)
+                out, stream synchronise per call) timed with the host clock, e2e.double_buffered = that loop
+                with the next input's copy overlapping the current forward, and e2e.streamed = the same with the
+                host synchronising only after the last call
+  roofline*     single kernels timed alone against a peak measured in the same run (integer XOR+POPC+ADD issue
+                rate, tcgen05 kind::mxf4 and kind::i8 rates) or MEASURED_PEAKS.json (HBM): the calls rotate over
+                copies of their buffers that together exceed twice the L2, and a whole rotation is one CUDA graph
+                between two events
+  gpu_reference the reference's own GPU xnor kernels compiled for sm_100a (oracle/_ref) beside this library's
+                layer call on BASELINE configuration 1
   cpu_baseline  the reference's own CPU xnor code (oracle/_ref) on the same layer shapes, all host cores and one
 
 --impl reference times only that CPU code (xnor layers of the same network) and prints its own line.
 With N > 1 (torchrun) every rank runs an independent replica on its GPU: replicas only, no collective on the data
 path; NCCL is used for the barrier and the max over ranks.  --global-batch cuts one batch over the ranks instead.
---kernel runs one kernel of the library on random operands and prints its median time (the command the profiler
-captures are made with).
+--kernel runs one kernel of the library on random operands and prints its median time, measured like the roofline
+legs; with --no-graph the calls are launched directly (the form the profiler captures are made with).
 """
 from __future__ import annotations
 
