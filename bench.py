@@ -619,6 +619,8 @@ def kernel_rooflines(net, batch, binops_per_image, stream, flush, dev):
         "peak_source": "measured in this run: back-to-back tcgen05.mma kind::mxf4 128x256x64 from resident shared memory",
         "kind_i8_rate": umma_i8_peak_tops, "frac_of_kind_i8_rate": big_tops / umma_i8_peak_tops,
         "vs_int_popc_peak": big_tops / popc_peak_tops, "ms": ms_big, "equals_integer_kernel": same,
+        # the other roofline of the same launch: its 88.6 MB fp32 output against the copy rate (pure writes reach about 0.57 of it)
+        "hbm_achieved_gbs": alg_big / (ms_big * 1e-3) / 1e9, "hbm_frac": alg_big / (ms_big * 1e-3) / 1e9 / hbm_peak,
     }
     # the longest rows of the three networks: tiny-yolo's last xnor layer at batch 256 (1024 filters, K = 9216)
     del As_, Bs_, Cs_
