@@ -315,9 +315,13 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	p.shortcut_in = shortcut_in; p.shortcut_out = shortcut_out; p.counts = counts;
 	int rc = tc_fill_launch_fields(p);
 	if (rc != XNOR_B200_OK) { return rc; }
-	// the persistent kind::i8 kernel only on request (xnor_b200_set_tuning): since this kernel moved to kind::mxf4 it is the
-	// faster one on every shape measured
-	if (tuning().tc_kernel == 2) { return launch_xnor_gemm_tcp(p, stream); }
+	// The persistent kernel where it measured faster (B200, batch 16..64 layer shapes, plain fp32 epilogue: 49 vs 67 us for
+	// 256 x 43264 x 3456, 187 vs 252 us for 1024 x 43264 x 4608, 335 vs 420 us at K = 9216, level at K = 1152): long rows, where
+	// its main loop never stops for an epilogue.  With a fused shortcut or short rows its 8 epilogue warps per SM are the limit
+	// (171 vs 101 us for 256 x 100352 x 1152 with shortcut).  xnor_b200_set_tuning pins either.
+	const int variant = tuning().tc_kernel;
+	const bool long_rows = (M > 64 && K >= 2048 && shortcut_in == nullptr && signs == nullptr && counts == nullptr && p.x.n_sinks == 0);
+	if (variant == 2 || (variant == 0 && long_rows)) { return launch_xnor_gemm_tcp(p, stream); }
 	// the kind::mxf4 kernel walks 256-bit K blocks; what they cover behind K is zero in both operands
 	p.kblocks = (K + 255) / 256;
 	p.pad_bits = p.kblocks * 256 - K;

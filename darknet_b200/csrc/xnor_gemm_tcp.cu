@@ -1,27 +1,21 @@
 // Persistent tcgen05 XNOR GEMM for large layers (more than 64 filters): one CTA per SM walks over 128-pixel x 128-filter
-// tiles; the same arithmetic as the one-tile-per-CTA kernel in xnor_gemm_tc.cu (binary dot product = integer GEMM over bytes
-// holding 0 / -1, kind::i8, exact int32 accumulators in TMEM).  Measured on B200, a kernel that widens both operands into
-// shared memory is bound by shared-memory bandwidth: per 128-bit K block the threads write as many bytes as the tensor core
-// reads back, and the epilogue's own shared-memory reads queue up behind them.  So here only the FILTER operand goes
-// through shared memory; the PIXEL operand is widened straight into tensor memory (tcgen05.st) and the MMA takes it from
-// there, which halves the shared-memory traffic per multiply-accumulate:
+// tiles; the same arithmetic as the one-tile-per-CTA kernel in xnor_gemm_tc.cu (bits widened to e2m1 +1.0 / -1.0,
+// tcgen05.mma kind::mxf4 with both scale factors at 2^0, exact fp32 accumulators in TMEM), with the roles separated so that
+// none of them waits for another more than once per stage and the epilogue of a tile runs under the main loop of the next:
 //
-//   warp 24        TMA producer: one lane brings the packed bit rows of the tile -- 128 pixel rows and 128 filter rows, four
-//                  128-bit K blocks (64 bytes) per row -- into a ring of raw stages with cp.async.bulk.tensor.2d (plain, no
-//                  multicast; rows past the end of a matrix arrive as zeros) and mbarrier expect_tx;
-//   warps  8..15   pixel expanders, one pixel row per thread (warp w owns the TMEM lanes of quarter w % 4): 128 bits ->
-//                  128 bytes in registers -> 32 columns of the operand ring in tensor memory;
-//   warps 16..23   filter expanders, one filter row per thread: 128 bits -> 128 bytes straight into the K-major
-//                  SWIZZLE_128B tile of the stage in shared memory.  Both kinds come in two groups that take the raw chunks
-//                  in turn, and hand over the four K blocks of a chunk per round of waits, fences and arrivals: one warp
-//                  alone needs about 200 cycles per row (measured), more than the tensor core needs per K block;
-//   warp 25        issuer: per K block 4 x tcgen05.mma.cta_group::1.kind::i8 (M=128, N=128, K=32; A from tensor memory, B
-//                  through a shared-memory descriptor) into one of TWO accumulator buffers, tcgen05.commit frees the stage,
+//   warp 24        TMA producer: one lane brings the packed bit rows of the tile -- 128 pixel rows and 128 filter rows, one
+//                  256-bit K block (32 bytes) per row and raw stage -- into a ring of raw stages with cp.async.bulk.tensor.2d
+//                  (plain, no multicast; rows and columns past the end of a matrix arrive as zeros) and mbarrier expect_tx;
+//   warps  8..15   pixel expanders, warps 16..23 filter expanders, one operand row per thread: 256 bits -> 256 four-bit
+//                  values = one 128-byte row of the stage's K-major SWIZZLE_128B tile in shared memory.  Both kinds come in
+//                  two groups that take the raw chunks in turn;
+//   warp 25        issuer: per stage 4 x tcgen05.mma.cta_group::1.kind::mxf4.block_scale (M=128, N=128, K=64, both operands
+//                  through shared-memory descriptors) into one of TWO accumulator buffers, tcgen05.commit frees the stage,
 //                  a last commit per tile hands the buffer to the epilogue;
-//   warps 0..7     epilogue: tcgen05.ld of the finished buffer, popcount correction, mean scale, bias, leaky, shortcut, sign
-//                  words and sinks (tc_common.cuh), while the issuer already fills the other buffer with the next tile.
+//   warps 0..7     epilogue: tcgen05.ld of the finished buffer, mean scale, bias, leaky, shortcut, sign words and sinks
+//                  (tc_common.cuh), while the issuer already fills the other buffer with the next tile.
 //
-// Tensor memory (512 columns): accumulators 2 x 128, pixel-operand ring 8 stages x 32 columns.
+// Tensor memory (512 columns): accumulators 2 x 128, then 16 columns of scale factors (every byte 0x7F = 2^0).
 // Every wait on an mbarrier is bounded.  When one runs out, every role leaves its loops, the producer waits (bounded) for the
 // copies it still has in flight, the issuer for its MMAs, the tensor memory is released, a status word is set, and the kernel
 // returns by itself.
@@ -42,19 +36,17 @@ constexpr int TP_FIL_WARP0 = TP_PIX_WARP0 + 4 * TP_GROUPS;
 constexpr int TP_TMA_WARP = TP_FIL_WARP0 + 4 * TP_GROUPS;
 constexpr int TP_MMA_WARP = TP_TMA_WARP + 1;
 constexpr int TP_THREADS = (TP_MMA_WARP + 1) * 32;
-constexpr int TP_RAW_KB = 2;                  // 128-bit K blocks per raw stage: 32 bytes per operand row
+constexpr int TP_RAW_KB = 2;                  // 128-bit pieces per raw stage: 32 bytes = one 256-bit K block per operand row
 constexpr int TP_RAW_STAGES = 6;
-constexpr int TP_STAGE_KB = 2;                // K blocks per operand stage: one wait and one commit of the issuer per stage (measured:
-                                              // a wait per K block costs the tensor core 40 % of its time, one per two blocks 17 %)
-constexpr int TP_STAGES = 4;                  // operand stages; per K block 16 KB of filter bytes in shared memory + 32 TMEM columns of pixel bytes
+constexpr int TP_STAGES = 4;                  // operand stages: the pixel tile and the filter tile of one 256-bit K block, 16 KB each
 constexpr int TP_ROWS = TC_PIX + TP_NF;
-constexpr int TP_SLOT_BYTES = TP_NF * 128;     // one K block of filter bytes
-constexpr int TP_STAGE_BYTES = TP_STAGE_KB * TP_SLOT_BYTES;
+constexpr int TP_SLOT_BYTES = TP_NF * 128;     // one tile of a stage (128 rows of 128 bytes); TC_PIX == TP_NF
+constexpr int TP_STAGE_BYTES = 2 * TP_SLOT_BYTES;
 constexpr int TP_RAW_STAGE_BYTES = TP_ROWS * 16 * TP_RAW_KB;
 constexpr int TP_RAW_PIX_BYTES = TC_PIX * 16 * TP_RAW_KB;
 constexpr int TP_SMEM_BYTES = TP_STAGES * TP_STAGE_BYTES + TP_RAW_STAGES * TP_RAW_STAGE_BYTES + 1024;   // + slack to align to 1024
 constexpr int TP_TMEM_COLS = 512;
-constexpr int TP_TMEM_A0 = 2 * TP_NF;         // first column of the pixel-operand ring
+constexpr int TP_SF_COL = 2 * TP_NF;          // scale factors of the pixel operand (4 columns used); the filter operand's at + 8
 
 // Wait that does not look at the CTA's failure flag (used while draining on the way out).
 __device__ __forceinline__ bool mbar_wait_plain(uint64_t * bar, uint32_t parity, uint32_t limit)
@@ -86,59 +78,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap * ma
 		:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
-// 16 bits -> 16 bytes, 0x00 or 0xFF each, with four byte-permutes and one shift: PRMT picks every output byte from an
-// 8-byte pool by the low three bits of a selector nibble taken from the packed word itself.  Three pools answer "is bit 0 /
-// bit 1 / bit 2 of the nibble set" for the same selector; bit 3 of a nibble is PRMT's sign-replication flag, harmless for
-// 0x00 / 0xFF bytes, and is read through a shifted selector.  Word q of the result holds bits q, q+4, q+8, q+12 of the
-// group: a permutation of K inside the 16-byte chunk that both operands share, so every dot product is unchanged.
-__device__ __forceinline__ uint4 expand16p(uint32_t sel)
-{
-	uint4 v;
-	v.x = __byte_perm(0xFF00FF00u, 0xFF00FF00u, sel);
-	v.y = __byte_perm(0xFFFF0000u, 0xFFFF0000u, sel);
-	v.z = __byte_perm(0x00000000u, 0xFFFFFFFFu, sel);
-	v.w = __byte_perm(0xFF00FF00u, 0xFF00FF00u, sel >> 3);
-	return v;
-}
-
-// One filter row of one K block: 128 bits -> 128 bytes at the row's place in a K-major SWIZZLE_128B tile (see expand_row).
-__device__ __forceinline__ void expand_row_p(uint32_t row_swz, const uint4 w)
-{
-	const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-	#pragma unroll
-	for (int c = 0; c < 8; ++c)
-	{
-		const uint4 v = expand16p((c & 1) ? (words[c >> 1] >> 16) : words[c >> 1]);
-		asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-				:: "r"(row_swz ^ (uint32_t)(c << 4)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-	}
-}
-
-// One pixel row of one K block: 128 bits -> 128 bytes -> 32 consecutive TMEM columns of this thread's lane.  Column 4c + q
-// takes word q of 16-byte chunk c, i.e. byte k of the row sits in column k / 4 at byte k % 4: the same K order as the
-// filter tile in shared memory.
-__device__ __forceinline__ void expand_row_tmem(uint32_t taddr, const uint4 w)
-{
-	const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-	uint32_t r[32];
-	#pragma unroll
-	for (int c = 0; c < 8; ++c)
-	{
-		const uint4 v = expand16p((c & 1) ? (words[c >> 1] >> 16) : words[c >> 1]);
-		r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
-	}
-	asm volatile(
-		"tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-		"{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-		"%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-		:: "r"(taddr),
-		   "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-		   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-		   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-		   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-		: "memory");
-}
-
 __global__ void __launch_bounds__(TP_THREADS, 1)
 xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_pix, const __grid_constant__ CUtensorMap map_fil)
 {
@@ -150,13 +89,10 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 	__shared__ uint64_t op_empty[TP_STAGES];                  // tcgen05.commit: the MMAs that read the stage have completed
 	__shared__ uint64_t acc_full[2];
 	__shared__ uint64_t acc_empty[2];
-	__shared__ uint64_t meta_full[2];
 	__shared__ uint64_t comb_full[2];
 	__shared__ uint64_t drain_bar;
 	__shared__ uint32_t tmem_base_slot;
-	__shared__ int s_part[2][TP_GROUPS][TP_ROWS];             // popc of every operand row over the K blocks one group widened
-	__shared__ int s_pop[2][TC_PIX];                          // popc of every pixel row, per accumulator buffer
-	__shared__ __align__(16) int s_fil[2][3][NF];             // per filter: -2 popc(row) | mean bits | bias bits
+	__shared__ __align__(16) int s_fil[2][3][NF];             // per accumulator buffer and filter: unused | mean bits | bias bits
 	__shared__ int s_failed_storage;
 	volatile int * s_failed = &s_failed_storage;
 
@@ -184,7 +120,6 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 		{
 			mbar_init(&acc_full[b], 1);
 			mbar_init(&acc_empty[b], TP_EPI_WARPS);
-			mbar_init(&meta_full[b], 8 * TP_GROUPS);
 			mbar_init(&comb_full[b], TP_EPI_WARPS);
 		}
 		mbar_init(&drain_bar, 1);
@@ -201,6 +136,18 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 	__syncthreads();
 	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 	const uint32_t tmem_base = tmem_base_slot;
+	if (warp < 4)
+	{
+		// the scale factors of both operands: 16 columns of 2^0 on every lane (warps 0..3 sit on the four lane quarters)
+		const uint32_t taddr = tmem_base + (uint32_t)TP_SF_COL + ((uint32_t)(warp * 32) << 16);
+		asm volatile(
+			"tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+			:: "r"(taddr), "r"(0x7F7F7F7Fu) : "memory");
+		asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+	}
+	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+	__syncthreads();
+	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
 	if (warp < TP_EPI_WARPS)
 	{
@@ -214,19 +161,15 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 			const uint32_t ph = (uint32_t)((it >> 1) & 1);
 			const int f0 = (t % p.tiles_f) * NF;
 			const int n0 = (t / p.tiles_f) * TC_PIX;
-			// thread `tid` of the 256 epilogue threads adds up the groups' popcounts of operand row `tid` (pixels, then filters)
+			// thread 128 + j of the 256 epilogue threads fetches filter j's constants; the buffer's previous readers are through
+			// (every epilogue warp has passed comb_full of the tile in between)
 			const bool is_fil = tid >= TC_PIX;
 			const int f_row = f0 + tid - TC_PIX;
-			const float mean = (is_fil && f_row < p.M && p.mean_arr != nullptr) ? __ldg(p.mean_arr + f_row) : 0.0f;
-			const float bias = (is_fil && f_row < p.M && p.bias != nullptr) ? __ldg(p.bias + f_row) : 0.0f;
-			if (!mbar_wait<512>(&meta_full[buf], ph, s_failed, limit)) { break; }
-			int sum = 0;
-			#pragma unroll
-			for (int g = 0; g < TP_GROUPS; ++g) { sum += s_part[buf][g][tid]; }
-			if (!is_fil) { s_pop[buf][tid] = sum; }
-			else
+			if (is_fil)
 			{
-				s_fil[buf][0][tid - TC_PIX] = -2 * sum;
+				const float mean = (f_row < p.M && p.mean_arr != nullptr) ? __ldg(p.mean_arr + f_row) : 0.0f;
+				const float bias = (f_row < p.M && p.bias != nullptr) ? __ldg(p.bias + f_row) : 0.0f;
+				s_fil[buf][0][tid - TC_PIX] = 0;
 				s_fil[buf][1][tid - TC_PIX] = __float_as_int(mean);
 				s_fil[buf][2][tid - TC_PIX] = __float_as_int(bias);
 			}
@@ -235,7 +178,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 			if (!mbar_wait<32>(&comb_full[buf], ph, s_failed, limit)) { break; }
 			if (!mbar_wait<512>(&acc_full[buf], ph, s_failed, limit)) { break; }
 			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-			epilogue_tile<NF>(p, s_pop[buf], FilterConsts{&s_fil[buf][0][0], NF}, tmem_base + (uint32_t)(buf * NF), quarter, lane, share,
+			epilogue_tile<NF, true>(p, nullptr, FilterConsts{&s_fil[buf][0][0], NF}, tmem_base + (uint32_t)(buf * NF), quarter, lane, share,
 					TP_EPI_WARPS / 4, f0, n0);
 			asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 			__syncwarp();
@@ -281,8 +224,10 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 		// ---- MMA issuer -------------------------------------------------------------------------------------------
 		if (lane == 0)
 		{
-			// instruction descriptor: D = s32, A = B = s8, both K-major, N = NF, M = 128
-			const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NF >> 3) << 17) | ((uint32_t)(TC_PIX >> 4) << 24);
+			// instruction descriptor (block-scaled): A = B = e2m1, both K-major, scales ue8m0, N = NF, M = 128, K = 64
+			const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NF >> 3) << 17) | (1u << 23) | ((uint32_t)(TC_PIX >> 4) << 24);
+			const uint32_t sfa = tmem_base + (uint32_t)TP_SF_COL;
+			const uint32_t sfb = sfa + 8u;
 			uint32_t sc = 0;                                  // operand stages consumed so far
 			bool ok = true;
 			int it = 0;
@@ -296,31 +241,24 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				}
 				asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 				const uint32_t acc = tmem_base + (uint32_t)(buf * NF);
-				for (int kb0 = 0; kb0 < p.kblocks; kb0 += TP_STAGE_KB, ++sc)
+				for (int c = 0; c < chunks; ++c, ++sc)
 				{
 					const uint32_t es = sc % TP_STAGES;
 					ok = mbar_wait<0>(&op_full[es], (sc / TP_STAGES) & 1u, s_failed, limit);
 					if (!ok) { break; }
 					asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-					const int nk = min(TP_STAGE_KB, p.kblocks - kb0);
+					const uint32_t pix_addr = fil_base + es * (uint32_t)TP_STAGE_BYTES;
+					const uint32_t fil_addr = pix_addr + (uint32_t)TP_SLOT_BYTES;
 					#pragma unroll
-					for (int j = 0; j < TP_STAGE_KB; ++j)
+					for (int k = 0; k < 4; ++k)                   // 64 elements = 32 bytes of every row per instruction
 					{
-						if (j >= nk) { break; }
-						// 32 bytes further along K = +2 in the shared-memory descriptor's address field, +8 TMEM columns
-						const uint64_t bdesc0 = make_smem_desc(fil_base + (es * TP_STAGE_KB + j) * (uint32_t)TP_SLOT_BYTES);
-						const uint32_t a0 = tmem_base + (uint32_t)(TP_TMEM_A0 + (int)(es * TP_STAGE_KB + j) * 32);
-						#pragma unroll
-						for (int k = 0; k < 4; ++k)
-						{
-							const uint32_t accumulate = (kb0 + j > 0 || k > 0) ? 1u : 0u;
-							asm volatile(
-								"{\n\t.reg .pred p;\n\t"
-								"setp.ne.b32 p, %4, 0;\n\t"
-								"tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-								:: "r"(acc), "r"(a0 + (uint32_t)(8 * k)), "l"(bdesc0 + (uint64_t)(2 * k)), "r"(idesc), "r"(accumulate),
-								   "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
-						}
+						const uint32_t accumulate = (c > 0 || k > 0) ? 1u : 0u;
+						asm volatile(
+							"{\n\t.reg .pred p;\n\t"
+							"setp.ne.b32 p, %4, 0;\n\t"
+							"tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+							:: "r"(acc), "l"(make_smem_desc(pix_addr + k * 32)), "l"(make_smem_desc(fil_addr + k * 32)), "r"(idesc),
+							   "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
 					}
 					// arrives on the stage's barrier once every MMA issued so far has finished reading its operands
 					asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
@@ -344,29 +282,21 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 	}
 	else if (warp >= TP_PIX_WARP0 && warp < TP_TMA_WARP)
 	{
-		// ---- expanders: pixel rows -> tensor memory (warps 8..15), filter rows -> shared memory (warps 16..23) -----------
+		// ---- expanders: pixel rows (warps 8..15) and filter rows (warps 16..23) -> the stage's tiles in shared memory -----------
 		const bool is_pix = warp < TP_FIL_WARP0;
 		const int grp = ((is_pix ? warp - TP_PIX_WARP0 : warp - TP_FIL_WARP0) >> 2);
 		const int row = (warp & 3) * 32 + lane;               // row of the tile this thread owns
 		const uint32_t raw_row = raw_base + (uint32_t)((is_pix ? row : TC_PIX + row) * 16 * TP_RAW_KB);
-		const uint32_t fil_row_swz0 = (fil_base + (uint32_t)row * 128u) ^ ((uint32_t)(row & 7) << 4);     // stage 0, swizzle folded in
-		const uint32_t pix_tmem0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)TP_TMEM_A0;   // this warp's lanes, stage 0
+		// this thread's row in stage 0 (pixel tile first, filter tile behind it), swizzle folded in
+		const uint32_t row_swz0 = (fil_base + (is_pix ? 0u : (uint32_t)TP_SLOT_BYTES) + (uint32_t)row * 128u) ^ ((uint32_t)(row & 7) << 4);
 		const bool withhold = (p.withhold != 0 && warp == TP_PIX_WARP0);
-		uint32_t rc = 0, sc = 0;                              // raw chunks and operand stages passed so far (every warp counts all of them)
+		uint32_t rc = 0;                                      // raw chunks = operand stages passed so far (every warp counts all of them)
 		bool ok = true;
-		int it = 0;
-		for (int t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it)
+		for (int t = blockIdx.x; t < p.tiles && ok; t += gridDim.x)
 		{
-			int pop = 0;
 			for (int c = 0; c < chunks && ok; ++c, ++rc)
 			{
-				const int nkb = min(TP_RAW_KB, p.kblocks - c * TP_RAW_KB);      // K blocks in this chunk (fewer at the end of a row)
-				const uint32_t nst = (uint32_t)(nkb + TP_STAGE_KB - 1) / TP_STAGE_KB;       // operand stages it fills
-				if ((int)(rc % TP_GROUPS) != grp)
-				{
-					sc += nst;                                                   // the other group's chunk
-					continue;
-				}
+				if ((int)(rc % TP_GROUPS) != grp) { continue; }              // the other group's chunk
 				const uint32_t rs = rc % TP_RAW_STAGES;
 				ok = mbar_wait<128>(&raw_full[rs], (rc / TP_RAW_STAGES) & 1u, s_failed, limit);
 				if (!ok) { break; }
@@ -381,69 +311,19 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				// the bits are in registers: the raw stage can take the next copy
 				__syncwarp();
 				if (lane == 0) { mbar_arrive(&raw_empty[rs]); }
-				// wait for the stages of this chunk's K blocks, widen them all, then one round of fences and arrivals
-				#pragma unroll
-				for (int js = 0; js < TP_RAW_KB / TP_STAGE_KB; ++js)
+				const uint32_t es = rc % TP_STAGES;
+				if (rc >= (uint32_t)TP_STAGES)
 				{
-					if (js < (int)nst && sc + js >= (uint32_t)TP_STAGES)
-					{
-						// the MMAs that read this stage (issued TP_STAGES stages ago) must have completed
-						ok = ok && mbar_wait<128>(&op_empty[(sc + js) % TP_STAGES], ((sc + js) / TP_STAGES - 1) & 1u, s_failed, limit);
-					}
+					// the MMAs that read this stage (issued TP_STAGES stages ago) must have completed
+					ok = mbar_wait<128>(&op_empty[es], (rc / TP_STAGES - 1) & 1u, s_failed, limit);
+					if (!ok) { break; }
 				}
-				if (!ok) { break; }
-				// K block j of the chunk goes to slot j % STAGE_KB of stage sc + j / STAGE_KB
-				if (is_pix)
-				{
-					asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-					#pragma unroll
-					for (int j = 0; j < TP_RAW_KB; ++j)
-					{
-						if (j < nkb) { expand_row_tmem(pix_tmem0 + (((sc + j / TP_STAGE_KB) % TP_STAGES) * TP_STAGE_KB + j % TP_STAGE_KB) * 32u, w[j]); }
-					}
-					asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-					asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-				}
-				else
-				{
-					#pragma unroll
-					for (int j = 0; j < TP_RAW_KB; ++j)
-					{
-						if (j < nkb)
-						{
-							expand_row_p(fil_row_swz0 + (((sc + j / TP_STAGE_KB) % TP_STAGES) * TP_STAGE_KB + j % TP_STAGE_KB) * (uint32_t)TP_SLOT_BYTES, w[j]);
-						}
-					}
-					// generic-proxy writes -> visible to the tensor core's async proxy
-					asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-				}
-				#pragma unroll
-				for (int j = 0; j < TP_RAW_KB; ++j)
-				{
-					if (j < nkb) { pop += __popc(w[j].x) + __popc(w[j].y) + __popc(w[j].z) + __popc(w[j].w); }
-				}
+				expand_row_fp4(row_swz0 + es * (uint32_t)TP_STAGE_BYTES, w[0], w[1]);
+				// generic-proxy writes -> visible to the tensor core's async proxy
+				asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 				__syncwarp();
-				if (lane == 0)
-				{
-					#pragma unroll
-					for (int js = 0; js < TP_RAW_KB / TP_STAGE_KB; ++js)
-					{
-						if (js < (int)nst && !(withhold && sc + js == 0)) { mbar_arrive(&op_full[(sc + js) % TP_STAGES]); }
-					}
-				}
-				sc += nst;
+				if (lane == 0 && !(withhold && rc == 0)) { mbar_arrive(&op_full[es]); }
 			}
-			if (!ok) { break; }
-			// this group's share of the row's popcount; the buffer is free once the epilogue of two tiles ago is through
-			const int buf = it & 1;
-			if (it >= 2)
-			{
-				ok = mbar_wait<512>(&acc_empty[buf], (uint32_t)(((it >> 1) - 1) & 1), s_failed, limit);
-				if (!ok) { break; }
-			}
-			s_part[buf][grp][is_pix ? row : TC_PIX + row] = pop;
-			__syncwarp();
-			if (lane == 0) { mbar_arrive(&meta_full[buf]); }
 		}
 	}
 
@@ -504,6 +384,8 @@ static int launch_tcp(TcParams & p, cudaStream_t stream)
 	const long long tiles = (long long)p.tiles_f * ((p.n_total + TC_PIX - 1) / TC_PIX);
 	if (tiles > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
 	p.tiles = (int)tiles;
+	// 256-bit K blocks; what they cover behind K is zero in both operands (rows are zero-padded, the copies zero-fill)
+	p.pad_bits = ((p.kblocks + TP_RAW_KB - 1) / TP_RAW_KB) * 256 - p.K;
 	CUtensorMap map_pix, map_fil;
 	int rc = make_row_map(&map_pix, p.B, p.n_total, (size_t)p.ldb_words * 4, TC_PIX);
 	if (rc != XNOR_B200_OK) { return rc; }

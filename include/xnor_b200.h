@@ -88,7 +88,7 @@ typedef struct xnor_b200_tuning
 	int gemm_tile;            /* ROUTE_TILED only: 1-based tile configuration to pin (0 = estimated)                   */
 	int gemm_split;           /* ROUTE_TILED only, with gemm_tile: cluster split-K factor 1..8 (0 = 1)                 */
 	int pack_ctas_per_sm;     /* CTAs per SM the pack kernels size their grid for (0 = default)                        */
-	int tc_kernel;            /* tcgen05 route: 0, 1 = one tile per CTA (kind::mxf4), 2 = the persistent kind::i8 kernel          */
+	int tc_kernel;            /* tcgen05 route: 0 = the library's choice, 1 = one tile per CTA, 2 = the persistent kernel         */
 	int tc_wait_polls;        /* polls after which a barrier wait of the tcgen05 kernel gives up (0 = default limit)   */
 	int tc_withhold_arrival;  /* failure-detection test aid: 1 = one producer arrival per tile is withheld, so that a  */
 	                          /* bounded wait runs out and the kernel leaves through its give-up path                  */
