@@ -320,7 +320,7 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	// its main loop never stops for an epilogue.  With a fused shortcut or short rows its 8 epilogue warps per SM are the limit
 	// (171 vs 101 us for 256 x 100352 x 1152 with shortcut).  xnor_b200_set_tuning pins either.
 	const int variant = tuning().tc_kernel;
-	const bool long_rows = (M > 64 && K >= 2048 && shortcut_in == nullptr && signs == nullptr && counts == nullptr && p.x.n_sinks == 0);
+	const bool long_rows = (M > 64 && K >= 2048 && shortcut_in == nullptr && counts == nullptr);      // sign words and sinks included
 	if (variant == 2 || (variant == 0 && long_rows)) { return launch_xnor_gemm_tcp(p, stream); }
 	// the kind::mxf4 kernel walks 256-bit K blocks; what they cover behind K is zero in both operands
 	p.kblocks = (K + 255) / 256;
