@@ -32,6 +32,7 @@ struct TcParams
 	int tiles;              // persistent kernel: filter tiles x pixel tiles
 	int * status;           // device word set to 1 when a bounded wait ran out
 	uint32_t spin_limit;    // polls per barrier wait
+	int bulk_out;           // persistent kernel: the plain fp32 output leaves through shared memory and bulk copies
 	int withhold;           // test aid: one producer arrival of the first K block is withheld (the issuer's wait then runs out)
 	GemmExtra x;            // window-major column order and direct sign sinks (all zero: none)
 };

@@ -38,13 +38,14 @@ constexpr int TP_MMA_WARP = TP_TMA_WARP + 1;
 constexpr int TP_THREADS = (TP_MMA_WARP + 1) * 32;
 constexpr int TP_RAW_KB = 2;                  // 128-bit pieces per raw stage: 32 bytes = one 256-bit K block per operand row
 constexpr int TP_RAW_STAGES = 6;
-constexpr int TP_STAGES = 4;                  // operand stages: the pixel tile and the filter tile of one 256-bit K block, 16 KB each
+constexpr int TP_STAGES = 3;                  // operand stages: the pixel tile and the filter tile of one 256-bit K block, 16 KB each
 constexpr int TP_ROWS = TC_PIX + TP_NF;
 constexpr int TP_SLOT_BYTES = TP_NF * 128;     // one tile of a stage (128 rows of 128 bytes); TC_PIX == TP_NF
 constexpr int TP_STAGE_BYTES = 2 * TP_SLOT_BYTES;
 constexpr int TP_RAW_STAGE_BYTES = TP_ROWS * 16 * TP_RAW_KB;
 constexpr int TP_RAW_PIX_BYTES = TC_PIX * 16 * TP_RAW_KB;
-constexpr int TP_SMEM_BYTES = TP_STAGES * TP_STAGE_BYTES + TP_RAW_STAGES * TP_RAW_STAGE_BYTES + 1024;   // + slack to align to 1024
+constexpr int TP_OUT_BYTES = TP_NF * TC_PIX * 4;   // one tile of fp32 results [filter][pixel], staged for bulk stores
+constexpr int TP_SMEM_BYTES = TP_STAGES * TP_STAGE_BYTES + TP_RAW_STAGES * TP_RAW_STAGE_BYTES + TP_OUT_BYTES + 1024;   // + slack to align to 1024
 constexpr int TP_TMEM_COLS = 512;
 constexpr int TP_SF_COL = 2 * TP_NF;          // scale factors of the pixel operand (4 columns used); the filter operand's at + 8
 
@@ -79,7 +80,8 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap * ma
 }
 
 __global__ void __launch_bounds__(TP_THREADS, 1)
-xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_pix, const __grid_constant__ CUtensorMap map_fil)
+xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_pix, const __grid_constant__ CUtensorMap map_fil,
+		const __grid_constant__ CUtensorMap map_out)
 {
 	constexpr int NF = TP_NF;
 	extern __shared__ uint8_t tp_smem_raw[];
@@ -90,6 +92,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 	__shared__ uint64_t acc_full[2];
 	__shared__ uint64_t acc_empty[2];
 	__shared__ uint64_t comb_full[2];
+	__shared__ uint64_t out_full;                             // every epilogue warp has staged its part of the tile's results
 	__shared__ uint64_t drain_bar;
 	__shared__ uint32_t tmem_base_slot;
 	__shared__ __align__(16) int s_fil[2][3][NF];             // per accumulator buffer and filter: unused | mean bits | bias bits
@@ -101,6 +104,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 	const int lane = tid & 31;
 	const uint32_t fil_base = (smem_u32(tp_smem_raw) + 1023u) & ~1023u;
 	const uint32_t raw_base = fil_base + (uint32_t)(TP_STAGES * TP_STAGE_BYTES);
+	const uint32_t out_base = raw_base + (uint32_t)(TP_RAW_STAGES * TP_RAW_STAGE_BYTES);
 	const uint32_t limit = p.spin_limit;
 	const int chunks = (p.kblocks + TP_RAW_KB - 1) / TP_RAW_KB;
 
@@ -122,6 +126,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 			mbar_init(&acc_empty[b], TP_EPI_WARPS);
 			mbar_init(&comb_full[b], TP_EPI_WARPS);
 		}
+		mbar_init(&out_full, TP_EPI_WARPS);
 		mbar_init(&drain_bar, 1);
 		s_failed_storage = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -173,17 +178,100 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				s_fil[buf][1][tid - TC_PIX] = __float_as_int(mean);
 				s_fil[buf][2][tid - TC_PIX] = __float_as_int(bias);
 			}
+			// the bulk stores of the previous tile have read the staging buffer (their issuers are threads 0..127)
+			if (p.bulk_out && tid < TP_NF) { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 			__syncwarp();
 			if (lane == 0) { mbar_arrive(&comb_full[buf]); }
 			if (!mbar_wait<32>(&comb_full[buf], ph, s_failed, limit)) { break; }
 			if (!mbar_wait<512>(&acc_full[buf], ph, s_failed, limit)) { break; }
 			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-			epilogue_tile<NF, true>(p, nullptr, FilterConsts{&s_fil[buf][0][0], NF}, tmem_base + (uint32_t)(buf * NF), quarter, lane, share,
-					TP_EPI_WARPS / 4, f0, n0);
-			asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-			__syncwarp();
-			if (lane == 0) { mbar_arrive(&acc_empty[buf]); }
+			if (!p.bulk_out)
+			{
+				epilogue_tile<NF, true>(p, nullptr, FilterConsts{&s_fil[buf][0][0], NF}, tmem_base + (uint32_t)(buf * NF), quarter, lane, share,
+						TP_EPI_WARPS / 4, f0, n0);
+				asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+				__syncwarp();
+				if (lane == 0) { mbar_arrive(&acc_empty[buf]); }
+				continue;
+			}
+			// Plain fp32 output, rows of the output contiguous in memory: the results go to shared memory as [filter][pixel] and
+			// leave as one bulk copy per filter row (per image the tile touches).  Ordinary stores from 8 warps would limit the
+			// tile rate: a store is only retired when the L2 has taken it, and in steady state that means evicting a dirty line.
+			{
+				const int pix_local = quarter * 32 + lane;
+				const float pad = (float)p.pad_bits;
+				const float slope = p.leaky ? 0.1f : 1.0f;
+				const bool has_bias = (p.bias != nullptr);
+				const uint32_t tlane = tmem_base + (uint32_t)(buf * NF) + ((uint32_t)(quarter * 32) << 16);
+				#pragma unroll 1
+				for (int chunk = share; chunk < NF / 32; chunk += TP_EPI_WARPS / 4)
+				{
+					uint32_t d[32];
+					tmem_load<32>(tlane + (uint32_t)(chunk * 32), d);
+					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+					#pragma unroll
+					for (int j0 = 0; j0 < 32; j0 += 8)
+					{
+						// eight filters' constants first (16-byte reads), then the values, then the stores
+						int fx[8], fm[8], fb[8];
+						FilterConsts{&s_fil[buf][0][0], NF}.load<8>(chunk * 32 + j0, fx, fm, fb);
+						float v[8];
+						#pragma unroll
+						for (int j = 0; j < 8; ++j)
+						{
+							v[j] = __fmul_rn(__fsub_rn(__uint_as_float(d[j0 + j]), pad), __int_as_float(fm[j]));
+							if (has_bias) { v[j] = __fadd_rn(v[j], __int_as_float(fb[j])); }
+							v[j] = fmaxf(v[j], __fmul_rn(v[j], slope));
+						}
+						#pragma unroll
+						for (int j = 0; j < 8; ++j)
+						{
+							asm volatile("st.shared.f32 [%0], %1;" :: "r"(out_base + (uint32_t)(((chunk * 32 + j0 + j) * TC_PIX + pix_local) * 4)), "f"(v[j]));
+						}
+					}
+				}
+				// the accumulator is read: the issuer may fill it again
+				asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+				__syncwarp();
+				if (lane == 0) { mbar_arrive(&acc_empty[buf]); }
+				// staged values -> visible to the bulk-copy engine; then every warp's part must be in place
+				asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+				__syncwarp();
+				if (lane == 0) { mbar_arrive(&out_full); }
+				if (!mbar_wait<32>(&out_full, (uint32_t)(it & 1), s_failed, limit)) { break; }
+				const int img0 = n0 / p.n_per_image;
+				const int pix0 = n0 - img0 * p.n_per_image;
+				if (pix0 + TC_PIX <= p.n_per_image || (img0 + 1) * p.n_per_image >= p.n_total)
+				{
+					// the whole tile lies in one image: one tensor store (filters past M and pixels past the image are clipped)
+					if (tid == 0)
+					{
+						asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+								:: "l"(reinterpret_cast<uint64_t>(&map_out)), "r"(pix0), "r"(f0), "r"(img0), "r"(out_base) : "memory");
+						asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+					}
+				}
+				else if (tid < NF && f0 + tid < p.M)
+				{
+					// the tile runs over the end of an image: one copy per filter row and image
+					const int g_end = min(n0 + TC_PIX, p.n_total);
+					int g = n0;
+					while (g < g_end)
+					{
+						const int img = g / p.n_per_image;
+						const int pix = g - img * p.n_per_image;
+						const int len = min(g_end - g, p.n_per_image - pix);
+						float * dst = p.C + ((size_t)img * p.M + f0 + tid) * p.ldc + pix;
+						asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+								:: "l"(dst), "r"(out_base + (uint32_t)((tid * TC_PIX + (g - n0)) * 4)), "r"(len * 4) : "memory");
+						g += len;
+					}
+					asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+				}
+			}
 		}
+		// the staging buffer must outlive the copies that read it
+		if (p.bulk_out && tid < TP_NF) { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 	}
 	else if (warp == TP_TMA_WARP)
 	{
@@ -378,6 +466,25 @@ static int make_row_map(CUtensorMap * map, const void * base, int rows, size_t l
 	return XNOR_B200_OK;
 }
 
+// Tensor map of the fp32 output [images][M][ldc] for stores of 128 pixels x 128 filters of one image.
+static int make_out_map(CUtensorMap * map, float * base, int n_per_image, int M, int images, int ldc)
+{
+	EncodeTiledFn enc = tensor_map_encoder();
+	if (enc == nullptr) { return XNOR_B200_ERR_CUDA; }
+	const cuuint64_t dims[3] = {(cuuint64_t)n_per_image, (cuuint64_t)M, (cuuint64_t)images};
+	const cuuint64_t strides[2] = {(cuuint64_t)ldc * 4, (cuuint64_t)M * (cuuint64_t)ldc * 4};
+	const cuuint32_t box[3] = {(cuuint32_t)TC_PIX, (cuuint32_t)TP_NF, 1};
+	const cuuint32_t elem[3] = {1, 1, 1};
+	const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, elem,
+			CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	if (r != CUDA_SUCCESS)
+	{
+		g_last_cuda_error = (int)cudaErrorInvalidValue;
+		return XNOR_B200_ERR_CUDA;
+	}
+	return XNOR_B200_OK;
+}
+
 static int launch_tcp(TcParams & p, cudaStream_t stream)
 {
 	p.tiles_f = (p.M + TP_NF - 1) / TP_NF;
@@ -386,15 +493,24 @@ static int launch_tcp(TcParams & p, cudaStream_t stream)
 	p.tiles = (int)tiles;
 	// 256-bit K blocks; what they cover behind K is zero in both operands (rows are zero-padded, the copies zero-fill)
 	p.pad_bits = ((p.kblocks + TP_RAW_KB - 1) / TP_RAW_KB) * 256 - p.K;
+	// bulk stores: plain fp32 output whose rows are contiguous runs of whole 16-byte pieces
+	p.bulk_out = (p.C != nullptr && p.shortcut_in == nullptr && p.signs == nullptr && p.counts == nullptr && p.x.n_sinks == 0 && p.x.win_w == 0
+			&& p.n_per_image % 4 == 0 && p.n_total % p.n_per_image == 0 && p.ldc % 4 == 0 && (((uintptr_t)p.C) & 15u) == 0) ? 1 : 0;
 	CUtensorMap map_pix, map_fil;
 	int rc = make_row_map(&map_pix, p.B, p.n_total, (size_t)p.ldb_words * 4, TC_PIX);
 	if (rc != XNOR_B200_OK) { return rc; }
 	rc = make_row_map(&map_fil, p.A, p.M, (size_t)p.lda_words * 4, TP_NF);
 	if (rc != XNOR_B200_OK) { return rc; }
+	CUtensorMap map_out = map_fil;                            // a valid map in any case; only read when bulk_out is set
+	if (p.bulk_out)
+	{
+		rc = make_out_map(&map_out, p.C, p.n_per_image, p.M, p.n_total / p.n_per_image, p.ldc);
+		if (rc != XNOR_B200_OK) { return rc; }
+	}
 	rc = ensure_dynamic_smem((const void *)xnor_gemm_tcp_kernel, TP_SMEM_BYTES);
 	if (rc != XNOR_B200_OK) { return rc; }
 	const int grid = (int)((tiles < (long long)sm_count()) ? tiles : (long long)sm_count());
-	xnor_gemm_tcp_kernel<<<grid, TP_THREADS, TP_SMEM_BYTES, stream>>>(p, map_pix, map_fil);
+	xnor_gemm_tcp_kernel<<<grid, TP_THREADS, TP_SMEM_BYTES, stream>>>(p, map_pix, map_fil, map_out);
 	return check_launch();
 }
 
