@@ -42,6 +42,8 @@ int tc_fill_launch_fields(TcParams & p);
 
 // The persistent kind::i8 kernel (xnor_gemm_tcp.cu); run only when xnor_b200_set_tuning asks for it.
 int launch_xnor_gemm_tcp(TcParams & p, cudaStream_t stream);
+// Whether the persistent kernel would send this call's fp32 results out through shared memory and tensor stores.
+bool tcp_stages_output(const TcParams & p);
 
 // read-once data (the shortcut operand): streaming load, evicted first
 __device__ __forceinline__ float ld_stream(const float * p) { return __ldcs(p); }

@@ -315,13 +315,22 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	p.shortcut_in = shortcut_in; p.shortcut_out = shortcut_out; p.counts = counts;
 	int rc = tc_fill_launch_fields(p);
 	if (rc != XNOR_B200_OK) { return rc; }
-	// The persistent kernel where it measured faster (B200, batch 16..64 layer shapes, plain fp32 epilogue: 49 vs 67 us for
-	// 256 x 43264 x 3456, 187 vs 252 us for 1024 x 43264 x 4608, 335 vs 420 us at K = 9216, level at K = 1152): long rows, where
-	// its main loop never stops for an epilogue.  With a fused shortcut or short rows its 8 epilogue warps per SM are the limit
-	// (171 vs 101 us for 256 x 100352 x 1152 with shortcut).  xnor_b200_set_tuning pins either.
+	// The persistent kernel where it measured faster (B200, layer shapes of batch 16..64; us per call, persistent vs one tile per
+	// CTA).  Plain fp32 output, which it writes with tensor stores: 55.7 vs 87.2 for 512 x 43264 x 2304, 320 vs 424 at
+	// 1024 x 43264 x 9216, 46.9 vs 74.2 at 256 x 100352 x 1152, 72.4 vs 108 at 128 x 401408 x 576, 23.1 vs 33.7 at
+	// 255 x 43264 x 1024.  Sign words and sinks: from K = 2048 on, where its main loop hides the 8 epilogue warps.  A fused
+	// shortcut stays with the other kernel's 24 epilogue warps per SM (171 vs 101 us for 256 x 100352 x 1152).
+	// xnor_b200_set_tuning pins either.
+#ifndef XNOR_TCP_MIN_K_STAGED
+#define XNOR_TCP_MIN_K_STAGED 512
+#endif
+#ifndef XNOR_TCP_MIN_K_OTHER
+#define XNOR_TCP_MIN_K_OTHER 2048
+#endif
 	const int variant = tuning().tc_kernel;
-	const bool long_rows = (M > 64 && K >= 2048 && shortcut_in == nullptr && counts == nullptr);      // sign words and sinks included
-	if (variant == 2 || (variant == 0 && long_rows)) { return launch_xnor_gemm_tcp(p, stream); }
+	const bool tcp_can = (M > 64 && shortcut_in == nullptr && counts == nullptr);
+	const bool tcp_wins = tcp_can && K >= (tcp_stages_output(p) ? XNOR_TCP_MIN_K_STAGED : XNOR_TCP_MIN_K_OTHER);
+	if (variant == 2 || (variant == 0 && tcp_wins)) { return launch_xnor_gemm_tcp(p, stream); }
 	// the kind::mxf4 kernel walks 256-bit K blocks; what they cover behind K is zero in both operands
 	p.kblocks = (K + 255) / 256;
 	p.pad_bits = p.kblocks * 256 - K;

@@ -96,6 +96,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 	__shared__ uint64_t drain_bar;
 	__shared__ uint32_t tmem_base_slot;
 	__shared__ __align__(16) int s_fil[2][3][NF];             // per accumulator buffer and filter: unused | mean bits | bias bits
+	__shared__ uint32_t raw_seen[TP_THREADS / 32][32];         // written only: see the expanders' release of a raw stage
 	__shared__ int s_failed_storage;
 	volatile int * s_failed = &s_failed_storage;
 
@@ -396,9 +397,18 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 							: "=r"(w[j].x), "=r"(w[j].y), "=r"(w[j].z), "=r"(w[j].w)
 							: "r"(raw_row + rs * (uint32_t)TP_RAW_STAGE_BYTES + (uint32_t)(j * 16)) : "memory");
 				}
-				// the bits are in registers: the raw stage can take the next copy
-				__syncwarp();
-				if (lane == 0) { mbar_arrive(&raw_empty[rs]); }
+				// The raw stage can take the next copy once the bits are in registers.  A store of the loaded words comes first: the
+				// warp cannot issue it before the loads have returned, and the arrival follows it in program order.  Without it the
+				// arrival could be performed while the loads still waited in the shared-memory pipeline (seen under heavy
+				// shared-memory traffic: the next copy overwrote the first pixel rows of the stage before they were read).
+				{
+					uint32_t got = 0;
+					#pragma unroll
+					for (int j = 0; j < TP_RAW_KB; ++j) { got |= w[j].x | w[j].y | w[j].z | w[j].w; }
+					asm volatile("st.shared.b32 [%0], %1;" :: "r"(smem_u32(&raw_seen[warp][lane])), "r"(got) : "memory");
+					__syncwarp();
+					if (lane == 0) { mbar_arrive(&raw_empty[rs]); }
+				}
 				const uint32_t es = rc % TP_STAGES;
 				if (rc >= (uint32_t)TP_STAGES)
 				{
@@ -485,6 +495,13 @@ static int make_out_map(CUtensorMap * map, float * base, int n_per_image, int M,
 	return XNOR_B200_OK;
 }
 
+// Plain fp32 output whose rows are contiguous runs of whole 16-byte pieces: what the staged epilogue can write.
+bool tcp_stages_output(const TcParams & p)
+{
+	return p.C != nullptr && p.shortcut_in == nullptr && p.signs == nullptr && p.counts == nullptr && p.x.n_sinks == 0 && p.x.win_w == 0
+			&& p.n_per_image % 4 == 0 && p.n_total % p.n_per_image == 0 && p.ldc % 4 == 0 && (((uintptr_t)p.C) & 15u) == 0;
+}
+
 static int launch_tcp(TcParams & p, cudaStream_t stream)
 {
 	p.tiles_f = (p.M + TP_NF - 1) / TP_NF;
@@ -493,9 +510,7 @@ static int launch_tcp(TcParams & p, cudaStream_t stream)
 	p.tiles = (int)tiles;
 	// 256-bit K blocks; what they cover behind K is zero in both operands (rows are zero-padded, the copies zero-fill)
 	p.pad_bits = ((p.kblocks + TP_RAW_KB - 1) / TP_RAW_KB) * 256 - p.K;
-	// bulk stores: plain fp32 output whose rows are contiguous runs of whole 16-byte pieces
-	p.bulk_out = (p.C != nullptr && p.shortcut_in == nullptr && p.signs == nullptr && p.counts == nullptr && p.x.n_sinks == 0 && p.x.win_w == 0
-			&& p.n_per_image % 4 == 0 && p.n_total % p.n_per_image == 0 && p.ldc % 4 == 0 && (((uintptr_t)p.C) & 15u) == 0) ? 1 : 0;
+	p.bulk_out = tcp_stages_output(p) ? 1 : 0;
 	CUtensorMap map_pix, map_fil;
 	int rc = make_row_map(&map_pix, p.B, p.n_total, (size_t)p.ldb_words * 4, TC_PIX);
 	if (rc != XNOR_B200_OK) { return rc; }
@@ -513,11 +528,6 @@ static int launch_tcp(TcParams & p, cudaStream_t stream)
 	xnor_gemm_tcp_kernel<<<grid, TP_THREADS, TP_SMEM_BYTES, stream>>>(p, map_pix, map_fil, map_out);
 	return check_launch();
 }
-
-// Where the persistent kernel is the library's own choice: long rows over many filters with the plain fp32 epilogue
-// (measured on B200 against the one-tile-per-CTA kernel: M=1024 N=43264 K=9216 471 vs 496 us, M=512 K=2304 level; with a
-// fused shortcut or short rows the other kernel's 24 epilogue warps per SM win, e.g. 137 vs 209 us for M=256 N=100352
-// K=1152 with shortcut).
 
 int launch_xnor_gemm_tcp(TcParams & p, cudaStream_t stream)
 {

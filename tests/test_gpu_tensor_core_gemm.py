@@ -263,6 +263,34 @@ def test_many_tiles_per_cta_repeatedly_equal_the_integer_kernel(force_tc, varian
         assert torch.equal(got, want), f"launch {i}: {int((got != want).sum())} values differ"
 
 
+def test_persistent_kernel_with_staged_output_is_the_same_on_every_launch(force_tc):
+    """Short rows, 128-filter tiles and the fp32 results leaving through shared memory: the shape on which a raw operand stage was
+    once handed back to the copy engine before every warp had read it (about one launch in thirty then differed in a few pixel
+    columns of one tile).  200 launches, each equal to the tile-per-CTA kernel bit for bit."""
+    M, N, K = 256, 64 * 676, 1152
+    rng = np.random.default_rng(20251)
+    A, ld = random_bits(rng, M, K)
+    B, _ = random_bits(rng, N, K)
+    Ag, Bg = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    mean = torch.from_numpy(rng.random(M, dtype=np.float32)).cuda()
+    bias = torch.from_numpy(rng.standard_normal(M).astype(np.float32)).cuda()
+    out = torch.empty((M, N), device="cuda")
+
+    def run():
+        out.fill_(float("nan"))
+        capi.check(capi.lib().xnor_b200_gemm_bin_mean_transposed(M, N, K, Ag.data_ptr(), ld, Bg.data_ptr(), ld, out.data_ptr(), N,
+                                                                 mean.data_ptr(), bias.data_ptr(), 1, None, None,
+                                                                 torch.cuda.current_stream().cuda_stream), "gemm")
+        return out
+
+    force_tc("1", 1)
+    want = run().clone()
+    force_tc("1", 2)
+    differing = [i for i in range(200) if not torch.equal(run(), want)]
+    assert device_status() == 0
+    assert differing == []
+
+
 @pytest.mark.parametrize("variant", [1, 2], ids=["tile-per-cta", "persistent"])
 def test_bounded_wait_runs_out_and_the_kernel_recovers(port, variant):
     """Failure detection without a fault: xnor_b200_set_tuning withholds one producer arrival of the first K block and gives
