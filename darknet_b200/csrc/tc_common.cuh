@@ -32,7 +32,7 @@ struct TcParams
 	int tiles;              // persistent kernel: filter tiles x pixel tiles
 	int * status;           // device word set to 1 when a bounded wait ran out
 	uint32_t spin_limit;    // polls per barrier wait
-	int bulk_out;           // persistent kernel: the plain fp32 output leaves through shared memory and bulk copies
+	int bulk_out;           // persistent kernel: fp32 results leave through shared memory and bulk copies (1: the output, 2: the shortcut sum)
 	int withhold;           // test aid: one producer arrival of the first K block is withheld (the issuer's wait then runs out)
 	GemmExtra x;            // window-major column order and direct sign sinks (all zero: none)
 };
@@ -40,10 +40,11 @@ struct TcParams
 // The status word of the current device (resolved once per device), the poll limit and the test switches for a launch.
 int tc_fill_launch_fields(TcParams & p);
 
-// The persistent kind::i8 kernel (xnor_gemm_tcp.cu); run only when xnor_b200_set_tuning asks for it.
+// The persistent kernel (xnor_gemm_tcp.cu).
 int launch_xnor_gemm_tcp(TcParams & p, cudaStream_t stream);
-// Whether the persistent kernel would send this call's fp32 results out through shared memory and tensor stores.
-bool tcp_stages_output(const TcParams & p);
+// How the persistent kernel would send this call's fp32 results out through shared memory and tensor stores: 0 = not at all,
+// 1 = the layer's output, 2 = the sum with a shortcut operand.
+int tcp_stages_output(const TcParams & p);
 
 // read-once data (the shortcut operand): streaming load, evicted first
 __device__ __forceinline__ float ld_stream(const float * p) { return __ldcs(p); }

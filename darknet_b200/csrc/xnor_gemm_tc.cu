@@ -328,8 +328,9 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 #define XNOR_TCP_MIN_K_OTHER 2048
 #endif
 	const int variant = tuning().tc_kernel;
-	const bool tcp_can = (M > 64 && shortcut_in == nullptr && counts == nullptr);
-	const bool tcp_wins = tcp_can && K >= (tcp_stages_output(p) ? XNOR_TCP_MIN_K_STAGED : XNOR_TCP_MIN_K_OTHER);
+	const int staged = tcp_stages_output(p);
+	const bool tcp_can = (M > 64 && counts == nullptr && (shortcut_in == nullptr || staged == 2));
+	const bool tcp_wins = tcp_can && K >= (staged != 0 ? XNOR_TCP_MIN_K_STAGED : XNOR_TCP_MIN_K_OTHER);
 	if (variant == 2 || (variant == 0 && tcp_wins)) { return launch_xnor_gemm_tcp(p, stream); }
 	// the kind::mxf4 kernel walks 256-bit K blocks; what they cover behind K is zero in both operands
 	p.kblocks = (K + 255) / 256;

@@ -81,7 +81,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap * ma
 
 __global__ void __launch_bounds__(TP_THREADS, 1)
 xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_pix, const __grid_constant__ CUtensorMap map_fil,
-		const __grid_constant__ CUtensorMap map_out)
+		const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_sc)
 {
 	constexpr int NF = TP_NF;
 	extern __shared__ uint8_t tp_smem_raw[];
@@ -93,6 +93,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 	__shared__ uint64_t acc_empty[2];
 	__shared__ uint64_t comb_full[2];
 	__shared__ uint64_t out_full;                             // every epilogue warp has staged its part of the tile's results
+	__shared__ uint64_t sc_full;                              // the tile's shortcut operand has arrived in the staging buffer
 	__shared__ uint64_t drain_bar;
 	__shared__ uint32_t tmem_base_slot;
 	__shared__ __align__(16) int s_fil[2][3][NF];             // per accumulator buffer and filter: unused | mean bits | bias bits
@@ -128,6 +129,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 			mbar_init(&comb_full[b], TP_EPI_WARPS);
 		}
 		mbar_init(&out_full, TP_EPI_WARPS);
+		mbar_init(&sc_full, 1);
 		mbar_init(&drain_bar, 1);
 		s_failed_storage = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -184,6 +186,44 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 			__syncwarp();
 			if (lane == 0) { mbar_arrive(&comb_full[buf]); }
 			if (!mbar_wait<32>(&comb_full[buf], ph, s_failed, limit)) { break; }
+			const int img0 = n0 / p.n_per_image;
+			const int pix0 = n0 - img0 * p.n_per_image;
+			const bool one_image = (pix0 + TC_PIX <= p.n_per_image || (img0 + 1) * p.n_per_image >= p.n_total);
+			if (p.bulk_out == 2)
+			{
+				// The staging buffer is free (every issuer of the previous tile's copies has seen them read it and has passed the
+				// barrier above): bring this tile's shortcut operand into it, [filter][pixel] like the results.
+				if (one_image)
+				{
+					if (tid == 0)
+					{
+						mbar_expect_tx(&sc_full, (uint32_t)TP_OUT_BYTES);       // a clipped box still counts in full
+						asm volatile(
+							"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+							:: "r"(out_base), "l"(reinterpret_cast<uint64_t>(&map_sc)), "r"(pix0), "r"(f0), "r"(img0), "r"(smem_u32(&sc_full)) : "memory");
+					}
+				}
+				else if (tid < NF)
+				{
+					const int g_end = min(n0 + TC_PIX, p.n_total);
+					const int rows = min(NF, p.M - f0);
+					if (tid == 0) { mbar_expect_tx(&sc_full, (uint32_t)(rows * (g_end - n0) * 4)); }
+					if (tid < rows)
+					{
+						int g = n0;
+						while (g < g_end)
+						{
+							const int img = g / p.n_per_image;
+							const int pix = g - img * p.n_per_image;
+							const int len = min(g_end - g, p.n_per_image - pix);
+							const float * src = p.shortcut_in + ((size_t)img * p.M + f0 + tid) * p.ldc + pix;
+							asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+									:: "r"(out_base + (uint32_t)((tid * TC_PIX + (g - n0)) * 4)), "l"(src), "r"(len * 4), "r"(smem_u32(&sc_full)) : "memory");
+							g += len;
+						}
+					}
+				}
+			}
 			if (!mbar_wait<512>(&acc_full[buf], ph, s_failed, limit)) { break; }
 			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 			if (!p.bulk_out)
@@ -204,12 +244,23 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				const float slope = p.leaky ? 0.1f : 1.0f;
 				const bool has_bias = (p.bias != nullptr);
 				const uint32_t tlane = tmem_base + (uint32_t)(buf * NF) + ((uint32_t)(quarter * 32) << 16);
+				const bool sc_mode = (p.bulk_out == 2);
+				const int col = n0 + pix_local;
+				const bool col_ok = col < p.n_total;
+				const int my_img = col_ok ? col / p.n_per_image : 0;
+				const int my_pix = col_ok ? col - my_img * p.n_per_image : 0;
+				uint32_t * sum_words = (sc_mode && p.x.sum_signs != nullptr)
+						? p.x.sum_signs + ((size_t)my_img * (p.M >> 5) + (f0 >> 5)) * p.n_per_image + my_pix : nullptr;
+				uint32_t * row_words = (sc_mode && p.x.sum_rows != nullptr)
+						? p.x.sum_rows + ((size_t)my_img * p.n_per_image + my_pix) * p.x.sum_ldw + (f0 >> 5) : nullptr;
+				if (sc_mode && !mbar_wait<64>(&sc_full, (uint32_t)(it & 1), s_failed, limit)) { break; }
 				#pragma unroll 1
 				for (int chunk = share; chunk < NF / 32; chunk += TP_EPI_WARPS / 4)
 				{
 					uint32_t d[32];
 					tmem_load<32>(tlane + (uint32_t)(chunk * 32), d);
 					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+					uint32_t word = 0;
 					#pragma unroll
 					for (int j0 = 0; j0 < 32; j0 += 8)
 					{
@@ -224,11 +275,35 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 							if (has_bias) { v[j] = __fadd_rn(v[j], __int_as_float(fb[j])); }
 							v[j] = fmaxf(v[j], __fmul_rn(v[j], slope));
 						}
+						if (sc_mode)
+						{
+							// the sum with the shortcut operand takes the value's place
+							float sc[8];
+							#pragma unroll
+							for (int j = 0; j < 8; ++j)
+							{
+								asm volatile("ld.shared.f32 %0, [%1];" : "=f"(sc[j]) : "r"(out_base + (uint32_t)(((chunk * 32 + j0 + j) * TC_PIX + pix_local) * 4)));
+							}
+							#pragma unroll
+							for (int j = 0; j < 8; ++j)
+							{
+								v[j] = __fadd_rn(sc[j], v[j]);
+								word |= (v[j] > 0.0f ? 1u : 0u) << (j0 + j);
+							}
+						}
 						#pragma unroll
 						for (int j = 0; j < 8; ++j)
 						{
 							asm volatile("st.shared.f32 [%0], %1;" :: "r"(out_base + (uint32_t)(((chunk * 32 + j0 + j) * TC_PIX + pix_local) * 4)), "f"(v[j]));
 						}
+					}
+					if (sc_mode && col_ok && f0 + chunk * 32 < p.M)
+					{
+						// sign words of the sum (32 filters = one channel-packed word of this pixel); filters past M stay clear
+						const int left = p.M - (f0 + chunk * 32);
+						if (left < 32) { word &= (1u << left) - 1u; }
+						if (sum_words != nullptr) { sum_words[(size_t)chunk * p.n_per_image] = word; }
+						if (row_words != nullptr) { row_words[chunk] = word; }
 					}
 				}
 				// the accumulator is read: the issuer may fill it again
@@ -240,9 +315,8 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				__syncwarp();
 				if (lane == 0) { mbar_arrive(&out_full); }
 				if (!mbar_wait<32>(&out_full, (uint32_t)(it & 1), s_failed, limit)) { break; }
-				const int img0 = n0 / p.n_per_image;
-				const int pix0 = n0 - img0 * p.n_per_image;
-				if (pix0 + TC_PIX <= p.n_per_image || (img0 + 1) * p.n_per_image >= p.n_total)
+				float * const dst_base = sc_mode ? p.shortcut_out : p.C;
+				if (one_image)
 				{
 					// the whole tile lies in one image: one tensor store (filters past M and pixels past the image are clipped)
 					if (tid == 0)
@@ -262,7 +336,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 						const int img = g / p.n_per_image;
 						const int pix = g - img * p.n_per_image;
 						const int len = min(g_end - g, p.n_per_image - pix);
-						float * dst = p.C + ((size_t)img * p.M + f0 + tid) * p.ldc + pix;
+						float * dst = dst_base + ((size_t)img * p.M + f0 + tid) * p.ldc + pix;
 						asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
 								:: "l"(dst), "r"(out_base + (uint32_t)((tid * TC_PIX + (g - n0)) * 4)), "r"(len * 4) : "memory");
 						g += len;
@@ -476,7 +550,7 @@ static int make_row_map(CUtensorMap * map, const void * base, int rows, size_t l
 	return XNOR_B200_OK;
 }
 
-// Tensor map of the fp32 output [images][M][ldc] for stores of 128 pixels x 128 filters of one image.
+// Tensor map of an fp32 tensor [images][M][ldc] (the output, or a shortcut operand) for boxes of 128 pixels x 128 filters of one image.
 static int make_out_map(CUtensorMap * map, float * base, int n_per_image, int M, int images, int ldc)
 {
 	EncodeTiledFn enc = tensor_map_encoder();
@@ -495,11 +569,17 @@ static int make_out_map(CUtensorMap * map, float * base, int n_per_image, int M,
 	return XNOR_B200_OK;
 }
 
-// Plain fp32 output whose rows are contiguous runs of whole 16-byte pieces: what the staged epilogue can write.
-bool tcp_stages_output(const TcParams & p)
+// What the staged epilogue can write: fp32 rows that are contiguous runs of whole 16-byte pieces, and nothing else but the sign
+// words of a shortcut sum.  1: the layer's own output; 2: only the sum with a shortcut operand of the same layout; 0: neither.
+int tcp_stages_output(const TcParams & p)
 {
-	return p.C != nullptr && p.shortcut_in == nullptr && p.signs == nullptr && p.counts == nullptr && p.x.n_sinks == 0 && p.x.win_w == 0
-			&& p.n_per_image % 4 == 0 && p.n_total % p.n_per_image == 0 && p.ldc % 4 == 0 && (((uintptr_t)p.C) & 15u) == 0;
+	if (p.signs != nullptr || p.counts != nullptr || p.x.n_sinks != 0 || p.x.win_w != 0) { return 0; }
+	if (p.n_per_image % 4 != 0 || p.n_total % p.n_per_image != 0 || p.ldc % 4 != 0) { return 0; }
+	if (p.shortcut_in == nullptr)
+	{
+		return (p.C != nullptr && p.x.sum_signs == nullptr && p.x.sum_rows == nullptr && (((uintptr_t)p.C) & 15u) == 0) ? 1 : 0;
+	}
+	return (p.C == nullptr && p.shortcut_out != nullptr && ((((uintptr_t)p.shortcut_in) | ((uintptr_t)p.shortcut_out)) & 15u) == 0) ? 2 : 0;
 }
 
 static int launch_tcp(TcParams & p, cudaStream_t stream)
@@ -510,22 +590,27 @@ static int launch_tcp(TcParams & p, cudaStream_t stream)
 	p.tiles = (int)tiles;
 	// 256-bit K blocks; what they cover behind K is zero in both operands (rows are zero-padded, the copies zero-fill)
 	p.pad_bits = ((p.kblocks + TP_RAW_KB - 1) / TP_RAW_KB) * 256 - p.K;
-	p.bulk_out = tcp_stages_output(p) ? 1 : 0;
+	p.bulk_out = tcp_stages_output(p);
 	CUtensorMap map_pix, map_fil;
 	int rc = make_row_map(&map_pix, p.B, p.n_total, (size_t)p.ldb_words * 4, TC_PIX);
 	if (rc != XNOR_B200_OK) { return rc; }
 	rc = make_row_map(&map_fil, p.A, p.M, (size_t)p.lda_words * 4, TP_NF);
 	if (rc != XNOR_B200_OK) { return rc; }
-	CUtensorMap map_out = map_fil;                            // a valid map in any case; only read when bulk_out is set
-	if (p.bulk_out)
+	CUtensorMap map_out = map_fil, map_sc = map_fil;          // valid maps in any case; only read when bulk_out is set
+	if (p.bulk_out != 0)
 	{
-		rc = make_out_map(&map_out, p.C, p.n_per_image, p.M, p.n_total / p.n_per_image, p.ldc);
+		rc = make_out_map(&map_out, (p.bulk_out == 2) ? p.shortcut_out : p.C, p.n_per_image, p.M, p.n_total / p.n_per_image, p.ldc);
+		if (rc != XNOR_B200_OK) { return rc; }
+	}
+	if (p.bulk_out == 2)
+	{
+		rc = make_out_map(&map_sc, const_cast<float *>(p.shortcut_in), p.n_per_image, p.M, p.n_total / p.n_per_image, p.ldc);
 		if (rc != XNOR_B200_OK) { return rc; }
 	}
 	rc = ensure_dynamic_smem((const void *)xnor_gemm_tcp_kernel, TP_SMEM_BYTES);
 	if (rc != XNOR_B200_OK) { return rc; }
 	const int grid = (int)((tiles < (long long)sm_count()) ? tiles : (long long)sm_count());
-	xnor_gemm_tcp_kernel<<<grid, TP_THREADS, TP_SMEM_BYTES, stream>>>(p, map_pix, map_fil, map_out);
+	xnor_gemm_tcp_kernel<<<grid, TP_THREADS, TP_SMEM_BYTES, stream>>>(p, map_pix, map_fil, map_out, map_sc);
 	return check_launch();
 }
 

@@ -263,6 +263,49 @@ def test_many_tiles_per_cta_repeatedly_equal_the_integer_kernel(force_tc, varian
         assert torch.equal(got, want), f"launch {i}: {int((got != want).sum())} values differ"
 
 
+@pytest.mark.parametrize("case", [(3, 128, 14, 14, 160, 3), (8, 64, 28, 28, 128, 3), (2, 256, 26, 26, 288, 1), (5, 64, 12, 20, 96, 3)],
+                         ids=lambda c: "b%d_c%d_%dx%d_n%d_k%d" % c)
+@pytest.mark.parametrize("variant", [1, 2], ids=["tile-per-cta", "persistent"])
+def test_shortcut_sum_only_with_its_sign_words_on_both_kernels(force_tc, case, variant):
+    """A layer of which only the fused shortcut sum is wanted, plus the sum's sign words or the 1x1 reader's operand: the persistent
+    kernel brings the shortcut operand into shared memory with the copy engine, adds there and writes the sum with tensor stores
+    (row copies where a 128-pixel tile runs over the end of an image, as it does in every case here).  Sum, words and operand
+    equal what the integer kernel and the pack kernel produce."""
+    batch, c, h, w, n, ks = case
+    x, wt, b = synth.conv_case(515 + n, batch, c, h, w, n, ks)
+    l = L.make_convolutional_layer(batch, h, w, c, n, ks, 1, ks // 2, capi.LEAKY)
+    l.load_weights(torch.from_numpy(wt).cuda(), torch.from_numpy(b).cuda())
+    L.binary_align_weights(l)
+    xg = torch.from_numpy(x).cuda()
+    l.bin_conv_shortcut_in_gpu = torch.from_numpy(synth.bell(27, (batch, n, h, w), 1.0)).cuda()
+    l.bin_conv_shortcut_out_gpu = torch.empty(batch, n, h, w, device="cuda")
+    force_tc("0")
+    L.forward_convolutional_layer_gpu(l, xg)
+    want_sum = l.bin_conv_shortcut_out_gpu.clone()
+    bits = (want_sum > 0).view(batch, n // 32, 32, h * w).to(torch.int64)
+    words = (bits << torch.arange(32, device="cuda").view(1, 1, 32, 1)).sum(2)
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
+    nxt = L.make_convolutional_layer(batch, h, w, n, 40, 1, 1, 0, capi.LEAKY)
+    nxt.load_weights(torch.from_numpy(synth.bell(19, (40, n), 0.05)).cuda(), torch.from_numpy(synth.bell(20, (40,), 0.3)).cuda())
+    L.binary_align_weights(nxt)
+    want_op = L.pack_input(nxt, want_sum).clone()
+    force_tc("1", variant)
+    for _ in range(3):
+        l.bin_conv_shortcut_out_gpu.fill_(float("nan"))
+        got = L.forward_convolutional_layer_io(l, x=xg, shortcut_only=True, shortcut_signs=True)
+        torch.cuda.synchronize()
+        assert device_status() == 0
+        assert torch.equal(got, want_sum)
+        assert torch.equal(l.shortcut_signs_gpu, words)
+        nxt.scratch.zero_()
+        l.bin_conv_shortcut_out_gpu.fill_(float("nan"))
+        got = L.forward_convolutional_layer_io(l, x=xg, shortcut_only=True, shortcut_sink=nxt)
+        torch.cuda.synchronize()
+        assert device_status() == 0
+        assert torch.equal(got, want_sum)
+        assert torch.equal(nxt.scratch[:want_op.numel()].view(want_op.shape), want_op)
+
+
 def test_persistent_kernel_with_staged_output_is_the_same_on_every_launch(force_tc):
     """Short rows, 128-filter tiles and the fp32 results leaving through shared memory: the shape on which a raw operand stage was
     once handed back to the copy engine before every warp had read it (about one launch in thirty then differed in a few pixel
