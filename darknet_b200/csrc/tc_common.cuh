@@ -32,6 +32,7 @@ struct TcParams
 	int tiles;              // persistent kernel: filter tiles x pixel tiles
 	int * status;           // device word set to 1 when a bounded wait ran out
 	uint32_t spin_limit;    // polls per barrier wait
+	int tiles_per_image;    // persistent kernel with the staged epilogue: 128-pixel tiles per image (0: tiles over the whole batch)
 	int bulk_out;           // persistent kernel: fp32 results leave through shared memory and bulk copies (1: the output, 2: the shortcut sum)
 	int withhold;           // test aid: one producer arrival of the first K block is withheld (the issuer's wait then runs out)
 	GemmExtra x;            // window-major column order and direct sign sinks (all zero: none)

@@ -35,7 +35,8 @@ constexpr int TP_PIX_WARP0 = 8;               // a multiple of 4: pixel warp w o
 constexpr int TP_FIL_WARP0 = TP_PIX_WARP0 + 4 * TP_GROUPS;
 constexpr int TP_TMA_WARP = TP_FIL_WARP0 + 4 * TP_GROUPS;
 constexpr int TP_MMA_WARP = TP_TMA_WARP + 1;
-constexpr int TP_THREADS = (TP_MMA_WARP + 1) * 32;
+constexpr int TP_COPY_WARP = TP_MMA_WARP + 1;
+constexpr int TP_THREADS = (TP_COPY_WARP + 1) * 32;
 constexpr int TP_RAW_KB = 2;                  // 128-bit pieces per raw stage: 32 bytes = one 256-bit K block per operand row
 constexpr int TP_RAW_STAGES = 6;
 constexpr int TP_STAGES = 3;                  // operand stages: the pixel tile and the filter tile of one 256-bit K block, 16 KB each
@@ -44,7 +45,9 @@ constexpr int TP_SLOT_BYTES = TP_NF * 128;     // one tile of a stage (128 rows 
 constexpr int TP_STAGE_BYTES = 2 * TP_SLOT_BYTES;
 constexpr int TP_RAW_STAGE_BYTES = TP_ROWS * 16 * TP_RAW_KB;
 constexpr int TP_RAW_PIX_BYTES = TC_PIX * 16 * TP_RAW_KB;
-constexpr int TP_OUT_BYTES = TP_NF * TC_PIX * 4;   // one tile of fp32 results [filter][pixel], staged for bulk stores
+constexpr int TP_HALF_ROWS = TP_NF / 2;       // filters per half of the staging buffer
+constexpr int TP_HALF_BYTES = TP_HALF_ROWS * TC_PIX * 4;
+constexpr int TP_OUT_BYTES = 2 * TP_HALF_BYTES;    // one tile of fp32 results [filter][pixel], staged for bulk stores, in two halves
 constexpr int TP_SMEM_BYTES = TP_STAGES * TP_STAGE_BYTES + TP_RAW_STAGES * TP_RAW_STAGE_BYTES + TP_OUT_BYTES + 1024;   // + slack to align to 1024
 constexpr int TP_TMEM_COLS = 512;
 constexpr int TP_SF_COL = 2 * TP_NF;          // scale factors of the pixel operand (4 columns used); the filter operand's at + 8
@@ -79,6 +82,37 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap * ma
 		:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
+// Tile number -> first filter, first operand row (pixel), and for the staged epilogue the image, the first pixel inside it and
+// the number of pixels of the tile that belong to that image.  With the staged epilogue no tile crosses an image (every image
+// has its own last, partly used tile: what lies behind it in the operand is computed and dropped), so that a half tile always
+// leaves, and its shortcut operand always arrives, as ONE tensor copy; otherwise the tiles run over all pixels of the batch.
+struct TileAt
+{
+	int f0, n0, img, pix0, valid;
+};
+
+__device__ __forceinline__ TileAt tile_at(const TcParams & p, int t)
+{
+	TileAt a;
+	const int nt = t / p.tiles_f;
+	a.f0 = (t - nt * p.tiles_f) * TP_NF;
+	if (p.tiles_per_image > 0)
+	{
+		a.img = nt / p.tiles_per_image;
+		a.pix0 = (nt - a.img * p.tiles_per_image) * TC_PIX;
+		a.n0 = a.img * p.n_per_image + a.pix0;
+		a.valid = min(TC_PIX, p.n_per_image - a.pix0);
+	}
+	else
+	{
+		a.img = 0;
+		a.pix0 = 0;
+		a.n0 = nt * TC_PIX;
+		a.valid = min(TC_PIX, p.n_total - a.n0);
+	}
+	return a;
+}
+
 __global__ void __launch_bounds__(TP_THREADS, 1)
 xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_pix, const __grid_constant__ CUtensorMap map_fil,
 		const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_sc)
@@ -92,8 +126,8 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 	__shared__ uint64_t acc_full[2];
 	__shared__ uint64_t acc_empty[2];
 	__shared__ uint64_t comb_full[2];
-	__shared__ uint64_t out_full;                             // every epilogue warp has staged its part of the tile's results
-	__shared__ uint64_t sc_full;                              // the tile's shortcut operand has arrived in the staging buffer
+	__shared__ uint64_t out_full[2];                          // per half of the staging buffer: every epilogue warp has staged its part
+	__shared__ uint64_t half_ready[2];                        // per half: free for the next tile, and that tile's shortcut operand is in it
 	__shared__ uint64_t drain_bar;
 	__shared__ uint32_t tmem_base_slot;
 	__shared__ __align__(16) int s_fil[2][3][NF];             // per accumulator buffer and filter: unused | mean bits | bias bits
@@ -128,8 +162,11 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 			mbar_init(&acc_empty[b], TP_EPI_WARPS);
 			mbar_init(&comb_full[b], TP_EPI_WARPS);
 		}
-		mbar_init(&out_full, TP_EPI_WARPS);
-		mbar_init(&sc_full, 1);
+		for (int h = 0; h < 2; ++h)
+		{
+			mbar_init(&out_full[h], TP_EPI_WARPS);
+			mbar_init(&half_ready[h], 1);
+		}
 		mbar_init(&drain_bar, 1);
 		s_failed_storage = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -167,8 +204,9 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 		{
 			const int buf = it & 1;
 			const uint32_t ph = (uint32_t)((it >> 1) & 1);
-			const int f0 = (t % p.tiles_f) * NF;
-			const int n0 = (t / p.tiles_f) * TC_PIX;
+			const TileAt at = tile_at(p, t);
+			const int f0 = at.f0;
+			const int n0 = at.n0;
 			// thread 128 + j of the 256 epilogue threads fetches filter j's constants; the buffer's previous readers are through
 			// (every epilogue warp has passed comb_full of the tile in between)
 			const bool is_fil = tid >= TC_PIX;
@@ -181,49 +219,9 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				s_fil[buf][1][tid - TC_PIX] = __float_as_int(mean);
 				s_fil[buf][2][tid - TC_PIX] = __float_as_int(bias);
 			}
-			// the bulk stores of the previous tile have read the staging buffer (their issuers are threads 0..127)
-			if (p.bulk_out && tid < TP_NF) { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 			__syncwarp();
 			if (lane == 0) { mbar_arrive(&comb_full[buf]); }
 			if (!mbar_wait<32>(&comb_full[buf], ph, s_failed, limit)) { break; }
-			const int img0 = n0 / p.n_per_image;
-			const int pix0 = n0 - img0 * p.n_per_image;
-			const bool one_image = (pix0 + TC_PIX <= p.n_per_image || (img0 + 1) * p.n_per_image >= p.n_total);
-			if (p.bulk_out == 2)
-			{
-				// The staging buffer is free (every issuer of the previous tile's copies has seen them read it and has passed the
-				// barrier above): bring this tile's shortcut operand into it, [filter][pixel] like the results.
-				if (one_image)
-				{
-					if (tid == 0)
-					{
-						mbar_expect_tx(&sc_full, (uint32_t)TP_OUT_BYTES);       // a clipped box still counts in full
-						asm volatile(
-							"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-							:: "r"(out_base), "l"(reinterpret_cast<uint64_t>(&map_sc)), "r"(pix0), "r"(f0), "r"(img0), "r"(smem_u32(&sc_full)) : "memory");
-					}
-				}
-				else if (tid < NF)
-				{
-					const int g_end = min(n0 + TC_PIX, p.n_total);
-					const int rows = min(NF, p.M - f0);
-					if (tid == 0) { mbar_expect_tx(&sc_full, (uint32_t)(rows * (g_end - n0) * 4)); }
-					if (tid < rows)
-					{
-						int g = n0;
-						while (g < g_end)
-						{
-							const int img = g / p.n_per_image;
-							const int pix = g - img * p.n_per_image;
-							const int len = min(g_end - g, p.n_per_image - pix);
-							const float * src = p.shortcut_in + ((size_t)img * p.M + f0 + tid) * p.ldc + pix;
-							asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-									:: "r"(out_base + (uint32_t)((tid * TC_PIX + (g - n0)) * 4)), "l"(src), "r"(len * 4), "r"(smem_u32(&sc_full)) : "memory");
-							g += len;
-						}
-					}
-				}
-			}
 			if (!mbar_wait<512>(&acc_full[buf], ph, s_failed, limit)) { break; }
 			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 			if (!p.bulk_out)
@@ -235,9 +233,11 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				if (lane == 0) { mbar_arrive(&acc_empty[buf]); }
 				continue;
 			}
-			// Plain fp32 output, rows of the output contiguous in memory: the results go to shared memory as [filter][pixel] and
-			// leave as one bulk copy per filter row (per image the tile touches).  Ordinary stores from 8 warps would limit the
-			// tile rate: a store is only retired when the L2 has taken it, and in steady state that means evicting a dirty line.
+			// fp32 rows that are contiguous in memory (the layer's output, or the sum with a shortcut operand): the results go to
+			// shared memory as [filter][pixel], in two halves of 64 filters, and the copy warp writes each half with one tensor
+			// store (one bulk copy per filter row and image where the tile runs over the end of an image).  Ordinary stores from 8
+			// warps would limit the tile rate: a store is only retired when the L2 has taken it, and in steady state that means
+			// evicting a dirty line.  With a shortcut the copy warp has brought the operand into the same place beforehand.
 			{
 				const int pix_local = quarter * 32 + lane;
 				const float pad = (float)p.pad_bits;
@@ -245,21 +245,30 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				const bool has_bias = (p.bias != nullptr);
 				const uint32_t tlane = tmem_base + (uint32_t)(buf * NF) + ((uint32_t)(quarter * 32) << 16);
 				const bool sc_mode = (p.bulk_out == 2);
-				const int col = n0 + pix_local;
-				const bool col_ok = col < p.n_total;
-				const int my_img = col_ok ? col / p.n_per_image : 0;
-				const int my_pix = col_ok ? col - my_img * p.n_per_image : 0;
+				const bool col_ok = pix_local < at.valid;
+				const int my_img = at.img;
+				const int my_pix = at.pix0 + pix_local;
 				uint32_t * sum_words = (sc_mode && p.x.sum_signs != nullptr)
 						? p.x.sum_signs + ((size_t)my_img * (p.M >> 5) + (f0 >> 5)) * p.n_per_image + my_pix : nullptr;
 				uint32_t * row_words = (sc_mode && p.x.sum_rows != nullptr)
 						? p.x.sum_rows + ((size_t)my_img * p.n_per_image + my_pix) * p.x.sum_ldw + (f0 >> 5) : nullptr;
-				if (sc_mode && !mbar_wait<64>(&sc_full, (uint32_t)(it & 1), s_failed, limit)) { break; }
+				bool alive = true;
 				#pragma unroll 1
-				for (int chunk = share; chunk < NF / 32; chunk += TP_EPI_WARPS / 4)
+				for (int half = 0; half < 2; ++half)
 				{
+					const int chunk = half * 2 + share;           // this warp's 32 filters of the half
 					uint32_t d[32];
 					tmem_load<32>(tlane + (uint32_t)(chunk * 32), d);
 					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+					if (half == 1)
+					{
+						// the accumulator is read: the issuer may fill it again
+						asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+						__syncwarp();
+						if (lane == 0) { mbar_arrive(&acc_empty[buf]); }
+					}
+					// the previous tile's copies have read this half (and this tile's shortcut operand has arrived in it)
+					if (!mbar_wait<32>(&half_ready[half], (uint32_t)(it & 1), s_failed, limit)) { alive = false; break; }
 					uint32_t word = 0;
 					#pragma unroll
 					for (int j0 = 0; j0 < 32; j0 += 8)
@@ -297,6 +306,10 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 							asm volatile("st.shared.f32 [%0], %1;" :: "r"(out_base + (uint32_t)(((chunk * 32 + j0 + j) * TC_PIX + pix_local) * 4)), "f"(v[j]));
 						}
 					}
+					// staged values -> visible to the bulk-copy engine; the copy warp takes the half once every warp's part is in place
+					asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+					__syncwarp();
+					if (lane == 0) { mbar_arrive(&out_full[half]); }
 					if (sc_mode && col_ok && f0 + chunk * 32 < p.M)
 					{
 						// sign words of the sum (32 filters = one channel-packed word of this pixel); filters past M stay clear
@@ -306,47 +319,73 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 						if (row_words != nullptr) { row_words[chunk] = word; }
 					}
 				}
-				// the accumulator is read: the issuer may fill it again
-				asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-				__syncwarp();
-				if (lane == 0) { mbar_arrive(&acc_empty[buf]); }
-				// staged values -> visible to the bulk-copy engine; then every warp's part must be in place
-				asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-				__syncwarp();
-				if (lane == 0) { mbar_arrive(&out_full); }
-				if (!mbar_wait<32>(&out_full, (uint32_t)(it & 1), s_failed, limit)) { break; }
-				float * const dst_base = sc_mode ? p.shortcut_out : p.C;
-				if (one_image)
-				{
-					// the whole tile lies in one image: one tensor store (filters past M and pixels past the image are clipped)
-					if (tid == 0)
-					{
-						asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
-								:: "l"(reinterpret_cast<uint64_t>(&map_out)), "r"(pix0), "r"(f0), "r"(img0), "r"(out_base) : "memory");
-						asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-					}
-				}
-				else if (tid < NF && f0 + tid < p.M)
-				{
-					// the tile runs over the end of an image: one copy per filter row and image
-					const int g_end = min(n0 + TC_PIX, p.n_total);
-					int g = n0;
-					while (g < g_end)
-					{
-						const int img = g / p.n_per_image;
-						const int pix = g - img * p.n_per_image;
-						const int len = min(g_end - g, p.n_per_image - pix);
-						float * dst = dst_base + ((size_t)img * p.M + f0 + tid) * p.ldc + pix;
-						asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-								:: "l"(dst), "r"(out_base + (uint32_t)((tid * TC_PIX + (g - n0)) * 4)), "r"(len * 4) : "memory");
-						g += len;
-					}
-					asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-				}
+				if (!alive) { break; }
 			}
 		}
-		// the staging buffer must outlive the copies that read it
-		if (p.bulk_out && tid < TP_NF) { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+	}
+	else if (warp == TP_COPY_WARP)
+	{
+		// ---- copy warp: writes the staged halves, hands them back, and fetches the next tile's shortcut operand ---------
+		if (p.bulk_out != 0)
+		{
+			const bool sc_mode = (p.bulk_out == 2);
+			uint32_t requested[2] = {0, 0};                   // completions of half_ready[h] asked for so far
+			// Makes half h ready for tile t2: with a shortcut, the copy of its operand (which completes the barrier through its
+			// byte count); without, the barrier's one arrival.
+			auto request = [&](int t2, int h)
+			{
+				++requested[h];
+				const TileAt at = tile_at(p, t2);
+				const int f2 = at.f0 + h * TP_HALF_ROWS;
+				if (lane != 0) { return; }
+				if (!sc_mode || f2 >= p.M)                    // no operand to fetch, or the half lies behind the last filter
+				{
+					mbar_arrive(&half_ready[h]);
+					return;
+				}
+				mbar_expect_tx(&half_ready[h], (uint32_t)TP_HALF_BYTES);      // a clipped box still counts in full
+				asm volatile(
+					"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+					:: "r"(out_base + (uint32_t)(h * TP_HALF_BYTES)), "l"(reinterpret_cast<uint64_t>(&map_sc)), "r"(at.pix0), "r"(f2), "r"(at.img),
+					   "r"(smem_u32(&half_ready[h])) : "memory");
+			};
+			if ((int)blockIdx.x < p.tiles)
+			{
+				request(blockIdx.x, 0);
+				request(blockIdx.x, 1);
+			}
+			int it = 0;
+			bool ok = true;
+			for (int t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it)
+			{
+				const TileAt at = tile_at(p, t);
+				for (int h = 0; h < 2; ++h)
+				{
+					ok = mbar_wait<64>(&out_full[h], (uint32_t)(it & 1), s_failed, limit);
+					if (!ok) { break; }
+					const int fh = at.f0 + h * TP_HALF_ROWS;
+					if (lane == 0 && fh < p.M)
+					{
+						// one tensor store per half: filters past M and pixels past the end of the image are clipped
+						asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+								:: "l"(reinterpret_cast<uint64_t>(&map_out)), "r"(at.pix0), "r"(fh), "r"(at.img), "r"(out_base + (uint32_t)(h * TP_HALF_BYTES))
+								: "memory");
+					}
+					asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+					// once the copies have read the half it belongs to the next tile
+					asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+					__syncwarp();
+					if (t + (int)gridDim.x < p.tiles) { request(t + (int)gridDim.x, h); }
+				}
+			}
+			// nothing of this CTA may still be in flight when it exits: the stores, and (after a failed wait) requested operands
+			asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+			for (int h = 0; h < 2; ++h)
+			{
+				if (requested[h] > 0) { mbar_wait_plain(&half_ready[h], (requested[h] - 1) & 1u, limit); }
+			}
+		}
+		__syncwarp();
 	}
 	else if (warp == TP_TMA_WARP)
 	{
@@ -357,8 +396,9 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 			bool ok = true;
 			for (int t = blockIdx.x; t < p.tiles && ok; t += gridDim.x)
 			{
-				const int f0 = (t % p.tiles_f) * NF;
-				const int n0 = (t / p.tiles_f) * TC_PIX;
+				const TileAt at = tile_at(p, t);
+				const int f0 = at.f0;
+				const int n0 = at.n0;
 				for (int c = 0; c < chunks; ++c, ++rc)
 				{
 					const uint32_t rs = rc % TP_RAW_STAGES;
@@ -550,14 +590,14 @@ static int make_row_map(CUtensorMap * map, const void * base, int rows, size_t l
 	return XNOR_B200_OK;
 }
 
-// Tensor map of an fp32 tensor [images][M][ldc] (the output, or a shortcut operand) for boxes of 128 pixels x 128 filters of one image.
+// Tensor map of an fp32 tensor [images][M][ldc] (the output, or a shortcut operand) for boxes of 128 pixels x 64 filters of one image.
 static int make_out_map(CUtensorMap * map, float * base, int n_per_image, int M, int images, int ldc)
 {
 	EncodeTiledFn enc = tensor_map_encoder();
 	if (enc == nullptr) { return XNOR_B200_ERR_CUDA; }
 	const cuuint64_t dims[3] = {(cuuint64_t)n_per_image, (cuuint64_t)M, (cuuint64_t)images};
 	const cuuint64_t strides[2] = {(cuuint64_t)ldc * 4, (cuuint64_t)M * (cuuint64_t)ldc * 4};
-	const cuuint32_t box[3] = {(cuuint32_t)TC_PIX, (cuuint32_t)TP_NF, 1};
+	const cuuint32_t box[3] = {(cuuint32_t)TC_PIX, (cuuint32_t)TP_HALF_ROWS, 1};
 	const cuuint32_t elem[3] = {1, 1, 1};
 	const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, elem,
 			CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -585,12 +625,15 @@ int tcp_stages_output(const TcParams & p)
 static int launch_tcp(TcParams & p, cudaStream_t stream)
 {
 	p.tiles_f = (p.M + TP_NF - 1) / TP_NF;
-	const long long tiles = (long long)p.tiles_f * ((p.n_total + TC_PIX - 1) / TC_PIX);
+	p.bulk_out = tcp_stages_output(p);
+	// staged epilogue: tiles per image (none crosses an image); otherwise tiles over all pixels of the batch
+	p.tiles_per_image = (p.bulk_out != 0) ? (p.n_per_image + TC_PIX - 1) / TC_PIX : 0;
+	const long long tiles_n = (p.bulk_out != 0) ? (long long)p.tiles_per_image * (p.n_total / p.n_per_image) : (p.n_total + TC_PIX - 1) / TC_PIX;
+	const long long tiles = (long long)p.tiles_f * tiles_n;
 	if (tiles > 0x7fffffffLL) { return XNOR_B200_ERR_TOO_LARGE; }
 	p.tiles = (int)tiles;
 	// 256-bit K blocks; what they cover behind K is zero in both operands (rows are zero-padded, the copies zero-fill)
 	p.pad_bits = ((p.kblocks + TP_RAW_KB - 1) / TP_RAW_KB) * 256 - p.K;
-	p.bulk_out = tcp_stages_output(p);
 	CUtensorMap map_pix, map_fil;
 	int rc = make_row_map(&map_pix, p.B, p.n_total, (size_t)p.ldb_words * 4, TC_PIX);
 	if (rc != XNOR_B200_OK) { return rc; }
