@@ -611,9 +611,9 @@ def kernel_rooflines(net, batch, binops_per_image, stream, flush, dev):
     same = bool(torch.equal(tc_out, C_))
     capi.set_tuning()
     big_tops, int_tops = ops_big / (ms_big * 1e-3) / 1e12, ops_big / (ms_int * 1e-3) / 1e12
-    traffic, traffic_source = captured_traffic("xnor_gemm_tc_m512_n43264_k2304")
+    traffic, traffic_source = captured_traffic("xnor_gemm_tcp_m512_n43264_k2304")
     out["roofline_large_batch"] = {
-        "kernel": "tcgen05 kind::mxf4 XNOR GEMM (bits widened to e2m1 +-1), M=512 N=64x676 K=2304", "bound": "tensor", "achieved": big_tops,
+        "kernel": "xnor_gemm_tcp_kernel: persistent tcgen05 kind::mxf4 XNOR GEMM (bits widened to e2m1 +-1, results staged in shared memory and written by tensor stores; the library's own choice for this shape), M=512 N=64x676 K=2304", "bound": "tensor", "achieved": big_tops,
         "peak": umma_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": big_tops / umma_peak_tops,
         "traffic": traffic, "traffic_source": traffic_source, "algorithmic_bytes": alg_big,
         "peak_source": "measured in this run: back-to-back tcgen05.mma kind::mxf4 128x256x64 from resident shared memory",
@@ -644,7 +644,7 @@ def kernel_rooflines(net, batch, binops_per_image, stream, flush, dev):
     ms_k = time_rotating([long_gemm(i) for i in range(len(Aks))])
     k_tops = 2.0 * Mk * Nk * Kk / (ms_k * 1e-3) / 1e12
     out["roofline_large_k"] = {
-        "kernel": "tcgen05 kind::mxf4 XNOR GEMM, M=1024 N=64x676 K=9216 (library's own choice of kernel)", "bound": "tensor", "achieved": k_tops,
+        "kernel": "xnor_gemm_tcp_kernel (persistent tcgen05 kind::mxf4 XNOR GEMM, the library's own choice), M=1024 N=64x676 K=9216", "bound": "tensor", "achieved": k_tops,
         "peak": umma_peak_tops, "unit": "TOP/s (binary ops, 2*M*N*K)", "frac": k_tops / umma_peak_tops, "traffic": None,
         "algorithmic_bytes": alg_k, "peak_source": out["roofline_large_batch"]["peak_source"],
         "frac_of_kind_i8_rate": k_tops / umma_i8_peak_tops, "vs_int_popc_peak": k_tops / popc_peak_tops, "ms": ms_k,

@@ -316,20 +316,25 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	int rc = tc_fill_launch_fields(p);
 	if (rc != XNOR_B200_OK) { return rc; }
 	// The persistent kernel where it measured faster (B200, layer shapes of batch 16..64; us per call, persistent vs one tile per
-	// CTA).  Plain fp32 output, which it writes with tensor stores: 55.7 vs 87.2 for 512 x 43264 x 2304, 320 vs 424 at
-	// 1024 x 43264 x 9216, 46.9 vs 74.2 at 256 x 100352 x 1152, 72.4 vs 108 at 128 x 401408 x 576, 23.1 vs 33.7 at
-	// 255 x 43264 x 1024.  Sign words and sinks: from K = 2048 on, where its main loop hides the 8 epilogue warps.  A fused
-	// shortcut stays with the other kernel's 24 epilogue warps per SM (171 vs 101 us for 256 x 100352 x 1152).
+	// CTA).  fp32-only epilogues, which it writes with tensor stores from shared memory -- plain output: 55.8 vs 87.2 for
+	// 512 x 43264 x 2304, 324 vs 424 at 1024 x 43264 x 9216, 46.9 vs 74.2 at 256 x 100352 x 1152, 73.5 vs 108 at
+	// 128 x 401408 x 576, 23.1 vs 33.7 at 255 x 43264 x 1024; only the sum with a shortcut operand (darknet53 at batch 32):
+	// 58 vs 93 for 256 filters at 56 x 56, 48 vs 62 for 512 at 28 x 28, 285 vs 392 for 64 filters at 224 x 224 (half of each
+	// 128-filter tile is idle there, but the layer is bound by its 0.8 GB of fp32 traffic).  Sign words and sinks: from K = 2048
+	// on, where its main loop hides the 8 epilogue warps.  An output AND a shortcut sum, or counts, stay with the other kernel.
 	// xnor_b200_set_tuning pins either.
 #ifndef XNOR_TCP_MIN_K_STAGED
-#define XNOR_TCP_MIN_K_STAGED 512
+#define XNOR_TCP_MIN_K_STAGED 256
 #endif
 #ifndef XNOR_TCP_MIN_K_OTHER
 #define XNOR_TCP_MIN_K_OTHER 2048
 #endif
 	const int variant = tuning().tc_kernel;
 	const int staged = tcp_stages_output(p);
-	const bool tcp_can = (M > 64 && counts == nullptr && (shortcut_in == nullptr || staged == 2));
+#ifndef XNOR_TCP_MIN_M_STAGED
+#define XNOR_TCP_MIN_M_STAGED 33
+#endif
+	const bool tcp_can = (M >= (staged != 0 ? XNOR_TCP_MIN_M_STAGED : 65) && counts == nullptr && (shortcut_in == nullptr || staged == 2));
 	const bool tcp_wins = tcp_can && K >= (staged != 0 ? XNOR_TCP_MIN_K_STAGED : XNOR_TCP_MIN_K_OTHER);
 	if (variant == 2 || (variant == 0 && tcp_wins)) { return launch_xnor_gemm_tcp(p, stream); }
 	// the kind::mxf4 kernel walks 256-bit K blocks; what they cover behind K is zero in both operands

@@ -1,7 +1,7 @@
-// Persistent tcgen05 XNOR GEMM for large layers (more than 64 filters): one CTA per SM walks over 128-pixel x 128-filter
-// tiles; the same arithmetic as the one-tile-per-CTA kernel in xnor_gemm_tc.cu (bits widened to e2m1 +1.0 / -1.0,
-// tcgen05.mma kind::mxf4 with both scale factors at 2^0, exact fp32 accumulators in TMEM), with the roles separated so that
-// none of them waits for another more than once per stage and the epilogue of a tile runs under the main loop of the next:
+// Persistent tcgen05 XNOR GEMM: one CTA per SM walks over 128-pixel x 128-filter tiles; the same arithmetic as the
+// one-tile-per-CTA kernel in xnor_gemm_tc.cu (bits widened to e2m1 +1.0 / -1.0, tcgen05.mma kind::mxf4 with both scale factors
+// at 2^0, exact fp32 accumulators in TMEM), with the roles separated so that none of them waits for another more than once per
+// stage and the epilogue of a tile runs under the main loop of the next:
 //
 //   warp 24        TMA producer: one lane brings the packed bit rows of the tile -- 128 pixel rows and 128 filter rows, one
 //                  256-bit K block (32 bytes) per row and raw stage -- into a ring of raw stages with cp.async.bulk.tensor.2d
@@ -12,13 +12,16 @@
 //   warp 25        issuer: per stage 4 x tcgen05.mma.cta_group::1.kind::mxf4.block_scale (M=128, N=128, K=64, both operands
 //                  through shared-memory descriptors) into one of TWO accumulator buffers, tcgen05.commit frees the stage,
 //                  a last commit per tile hands the buffer to the epilogue;
-//   warps 0..7     epilogue: tcgen05.ld of the finished buffer, mean scale, bias, leaky, shortcut, sign words and sinks
-//                  (tc_common.cuh), while the issuer already fills the other buffer with the next tile.
+//   warps 0..7     epilogue: tcgen05.ld of the finished buffer, mean scale, bias, leaky, then either the shared epilogue of
+//                  tc_common.cuh (sign words, sinks, counts, output + shortcut) or, for fp32 rows only, the staged one: values
+//                  (or their sum with the shortcut operand found there) go to a [filter][pixel] staging buffer in two halves;
+//   warp 26        copy warp of the staged epilogue: one tensor store per half, then -- once the copy has read the half -- the
+//                  hand-back to the epilogue, which with a shortcut is the tensor load of the next tile's operand into it.
 //
 // Tensor memory (512 columns): accumulators 2 x 128, then 16 columns of scale factors (every byte 0x7F = 2^0).
-// Every wait on an mbarrier is bounded.  When one runs out, every role leaves its loops, the producer waits (bounded) for the
-// copies it still has in flight, the issuer for its MMAs, the tensor memory is released, a status word is set, and the kernel
-// returns by itself.
+// Every wait on an mbarrier is bounded.  When one runs out, every role leaves its loops, the producer and the copy warp wait
+// (bounded) for the copies they still have in flight, the issuer for its MMAs, the tensor memory is released, a status word is
+// set, and the kernel returns by itself.
 #include "tc_common.cuh"
 
 #include <cuda.h>       // CUtensorMap and its enums; the encoder itself is fetched through cudaGetDriverEntryPoint
@@ -38,6 +41,7 @@ constexpr int TP_MMA_WARP = TP_TMA_WARP + 1;
 constexpr int TP_COPY_WARP = TP_MMA_WARP + 1;
 constexpr int TP_THREADS = (TP_COPY_WARP + 1) * 32;
 constexpr int TP_RAW_KB = 2;                  // 128-bit pieces per raw stage: 32 bytes = one 256-bit K block per operand row
+static_assert(TP_RAW_KB == 2, "the expanders read a row as two 16-byte halves");
 constexpr int TP_RAW_STAGES = 6;
 constexpr int TP_STAGES = 3;                  // operand stages: the pixel tile and the filter tile of one 256-bit K block, 16 KB each
 constexpr int TP_ROWS = TC_PIX + TP_NF;
@@ -257,6 +261,19 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				for (int half = 0; half < 2; ++half)
 				{
 					const int chunk = half * 2 + share;           // this warp's 32 filters of the half
+					if (f0 + half * TP_HALF_ROWS >= p.M)
+					{
+						// the half lies behind the last filter: nothing to compute, only the hand-overs (the copy warp skips it too)
+						if (half == 1)
+						{
+							asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+							__syncwarp();
+							if (lane == 0) { mbar_arrive(&acc_empty[buf]); }
+						}
+						__syncwarp();
+						if (lane == 0) { mbar_arrive(&out_full[half]); }
+						continue;
+					}
 					uint32_t d[32];
 					tmem_load<32>(tlane + (uint32_t)(chunk * 32), d);
 					asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -492,6 +509,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 		const uint32_t raw_row = raw_base + (uint32_t)((is_pix ? row : TC_PIX + row) * 16 * TP_RAW_KB);
 		// this thread's row in stage 0 (pixel tile first, filter tile behind it), swizzle folded in
 		const uint32_t row_swz0 = (fil_base + (is_pix ? 0u : (uint32_t)TP_SLOT_BYTES) + (uint32_t)row * 128u) ^ ((uint32_t)(row & 7) << 4);
+		const int swap = (lane >> 2) & 1;
 		const bool withhold = (p.withhold != 0 && warp == TP_PIX_WARP0);
 		uint32_t rc = 0;                                      // raw chunks = operand stages passed so far (every warp counts all of them)
 		bool ok = true;
@@ -503,13 +521,23 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 				const uint32_t rs = rc % TP_RAW_STAGES;
 				ok = mbar_wait<128>(&raw_full[rs], (rc / TP_RAW_STAGES) & 1u, s_failed, limit);
 				if (!ok) { break; }
+				// Rows are 32 bytes apart, so the eight lanes of a quarter warp would meet in the same banks twice if each read
+				// the first half of its row: lanes 4..7 of every eight take the second half first (swap) and put them back in order.
 				uint4 w[TP_RAW_KB];
 				#pragma unroll
 				for (int j = 0; j < TP_RAW_KB; ++j)
 				{
+					uint4 v;
 					asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-							: "=r"(w[j].x), "=r"(w[j].y), "=r"(w[j].z), "=r"(w[j].w)
-							: "r"(raw_row + rs * (uint32_t)TP_RAW_STAGE_BYTES + (uint32_t)(j * 16)) : "memory");
+							: "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+							: "r"(raw_row + rs * (uint32_t)TP_RAW_STAGE_BYTES + (uint32_t)((j ^ swap) * 16)) : "memory");
+					w[j] = v;
+				}
+				if (swap != 0)
+				{
+					const uint4 t0 = w[0];
+					w[0] = w[1];
+					w[1] = t0;
 				}
 				// The raw stage can take the next copy once the bits are in registers.  A store of the loaded words comes first: the
 				// warp cannot issue it before the loads have returned, and the arrival follows it in program order.  Without it the
