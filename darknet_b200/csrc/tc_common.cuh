@@ -333,6 +333,44 @@ __device__ __forceinline__ void epilogue_values(const TcParams & p, const Filter
 	}
 }
 
+// One channel-packed word of sign bits (32 filters from 32 * mw on, of this thread's pixel): into the layer's sign words and
+// into the operands of the consumers behind its sinks.  Every lane of the warp calls it (a pooled sink combines the four lanes
+// of a 2x2 window with shuffles); word_ok = this lane's pixel and filter group exist.
+__device__ __forceinline__ void emit_sign_word(const TcParams & p, uint32_t word, bool word_ok, int img, int pixcol, int pix, int col, int mw)
+{
+	if (p.signs != nullptr && word_ok) { p.signs[((size_t)img * (p.M >> 5) + mw) * p.n_per_image + pix] = word; }
+	#pragma unroll
+	for (int si = 0; si < 2; ++si)
+	{
+		if (si >= p.x.n_sinks) { break; }
+		const SinkParams & sk = p.x.sinks[si];
+		if (sk.pool != 0)
+		{
+			// window-major columns: lanes 4w .. 4w+3 hold one 2x2 window and share the taps of its pooled word
+			uint32_t w = word;
+			w |= __shfl_xor_sync(0xffffffffu, w, 1);
+			w |= __shfl_xor_sync(0xffffffffu, w, 2);
+			if (!word_ok) { continue; }
+			const int q = pixcol >> 2;
+			const int wy = q / p.x.win_w;
+			const int wx = q - wy * p.x.win_w;
+			for (int tap = col & 3; tap < sk.taps; tap += 4) { sink_store_tap(sk, img, wy, wx, mw, tap, w); }
+		}
+		else if (word_ok)
+		{
+			const int oy = pix / p.x.out_w;
+			const int ox = pix - oy * p.x.out_w;
+			const int copies = (sk.up == 2) ? 4 : 1;
+			for (int t = 0; t < copies * sk.taps; ++t)
+			{
+				const int cp = t / sk.taps;
+				const int tap = t - cp * sk.taps;
+				sink_store_tap(sk, img, (sk.up == 2) ? 2 * oy + (cp >> 1) : oy, (sk.up == 2) ? 2 * ox + (cp & 1) : ox, mw, tap, word);
+			}
+		}
+	}
+}
+
 // Epilogue of one 128-pixel x NF-filter tile for one warp.  A warp may read the TMEM lanes 32*(warp % 4) .. +31 (`quarter`);
 // the `shares` warps that sit on the same quarter interleave over the tile's 32-column chunks (share, share + shares, ...).
 // tmem_acc = TMEM address of the accumulator's first column at lane 0; s_pop[pixel of the tile] = popc of its row;
@@ -398,39 +436,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams & p, const int * s_
 					}
 				}
 			}
-			const int mw = (f0 + fbase) >> 5;
-			const bool word_ok = col_ok && f0 + fbase < p.M;
-			if (p.signs != nullptr && word_ok) { p.signs[((size_t)img * (p.M >> 5) + mw) * p.n_per_image + pix] = word; }
-			#pragma unroll
-			for (int si = 0; si < 2; ++si)
-			{
-				if (si >= p.x.n_sinks) { break; }
-				const SinkParams & sk = p.x.sinks[si];
-				if (sk.pool != 0)
-				{
-					// window-major columns: lanes 4w .. 4w+3 hold one 2x2 window and share the taps of its pooled word
-					uint32_t w = word;
-					w |= __shfl_xor_sync(0xffffffffu, w, 1);
-					w |= __shfl_xor_sync(0xffffffffu, w, 2);
-					if (!word_ok) { continue; }
-					const int q = pixcol >> 2;
-					const int wy = q / p.x.win_w;
-					const int wx = q - wy * p.x.win_w;
-					for (int tap = col & 3; tap < sk.taps; tap += 4) { sink_store_tap(sk, img, wy, wx, mw, tap, w); }
-				}
-				else if (word_ok)
-				{
-					const int oy = pix / p.x.out_w;
-					const int ox = pix - oy * p.x.out_w;
-					const int copies = (sk.up == 2) ? 4 : 1;
-					for (int t = 0; t < copies * sk.taps; ++t)
-					{
-						const int cp = t / sk.taps;
-						const int tap = t - cp * sk.taps;
-						sink_store_tap(sk, img, (sk.up == 2) ? 2 * oy + (cp >> 1) : oy, (sk.up == 2) ? 2 * ox + (cp & 1) : ox, mw, tap, word);
-					}
-				}
-			}
+			emit_sign_word(p, word, col_ok && f0 + fbase < p.M, img, pixcol, pix, col, (f0 + fbase) >> 5);
 			if (p.C == nullptr) { continue; }
 		}
 		if (!col_ok) { continue; }

@@ -256,6 +256,7 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 						? p.x.sum_signs + ((size_t)my_img * (p.M >> 5) + (f0 >> 5)) * p.n_per_image + my_pix : nullptr;
 				uint32_t * row_words = (sc_mode && p.x.sum_rows != nullptr)
 						? p.x.sum_rows + ((size_t)my_img * p.n_per_image + my_pix) * p.x.sum_ldw + (f0 >> 5) : nullptr;
+				const bool want_words = (!sc_mode && (p.signs != nullptr || p.x.n_sinks > 0));
 				bool alive = true;
 				#pragma unroll 1
 				for (int half = 0; half < 2; ++half)
@@ -301,6 +302,11 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 							if (has_bias) { v[j] = __fadd_rn(v[j], __int_as_float(fb[j])); }
 							v[j] = fmaxf(v[j], __fmul_rn(v[j], slope));
 						}
+						if (want_words)
+						{
+							#pragma unroll
+							for (int j = 0; j < 8; ++j) { word |= (v[j] > 0.0f ? 1u : 0u) << (j0 + j); }
+						}
 						if (sc_mode)
 						{
 							// the sum with the shortcut operand takes the value's place
@@ -327,6 +333,11 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 					asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 					__syncwarp();
 					if (lane == 0) { mbar_arrive(&out_full[half]); }
+					if (want_words)
+					{
+						// the layer's sign words and the consumers' operands behind its sinks (filters past M have value 0: bit clear)
+						emit_sign_word(p, word, col_ok && f0 + chunk * 32 < p.M, my_img, my_pix, my_pix, n0 + pix_local, (f0 + chunk * 32) >> 5);
+					}
 					if (sc_mode && col_ok && f0 + chunk * 32 < p.M)
 					{
 						// sign words of the sum (32 filters = one channel-packed word of this pixel); filters past M stay clear
@@ -637,16 +648,19 @@ static int make_out_map(CUtensorMap * map, float * base, int n_per_image, int M,
 	return XNOR_B200_OK;
 }
 
-// What the staged epilogue can write: fp32 rows that are contiguous runs of whole 16-byte pieces, and nothing else but the sign
-// words of a shortcut sum.  1: the layer's own output; 2: only the sum with a shortcut operand of the same layout; 0: neither.
+// What the staged epilogue can write: fp32 rows that are contiguous runs of whole 16-byte pieces, in plain pixel order, with sign
+// words beside them.  1: the layer's own output (+ its sign words and sinks); 2: only the sum with a shortcut operand of the
+// same layout (+ the sum's sign words); 0: neither.
 int tcp_stages_output(const TcParams & p)
 {
-	if (p.signs != nullptr || p.counts != nullptr || p.x.n_sinks != 0 || p.x.win_w != 0) { return 0; }
+	if (p.counts != nullptr || p.x.win_w != 0) { return 0; }
 	if (p.n_per_image % 4 != 0 || p.n_total % p.n_per_image != 0 || p.ldc % 4 != 0) { return 0; }
 	if (p.shortcut_in == nullptr)
 	{
+		// the layer's sign words and plain (or upsampling) sinks ride along: one word per pixel and 32 filters
 		return (p.C != nullptr && p.x.sum_signs == nullptr && p.x.sum_rows == nullptr && (((uintptr_t)p.C) & 15u) == 0) ? 1 : 0;
 	}
+	if (p.signs != nullptr || p.x.n_sinks != 0) { return 0; }
 	return (p.C == nullptr && p.shortcut_out != nullptr && ((((uintptr_t)p.shortcut_in) | ((uintptr_t)p.shortcut_out)) & 15u) == 0) ? 2 : 0;
 }
 

@@ -128,6 +128,37 @@ def test_upsample_and_route_sinks_build_a_concatenated_operand():
     assert torch.equal(L.forward_convolutional_layer_io(b, packed=True), want)
 
 
+@pytest.mark.parametrize("variant", [1, 2], ids=["tile-per-cta", "persistent"])
+@pytest.mark.parametrize("case", [(4, 64, 28, 28, 128, 2), (2, 32, 20, 24, 96, 1), (3, 128, 14, 14, 160, 1)], ids=lambda c: "b%d_c%d_%dx%d_n%d_s%d" % c)
+def test_output_and_plain_sinks_from_both_tensor_core_kernels(case, variant):
+    """darknet53's stride-2 layers: the fp32 tensor (the next block's shortcut operand) AND the operand of the 1x1 layer behind.
+    The persistent kernel stages the values in shared memory, writes them with tensor stores and emits the sign words from the
+    same registers; the other kernel stores both directly.  Tensor and operands equal the unfused chain, bit for bit; a second,
+    upsampling sink rides along."""
+    batch, c1, h, w, n1, stride = case
+    a = L.make_convolutional_layer(batch, h, w, c1, n1, 3, stride, 1, capi.LEAKY)
+    a.load_weights(torch.from_numpy(synth.bell(61, (n1, c1 * 9), 0.05)).cuda(), torch.from_numpy(synth.bell(62, (n1,), 0.3)).cuda())
+    L.binary_align_weights(a)
+    oh, ow = a.geom.out_h, a.geom.out_w
+    near = make(batch, n1, oh, ow, 40, 1, 63, capi.LEAKY)
+    far = make(batch, n1, 2 * oh, 2 * ow, 32, 3, 65)
+    x = torch.from_numpy(synth.bell(67, (batch, c1, h, w), 1.0)).cuda()
+    capi.set_tuning(gemm_route=capi.ROUTE_INTEGER)
+    y = L.forward_convolutional_layer_gpu(a, x).clone()
+    want_near = operand(near, y)
+    want_far = operand(far, F.interpolate(y, scale_factor=2, mode="nearest").contiguous())
+    capi.set_tuning(gemm_route=capi.ROUTE_TENSOR, tc_kernel=variant)
+    for _ in range(3):
+        near.scratch.zero_()
+        far.scratch.zero_()
+        a.output_gpu.fill_(float("nan"))
+        got = L.forward_convolutional_layer_io(a, x=x, sinks=[L.Sink(near), L.Sink(far, upsample=2)], want_output=True)
+        torch.cuda.synchronize()
+        assert torch.equal(got, y)
+        assert torch.equal(near.scratch[:want_near.numel()].view(want_near.shape), want_near)
+        assert torch.equal(far.scratch[:want_far.numel()].view(want_far.shape), want_far)
+
+
 def test_two_sinks_from_one_layer():
     """yolov3-tiny's layer 8: fp32 for the route, a pooled sink for the next layer and a plain sink for the far one."""
     batch = 1
