@@ -334,7 +334,10 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 #ifndef XNOR_TCP_MIN_M_STAGED
 #define XNOR_TCP_MIN_M_STAGED 33
 #endif
-	const bool tcp_can = (M >= (staged != 0 ? XNOR_TCP_MIN_M_STAGED : 65) && counts == nullptr && (shortcut_in == nullptr || staged == 2));
+	// up to 64 filters half of every 128-filter tile is idle: only worth it where the epilogue is heavy (a shortcut operand to
+	// fetch, or sign words / sinks beside the tensor); the plain output of such a layer is 10-15 % faster on the other kernel
+	const bool heavy = (staged == 2 || (staged == 1 && (signs != nullptr || p.x.n_sinks > 0)));
+	const bool tcp_can = (M >= (heavy ? XNOR_TCP_MIN_M_STAGED : 65) && counts == nullptr && (shortcut_in == nullptr || staged == 2));
 	const bool tcp_wins = tcp_can && K >= (staged != 0 ? XNOR_TCP_MIN_K_STAGED : XNOR_TCP_MIN_K_OTHER);
 	if (variant == 2 || (variant == 0 && tcp_wins)) { return launch_xnor_gemm_tcp(p, stream); }
 	// the kind::mxf4 kernel walks 256-bit K blocks; what they cover behind K is zero in both operands
