@@ -239,9 +239,9 @@ xnor_gemm_tcp_kernel(const TcParams p, const __grid_constant__ CUtensorMap map_p
 			}
 			// fp32 rows that are contiguous in memory (the layer's output, or the sum with a shortcut operand): the results go to
 			// shared memory as [filter][pixel], in two halves of 64 filters, and the copy warp writes each half with one tensor
-			// store (one bulk copy per filter row and image where the tile runs over the end of an image).  Ordinary stores from 8
-			// warps would limit the tile rate: a store is only retired when the L2 has taken it, and in steady state that means
-			// evicting a dirty line.  With a shortcut the copy warp has brought the operand into the same place beforehand.
+			// store (a tile never crosses an image in this mode, see tile_at).  Ordinary stores from 8 warps would limit the
+			// tile rate: a store is only retired when the L2 has taken it, and in steady state that means evicting a dirty
+			// line.  With a shortcut the copy warp has brought the operand into the same place beforehand.
 			{
 				const int pix_local = quarter * 32 + lane;
 				const float pad = (float)p.pad_bits;
@@ -654,7 +654,8 @@ static int make_out_map(CUtensorMap * map, float * base, int n_per_image, int M,
 int tcp_stages_output(const TcParams & p)
 {
 	if (p.counts != nullptr || p.x.win_w != 0) { return 0; }
-	if (p.n_per_image % 4 != 0 || p.n_total % p.n_per_image != 0 || p.ldc % 4 != 0) { return 0; }
+	// images smaller than a tile would leave most of every tile idle (and the tensor maps' boxes wider than the tensor)
+	if (p.n_per_image < TC_PIX || p.n_per_image % 4 != 0 || p.n_total % p.n_per_image != 0 || p.ldc % 4 != 0) { return 0; }
 	if (p.shortcut_in == nullptr)
 	{
 		// the layer's sign words and plain (or upsampling) sinks ride along: one word per pixel and 32 filters
