@@ -4,6 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
                     [--workload NET] [--batch B | --global-batch B] [--forwards-per-step F]
     python bench.py --kernel gemm --shape M N K [--route auto|integer|tensor|tiled] [--tc-kernel 1|2] [--shortcut] [--reps R] [--no-graph]
+    python bench.py --kernel layer --shape BATCH C H W N KS [STRIDE] [--sum-only] [--route ...] [--tc-kernel 1|2]
     python bench.py --kernel pack --shape BATCH C H W N KS [--pack-ctas-per-sm C] [--reps R] [--no-graph]
     python bench.py --kernel gemms | --kernel fconv --shape CASE
 
@@ -73,7 +74,8 @@ def parse_args():
     ap.add_argument("--workload", default="yolov3-tiny_xnor", choices=["yolov3-tiny_xnor", "tiny-yolo_xnor", "darknet53_448_xnor"],
                     help="network to run; the default is the configuration the metric is quoted on, the others are the "
                          "batched BASELINE configurations (use with --batch or --global-batch)")
-    ap.add_argument("--kernel", default=None, choices=["gemm", "gemms", "pack", "fconv"], help="time one kernel instead of the network")
+    ap.add_argument("--kernel", default=None, choices=["gemm", "gemms", "pack", "fconv", "layer"], help="time one kernel instead of the network")
+    ap.add_argument("--sum-only", action="store_true", help="--kernel layer: only the sum with a fused shortcut operand is written, plus its sign words")
     ap.add_argument("--shape", type=int, nargs="*", default=[])
     ap.add_argument("--route", default="auto", choices=sorted(ROUTES))
     ap.add_argument("--tc-kernel", type=int, default=0, choices=[0, 1, 2], help="--kernel gemm with --route tensor: 1 = one tile per CTA, 2 = persistent")
@@ -924,6 +926,36 @@ def run_kernel(args) -> None:
             capi.set_tuning()
             print(f"pack b={batch} c={c} {h}x{w} ks={ks} in two passes: {us:.1f} us/call, {moved / us / 1e3:.0f} GB/s, "
                   f"equal={bool(torch.equal(want, outs[-1]))}")
+    elif args.kernel == "layer":
+        # one xnor layer's GEMM on an operand packed beforehand: the fp32 tensor, or (--sum-only) only the sum with a shortcut
+        # operand and the sum's sign words, as darknet53's residual blocks ask for it
+        batch, c, h, w, n, ks = args.shape[:6]
+        stride = args.shape[6] if len(args.shape) > 6 else 1
+        wt = torch.randn(n, c * ks * ks, device="cuda") * 0.05
+        bias = torch.randn(n, device="cuda") * 0.3
+        x = torch.randn(batch, c, h, w, device="cuda")
+        probe = L.make_convolutional_layer(batch, h, w, c, n, ks, stride, ks // 2, capi.LEAKY)
+        out_bytes = 4 * batch * n * probe.geom.n_out
+        moved = batch * probe.geom.n_out * probe.new_lda // 8 + out_bytes * (2 if args.sum_only else 1)
+        layers = []
+        for _ in range(copies_for(moved)):
+            l = L.make_convolutional_layer(batch, h, w, c, n, ks, stride, ks // 2, capi.LEAKY)
+            l.load_weights(wt, bias)
+            L.binary_align_weights(l)
+            op = L.pack_input(l, x)
+            l.scratch[:op.numel()].copy_(op.view(-1))
+            if args.sum_only:
+                l.bin_conv_shortcut_in_gpu = torch.randn(batch, n, probe.geom.out_h, probe.geom.out_w, device="cuda")
+                l.bin_conv_shortcut_out_gpu = torch.empty_like(l.bin_conv_shortcut_in_gpu)
+            layers.append(l)
+
+        def layer_call(l):
+            if args.sum_only:
+                return lambda: L.forward_convolutional_layer_io(l, packed=True, shortcut_only=True, shortcut_signs=True)
+            return lambda: L.forward_convolutional_layer_io(l, packed=True, want_output=True)
+        us = timed([layer_call(l) for l in layers], args.reps)
+        print(f"layer b={batch} c={c} {h}x{w} n={n} ks={ks} stride={stride} route={args.route} sum_only={int(args.sum_only)}: {us:.1f} us/call, "
+              f"{moved / us / 1e3:.0f} GB/s of operand + fp32 bytes")
     else:
         b, c, h, w, n, ks, leaky = FCONV_CASES[args.shape[0]]
         x = torch.randn(b, c, h, w, device="cuda")

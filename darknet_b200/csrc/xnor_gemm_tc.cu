@@ -320,7 +320,7 @@ int launch_xnor_gemm_tc(int M, int n_total, int n_per_image, int K,
 	// 512 x 43264 x 2304, 324 vs 424 at 1024 x 43264 x 9216, 46.9 vs 74.2 at 256 x 100352 x 1152, 73.5 vs 108 at
 	// 128 x 401408 x 576, 23.1 vs 33.7 at 255 x 43264 x 1024; only the sum with a shortcut operand (darknet53 at batch 32):
 	// 58 vs 93 for 256 filters at 56 x 56, 48 vs 62 for 512 at 28 x 28, 285 vs 392 for 64 filters at 224 x 224 (half of each
-	// 128-filter tile is idle there, but the layer is bound by its 0.8 GB of fp32 traffic).  Sign words and sinks: from K = 2048
+	// 128-filter tile is idle there, but the layer is bound by its epilogue and its 0.8 GB of fp32 traffic).  Sign words and sinks: from K = 2048
 	// on, where its main loop hides the 8 epilogue warps.  An output AND a shortcut sum, or counts, stay with the other kernel.
 	// xnor_b200_set_tuning pins either.
 #ifndef XNOR_TCP_MIN_K_STAGED

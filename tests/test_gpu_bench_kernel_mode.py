@@ -29,3 +29,10 @@ def test_pack_mode_reports_both_routes_equal():
     out = run("--kernel", "pack", "--shape", "4", "64", "26", "26", "32", "3", "--reps", "2")
     lines = [l for l in out.splitlines() if l.startswith("pack ")]
     assert len(lines) == 2 and "equal=True" in lines[1]
+
+
+def test_layer_mode_with_output_and_with_the_shortcut_sum_only():
+    out = run("--kernel", "layer", "--shape", "2", "64", "28", "28", "128", "3", "--route", "tensor", "--reps", "2")
+    assert "sum_only=0" in out and "us/call" in out
+    out = run("--kernel", "layer", "--shape", "2", "64", "28", "28", "128", "3", "2", "--sum-only", "--route", "tensor", "--tc-kernel", "2", "--reps", "2", "--no-graph")
+    assert "stride=2" in out and "sum_only=1" in out
