@@ -5,7 +5,7 @@
 //
 //   warp 24        TMA producer: one lane brings the packed bit rows of the tile -- 128 pixel rows and 128 filter rows, one
 //                  256-bit K block (32 bytes) per row and raw stage -- into a ring of raw stages with cp.async.bulk.tensor.2d
-//                  (plain, no multicast; rows and columns past the end of a matrix arrive as zeros) and mbarrier expect_tx;
+//                  (one plain copy per CTA; rows and columns past the end of a matrix arrive as zeros) and mbarrier expect_tx;
 //   warps  8..15   pixel expanders, warps 16..23 filter expanders, one operand row per thread: 256 bits -> 256 four-bit
 //                  values = one 128-byte row of the stage's K-major SWIZZLE_128B tile in shared memory.  Both kinds come in
 //                  two groups that take the raw chunks in turn;
